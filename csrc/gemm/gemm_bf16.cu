@@ -1,0 +1,390 @@
+// Persistent bf16 GEMM for sm_100a: C[M,N] = A * B^T (+ bias) (+ addend | += C).
+//
+//   * operands staged in shared memory by TMA (128-byte swizzle, never multicast),
+//   * tcgen05.mma (kind::f16, M=128, N=BN, K=16) issued by one thread, fp32 accumulators
+//     in tensor memory, two accumulator buffers so the epilogue of tile i overlaps the
+//     main loop of tile i+1,
+//   * warp roles: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..5 =
+//     epilogue (tcgen05.ld -> registers -> global).
+//
+// Operand layouts ("K-major" = the reduction dimension is contiguous):
+//   A K-major : A stored [M, K] row-major (lda)        -- activations in fwd / dgrad
+//   A MN-major: A stored [K, M] row-major (lda)        -- dY^T in wgrad
+//   B K-major : B stored [N, K] row-major (ldb)        -- nn.Linear weight in fwd
+//   B MN-major: B stored [K, N] row-major (ldb)        -- weight in dgrad, X in wgrad
+//
+// Plays the role of the cuBLAS calls behind nn.Linear and its autograd in the reference
+// (models/llama_simple.py:206-221, models/llama_v2.py:222-229).
+#include "../common/host.h"
+#include "../common/ptx.cuh"
+
+namespace zb {
+
+enum : int {
+  GEMM_OUT_F32 = 1,     // C is fp32 (else bf16)
+  GEMM_ACCUMULATE = 2,  // C += result (read-modify-write in C's dtype, fp32 add)
+  GEMM_GELU = 4,        // tanh-GELU applied after bias (forward of GPT-style MLPs)
+  GEMM_RELU = 8,
+};
+
+struct GemmParams {
+  void* C;
+  const __nv_bfloat16* bias;    // [N] or nullptr
+  const __nv_bfloat16* addend;  // [M, ld_addend] bf16 or nullptr (e.g. residual)
+  int M, N, K;
+  int ldc, ld_addend;
+  int flags;
+  int* status;
+  // optional arrival gating of B tiles (all-gather fused GEMM): before loading rows
+  // [n0, n0+BN) of B the producer waits until gate_flags[chunk] >= gate_epoch for every
+  // chunk overlapping those rows; rows_per_chunk rows of B per chunk. nullptr = off.
+  const int* gate_flags;
+  int gate_epoch;
+  int gate_rows_per_chunk;
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int BM = 128;
+  static constexpr int BK = 64;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int NUM_THREADS = 192;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.f + tanhf(u));
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int BM = Cfg::BM, BK = Cfg::BK, STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tmem_full = bars + 2 * STAGES;
+  uint64_t* tmem_empty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  WaitCtx wctx{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM;
+        const int n0 = (tile / tiles_m) * BN;
+        if (p.gate_flags != nullptr) {
+          int c0 = n0 / p.gate_rows_per_chunk;
+          int n_end = min(n0 + BN, p.N) - 1;
+          int c1 = n_end / p.gate_rows_per_chunk;
+          for (int c = c0; c <= c1 && ok; ++c)
+            ok = flag_wait_ge(p.gate_flags + c, p.gate_epoch, ZB_WAIT_NS, p.status, ST_TIMEOUT_FLAG);
+          if (!ok) {
+            *abort_flag = 1;
+            break;
+          }
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, wctx, ST_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+          if (!A_MN) {
+            tma_load_2d(sa, &tmap_a, &full[stage], kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * (BK * 128), &tmap_a, &full[stage], m0 + j * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tmap_b, &full[stage], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (BK * 128), &tmap_b, &full[stage], n0 + j * 64, kb * BK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        const uint32_t use = uint32_t(local >> 1);
+        if (!mbar_wait(&tmem_empty[buf], (use & 1) ^ 1, wctx, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + uint32_t(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, wctx, ST_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            uint64_t da = A_MN ? umma_desc_mnmajor(sa + kk * 16 * 128, BK * 128)
+                               : umma_desc_kmajor(sa + kk * 32);
+            uint64_t db = B_MN ? umma_desc_mnmajor(sb + kk * 16 * 128, BK * 128)
+                               : umma_desc_kmajor(sb + kk * 32);
+            umma_f16_ss(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(&tmem_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const bool out_f32 = (p.flags & GEMM_OUT_F32) != 0;
+    const bool accum = (p.flags & GEMM_ACCUMULATE) != 0;
+    const bool vec_ok = (p.ldc % 8 == 0) && (p.addend == nullptr || p.ld_addend % 8 == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.addend) & 15) == 0);
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int m0 = (tile % tiles_m) * BM;
+      const int n0 = (tile / tiles_m) * BN;
+      const int buf = local & 1;
+      const uint32_t use = uint32_t(local >> 1);
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[buf], use & 1, wctx, ST_TIMEOUT_TMEM_FULL))) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * BN + c * 32), r);
+        tmem_wait_ld();
+        if (!row_ok) continue;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        const bool full_cols = (col0 + 32 <= p.N);
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (full_cols || col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+        }
+        if (p.flags & GEMM_GELU) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+        } else if (p.flags & GEMM_RELU) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
+        }
+        if (full_cols && vec_ok) {
+          if (p.addend != nullptr) {
+            const uint4* ap = reinterpret_cast<const uint4*>(p.addend + size_t(row) * p.ld_addend + col0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 a = ap[j];
+              float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z),
+                     f3 = unpack_bf16x2(a.w);
+              v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
+              v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
+            }
+          }
+          if (out_f32) {
+            float4* cp = reinterpret_cast<float4*>(static_cast<float*>(p.C) + size_t(row) * p.ldc + col0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 o = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+              if (accum) {
+                float4 old = cp[j];
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              cp[j] = o;
+            }
+          } else {
+            uint4* cp = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.C) + size_t(row) * p.ldc + col0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (accum) {
+                uint4 a = cp[j];
+                float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z),
+                       f3 = unpack_bf16x2(a.w);
+                v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
+                v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
+              }
+              uint4 o;
+              o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+              o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+              o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+              o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+              cp[j] = o;
+            }
+          }
+        } else {
+          for (int i = 0; i < 32; ++i) {
+            const int col = col0 + i;
+            if (col >= p.N) break;
+            float x = v[i];
+            if (p.addend != nullptr) x += __bfloat162float(p.addend[size_t(row) * p.ld_addend + col]);
+            if (out_f32) {
+              float* cp = static_cast<float*>(p.C) + size_t(row) * p.ldc + col;
+              *cp = accum ? (*cp + x) : x;
+            } else {
+              __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(p.C) + size_t(row) * p.ldc + col;
+              *cp = __float2bfloat16(accum ? (__bfloat162float(*cp) + x) : x);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  __syncwarp();
+  if (*abort_flag) {
+    // copies may still be in flight towards this CTA's shared memory: give them time
+    // to land before the CTA exits (bounded).
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const void* A, const void* B, const GemmParams& p, int lda, int ldb,
+                       int max_ctas, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap ta, tb;
+  int rc;
+  if (!A_MN) rc = make_tmap_2d_bf16(&ta, A, p.M, p.K, lda, Cfg::BM, 64);
+  else rc = make_tmap_2d_bf16(&ta, A, p.K, p.M, lda, 64, 64);
+  if (rc) return rc;
+  if (!B_MN) rc = make_tmap_2d_bf16(&tb, B, p.N, p.K, ldb, BN, 64);
+  else rc = make_tmap_2d_bf16(&tb, B, p.K, p.N, ldb, 64, 64);
+  if (rc) return rc;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    ZB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    attr_set = true;
+  }
+  const int tiles = ((p.M + Cfg::BM - 1) / Cfg::BM) * ((p.N + BN - 1) / BN);
+  int ctas = num_sms();
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  if (tiles < ctas) ctas = tiles;
+  kern<<<ctas, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  ZB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace zb
+
+extern "C" {
+
+// Returns 0 on success; on failure zb_last_error() describes it. `status` is a device
+// int the kernel writes a non-zero code to if one of its bounded waits ran out.
+int zb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                 int ldc, int a_mn_major, int b_mn_major, const void* bias, const void* addend,
+                 int ld_addend, int flags, int bn, int max_ctas, const int* gate_flags,
+                 int gate_epoch, int gate_rows_per_chunk, int* status, cudaStream_t stream) {
+  using namespace zb;
+  if (M <= 0 || N <= 0 || K <= 0) ZB_FAIL(-1, "gemm: empty problem %d x %d x %d", M, N, K);
+  GemmParams p;
+  p.C = C;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.addend = static_cast<const __nv_bfloat16*>(addend);
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc; p.ld_addend = ld_addend;
+  p.flags = flags;
+  p.status = status;
+  p.gate_flags = gate_flags;
+  p.gate_epoch = gate_epoch;
+  p.gate_rows_per_chunk = gate_rows_per_chunk > 0 ? gate_rows_per_chunk : 1;
+  if (bn != 128 && bn != 256) {
+    // 256-wide tiles unless that leaves most SMs idle
+    long tiles256 = long((M + 127) / 128) * ((N + 255) / 256);
+    bn = (tiles256 >= num_sms() || N > 128 * 2 && tiles256 * 2 > num_sms() * 3) ? 256 : 128;
+    if (N <= 128) bn = 128;
+  }
+#define ZB_DISPATCH(BN_)                                                                          \
+  if (!a_mn_major && !b_mn_major) return launch_gemm<BN_, false, false>(A, B, p, lda, ldb, max_ctas, stream); \
+  if (!a_mn_major && b_mn_major) return launch_gemm<BN_, false, true>(A, B, p, lda, ldb, max_ctas, stream);   \
+  if (a_mn_major && b_mn_major) return launch_gemm<BN_, true, true>(A, B, p, lda, ldb, max_ctas, stream);     \
+  return launch_gemm<BN_, true, false>(A, B, p, lda, ldb, max_ctas, stream);
+  if (bn == 256) { ZB_DISPATCH(256) }
+  ZB_DISPATCH(128)
+#undef ZB_DISPATCH
+}
+
+const char* zb_last_error() { return zb::last_error_buf(); }
+
+}  // extern "C"

@@ -1,0 +1,283 @@
+// RMSNorm and LayerNorm, forward and backward, bf16 I/O with fp32 math.
+// One CTA per row keeps the row in registers (16-byte loads), so every tensor is read
+// once and written once.  Weight/bias gradients are reduced in two deterministic steps:
+// per-CTA partial sums over a strided set of rows, then a column reduction that adds
+// into the unit's gradient bucket (fp32 or bf16).
+//
+// Replaces the composed ATen kernels behind HF LlamaRMSNorm and nn.LayerNorm in the
+// reference (models/llama_simple.py:419-422, models/gpt_simple.py:142-144).
+#include "../common/host.h"
+#include "../common/ptx.cuh"
+
+namespace zb {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAXV = 4;  // 16-byte chunks per thread kept in registers -> H <= 8192
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+  if (w == 0) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (l == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+  return u;
+}
+
+// ------------------------------- forward -------------------------------
+// LN = false: y = x * rstd * w;  LN = true: y = (x - mean) * rstd * w + b.
+template <bool LN>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                float* __restrict__ stats /* [T,2]: mean, rstd */, int T, int H, float eps) {
+  __shared__ float red[33];
+  const int row = blockIdx.x;
+  const int nchunk = H >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + size_t(row) * H);
+  float v[NORM_MAXV][8];
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    int c = threadIdx.x + i * NORM_THREADS;
+    if (c < nchunk) {
+      unpack8(xr[c], v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { s += v[i][j]; ss += v[i][j] * v[i][j]; }
+    }
+  }
+  float mean = 0.f;
+  if (LN) {
+    mean = block_sum(s, red) / H;
+    // two-pass variance from registers
+    float d2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nchunk) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { float d = v[i][j] - mean; d2 += d * d; }
+      }
+    }
+    ss = d2;
+  }
+  const float var = block_sum(ss, red) / H;
+  const float rstd = rsqrtf(var + eps);
+  if (threadIdx.x == 0 && stats != nullptr) {
+    stats[2 * row] = mean;
+    stats[2 * row + 1] = rstd;
+  }
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  const uint4* br = reinterpret_cast<const uint4*>(b);
+  uint4* yr = reinterpret_cast<uint4*>(y + size_t(row) * H);
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    int c = threadIdx.x + i * NORM_THREADS;
+    if (c < nchunk) {
+      float wf[8], bf[8], o[8];
+      unpack8(wr[c], wf);
+      if (LN && b != nullptr) unpack8(br[c], bf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = (v[i][j] - mean) * rstd * wf[j];
+        if (LN && b != nullptr) o[j] += bf[j];
+      }
+      yr[c] = pack8(o);
+    }
+  }
+}
+
+// ------------------------------- backward -------------------------------
+// dx = (dres) + rstd * (g - xhat * mean(g * xhat) [- mean(g)]) with g = dy * w.
+// Each CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ... and keeps its partial
+// dw (and db) in registers; partials go to part_dw[gridDim.x, H] (and part_db).
+template <bool LN>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                const __nv_bfloat16* __restrict__ w, const float* __restrict__ stats,
+                const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                float* __restrict__ part_dw, float* __restrict__ part_db, int T, int H) {
+  __shared__ float red[33];
+  const int nchunk = H >> 3;
+  float aw[NORM_MAXV][8], ab[NORM_MAXV][8], wf[NORM_MAXV][8];
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    int c = threadIdx.x + i * NORM_THREADS;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { aw[i][j] = 0.f; ab[i][j] = 0.f; wf[i][j] = 0.f; }
+    if (c < nchunk) unpack8(wr[c], wf[i]);
+  }
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + size_t(row) * H);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + size_t(row) * H);
+    const float mean = stats[2 * row], rstd = stats[2 * row + 1];
+    float xh[NORM_MAXV][8], g[NORM_MAXV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nchunk) {
+        float xf[8], df[8];
+        unpack8(xr[c], xf);
+        unpack8(gr[c], df);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xf[j] - mean) * rstd;
+          g[i][j] = df[j] * wf[i][j];
+          s1 += g[i][j] * xh[i][j];
+          s2 += g[i][j];
+          aw[i][j] += df[j] * xh[i][j];
+          ab[i][j] += df[j];
+        }
+      }
+    }
+    const float m1 = block_sum(s1, red) / H;
+    float m2 = 0.f;
+    if (LN) m2 = block_sum(s2, red) / H;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + size_t(row) * H);
+    const uint4* rr = reinterpret_cast<const uint4*>(dres ? dres + size_t(row) * H : nullptr);
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nchunk) {
+        float o[8], rf[8];
+        if (dres) unpack8(rr[c], rf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[j] = rstd * (g[i][j] - xh[i][j] * m1 - m2);
+          if (dres) o[j] += rf[j];
+        }
+        dxr[c] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    int c = threadIdx.x + i * NORM_THREADS;
+    if (c < nchunk) {
+      float4* pw = reinterpret_cast<float4*>(part_dw + size_t(blockIdx.x) * H + c * 8);
+      pw[0] = make_float4(aw[i][0], aw[i][1], aw[i][2], aw[i][3]);
+      pw[1] = make_float4(aw[i][4], aw[i][5], aw[i][6], aw[i][7]);
+      if (LN && part_db != nullptr) {
+        float4* pb = reinterpret_cast<float4*>(part_db + size_t(blockIdx.x) * H + c * 8);
+        pb[0] = make_float4(ab[i][0], ab[i][1], ab[i][2], ab[i][3]);
+        pb[1] = make_float4(ab[i][4], ab[i][5], ab[i][6], ab[i][7]);
+      }
+    }
+  }
+}
+
+// out[h] (+)= sum_p part[p, h]; out is fp32 or bf16.
+template <typename OutT>
+__global__ void colsum_accumulate_kernel(const float* __restrict__ part, int P, int H,
+                                         OutT* __restrict__ out, int accumulate) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= H) return;
+  float s = 0.f;
+  for (int p = 0; p < P; ++p) s += part[size_t(p) * H + h];
+  if (accumulate) s += float(out[h]);
+  out[h] = OutT(s);
+}
+
+// Column sums of a bf16 matrix [T, N] (bias gradients): partial sums per CTA over a
+// strided set of rows, finished by colsum_accumulate_kernel.
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const __nv_bfloat16* __restrict__ dy, int T, int N, int ld,
+                      float* __restrict__ part) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= N) return;
+  float s = 0.f;
+  for (int r = blockIdx.y; r < T; r += gridDim.y) s += __bfloat162float(dy[size_t(r) * ld + col]);
+  part[size_t(blockIdx.y) * N + col] = s;
+}
+
+}  // namespace zb
+
+extern "C" {
+
+int zb_norm_partial_rows(int T) {
+  int n = zb::num_sms() * 2;
+  return T < n ? T : n;
+}
+
+// stats: fp32 [T, 2]; ln: 0 = RMSNorm (bias ignored), 1 = LayerNorm.
+int zb_norm_fwd(const void* x, const void* w, const void* b, void* y, float* stats, int T, int H,
+                float eps, int ln, cudaStream_t stream) {
+  using namespace zb;
+  if (H % 8 != 0 || H > NORM_THREADS * NORM_MAXV * 8) ZB_FAIL(-1, "norm: H=%d unsupported", H);
+  if (T <= 0) return 0;
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto W = static_cast<const __nv_bfloat16*>(w);
+  auto B = static_cast<const __nv_bfloat16*>(b);
+  auto Y = static_cast<__nv_bfloat16*>(y);
+  if (ln) norm_fwd_kernel<true><<<T, NORM_THREADS, 0, stream>>>(X, W, B, Y, stats, T, H, eps);
+  else norm_fwd_kernel<false><<<T, NORM_THREADS, 0, stream>>>(X, W, B, Y, stats, T, H, eps);
+  ZB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// part_dw / part_db: fp32 scratch [zb_norm_partial_rows(T), H]. dw/db: gradient slots
+// (fp32 if grad_f32 else bf16) that are accumulated into when `accumulate` is set.
+int zb_norm_bwd(const void* dy, const void* x, const void* w, const float* stats, const void* dres,
+                void* dx, float* part_dw, float* part_db, void* dw, void* db, int T, int H, int ln,
+                int grad_f32, int accumulate, cudaStream_t stream) {
+  using namespace zb;
+  if (H % 8 != 0 || H > NORM_THREADS * NORM_MAXV * 8) ZB_FAIL(-1, "norm: H=%d unsupported", H);
+  if (T <= 0) return 0;
+  const int P = zb_norm_partial_rows(T);
+  auto DY = static_cast<const __nv_bfloat16*>(dy);
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto W = static_cast<const __nv_bfloat16*>(w);
+  auto DR = static_cast<const __nv_bfloat16*>(dres);
+  auto DX = static_cast<__nv_bfloat16*>(dx);
+  if (ln) norm_bwd_kernel<true><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, part_db, T, H);
+  else norm_bwd_kernel<false><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, nullptr, T, H);
+  ZB_CUDA_OK(cudaGetLastError());
+  const int nb = (H + 255) / 256;
+  if (dw != nullptr) {
+    if (grad_f32) colsum_accumulate_kernel<float><<<nb, 256, 0, stream>>>(part_dw, P, H, static_cast<float*>(dw), accumulate);
+    else colsum_accumulate_kernel<__nv_bfloat16><<<nb, 256, 0, stream>>>(part_dw, P, H, static_cast<__nv_bfloat16*>(dw), accumulate);
+  }
+  if (ln && db != nullptr) {
+    if (grad_f32) colsum_accumulate_kernel<float><<<nb, 256, 0, stream>>>(part_db, P, H, static_cast<float*>(db), accumulate);
+    else colsum_accumulate_kernel<__nv_bfloat16><<<nb, 256, 0, stream>>>(part_db, P, H, static_cast<__nv_bfloat16*>(db), accumulate);
+  }
+  ZB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Bias gradient: out[n] (+)= sum_t dy[t, n]. part: fp32 scratch [64, N].
+int zb_colsum(const void* dy, int T, int N, int ld, float* part, void* out, int grad_f32,
+              int accumulate, cudaStream_t stream) {
+  using namespace zb;
+  if (T <= 0 || N <= 0) return 0;
+  const int P = T < 64 ? T : 64;
+  dim3 grid((N + 255) / 256, P);
+  colsum_partial_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(dy), T, N, ld, part);
+  const int nb = (N + 255) / 256;
+  if (grad_f32) colsum_accumulate_kernel<float><<<nb, 256, 0, stream>>>(part, P, N, static_cast<float*>(out), accumulate);
+  else colsum_accumulate_kernel<__nv_bfloat16><<<nb, 256, 0, stream>>>(part, P, N, static_cast<__nv_bfloat16*>(out), accumulate);
+  ZB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,260 @@
+"""ctypes bindings of the hand-written sm_100a kernels (`csrc/`, built by `ops/build.py`).
+
+Every function here launches one of this repository's own CUDA kernels on the current
+torch stream; there is no fallback: if the library is missing on a machine with a GPU
+the import of the library raises.  Tensors are passed as raw device pointers.
+
+`launch_count()` counts the kernels launched through this module (bench.py reports it).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from ctypes import c_float, c_int, c_long, c_void_p
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parents[1] / "_C" / "libzorse_sm100.so"
+_lib = None
+_launches = 0
+_status: dict[int, torch.Tensor] = {}
+
+GEMM_OUT_F32 = 1
+GEMM_ACCUMULATE = 2
+GEMM_GELU = 4
+GEMM_RELU = 8
+
+ACT_GELU_TANH = 0
+ACT_RELU = 1
+ACT_GELU_ERF = 2
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def available() -> bool:
+    return _LIB_PATH.exists()
+
+
+def lib():
+    """Loads (building if needed) the kernel library. Raises if it cannot be had."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            from . import build as _build
+
+            _build.build()
+        _lib = ctypes.CDLL(str(_LIB_PATH))
+        _lib.zb_last_error.restype = ctypes.c_char_p
+    return _lib
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Device int32 that kernels write a non-zero code to when a bounded wait runs out."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    if dev not in _status:
+        _status[dev] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+    return _status[dev]
+
+
+_STATUS_NAMES = {
+    1: "TMA stage never landed", 2: "stage never released", 3: "accumulator never completed",
+    4: "accumulator never drained", 5: "flag wait ran out", 6: "bad argument", 7: "wait ran out",
+}
+
+
+def check_status(device=None) -> None:
+    """Synchronising read of the status word; raises KernelError if a kernel gave up."""
+    s = status_word(device)
+    v = int(s.item())
+    if v != 0:
+        s.zero_()
+        raise KernelError(
+            f"sm100 kernel reported status {v & 0xff} ({_STATUS_NAMES.get(v & 0xff, '?')}) in block {v >> 8}")
+
+
+def _check(rc: int, what: str) -> None:
+    global _launches
+    if rc != 0:
+        raise KernelError(f"{what}: {lib().zb_last_error().decode()}")
+    _launches += 1
+
+
+def _bf16(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.bfloat16 or not t.is_cuda:
+        raise TypeError(f"{name} must be a CUDA bf16 tensor, got {t.dtype} on {t.device}")
+
+
+# --------------------------------------------------------------------------- GEMM
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         bias: Optional[torch.Tensor] = None, addend: Optional[torch.Tensor] = None, accumulate: bool = False,
+         act: Optional[str] = None, bn: int = 0, max_ctas: int = 0,
+         gate: Optional[tuple] = None) -> torch.Tensor:
+    """out[M,N] = A @ B^T (+bias) (+addend), or out += ... with accumulate.
+
+    a: [M,K] (K-major) or [K,M] when a_mn; b: [N,K] (K-major) or [K,N] when b_mn.
+    out: bf16 or fp32 [M,N]. gate = (flags int32 tensor, epoch, rows_per_chunk) makes the
+    loader of B wait for chunk-arrival flags (all-gather fused GEMM).
+    """
+    _bf16(a, "a"); _bf16(b, "b")
+    M, N = out.shape
+    K = a.shape[0] if a_mn else a.shape[1]
+    assert (a.shape[1] if a_mn else a.shape[0]) == M, (a.shape, out.shape, a_mn)
+    assert (b.shape == (K, N)) if b_mn else (b.shape == (N, K)), (b.shape, (N, K), b_mn)
+    assert a.stride(-1) == 1 and b.stride(-1) == 1 and out.stride(-1) == 1
+    flags = 0
+    if out.dtype == torch.float32:
+        flags |= GEMM_OUT_F32
+    elif out.dtype != torch.bfloat16:
+        raise TypeError("gemm output must be bf16 or fp32")
+    if accumulate:
+        flags |= GEMM_ACCUMULATE
+    if act == "gelu":
+        flags |= GEMM_GELU
+    elif act == "relu":
+        flags |= GEMM_RELU
+    gflags, gepoch, grows = (None, 0, 1) if gate is None else gate
+    rc = lib().zb_gemm_bf16(_p(a), _p(b), _p(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
+                            c_int(b.stride(0)), c_int(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)),
+                            _p(bias), _p(addend), c_int(0 if addend is None else addend.stride(0)),
+                            c_int(flags), c_int(bn), c_int(max_ctas), _p(gflags), c_int(gepoch), c_int(grows),
+                            _p(status_word(a.device)), _stream())
+    _check(rc, "gemm")
+    return out
+
+
+# --------------------------------------------------------------------------- norms
+def norm_fwd(x, w, b, eps: float, layernorm: bool):
+    _bf16(x, "x")
+    T, H = x.shape
+    y = torch.empty_like(x)
+    stats = torch.empty(T, 2, dtype=torch.float32, device=x.device)
+    _check(lib().zb_norm_fwd(_p(x), _p(w), _p(b), _p(y), _p(stats), c_int(T), c_int(H), c_float(eps),
+                             c_int(int(layernorm)), _stream()), "norm_fwd")
+    return y, stats
+
+
+def norm_bwd(dy, x, w, stats, dres, dw, db, layernorm: bool, accumulate: bool = True):
+    """Returns dx (+dres). dw/db: gradient slots (fp32 or bf16) accumulated into."""
+    T, H = x.shape
+    dx = torch.empty_like(x)
+    P = lib().zb_norm_partial_rows(c_int(T))
+    part_dw = torch.empty(P, H, dtype=torch.float32, device=x.device)
+    part_db = torch.empty(P, H, dtype=torch.float32, device=x.device) if (layernorm and db is not None) else None
+    gf32 = int(dw.dtype == torch.float32)
+    _check(lib().zb_norm_bwd(_p(dy), _p(x), _p(w), _p(stats), _p(dres), _p(dx), _p(part_dw), _p(part_db),
+                             _p(dw), _p(db), c_int(T), c_int(H), c_int(int(layernorm)), c_int(gf32),
+                             c_int(int(accumulate)), _stream()), "norm_bwd")
+    return dx
+
+
+def colsum_accumulate(dy, out, accumulate: bool = True):
+    """out[n] (+)= sum_t dy[t, n] (bias gradients)."""
+    T, N = dy.shape
+    part = torch.empty(min(T, 64), N, dtype=torch.float32, device=dy.device)
+    _check(lib().zb_colsum(_p(dy), c_int(T), c_int(N), c_int(dy.stride(0)), _p(part), _p(out),
+                           c_int(int(out.dtype == torch.float32)), c_int(int(accumulate)), _stream()), "colsum")
+    return out
+
+
+# --------------------------------------------------------------------------- elementwise
+def rope_(buf, cs, S: int, nheads: int, d: int, backward: bool = False):
+    """In-place rotate-half RoPE on heads [0, nheads) of a packed [T, width] buffer."""
+    T = buf.shape[0]
+    _check(lib().zb_rope(_p(buf), _p(cs), c_int(T), c_int(S), c_int(nheads), c_int(d), c_int(buf.stride(0)),
+                         c_int(int(backward)), _stream()), "rope")
+    return buf
+
+
+def swiglu_fwd(gu):
+    T, F2 = gu.shape
+    out = torch.empty(T, F2 // 2, dtype=gu.dtype, device=gu.device)
+    _check(lib().zb_swiglu_fwd(_p(gu), _p(out), c_long(T), c_int(F2 // 2), _stream()), "swiglu_fwd")
+    return out
+
+
+def swiglu_bwd(gu, dout):
+    dgu = torch.empty_like(gu)
+    T, F2 = gu.shape
+    _check(lib().zb_swiglu_bwd(_p(gu), _p(dout), _p(dgu), c_long(T), c_int(F2 // 2), _stream()), "swiglu_bwd")
+    return dgu
+
+
+def act_fwd(x, kind: int):
+    y = torch.empty_like(x)
+    _check(lib().zb_act_fwd(_p(x), _p(y), c_long(x.numel()), c_int(kind), _stream()), "act_fwd")
+    return y
+
+
+def act_bwd(x, dy, kind: int):
+    dx = torch.empty_like(x)
+    _check(lib().zb_act_bwd(_p(x), _p(dy), _p(dx), c_long(x.numel()), c_int(kind), _stream()), "act_bwd")
+    return dx
+
+
+def embedding_fwd(ids, table, pos_table=None, S: int = 1, pos_offset: int = 0):
+    T = ids.numel()
+    V, H = table.shape
+    out = torch.empty(T, H, dtype=table.dtype, device=table.device)
+    _check(lib().zb_embedding_fwd(_p(ids), _p(table), _p(pos_table), _p(out), c_int(T), c_int(H), c_int(V),
+                                  c_int(S), c_int(pos_offset), _stream()), "embedding_fwd")
+    return out
+
+
+def embedding_bwd(ids, dout, dtable, dpos=None, S: int = 1, pos_offset: int = 0):
+    T = ids.numel()
+    V, H = dtable.shape
+    _check(lib().zb_embedding_bwd(_p(ids), _p(dout), _p(dtable), _p(dpos), c_int(T), c_int(H), c_int(V),
+                                  c_int(S), c_int(pos_offset), c_int(int(dtable.dtype == torch.float32)),
+                                  _stream()), "embedding_bwd")
+
+
+# --------------------------------------------------------------------------- loss
+def cross_entropy(logits, targets, grad_scale: float, dlogits=None, ignore_index: int = -100):
+    """Returns per-row losses (fp32). Writes d(loss)/d(logits) * grad_scale into dlogits
+    (may alias logits) when given."""
+    T, V = logits.shape
+    loss_rows = torch.empty(T, dtype=torch.float32, device=logits.device)
+    _check(lib().zb_cross_entropy(_p(logits), _p(targets), _p(dlogits), _p(loss_rows), c_int(T), c_int(V),
+                                  c_long(logits.stride(0)), c_float(grad_scale), c_long(ignore_index),
+                                  _stream()), "cross_entropy")
+    return loss_rows
+
+
+# --------------------------------------------------------------------------- optimizer
+def adam_step(p, m, v, g, p16, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0, zero_grad=False):
+    n = p.numel()
+    _check(lib().zb_adam(_p(p), _p(m), _p(v), _p(g), _p(p16), c_long(n), c_float(lr), c_float(beta1),
+                         c_float(beta2), c_float(eps), c_float(weight_decay), c_int(step), c_float(grad_scale),
+                         c_int(int(g.dtype == torch.float32)), c_int(int(zero_grad)), _stream()), "adam")
+
+
+# --------------------------------------------------------------------------- attention
+def flash_fwd(qkv, B: int, S: int, Hq: int, Hkv: int, D: int, causal: bool = True, window: int = 0,
+              scale: Optional[float] = None):
+    """qkv: packed [B*S, (Hq+2Hkv)*D]. Returns (out [B*S, Hq*D], lse [B, Hq, S])."""
+    _bf16(qkv, "qkv")
+    assert qkv.shape == (B * S, (Hq + 2 * Hkv) * D) and qkv.is_contiguous()
+    out = torch.empty(B * S, Hq * D, dtype=qkv.dtype, device=qkv.device)
+    lse = torch.empty(B, Hq, S, dtype=torch.float32, device=qkv.device)
+    sc = (1.0 / math.sqrt(D)) if scale is None else scale
+    _check(lib().zb_flash_fwd(_p(qkv), _p(out), _p(lse), c_int(B), c_int(S), c_int(Hq), c_int(Hkv), c_int(D),
+                              c_int(int(causal)), c_int(window), c_float(sc), c_int(out.stride(0)),
+                              _p(status_word(qkv.device)), _stream()), "flash_fwd")
+    return out, lse
