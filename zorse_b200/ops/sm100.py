@@ -258,3 +258,27 @@ def flash_fwd(qkv, B: int, S: int, Hq: int, Hkv: int, D: int, causal: bool = Tru
                               c_int(int(causal)), c_int(window), c_float(sc), c_int(out.stride(0)),
                               _p(status_word(qkv.device)), _stream()), "flash_fwd")
     return out, lse
+
+
+_attn_scratch: dict = {}
+
+
+def flash_bwd(do, qkv, o, lse, B: int, S: int, Hq: int, Hkv: int, D: int, causal: bool = True, window: int = 0,
+              scale: Optional[float] = None):
+    """Returns dqkv packed like qkv. Scratch (fp32 dQ accumulator, delta) is cached per shape
+    and device; the accumulator is left zeroed by the kernel that converts it to bf16."""
+    _bf16(do, "do"); _bf16(qkv, "qkv")
+    assert do.is_contiguous() and qkv.is_contiguous() and o.is_contiguous()
+    key = (qkv.device.index, B, S, Hq, D)
+    if key not in _attn_scratch:
+        _attn_scratch[key] = (torch.empty(B * Hq * S, dtype=torch.float32, device=qkv.device),
+                              torch.zeros(B * S * Hq * D, dtype=torch.float32, device=qkv.device))
+    delta, dq_acc = _attn_scratch[key]
+    dqkv = torch.empty_like(qkv)
+    sc = (1.0 / math.sqrt(D)) if scale is None else scale
+    _check(lib().zb_flash_bwd(_p(do), _p(qkv), _p(o), _p(lse), _p(dqkv), _p(delta), _p(dq_acc), c_int(B), c_int(S),
+                              c_int(Hq), c_int(Hkv), c_int(D), c_int(int(causal)), c_int(window), c_float(sc),
+                              _p(status_word(qkv.device)), _stream()), "flash_bwd")
+    global _launches
+    _launches += 2  # delta + finish kernels
+    return dqkv
