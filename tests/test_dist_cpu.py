@@ -1,0 +1,118 @@
+"""Distributed plumbing on CPU ranks (gloo): every stage split / DP width / schedule must
+reproduce the single-process oracle trainer (same loss, same parameters after two steps)."""
+import pytest
+import torch
+
+from dist_utils import run_workers
+from zorse_b200.config.training_config import parse_pipeline_dict
+
+
+def tiny_cfg(pipeline, gbs=8, mbs=2, seq=32, vocab=512, **kw):
+    d = {"model_name": "tiny_llama", "global_batch_size": gbs, "microbatch_size": mbs, "sequence_length": seq,
+         "vocab_size": vocab, "autocast_dtype": "float32", "reduce_dtype": "float32", "pipeline_config": pipeline}
+    d.update(kw)
+    return d
+
+
+def _worker(rank, world, cfg_dict, opts, steps):
+    from zorse_b200.trainer import Trainer, TrainerOptions
+
+    cfg = parse_pipeline_dict(cfg_dict)
+    tr = Trainer(cfg, TrainerOptions(backend="gloo", **opts))
+    batch = tr.synthetic_batch()
+    losses = []
+    for _ in range(steps):
+        loss = tr.train_step_from_host(batch)
+        losses.append(tr.global_loss(loss))
+    params = {}
+    for st in tr.stages:
+        for u in st.engine.units:
+            params[u.gid] = u.full_master()[: u.layer.layout()[1]].clone()
+    cnt = [(c.all_gathers, c.reduce_scatters, c.all_reduces, c.adam_steps) for c in tr.counters()]
+    return {"losses": losses, "params": params, "counters": cnt}
+
+
+def _oracle(cfg_dict, steps):
+    from zorse_b200.utils.oracle import OracleTrainer
+
+    cfg = parse_pipeline_dict(cfg_dict)
+    orc = OracleTrainer(cfg)
+    g = torch.Generator().manual_seed(7919)
+    M, B, S = cfg.num_microbatches, cfg.microbatch_size, cfg.sequence_length
+    batch = {"inputs": torch.randint(0, cfg.vocab_size, (M, B, S), generator=g),
+             "targets": torch.randint(0, cfg.vocab_size, (M, B, S), generator=g)}
+    losses = [orc.step(batch) for _ in range(steps)]
+    return losses, [f.detach() for f in orc.flats]
+
+
+def _check(results, cfg_dict, steps=2, ptol=5e-4):
+    want_losses, want_params = _oracle(cfg_dict, steps)
+    for res in results:
+        for a, b in zip(res["losses"], want_losses):
+            assert abs(a - b) < 2e-4, (res["losses"], want_losses)
+        for gid, p in res["params"].items():
+            err = (p - want_params[gid]).abs().max().item()
+            assert err < ptol, f"unit {gid}: max param error {err}"
+
+
+PIPE_2x1 = [{"gpu_ranks": [0], "num_microbatches_per_rank": [4], "layer_partition": [0, 2], "zero_config": [[0]]},
+            {"gpu_ranks": [1], "num_microbatches_per_rank": [4], "layer_partition": [2, 4], "zero_config": [[1]]}]
+PIPE_1x2 = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [2, 2], "layer_partition": [0, 4],
+             "zero_config": [[0, 1]]}]
+PIPE_1x2_UNEVEN = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [3, 1], "layer_partition": [0, 4],
+                    "zero_config": [[0, 1]]}]
+
+
+@pytest.mark.parametrize("schedule", ["layer_major", "zero2", "1f1b", "no_overlap", "two_stage_sync", "flashflex"])
+def test_two_stages_one_dp(schedule):
+    """Benchmark configuration 1: tiny Llama, 2 stages x 1 DP over gloo."""
+    cfg = tiny_cfg(PIPE_2x1)
+    res = run_workers(2, _worker, cfg, {"schedule": schedule}, 2)
+    _check(res, cfg)
+
+
+@pytest.mark.parametrize("schedule,oib", [("layer_major", False), ("layer_major", True), ("zero2", True), ("1f1b", False)])
+def test_one_stage_two_dp(schedule, oib):
+    cfg = tiny_cfg(PIPE_1x2)
+    res = run_workers(2, _worker, cfg, {"schedule": schedule, "optimizer_in_backward": oib}, 2)
+    _check(res, cfg)
+    # layer-major ZeRO-3: each unit gathered twice per step (forward, backward) and reduced once
+    ag, rs, ar, adam = res[0]["counters"][0]
+    n_units = 6
+    assert rs == 2 * n_units and adam == 2 * n_units
+    if schedule == "layer_major":
+        assert ag == 2 * (2 * n_units - 1)
+
+
+def test_uneven_microbatches_per_rank():
+    cfg = tiny_cfg(PIPE_1x2_UNEVEN)
+    res = run_workers(2, _worker, cfg, {"schedule": "layer_major"}, 2)
+    _check(res, cfg)
+
+
+def test_offload_params():
+    cfg = tiny_cfg(PIPE_1x2)
+    res = run_workers(2, _worker, cfg, {"schedule": "zero2", "optimizer_in_backward": True,
+                                        "offload_model_params": True}, 2)
+    _check(res, cfg)
+
+
+@pytest.mark.parametrize("schedule", ["layer_major", "zero2", "1f1b"])
+def test_mixed_widths_and_hybrid(schedule):
+    """4 ranks: stage 0 on one... two ranks (2-way shard), stage 1 on two ranks as two
+    replicate groups of one (hybrid: all-reduce only), uneven microbatch counts."""
+    pipe = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [3, 1], "layer_partition": [0, 1], "zero_config": [[0, 1]]},
+            {"gpu_ranks": [2, 3], "num_microbatches_per_rank": [1, 3], "layer_partition": [1, 4], "zero_config": [[2], [3]]}]
+    cfg = tiny_cfg(pipe)
+    res = run_workers(4, _worker, cfg, {"schedule": schedule}, 2)
+    _check(res, cfg)
+
+
+def test_interleaved_stages_three_ranks():
+    """1 -> 2 -> 1 widths with rank 0 hosting the first and the last stage."""
+    pipe = [{"gpu_ranks": [0], "num_microbatches_per_rank": [4], "layer_partition": [0, 1], "zero_config": [[0]]},
+            {"gpu_ranks": [1, 2], "num_microbatches_per_rank": [2, 2], "layer_partition": [1, 3], "zero_config": [[1, 2]]},
+            {"gpu_ranks": [0], "num_microbatches_per_rank": [4], "layer_partition": [3, 4], "zero_config": [[0]]}]
+    cfg = tiny_cfg(pipe)
+    res = run_workers(3, _worker, cfg, {"schedule": "layer_major"}, 2)
+    _check(res, cfg)

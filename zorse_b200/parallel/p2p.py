@@ -1,0 +1,171 @@
+"""Point-to-point transports for activations and activation gradients between stages.
+
+`NcclP2P`  – NCCL send/recv issued on two side streams with event hand-off to the compute
+             stream (the reference does the same with two class-wide streams,
+             zorse_utils/pipeline_comm.py:322-402).  NCCL matches messages of a rank pair by
+             order only, and torch serialises all p2p operations of one pair and one process
+             group on one internal stream; a send queued behind an unmatched send of the
+             other direction is the classic pipeline deadlock the reference works around with
+             its "sync" schedules and its Gloo path.  Here the four kinds of traffic
+             (activations / gradients x towards higher / lower rank) each get their own
+             process group, so every queue carries one kind in one direction, in increasing
+             (or, for gradients, decreasing) microbatch order on both ends.
+`GlooP2P`  – tagged Gloo send/recv; CUDA tensors are staged through pinned host buffers on a
+             copy stream (reference zorse_utils/gloo_pipeline_comm.py:8-160).  Also the CPU path.
+`LoopbackP2P` – in-process mailbox for single-process tests.
+"""
+from __future__ import annotations
+
+import datetime
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+class Handle:
+    """Result of an asynchronous transfer. wait() returns the received tensor (None for sends)."""
+
+    def __init__(self, wait_fn):
+        self._wait_fn = wait_fn
+        self._done = False
+        self._val = None
+
+    def wait(self):
+        if not self._done:
+            self._val = self._wait_fn()
+            self._done = True
+        return self._val
+
+
+class NcclP2P:
+    KINDS = ("act", "grad")
+
+    def __init__(self, device: torch.device, timeout_s: float = 300.0):
+        self.device = device
+        self.rank = dist.get_rank()
+        self.send_stream = torch.cuda.Stream(device=device)
+        self.recv_stream = torch.cuda.Stream(device=device)
+        to = datetime.timedelta(seconds=timeout_s)
+        # collective: every rank creates the same four world-wide groups in the same order
+        self.groups = {(k, up): dist.new_group(backend="nccl", timeout=to) for k in self.KINDS for up in (True, False)}
+        self._pending: list = []
+        self.bytes_sent = 0
+
+    def _group(self, kind: str, src: int, dst: int):
+        return self.groups[(kind, dst > src)]
+
+    def send(self, t: torch.Tensor, dst: int, tag: int, kind: str = "act") -> Handle:
+        cur = torch.cuda.current_stream()
+        self.send_stream.wait_stream(cur)
+        with torch.cuda.stream(self.send_stream):
+            work = dist.isend(t, dst, group=self._group(kind, self.rank, dst))
+        t.record_stream(self.send_stream)
+        self.bytes_sent += t.numel() * t.element_size()
+        self._pending.append((work, t))
+        return Handle(lambda: work.wait())
+
+    def recv(self, shape, dtype, src: int, tag: int, kind: str = "act") -> Handle:
+        cur = torch.cuda.current_stream()
+        buf = torch.empty(shape, dtype=dtype, device=self.device)
+        self.recv_stream.wait_stream(cur)
+        with torch.cuda.stream(self.recv_stream):
+            work = dist.irecv(buf, src, group=self._group(kind, src, self.rank))
+        buf.record_stream(self.recv_stream)
+
+        def wait():
+            with torch.cuda.stream(self.recv_stream):
+                work.wait()
+            torch.cuda.current_stream().wait_stream(self.recv_stream)
+            return buf
+
+        return Handle(wait)
+
+    def flush(self) -> None:
+        """Waits (stream-wise) for every send issued so far."""
+        if not self._pending:
+            return
+        with torch.cuda.stream(self.send_stream):
+            for work, _ in self._pending:
+                work.wait()
+        self._pending.clear()
+        torch.cuda.current_stream().wait_stream(self.send_stream)
+
+
+class GlooP2P:
+    def __init__(self, device: torch.device, group=None):
+        self.device = device
+        self.group = group
+        self.cuda = device.type == "cuda"
+        if self.cuda:
+            self.copy_send = torch.cuda.Stream(device=device)
+            self.copy_recv = torch.cuda.Stream(device=device)
+        self._pending: list = []
+        self.bytes_sent = 0
+
+    def send(self, t: torch.Tensor, dst: int, tag: int, kind: str = "act") -> Handle:
+        if self.cuda:
+            host = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+            self.copy_send.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.copy_send):
+                host.copy_(t, non_blocking=True)
+            t.record_stream(self.copy_send)
+            self.copy_send.synchronize()
+        else:
+            host = t.contiguous()
+        work = dist.isend(host, dst, group=self.group, tag=tag)
+        self.bytes_sent += t.numel() * t.element_size()
+        h = Handle(lambda: work.wait())
+        self._pending.append((h, host))
+        return h
+
+    def recv(self, shape, dtype, src: int, tag: int, kind: str = "act") -> Handle:
+        host = torch.empty(shape, dtype=dtype, device="cpu", pin_memory=self.cuda)
+        work = dist.irecv(host, src, group=self.group, tag=tag)
+
+        def wait():
+            work.wait()
+            if not self.cuda:
+                return host
+            with torch.cuda.stream(self.copy_recv):
+                dev = host.to(self.device, non_blocking=True)
+            torch.cuda.current_stream().wait_stream(self.copy_recv)
+            dev.record_stream(torch.cuda.current_stream())
+            return dev
+
+        return Handle(wait)
+
+    def flush(self) -> None:
+        for h, _ in self._pending:
+            h.wait()  # idempotent: a Gloo work object must not be waited on twice
+        self._pending.clear()
+
+
+class LoopbackP2P:
+    """Mailbox shared by simulated ranks of one process: {(src, dst, tag): tensor}."""
+
+    def __init__(self, rank: int, mailbox: dict):
+        self.rank, self.mailbox = rank, mailbox
+        self.bytes_sent = 0
+
+    def send(self, t, dst, tag, kind="act"):
+        self.mailbox[(self.rank, dst, tag)] = t.detach().clone()
+        self.bytes_sent += t.numel() * t.element_size()
+        return Handle(lambda: None)
+
+    def recv(self, shape, dtype, src, tag, kind="act"):
+        def wait():
+            return self.mailbox.pop((src, self.rank, tag))
+
+        return Handle(wait)
+
+    def flush(self):
+        pass
+
+
+def make_transport(device: torch.device, use_gloo: bool = False, gloo_group=None):
+    if not (dist.is_available() and dist.is_initialized()):
+        return LoopbackP2P(0, {})
+    if device.type == "cuda" and not use_gloo:
+        return NcclP2P(device)
+    return GlooP2P(device, gloo_group)

@@ -1,0 +1,134 @@
+"""Static routing of microbatches between pipeline stages.
+
+Stages may have different widths and every rank of a stage may run a different number of
+microbatches (heterogeneous data parallelism), so "who sends microbatch g to whom" is a
+many-to-many plan fixed before training, as in the reference
+(zorse_utils/pipeline_comm.py:17-312).  Here the plan is built from one rule: every stage
+orders the M global microbatches 0..M-1 and hands them to its ranks by a largest-remainder
+interleave of `num_microbatches_per_rank` (which reduces to `g % n` for an even split, the
+reference's even plan at :99-171); microbatch g then travels from its owner on stage s to
+its owner on stage s+1.  Ranks work through their microbatches in increasing g, so every
+pair of ranks sees its messages in one consistent order.
+
+Tags are unique per (stage boundary, microbatch, direction): `2*(b*M + g)` forward,
+`2*(b*M + g) + 1` backward.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+
+def interleave_owners(counts: Sequence[int]) -> list[int]:
+    """Owner (index into the stage's rank list) of each of sum(counts) microbatches, spreading
+    every rank's share evenly over the sequence. counts=[2,2] -> [0,1,0,1]; [3,1] -> [0,0,1,0]."""
+    total = sum(counts)
+    done = [0] * len(counts)
+    out = []
+    for g in range(total):
+        # the rank that is furthest behind its ideal share (g+1) * counts[k] / total
+        best, best_def = -1, None
+        for k, c in enumerate(counts):
+            if done[k] >= c:
+                continue
+            deficit = (g + 1) * c / total - done[k]
+            if best_def is None or deficit > best_def + 1e-12:
+                best, best_def = k, deficit
+        done[best] += 1
+        out.append(best)
+    return out
+
+
+@dataclass
+class StageCommPattern:
+    """For one local stage of one rank: its microbatches (global ids, increasing) and, per
+    local microbatch index, the peer rank + tag for each of the four transfers (None = no transfer)."""
+    stage_id: int
+    microbatches: list[int] = field(default_factory=list)
+    fwd_recv: list = field(default_factory=list)   # (src_rank, tag) | None
+    fwd_send: list = field(default_factory=list)   # (dst_rank, tag) | None
+    bwd_recv: list = field(default_factory=list)   # (src_rank, tag) | None  (gradient from next stage)
+    bwd_send: list = field(default_factory=list)   # (dst_rank, tag) | None  (gradient to previous stage)
+
+
+@dataclass
+class RankCommPlan:
+    rank: int
+    stages: dict[int, StageCommPattern] = field(default_factory=dict)
+
+
+def stage_owners(stage) -> list[int]:
+    """Global rank owning each global microbatch on `stage`."""
+    idx = interleave_owners(stage.num_microbatches_per_rank)
+    return [stage.gpu_ranks[k] for k in idx]
+
+
+def create_static_comm_plans(cfg) -> dict[int, RankCommPlan]:
+    """rank -> plan, for every rank named in the config."""
+    stages = cfg.stages
+    M = cfg.num_microbatches
+    owners = [stage_owners(s) for s in stages]
+    plans: dict[int, RankCommPlan] = {}
+    for si, st in enumerate(stages):
+        for r in st.gpu_ranks:
+            plans.setdefault(r, RankCommPlan(r)).stages[st.stage_id] = StageCommPattern(st.stage_id)
+    for si, st in enumerate(stages):
+        for g in range(M):
+            r = owners[si][g]
+            pat = plans[r].stages[st.stage_id]
+            pat.microbatches.append(g)
+            if si > 0:
+                tag = 2 * ((si - 1) * M + g)
+                pat.fwd_recv.append((owners[si - 1][g], tag))
+                pat.bwd_send.append((owners[si - 1][g], tag + 1))
+            else:
+                pat.fwd_recv.append(None)
+                pat.bwd_send.append(None)
+            if si + 1 < len(stages):
+                tag = 2 * (si * M + g)
+                pat.fwd_send.append((owners[si + 1][g], tag))
+                pat.bwd_recv.append((owners[si + 1][g], tag + 1))
+            else:
+                pat.fwd_send.append(None)
+                pat.bwd_recv.append(None)
+    validate_static_comm_plans(cfg, plans)
+    return plans
+
+
+def validate_static_comm_plans(cfg, plans: dict[int, RankCommPlan]) -> None:
+    """Every microbatch crosses every boundary exactly once each way, send and receive sides
+    mirror each other, tags are unique, and every rank runs the count the config gives it."""
+    M = cfg.num_microbatches
+    sends, recvs = {}, {}
+    for r, plan in plans.items():
+        for sid, pat in plan.stages.items():
+            st = cfg.stages[sid]
+            want = st.num_microbatches_per_rank[st.gpu_ranks.index(r)]
+            if len(pat.microbatches) != want:
+                raise AssertionError(f"rank {r} stage {sid}: {len(pat.microbatches)} microbatches, config says {want}")
+            if pat.microbatches != sorted(pat.microbatches):
+                raise AssertionError(f"rank {r} stage {sid}: microbatches not in increasing order")
+            for g, fs, fr, bs, br in zip(pat.microbatches, pat.fwd_send, pat.fwd_recv, pat.bwd_send, pat.bwd_recv):
+                for kind, ent in (("send", fs), ("send", bs)):
+                    if ent is not None:
+                        key = (r, ent[0], ent[1])
+                        if key in sends:
+                            raise AssertionError(f"duplicate send {key}")
+                        sends[key] = g
+                for ent in (fr, br):
+                    if ent is not None:
+                        key = (ent[0], r, ent[1])
+                        if key in recvs:
+                            raise AssertionError(f"duplicate recv {key}")
+                        recvs[key] = g
+    if sends.keys() != recvs.keys():
+        raise AssertionError(f"unmatched transfers: {set(sends) ^ set(recvs)}")
+    for key in sends:
+        if sends[key] != recvs[key]:
+            raise AssertionError(f"transfer {key} carries different microbatches on its two ends")
+    tags = [k[2] for k in sends]
+    if len(tags) != len(set(tags)):
+        raise AssertionError("tags are not unique")
+    expect = 2 * M * (len(cfg.stages) - 1)
+    if len(sends) != expect:
+        raise AssertionError(f"{len(sends)} transfers planned, expected {expect}")

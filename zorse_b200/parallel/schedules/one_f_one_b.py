@@ -1,0 +1,82 @@
+"""True 1F1B: warm-up forwards, steady one-forward-one-backward, cool-down backwards.
+
+The reference ships no 1F1B on its live path (its schedules are all-forward-then-all-backward,
+zorse_utils/pipeline_schedule_v2.py:391-402; "1f1b" only names a dormant
+torch.distributed.pipelining wrapper, models/pipeline_model.py:51-78).  Parameters stay
+unsharded for the whole step (gathered once), gradients are reduced after a layer's last
+backward microbatch.  By default activations are kept (no recompute): at most
+`num_stages - stage_index` microbatches are in flight per rank.
+"""
+from __future__ import annotations
+
+from ..stage import PipelineStage
+from .base import ScheduleBase
+
+
+class OneFOneBSchedule(ScheduleBase):
+    name = "1f1b"
+    recompute_default = False
+
+    def step(self, step_idx, inputs, targets):
+        if len(self.stages) != 1:
+            raise ValueError("the 1F1B schedule runs one stage per rank (no interleaving)")
+        if self.log:
+            self.log.set_step(step_idx)
+        st = self.stages[0]
+        st.loss_sum = None
+        L, M = len(st.layers), st.M
+        units = st.engine.units
+        st.engine.prefetch_all()
+        stage_pos = [s.stage_id for s in self.cfg.stages].index(st.stage_id)
+        warm = min(len(self.cfg.stages) - stage_pos - 1, M)
+        frecv = {}
+        brecv = {}
+
+        def post_f(mbl):
+            if not st.is_first and mbl < M and mbl not in frecv:
+                frecv[mbl] = st.recv_fwd(mbl)
+
+        def post_b(mbl):
+            if not st.is_last and mbl < M and mbl not in brecv:
+                brecv[mbl] = st.recv_bwd(mbl)
+
+        def fwd(mbl):
+            post_f(mbl)
+            x = self._inp(st, inputs, mbl) if st.is_first else frecv.pop(mbl).wait()
+            post_f(mbl + 1)
+            for li in range(L):
+                units[li].acquire()
+                x = st.forward_layer(li, mbl, x, self._tgt(st, targets, mbl), self.recompute)
+            if not st.is_last:
+                st.send_fwd(mbl, x)
+
+        def bwd(mbl):
+            post_b(mbl)
+            dy = None if st.is_last else brecv.pop(mbl).wait()
+            post_b(mbl + 1)
+            for li in reversed(range(L)):
+                units[li].acquire()
+                units[li].grad_views()
+                dy = st.backward_layer(li, mbl, dy, self._tgt(st, targets, mbl), self.recompute)
+                if mbl == M - 1:
+                    units[li].reduce_grads()
+            if not st.is_first:
+                st.send_bwd(mbl, dy)
+
+        for i in range(warm):
+            fwd(i)
+        for i in range(M - warm):
+            fwd(warm + i)
+            bwd(i)
+        for i in range(M - warm, M):
+            bwd(i)
+        if M == 0:
+            for u in units:
+                u.grad_views()
+                u.reduce_grads()
+        st.transport.flush()
+        st.engine.optimizer_step()
+        st.engine.finish_step()
+        st.stash.clear()
+        st.saved.clear()
+        return st.loss_sum if st.is_last else None

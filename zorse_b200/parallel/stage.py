@@ -1,0 +1,171 @@
+"""Run-time object of one pipeline stage on one rank, and the activation stash.
+
+A stage owns a contiguous range of transformer blocks (plus the embedding on the first
+stage and norm + head + loss on the last), one ZeRO unit per layer, the microbatches the
+static plan assigns to this rank and the four transfers of each.  A rank may hold several
+stages (interleaving), as in the reference (zorse_utils/pipeline.py:36-318).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..config.training_config import PipelineConfig, StageConfig, dtype_from_str
+from ..engine.zero import EngineConfig, StageEngine, Streams
+from ..models import registry
+from .groups import StageGroups
+from .p2p_plan import StageCommPattern
+
+
+class ActivationStash:
+    """Layer-boundary activations of a stage, keyed by (layer, local microbatch); optionally
+    parked in pinned host memory through a copy stream (the reference always does this,
+    zorse_utils/pipeline_schedule_v2.py:66-84, 256-262; on a 180 GB GPU it is an option)."""
+
+    def __init__(self, device: torch.device, offload: bool, copy_stream=None):
+        self.device, self.offload = device, offload and device.type == "cuda"
+        self.copy_stream = copy_stream
+        self.store: dict = {}
+        self.d2h_bytes = 0
+        self.h2d_bytes = 0
+        self._pool: dict = {}
+
+    def put(self, key, t: torch.Tensor) -> None:
+        if not self.offload or t.dtype == torch.long:
+            self.store[key] = t
+            return
+        pk = (tuple(t.shape), t.dtype)
+        free = self._pool.setdefault(pk, [])
+        host = free.pop() if free else torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+        self.copy_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.copy_stream):
+            host.copy_(t, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.copy_stream)
+        t.record_stream(self.copy_stream)
+        self.d2h_bytes += t.numel() * t.element_size()
+        self.store[key] = (host, ev)
+
+    def get(self, key, pop: bool = True):
+        v = self.store.pop(key) if pop else self.store[key]
+        if not isinstance(v, tuple):
+            return v
+        host, ev = v
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(ev)
+            dev = host.to(self.device, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(self.copy_stream)
+        torch.cuda.current_stream().wait_event(done)
+        dev.record_stream(torch.cuda.current_stream())
+        self.h2d_bytes += host.numel() * host.element_size()
+        if pop:
+            # the pinned buffer may be reused once the H2D copy has been issued on the same stream
+            self._pool.setdefault((tuple(host.shape), host.dtype), []).append(host)
+        return dev
+
+    def clear(self):
+        self.store.clear()
+
+
+class PipelineStage:
+    def __init__(self, cfg: PipelineConfig, st: StageConfig, *, rank: int, device: torch.device, ops,
+                 engine_cfg: EngineConfig, groups: StageGroups, streams: Streams, pattern: StageCommPattern,
+                 transport, gloo_transport=None, activation_offload: bool = False, model_overrides: Optional[dict] = None):
+        self.cfg, self.st, self.rank, self.device, self.ops = cfg, st, rank, device, ops
+        self.stage_id = st.stage_id
+        self.num_stages = len(cfg.stages)
+        self.is_first = st.layer_partition[0] == 0
+        self.spec = registry.get_spec(cfg.model_name, vocab=cfg.vocab_size, **(model_overrides or {}))
+        self.is_last = st.layer_partition[1] == self.spec.layers
+        self.layers = registry.build_stage_layers(self.spec, st.layer_partition[0], st.layer_partition[1],
+                                                  cfg.sequence_length)
+        gids = [registry.global_layer_index(self.spec, st.layer_partition[0], i, self.layers)
+                for i in range(len(self.layers))]
+        self.engine = StageEngine(self.layers, gids, device=device, cfg=engine_cfg, ops=ops, shard=groups.shard,
+                                  replicate=groups.replicate, rank=rank, streams=streams, zero_level=st.zero_level,
+                                  meta_init=False)
+        self.pattern = pattern
+        self.transport = transport
+        self.gloo_transport = gloo_transport
+        self.microbatches = list(pattern.microbatches)  # global ids, increasing
+        self.M = len(self.microbatches)
+        self.B, self.S, self.hidden = cfg.microbatch_size, cfg.sequence_length, self.spec.hidden
+        self.tokens = self.B * self.S
+        if self.spec.family == "vit":
+            self.S = self.layers[0].tokens_per_image() if self.is_first else (self.spec.image // self.spec.patch) ** 2 + 1
+            self.tokens = self.B * self.S
+        self.act_dtype = engine_cfg.compute_dtype
+        self.stash = ActivationStash(device, activation_offload, streams.copy)
+        self.saved: dict = {}
+        self.loss_sum: Optional[torch.Tensor] = None
+        # gradient scale: true mean over every token of the global batch, or the reference's
+        # arithmetic (per-microbatch mean, summed over local microbatches, averaged over DP ranks)
+        per_mb = 1.0 / (self.B if self.spec.pool else self.tokens)
+        if cfg.grad_norm_compat == "reference":
+            self.loss_scale = per_mb
+        else:
+            self.loss_scale = per_mb / cfg.num_microbatches
+
+    # -- helpers ----------------------------------------------------------------------
+    def ctx(self, mbl: int, targets=None) -> dict:
+        c = {"B": self.B, "S": self.S, "loss_scale": self.loss_scale}
+        if targets is not None:
+            c["targets"] = targets
+        return c
+
+    def act_shape(self):
+        return (self.tokens, self.hidden)
+
+    def tp(self, kind_is_grad: bool = False):
+        return self.transport
+
+    def recv_fwd(self, mbl: int):
+        src, tag = self.pattern.fwd_recv[mbl]
+        return self.transport.recv(self.act_shape(), self.act_dtype, src, tag, "act")
+
+    def send_fwd(self, mbl: int, y: torch.Tensor):
+        dst, tag = self.pattern.fwd_send[mbl]
+        return self.transport.send(y, dst, tag, "act")
+
+    def recv_bwd(self, mbl: int):
+        src, tag = self.pattern.bwd_recv[mbl]
+        return self.transport.recv(self.act_shape(), self.act_dtype, src, tag, "grad")
+
+    def send_bwd(self, mbl: int, dx: torch.Tensor):
+        dst, tag = self.pattern.bwd_send[mbl]
+        return self.transport.send(dx, dst, tag, "grad")
+
+    def add_loss(self, rows: torch.Tensor) -> None:
+        v = rows.float().sum() * self.loss_scale
+        self.loss_sum = v if self.loss_sum is None else self.loss_sum + v
+
+    # -- one layer, one microbatch ---------------------------------------------------
+    def forward_layer(self, li: int, mbl: int, x, targets, recompute: bool, want_loss: bool = True):
+        """Runs layer li on microbatch mbl. With recompute only the layer input is stashed."""
+        layer = self.layers[li]
+        c = self.ctx(mbl, targets if layer.kind == "head" else None)
+        if recompute:
+            self.stash.put((li, mbl), x)
+            y = layer.forward(x, c, self.ops, None)
+        else:
+            sv: dict = {}
+            y = layer.forward(x, c, self.ops, sv)
+            self.saved[(li, mbl)] = sv
+        if layer.kind == "head":
+            if want_loss:
+                self.add_loss(y)
+            return None
+        return y
+
+    def backward_layer(self, li: int, mbl: int, dy, targets, recompute: bool):
+        layer = self.layers[li]
+        c = self.ctx(mbl, targets if layer.kind == "head" else None)
+        if recompute:
+            x = self.stash.get((li, mbl))
+            sv: dict = {}
+            layer.forward(x, c, self.ops, sv)
+        else:
+            sv = self.saved.pop((li, mbl))
+        return layer.backward(dy, c, self.ops, sv)

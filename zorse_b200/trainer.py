@@ -1,0 +1,180 @@
+"""Builds the whole training job of one rank from a `PipelineConfig` and runs steps.
+
+This is the public API behind `zorse.py` (and what `bench.py` times end to end):
+
+    trainer = Trainer(cfg, TrainerOptions(...))       # groups, plan, stages, engine, schedule
+    batch = trainer.synthetic_batch()                 # pinned host token ids / labels
+    loss = trainer.train_step_from_host(batch)        # H2D copy, schedule.step, loss read-back
+
+Call stack parity with the reference trainer (zorse.py:212-283): dist init -> parse config ->
+build stages (+ communicators, static plan) -> wrap each stage in the ZeRO engine -> pick a
+schedule -> loop over `schedule.step`.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .config.training_config import PipelineConfig, dtype_from_str
+from .engine.zero import AdamConfig, EngineConfig, Streams
+from .ops.api import default_ops_for, get_ops
+from .parallel import groups as G
+from .parallel.p2p import GlooP2P, make_transport
+from .parallel.p2p_plan import create_static_comm_plans
+from .parallel.schedules import build_schedule
+from .parallel.stage import PipelineStage
+
+
+@dataclass
+class TrainerOptions:
+    schedule: str = "layer_major"
+    ops: Optional[str] = None              # "sm100" | "ref"; default by device
+    optimizer_in_backward: bool = False
+    offload_model_params: bool = False
+    gloo_p2p: bool = False
+    collectives: str = "library"           # "library" | "fused"
+    activation_recompute: Optional[bool] = None
+    activation_offload: Optional[bool] = None
+    lr: float = 1e-3
+    seed: int = 0
+    backend: Optional[str] = None          # torch.distributed backend override ("gloo" forces CPU)
+    model_overrides: dict = field(default_factory=dict)
+    pipeline_log: object = None
+
+
+class Trainer:
+    def __init__(self, cfg: PipelineConfig, opt: TrainerOptions):
+        if opt.offload_model_params and not opt.optimizer_in_backward:
+            raise ValueError("--offload_model_params requires --optimizer_in_backwards")
+        self.cfg, self.opt = cfg, opt
+        self.device = G.dist_init(opt.backend)
+        self.rank, self.world = G.rank(), G.world_size()
+        need = cfg.world_size
+        if need != self.world:
+            raise ValueError(f"the training config names {need} ranks but the job has {self.world}")
+        self.ops = get_ops(opt.ops or default_ops_for(self.device))
+        compute = dtype_from_str(cfg.autocast_dtype)
+        if self.ops.name == "sm100" and compute != torch.bfloat16:
+            raise ValueError("the sm100 kernels compute in bfloat16; set autocast_dtype to bfloat16")
+        self.engine_cfg = EngineConfig(
+            compute_dtype=compute, reduce_dtype=dtype_from_str(cfg.reduce_dtype),
+            optimizer_in_backward=opt.optimizer_in_backward, offload_params=opt.offload_model_params,
+            collectives=opt.collectives, grad_divide_by_group=cfg.grad_norm_compat == "reference",
+            adam=AdamConfig(lr=opt.lr), seed=opt.seed)
+        self.streams = Streams(self.device)
+        stage_groups = G.StageGroups.create_all(cfg.stages, self.rank)
+        self.gloo_group = G.gloo_world_group() if (opt.gloo_p2p or self.device.type == "cuda") and G.is_dist() else None
+        self.transport = make_transport(self.device, use_gloo=opt.gloo_p2p, gloo_group=self.gloo_group)
+        plans = create_static_comm_plans(cfg)
+        self.plan = plans[self.rank]
+        offload_act = cfg.activation_offload if opt.activation_offload is None else opt.activation_offload
+        self.stages = [
+            PipelineStage(cfg, st, rank=self.rank, device=self.device, ops=self.ops, engine_cfg=self.engine_cfg,
+                          groups=stage_groups[st.stage_id], streams=self.streams, pattern=self.plan.stages[st.stage_id],
+                          transport=self.transport, activation_offload=bool(offload_act),
+                          model_overrides=opt.model_overrides)
+            for st in cfg.stages_of_rank(self.rank)]
+        recompute = cfg.activation_recompute if opt.activation_recompute is None else opt.activation_recompute
+        name = cfg.schedule or opt.schedule
+        self.schedule = build_schedule(name, self.stages, cfg, recompute=recompute, pipeline_log=opt.pipeline_log)
+        self.step_idx = 0
+        self._dev_batch = None
+
+    # ------------------------------------------------------------------ data
+    def synthetic_batch(self, seed: Optional[int] = None, pin: bool = True) -> dict:
+        """Uniform random token ids and labels for the whole global batch, [M, B, S] int64 on
+        the host (pinned when a GPU is used) — the reference trains on exactly this kind of data,
+        generated once and reused every step (zorse.py:42-47, 73-85)."""
+        cfg = self.cfg
+        g = torch.Generator().manual_seed(cfg_seed(self.opt.seed if seed is None else seed))
+        M, B, S = cfg.num_microbatches, cfg.microbatch_size, cfg.sequence_length
+        spec = self.stages[0].spec
+        if spec.family == "vit":
+            x = torch.randn(M, B, 3, spec.image, spec.image, generator=g)
+            y = torch.randint(0, spec.classes, (M, B), generator=g)
+        else:
+            x = torch.randint(0, cfg.vocab_size, (M, B, S), generator=g)
+            y = torch.randint(0, cfg.vocab_size, (M, B, S), generator=g)
+        if pin and self.device.type == "cuda":
+            x, y = x.pin_memory(), y.pin_memory()
+        return {"inputs": x, "targets": y}
+
+    def needed_microbatches(self):
+        first = sorted({g for st in self.stages if st.is_first for g in st.microbatches})
+        last = sorted({g for st in self.stages if st.is_last for g in st.microbatches})
+        return first, last
+
+    def to_device(self, batch: dict):
+        """Copies the microbatches this rank consumes to its device. Returns (inputs, targets,
+        bytes copied)."""
+        first, last = self.needed_microbatches()
+        inputs, targets, nbytes = {}, {}, 0
+        for g in first:
+            t = batch["inputs"][g]
+            inputs[g] = t.to(self.device, non_blocking=True)
+            nbytes += t.numel() * t.element_size()
+        for g in last:
+            t = batch["targets"][g]
+            targets[g] = t.to(self.device, non_blocking=True)
+            nbytes += t.numel() * t.element_size()
+        return inputs, targets, nbytes
+
+    # ------------------------------------------------------------------ steps
+    def train_step(self, inputs: dict, targets: dict):
+        """One optimizer step on device-resident microbatches. Returns this rank's share of
+        the mean loss as a device scalar (None on ranks without the last stage)."""
+        loss = self.schedule.step(self.step_idx, inputs, targets)
+        self.step_idx += 1
+        return loss
+
+    def train_step_from_host(self, batch: dict) -> Optional[float]:
+        """Host-to-device copy of this step's inputs, one step, device-to-host read of the loss."""
+        inputs, targets, _ = self.to_device(batch)
+        loss = self.train_step(inputs, targets)
+        return None if loss is None else float(loss.item())
+
+    def global_loss(self, loss) -> float:
+        """Sum of the last-stage ranks' loss shares (= mean loss of the global batch)."""
+        v = torch.zeros(1, dtype=torch.float64)
+        if loss is not None:
+            v[0] = float(loss)
+        if not G.is_dist():
+            return float(v[0])
+        if self.gloo_group is not None:
+            dist.all_reduce(v, group=self.gloo_group)
+        elif dist.get_backend() == "gloo":
+            dist.all_reduce(v)
+        else:
+            t = v.to(self.device)
+            dist.all_reduce(t)
+            v = t.cpu()
+        return float(v[0])
+
+    def synchronize(self):
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+
+    def barrier(self):
+        if G.is_dist():
+            if self.gloo_group is not None:
+                dist.barrier(group=self.gloo_group)
+            else:
+                dist.barrier()
+
+    def check_kernels(self):
+        if self.ops.name == "sm100":
+            self.ops.k.check_status(self.device)
+
+    def num_params(self) -> int:
+        return sum(st.engine.num_params() for st in self.stages)
+
+    def counters(self):
+        return [st.engine.counters for st in self.stages]
+
+
+def cfg_seed(seed: int) -> int:
+    return 7919 * (seed + 1)
