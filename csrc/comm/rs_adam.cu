@@ -1,0 +1,215 @@
+// Fused reduce-scatter + cast/scale + sharded Adam over NVLink peer memory.
+//
+// Every rank of a shard group keeps the unit's full gradient bucket (bf16 or fp32) in
+// symmetric memory, so each rank can address its peers' buckets directly.  Rank r owns
+// elements [r*n/R, (r+1)*n/R): this kernel loads that slice from all R buckets with plain
+// 16-byte peer loads (fixed rank order -> deterministic sum), scales it, runs Adam on the
+// fp32 master / m / v shard and writes the refreshed bf16 parameter shard the next
+// all-gather sends.  One pass: no reduced-gradient tensor, no separate cast, no separate
+// optimizer launch.  (Reference: dist.reduce_scatter_tensor + cast + fused Adam,
+// utils/patch.py:585-589, 99-143.)
+//
+// Cross-GPU ordering uses three int flags per (unit, rank) in symmetric memory, written
+// with st.release.sys by the producer and polled with ld.acquire.sys by the consumer:
+//   ready[p]   rank p finished accumulating the unit's gradients for epoch e
+//   done[p]    rank p finished reading its slice of everybody's bucket for epoch e
+//   version[p] rank p's bf16 shard holds the parameters of epoch e
+// Every wait is bounded; on a timeout the kernel records ST_TIMEOUT_FLAG and returns
+// without touching the optimizer state.
+#include "../common/host.h"
+#include "../common/ptx.cuh"
+
+namespace zb {
+
+constexpr int MAX_R = 8;
+
+struct RsAdamParams {
+  const void* grad[MAX_R];  // bucket base of every rank of the group (own one included)
+  int* flags[MAX_R];        // flag block of every rank: [3][R] ints (ready, done, version)
+  int R, r;
+  long shard_n;             // elements per shard
+  float* master; float* m; float* v;
+  __nv_bfloat16* p16;
+  float lr, beta1, beta2, eps, weight_decay, bc1, bc2_sqrt, grad_scale;
+  int epoch;
+  int* status;
+  unsigned int* counter;    // zeroed int in local memory (last-block detection)
+  unsigned long long wait_ns;
+};
+
+template <typename GT> struct GradVec;
+template <> struct GradVec<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    uint4 u = ld_v4_relaxed_sys(p);
+    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+  }
+};
+template <> struct GradVec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    uint4 u = ld_v4_relaxed_sys(p);
+    float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+  }
+};
+
+template <typename GT>
+__global__ void __launch_bounds__(256)
+rs_adam_kernel(const RsAdamParams p) {
+  constexpr int N = GradVec<GT>::N;
+  __shared__ int s_ok;
+  // 1. announce that this rank's bucket is complete (the launch is stream-ordered after the
+  //    last wgrad kernel of the unit), then wait for everybody else's announcement.
+  if (blockIdx.x == 0 && threadIdx.x < p.R) {
+    __threadfence_system();
+    st_release_sys(p.flags[threadIdx.x] + 0 * p.R + p.r, p.epoch);
+  }
+  if (threadIdx.x == 0) {
+    bool ok = true;
+    for (int q = 0; q < p.R && ok; ++q)
+      ok = flag_wait_ge(p.flags[p.r] + 0 * p.R + q, p.epoch, p.wait_ns, p.status, ST_TIMEOUT_FLAG);
+    s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+
+  // 2. reduce + Adam over this rank's slice
+  const long nvec = p.shard_n / N;
+  const long lo = long(p.r) * p.shard_n;
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < nvec; i += long(gridDim.x) * blockDim.x) {
+    float g[N];
+#pragma unroll
+    for (int k = 0; k < N; ++k) g[k] = 0.f;
+    for (int q = 0; q < p.R; ++q) {
+      float t[N];
+      GradVec<GT>::load(static_cast<const GT*>(p.grad[q]) + lo + i * N, t);
+#pragma unroll
+      for (int k = 0; k < N; ++k) g[k] += t[k];
+    }
+    float pm[N], mm[N], vv[N];
+#pragma unroll
+    for (int k = 0; k < N; k += 4) {
+      *reinterpret_cast<float4*>(pm + k) = *reinterpret_cast<const float4*>(p.master + i * N + k);
+      *reinterpret_cast<float4*>(mm + k) = *reinterpret_cast<const float4*>(p.m + i * N + k);
+      *reinterpret_cast<float4*>(vv + k) = *reinterpret_cast<const float4*>(p.v + i * N + k);
+    }
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      float gg = g[k] * p.grad_scale;
+      if (p.weight_decay != 0.f) gg += p.weight_decay * pm[k];
+      mm[k] = p.beta1 * mm[k] + (1.f - p.beta1) * gg;
+      vv[k] = p.beta2 * vv[k] + (1.f - p.beta2) * gg * gg;
+      pm[k] -= (p.lr / p.bc1) * (mm[k] / (sqrtf(vv[k]) / p.bc2_sqrt + p.eps));
+    }
+#pragma unroll
+    for (int k = 0; k < N; k += 4) {
+      *reinterpret_cast<float4*>(p.master + i * N + k) = *reinterpret_cast<float4*>(pm + k);
+      *reinterpret_cast<float4*>(p.m + i * N + k) = *reinterpret_cast<float4*>(mm + k);
+      *reinterpret_cast<float4*>(p.v + i * N + k) = *reinterpret_cast<float4*>(vv + k);
+    }
+    if (N == 8) {
+      uint4 u;
+      u.x = pack_bf16x2(pm[0], pm[1]); u.y = pack_bf16x2(pm[2], pm[3]);
+      u.z = pack_bf16x2(pm[4], pm[5]); u.w = pack_bf16x2(pm[6], pm[7]);
+      *reinterpret_cast<uint4*>(p.p16 + i * N) = u;
+    } else {
+      *reinterpret_cast<uint2*>(p.p16 + i * N) = make_uint2(pack_bf16x2(pm[0], pm[1]), pack_bf16x2(pm[2], pm[3]));
+    }
+  }
+
+  // 3. the last block to finish tells every peer that this rank is done reading their
+  //    buckets and that its bf16 shard now holds the parameters of this epoch.
+  __threadfence_system();
+  __syncthreads();
+  __shared__ unsigned int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(p.counter, 1u) == gridDim.x - 1) ? 1u : 0u;
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x < p.R) {
+      st_release_sys(p.flags[threadIdx.x] + 1 * p.R + p.r, p.epoch);
+      st_release_sys(p.flags[threadIdx.x] + 2 * p.R + p.r, p.epoch);
+    }
+    if (threadIdx.x == 0) *p.counter = 0u;
+  }
+}
+
+// Waits until flags[which*R + q] >= epoch for every q (one thread; bounded).
+__global__ void wait_flags_kernel(const int* flags, int R, int which, int epoch, unsigned long long wait_ns,
+                                  int* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    for (int q = 0; q < R; ++q)
+      if (!flag_wait_ge(flags + which * R + q, epoch, wait_ns, status, ST_TIMEOUT_FLAG)) break;
+  }
+}
+
+// Copies `bytes` (multiple of 16) from a peer-mapped pointer into local memory.
+__global__ void __launch_bounds__(256)
+peer_pull_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long n16) {
+  long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+  const long stride = long(gridDim.x) * blockDim.x;
+  for (; i + 3 * stride < n16; i += 4 * stride) {
+    uint4 a = ld_v4_relaxed_sys(src + i), b = ld_v4_relaxed_sys(src + i + stride),
+          c = ld_v4_relaxed_sys(src + i + 2 * stride), d = ld_v4_relaxed_sys(src + i + 3 * stride);
+    dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+  }
+  for (; i < n16; i += stride) dst[i] = ld_v4_relaxed_sys(src + i);
+}
+
+}  // namespace zb
+
+extern "C" {
+
+// grad_ptrs / flag_ptrs: host arrays of R device pointers (peer-mapped), ordered by rank in
+// the shard group. counter: a zeroed device int owned by the caller.
+int zb_rs_adam(const void* const* grad_ptrs, int* const* flag_ptrs, int R, int r, long shard_n, float* master,
+               float* m, float* v, void* p16, float lr, float beta1, float beta2, float eps, float weight_decay,
+               int step, float grad_scale, int grad_f32, int epoch, unsigned int* counter, int max_blocks,
+               double wait_seconds, int* status, cudaStream_t stream) {
+  using namespace zb;
+  if (R < 1 || R > MAX_R) ZB_FAIL(-1, "rs_adam: group size %d unsupported (1..%d)", R, MAX_R);
+  if (shard_n % 8 != 0) ZB_FAIL(-1, "rs_adam: shard size %ld not a multiple of 8", shard_n);
+  RsAdamParams p;
+  for (int i = 0; i < R; ++i) { p.grad[i] = grad_ptrs[i]; p.flags[i] = flag_ptrs[i]; }
+  p.R = R; p.r = r; p.shard_n = shard_n;
+  p.master = master; p.m = m; p.v = v; p.p16 = static_cast<__nv_bfloat16*>(p16);
+  p.lr = lr; p.beta1 = beta1; p.beta2 = beta2; p.eps = eps; p.weight_decay = weight_decay;
+  p.bc1 = 1.f - powf(beta1, float(step));
+  p.bc2_sqrt = sqrtf(1.f - powf(beta2, float(step)));
+  p.grad_scale = grad_scale;
+  p.epoch = epoch; p.status = status; p.counter = counter;
+  p.wait_ns = (unsigned long long)(wait_seconds * 1e9);
+  int blocks = num_sms() * 2;
+  if (max_blocks > 0 && max_blocks < blocks) blocks = max_blocks;
+  long need = (shard_n / (grad_f32 ? 4 : 8) + 255) / 256;
+  if (need < blocks) blocks = int(need < 1 ? 1 : need);
+  if (grad_f32) rs_adam_kernel<float><<<blocks, 256, 0, stream>>>(p);
+  else rs_adam_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(p);
+  ZB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int zb_wait_flags(const int* flags, int R, int which, int epoch, double wait_seconds, int* status,
+                  cudaStream_t stream) {
+  using namespace zb;
+  wait_flags_kernel<<<1, 32, 0, stream>>>(flags, R, which, epoch, (unsigned long long)(wait_seconds * 1e9), status);
+  ZB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int zb_peer_pull(const void* src, void* dst, long bytes, int max_blocks, cudaStream_t stream) {
+  using namespace zb;
+  if (bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15))
+    ZB_FAIL(-1, "peer_pull: pointers and size must be multiples of 16 bytes");
+  if (bytes <= 0) return 0;
+  long n16 = bytes / 16;
+  int blocks = num_sms() * 2;
+  if (max_blocks > 0 && max_blocks < blocks) blocks = max_blocks;
+  long need = (n16 + 1023) / 1024;
+  if (need < blocks) blocks = int(need < 1 ? 1 : need);
+  peer_pull_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), n16);
+  ZB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,137 @@
+"""`zorse.py` main: parse flags + training config, build the job, run warm-up and measured
+iterations, print the metrics block (reference zorse.py:109-283)."""
+from __future__ import annotations
+
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+from ..config.flags import parse_args_zorse
+from ..config.training_config import dtype_to_str, parse_pipeline_config
+from ..models import registry
+from ..parallel import groups as G
+from ..parallel.schedules import schedule_name_from_flags
+from ..trainer import Trainer, TrainerOptions
+from ..utils import metrics
+from ..utils.logger import init_logger
+from ..utils.pipeline_log import init_pipeline_logger
+
+
+def main(argv=None) -> int:
+    args = parse_args_zorse(argv)
+    log = init_logger(args.log_level)
+    cfg = parse_pipeline_config(args.config_file)
+    if args.grad_norm_compat:
+        cfg.grad_norm_compat = args.grad_norm_compat
+    plog = init_pipeline_logger("./zorse_logs", int(os.environ.get("RANK", "0")), args.log_level) \
+        if args.log_level == "DEBUG" else None
+    opt = TrainerOptions(
+        schedule=schedule_name_from_flags(args), ops=args.ops, optimizer_in_backward=args.optimizer_in_backwards,
+        offload_model_params=args.offload_model_params, gloo_p2p=args.gloo_p2p, collectives=args.collectives,
+        activation_recompute=False if args.no_recompute else None,
+        activation_offload=True if args.offload_activations_to_host else None, lr=args.lr, seed=args.seed,
+        backend=args.backend, pipeline_log=plog)
+    tr = Trainer(cfg, opt)
+    log.info(f"rank {tr.rank}/{tr.world} on {tr.device}; schedule {tr.schedule.name}; ops {tr.ops.name}; "
+             f"stages {[s.stage_id for s in tr.stages]}", leader_only=False)
+    if args.resume:
+        from ..ckpt.reader import load_checkpoint
+
+        load_checkpoint(tr, args.resume)
+    watchdog = None
+    if args.heartbeat_timeout > 0:
+        from ..utils.health import Watchdog
+
+        watchdog = Watchdog(args.heartbeat_timeout, rank=tr.rank)
+        watchdog.start()
+    batch = tr.synthetic_batch()
+    inputs, targets, _ = tr.to_device(batch)
+    cuda = tr.device.type == "cuda"
+    total = args.warmup_iterations + args.iterations
+    start = end = None
+    iter_ms = []
+    prof = None
+    t0 = time.perf_counter()
+    loss = None
+    for step in range(total):
+        if step == args.warmup_iterations:
+            tr.synchronize()
+            tr.barrier()
+            if cuda:
+                start = torch.cuda.Event(enable_timing=True)
+                start.record()
+            t0 = time.perf_counter()
+        if (not args.skip_profile and args.trace_dir and prof is None
+                and step == args.warmup_iterations - args.profiling_iterations and args.profiling_iterations > 0):
+            from ..utils.trace import profiler_context
+
+            prof = profiler_context(args.trace_dir, args.experiment_name, tr.rank)
+            prof.__enter__()
+        if cuda:
+            a = torch.cuda.Event(enable_timing=True)
+            b = torch.cuda.Event(enable_timing=True)
+            a.record()
+        ti = time.perf_counter()
+        loss = tr.train_step(inputs, targets)
+        if cuda:
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b)
+        else:
+            ms = (time.perf_counter() - ti) * 1e3
+        tr.check_kernels()
+        if watchdog:
+            watchdog.beat(step)
+        iter_ms.append(ms)
+        log.info(f"Iteration {step} Time {ms:.2f} ms" + (f" loss {float(loss):.4f}" if loss is not None else ""))
+        if prof is not None and step == args.warmup_iterations - 1:
+            prof.__exit__(None, None, None)
+            prof = None
+        if args.checkpoint_dir and args.checkpoint_every and (step + 1) % args.checkpoint_every == 0:
+            from ..ckpt.writer import save_checkpoint
+
+            save_checkpoint(tr, args.checkpoint_dir, step + 1)
+    if cuda:
+        end = torch.cuda.Event(enable_timing=True)
+        end.record()
+        torch.cuda.synchronize()
+        avg_ms = start.elapsed_time(end) / max(args.iterations, 1) if start is not None else 0.0
+    else:
+        avg_ms = (time.perf_counter() - t0) * 1e3 / max(args.iterations, 1)
+    tr.barrier()
+    # max over ranks, memory and GPU names over the host-side group
+    t = torch.tensor([avg_ms, metrics.memory_stats(tr.device)["max_allocated_gb"]], dtype=torch.float64)
+    gpu = metrics.clean_gpu_name(torch.cuda.get_device_name(tr.device)) if cuda else "cpu"
+    if G.is_dist():
+        grp = tr.gloo_group if tr.gloo_group is not None else None
+        outs = [torch.zeros_like(t) for _ in range(tr.world)]
+        names = [None] * tr.world
+        if grp is not None or dist.get_backend() == "gloo":
+            dist.all_gather(outs, t, group=grp)
+            dist.all_gather_object(names, gpu, group=grp)
+        else:
+            outs, names = [t], [gpu]
+    else:
+        outs, names = [t], [gpu]
+    step_ms = max(float(o[0]) for o in outs)
+    spec = tr.stages[0].spec
+    flops = metrics.compute_model_flops(registry.total_params(spec, cfg.sequence_length), spec.layers, spec.hidden,
+                                        cfg.sequence_length, cfg.global_batch_size, recompute=tr.schedule.recompute)
+    gl = tr.global_loss(loss)
+    if tr.rank == 0:
+        print(metrics.format_summary(global_batch=cfg.global_batch_size, seq=cfg.sequence_length, step_ms=step_ms,
+                                     flops_per_step=flops, gpu_names=names, dtype=cfg.autocast_dtype,
+                                     max_alloc_gb=[float(o[1]) for o in outs], predicted_ms=cfg.latency, loss=gl,
+                                     flashflex_ga=args.flashflex_ga))
+    if watchdog:
+        watchdog.stop()
+    if G.is_dist():
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -117,7 +117,7 @@ class PipelineConfig:
     large_model_init: bool = False
     # extensions
     schedule: Optional[str] = None
-    activation_recompute: bool = True
+    activation_recompute: Optional[bool] = None
     activation_offload: Optional[bool] = None
     grad_norm_compat: str = "mean"
     extra: dict = field(default_factory=dict)
@@ -213,7 +213,7 @@ def parse_pipeline_dict(d: dict[str, Any]) -> PipelineConfig:
         interleave_stage_sync=bool(d.get("interleave_stage_sync", False)),
         gloo_batch_recv=bool(d.get("gloo_batch_recv", True)), alternate_nccl_gloo=bool(d.get("alternate_nccl_gloo", True)),
         large_model_init=bool(d.get("large_model_init", False)), schedule=d.get("schedule"),
-        activation_recompute=bool(d.get("activation_recompute", True)), activation_offload=d.get("activation_offload"),
+        activation_recompute=d.get("activation_recompute"), activation_offload=d.get("activation_offload"),
         grad_norm_compat=str(d.get("grad_norm_compat", "mean")),
         extra={k: v for k, v in d.items() if k not in known})
     cfg.validate()
@@ -246,9 +246,11 @@ def to_dict(cfg: PipelineConfig) -> dict[str, Any]:
     for k in ("interleave_stage_sync", "large_model_init"):
         if getattr(cfg, k):
             d[k] = True
-    for k in ("gloo_batch_recv", "alternate_nccl_gloo", "activation_recompute"):
+    for k in ("gloo_batch_recv", "alternate_nccl_gloo"):
         if not getattr(cfg, k):
             d[k] = False
+    if cfg.activation_recompute is not None:
+        d["activation_recompute"] = cfg.activation_recompute
     if cfg.schedule:
         d["schedule"] = cfg.schedule
     if cfg.activation_offload is not None:

@@ -71,20 +71,23 @@ class Layer:
             self.g = {}
 
     def init_flat(self, flat: torch.Tensor, seed: int) -> None:
-        """Fills `flat` (any float dtype, CPU or GPU) deterministically from `seed`: the same
-        seed gives the same tensor on every rank, whatever the sharding."""
+        """Fills `flat` (any float dtype) deterministically from `seed` with a generator on
+        flat's own device: the same seed gives the same tensor on every rank of a job, whatever
+        the sharding or stage split (CPU and CUDA generators give different streams)."""
         lay, total = self.layout()
         flat.zero_()
-        gen = torch.Generator(device="cpu").manual_seed(seed)
+        dev = flat.device
+        gen = torch.Generator(device=dev).manual_seed(seed)
         for s in self.param_specs():
             o, sh = lay[s.name]
+            dst = flat[o:o + s.numel]
             if s.init == "normal":
-                v = torch.empty(s.numel, dtype=torch.float32).normal_(0.0, s.std, generator=gen)
+                if dst.dtype == torch.float32:
+                    dst.normal_(0.0, s.std, generator=gen)
+                else:
+                    dst.copy_(torch.empty(s.numel, dtype=torch.float32, device=dev).normal_(0.0, s.std, generator=gen))
             elif s.init == "ones":
-                v = torch.ones(s.numel, dtype=torch.float32)
-            else:
-                v = torch.zeros(s.numel, dtype=torch.float32)
-            flat[o:o + s.numel].copy_(v)
+                dst.fill_(1.0)
 
     # -- compute ------------------------------------------------------------------
     def forward(self, x, ctx: dict, ops, saved: Optional[dict]):
