@@ -35,12 +35,32 @@ struct GemmParams {
   int ldc, ld_addend;
   int flags;
   int* status;
-  // optional arrival gating of B tiles (all-gather fused GEMM): before loading rows
-  // [n0, n0+BN) of B the producer waits until gate_flags[chunk] >= gate_epoch for every
-  // chunk overlapping those rows; rows_per_chunk rows of B per chunk. nullptr = off.
+  // optional arrival gating of B tiles (all-gather fused GEMM): B lives inside a flat
+  // unsharded parameter buffer that is being filled shard by shard, chunk by chunk. Before
+  // loading rows [n0, n_end] of B the producer waits until the flag of every chunk that
+  // overlaps bytes [gate_base + n0*row_bytes, gate_base + (n_end+1)*row_bytes) of the flat
+  // buffer is >= gate_epoch. Flag index of flat byte b: (b / shard_bytes) * cps +
+  // (b % shard_bytes) / chunk_bytes; the rank's own shard needs no wait. nullptr = off.
   const int* gate_flags;
   int gate_epoch;
-  int gate_rows_per_chunk;
+  long gate_base, gate_row_bytes, gate_shard_bytes;
+  int gate_chunk_bytes, gate_cps, gate_self;
+};
+
+// All-gather half of the fused kernel: four extra warps per CTA pull the peers' shards of
+// the unit into the local unsharded buffer with plain 16-byte peer loads, chunk by chunk,
+// and publish a per-chunk flag that the TMA producers above wait for.
+constexpr int AG_MAX_R = 8;
+struct AgParams {
+  const uint4* src[AG_MAX_R];  // shard base of every rank of the group (peer-mapped)
+  uint4* dst;                  // local unsharded buffer
+  long shard_bytes;
+  int R, r;
+  int chunk_bytes, cps;        // chunk size and chunks per shard
+  int* chunk_flags;            // local, [R * cps]
+  int epoch;
+  const int* version_flags;    // local, [R]: peers publish the epoch of their bf16 shard here
+  int need_version;
 };
 
 template <int BN>
@@ -62,10 +82,10 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   return 0.5f * x * (1.f + tanhf(u));
 }
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(192, 1)
+template <int BN, bool A_MN, bool B_MN, bool FUSED_AG>
+__global__ void __launch_bounds__(FUSED_AG ? 320 : 192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const GemmParams p) {
+                 const GemmParams p, const AgParams ag) {
   using Cfg = GemmCfg<BN>;
   constexpr int BM = Cfg::BM, BK = Cfg::BK, STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -120,11 +140,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int m0 = (tile % tiles_m) * BM;
         const int n0 = (tile / tiles_m) * BN;
         if (p.gate_flags != nullptr) {
-          int c0 = n0 / p.gate_rows_per_chunk;
-          int n_end = min(n0 + BN, p.N) - 1;
-          int c1 = n_end / p.gate_rows_per_chunk;
-          for (int c = c0; c <= c1 && ok; ++c)
+          const long b0 = p.gate_base + long(n0) * p.gate_row_bytes;
+          const long b1 = p.gate_base + long(min(n0 + BN, p.N)) * p.gate_row_bytes - 1;
+          const long i0 = (b0 / p.gate_shard_bytes) * p.gate_cps + (b0 % p.gate_shard_bytes) / p.gate_chunk_bytes;
+          const long i1 = (b1 / p.gate_shard_bytes) * p.gate_cps + (b1 % p.gate_shard_bytes) / p.gate_chunk_bytes;
+          for (long c = i0; c <= i1 && ok; ++c) {
+            if (int(c / p.gate_cps) == p.gate_self) continue;
             ok = flag_wait_ge(p.gate_flags + c, p.gate_epoch, ZB_WAIT_NS, p.status, ST_TIMEOUT_FLAG);
+          }
           if (!ok) {
             *abort_flag = 1;
             break;
@@ -198,7 +221,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (ok) umma_commit(&tmem_full[buf]);
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const bool out_f32 = (p.flags & GEMM_OUT_F32) != 0;
@@ -304,6 +327,49 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   }
 
+  if (FUSED_AG && warp >= 6) {
+    // ------------------------------ all-gather copy warps ------------------------------
+    const int ct = threadIdx.x - 192;  // 0..127
+    __shared__ int s_peer_ok;
+    const int total = (ag.R - 1) * ag.cps;
+    const long chunk16 = ag.chunk_bytes / 16;
+    const long shard16 = ag.shard_bytes / 16;
+    int checked_peer = -1;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+      // ascending chunk order inside each peer, peers visited starting after this rank
+      const int c = w / (ag.R - 1);
+      const int pi = w % (ag.R - 1);
+      const int peer = (ag.r + 1 + pi) % ag.R;
+      if (peer != checked_peer) {
+        if (ct == 0)
+          s_peer_ok = flag_wait_ge(ag.version_flags + peer, ag.need_version, ZB_WAIT_NS, p.status, ST_TIMEOUT_FLAG) ? 1 : 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        ok = s_peer_ok != 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        checked_peer = peer;
+        if (!ok) break;
+      }
+      const long beg = long(c) * chunk16;
+      const long end = min(beg + chunk16, shard16);
+      const uint4* src = ag.src[peer];
+      uint4* dst = ag.dst + long(peer) * shard16;
+      long i = beg + ct;
+      for (; i + 7 * 128 < end; i += 8 * 128) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = ld_v4_relaxed_sys(src + i + u * 128);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) dst[i + u * 128] = v[u];
+      }
+      for (; i < end; i += 128) dst[i] = ld_v4_relaxed_sys(src + i);
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ct == 0) st_release_sys(ag.chunk_flags + peer * ag.cps + c, ag.epoch);
+    }
+    if (!ok) *abort_flag = 1;
+  }
+
   // ------------------------------ teardown ------------------------------
   __syncwarp();
   if (*abort_flag) {
@@ -319,8 +385,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
-static int launch_gemm(const void* A, const void* B, const GemmParams& p, int lda, int ldb,
+template <int BN, bool A_MN, bool B_MN, bool FUSED_AG>
+static int launch_gemm(const void* A, const void* B, const GemmParams& p, const AgParams& ag, int lda, int ldb,
                        int max_ctas, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap ta, tb;
@@ -331,7 +397,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
   if (!B_MN) rc = make_tmap_2d_bf16(&tb, B, p.N, p.K, ldb, BN, 64);
   else rc = make_tmap_2d_bf16(&tb, B, p.K, p.N, ldb, 64, 64);
   if (rc) return rc;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, FUSED_AG>;
   static bool attr_set = false;
   if (!attr_set) {
     ZB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
@@ -341,7 +407,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
   int ctas = num_sms();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (tiles < ctas) ctas = tiles;
-  kern<<<ctas, Cfg::NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  kern<<<ctas, FUSED_AG ? 320 : Cfg::NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p, ag);
   ZB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -350,15 +416,8 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
 
 extern "C" {
 
-// Returns 0 on success; on failure zb_last_error() describes it. `status` is a device
-// int the kernel writes a non-zero code to if one of its bounded waits ran out.
-int zb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
-                 int ldc, int a_mn_major, int b_mn_major, const void* bias, const void* addend,
-                 int ld_addend, int flags, int bn, int max_ctas, const int* gate_flags,
-                 int gate_epoch, int gate_rows_per_chunk, int* status, cudaStream_t stream) {
-  using namespace zb;
-  if (M <= 0 || N <= 0 || K <= 0) ZB_FAIL(-1, "gemm: empty problem %d x %d x %d", M, N, K);
-  GemmParams p;
+static void fill_gemm_params(zb::GemmParams& p, void* C, int M, int N, int K, int ldc, const void* bias,
+                             const void* addend, int ld_addend, int flags, int* status) {
   p.C = C;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.addend = static_cast<const __nv_bfloat16*>(addend);
@@ -366,23 +425,80 @@ int zb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
   p.ldc = ldc; p.ld_addend = ld_addend;
   p.flags = flags;
   p.status = status;
-  p.gate_flags = gate_flags;
-  p.gate_epoch = gate_epoch;
-  p.gate_rows_per_chunk = gate_rows_per_chunk > 0 ? gate_rows_per_chunk : 1;
-  if (bn != 128 && bn != 256) {
-    // 256-wide tiles unless that leaves most SMs idle
-    long tiles256 = long((M + 127) / 128) * ((N + 255) / 256);
-    bn = (tiles256 >= num_sms() || N > 128 * 2 && tiles256 * 2 > num_sms() * 3) ? 256 : 128;
-    if (N <= 128) bn = 128;
-  }
+  p.gate_flags = nullptr;
+  p.gate_epoch = 0;
+  p.gate_base = 0; p.gate_row_bytes = 0; p.gate_shard_bytes = 1;
+  p.gate_chunk_bytes = 1; p.gate_cps = 1; p.gate_self = -1;
+}
+
+static int pick_bn(int M, int N, int bn) {
+  if (bn == 128 || bn == 256) return bn;
+  long tiles256 = long((M + 127) / 128) * ((N + 255) / 256);
+  bn = (tiles256 >= zb::num_sms() || (N > 256 && tiles256 * 2 > zb::num_sms() * 3)) ? 256 : 128;
+  if (N <= 128) bn = 128;
+  return bn;
+}
+
+// Returns 0 on success; on failure zb_last_error() describes it. `status` is a device
+// int the kernel writes a non-zero code to if one of its bounded waits ran out.
+int zb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                 int ldc, int a_mn_major, int b_mn_major, const void* bias, const void* addend,
+                 int ld_addend, int flags, int bn, int max_ctas, int* status, cudaStream_t stream) {
+  using namespace zb;
+  if (M <= 0 || N <= 0 || K <= 0) ZB_FAIL(-1, "gemm: empty problem %d x %d x %d", M, N, K);
+  GemmParams p;
+  fill_gemm_params(p, C, M, N, K, ldc, bias, addend, ld_addend, flags, status);
+  AgParams ag = {};
+  bn = pick_bn(M, N, bn);
 #define ZB_DISPATCH(BN_)                                                                          \
-  if (!a_mn_major && !b_mn_major) return launch_gemm<BN_, false, false>(A, B, p, lda, ldb, max_ctas, stream); \
-  if (!a_mn_major && b_mn_major) return launch_gemm<BN_, false, true>(A, B, p, lda, ldb, max_ctas, stream);   \
-  if (a_mn_major && b_mn_major) return launch_gemm<BN_, true, true>(A, B, p, lda, ldb, max_ctas, stream);     \
-  return launch_gemm<BN_, true, false>(A, B, p, lda, ldb, max_ctas, stream);
+  if (!a_mn_major && !b_mn_major) return launch_gemm<BN_, false, false, false>(A, B, p, ag, lda, ldb, max_ctas, stream); \
+  if (!a_mn_major && b_mn_major) return launch_gemm<BN_, false, true, false>(A, B, p, ag, lda, ldb, max_ctas, stream);   \
+  if (a_mn_major && b_mn_major) return launch_gemm<BN_, true, true, false>(A, B, p, ag, lda, ldb, max_ctas, stream);     \
+  return launch_gemm<BN_, true, false, false>(A, B, p, ag, lda, ldb, max_ctas, stream);
   if (bn == 256) { ZB_DISPATCH(256) }
   ZB_DISPATCH(128)
 #undef ZB_DISPATCH
+}
+
+// All-gather fused with the GEMM that first consumes the gathered weights:
+//   C[M,N] = A[M,K] * B[N,K]^T (+bias)(+addend), B = a [N,K] weight inside the unit's flat
+//   unsharded buffer `full` (byte offset b_offset), whose remote shards this same kernel pulls
+//   from the peers (shard_ptrs, peer-mapped) while the tiles of already-present rows run.
+// chunk_flags: local int[R*cps], cps = ceil(shard_bytes / chunk_bytes); a chunk is complete
+// when its flag equals `epoch`. version_flags: local int[R] the peers write their shard epoch to.
+int zb_ag_gemm_bf16(const void* A, void* full, long b_offset_bytes, void* C, int M, int N, int K, int lda, int ldc,
+                    const void* bias, const void* addend, int ld_addend, int flags, const void* const* shard_ptrs,
+                    int R, int r, long shard_bytes, int chunk_bytes, int* chunk_flags, int epoch,
+                    const int* version_flags, int need_version, int* status, cudaStream_t stream) {
+  using namespace zb;
+  if (M <= 0 || N <= 0 || K <= 0) ZB_FAIL(-1, "ag_gemm: empty problem %d x %d x %d", M, N, K);
+  if (R < 2 || R > AG_MAX_R) ZB_FAIL(-1, "ag_gemm: group size %d unsupported (2..%d)", R, AG_MAX_R);
+  if (shard_bytes % 16 || chunk_bytes % 2048 || chunk_bytes <= 0) ZB_FAIL(-1, "ag_gemm: bad shard/chunk size");
+  GemmParams p;
+  fill_gemm_params(p, C, M, N, K, ldc, bias, addend, ld_addend, flags, status);
+  AgParams ag;
+  for (int i = 0; i < R; ++i) ag.src[i] = static_cast<const uint4*>(shard_ptrs[i]);
+  ag.dst = static_cast<uint4*>(full);
+  ag.shard_bytes = shard_bytes;
+  ag.R = R; ag.r = r;
+  ag.chunk_bytes = chunk_bytes;
+  ag.cps = int((shard_bytes + chunk_bytes - 1) / chunk_bytes);
+  ag.chunk_flags = chunk_flags;
+  ag.epoch = epoch;
+  ag.version_flags = version_flags;
+  ag.need_version = need_version;
+  p.gate_flags = chunk_flags;
+  p.gate_epoch = epoch;
+  p.gate_base = b_offset_bytes;
+  p.gate_row_bytes = long(K) * 2;
+  p.gate_shard_bytes = shard_bytes;
+  p.gate_chunk_bytes = chunk_bytes;
+  p.gate_cps = ag.cps;
+  p.gate_self = r;
+  const void* B = static_cast<const char*>(full) + b_offset_bytes;
+  const int bn = pick_bn(M, N, 0);
+  if (bn == 256) return launch_gemm<256, false, false, true>(A, B, p, ag, lda, K, 0, stream);
+  return launch_gemm<128, false, false, true>(A, B, p, ag, lda, K, 0, stream);
 }
 
 const char* zb_last_error() { return zb::last_error_buf(); }

@@ -1,0 +1,40 @@
+"""Multi-GPU tests (one process per GPU, NCCL): library collectives and the fused NVLink
+kernels must agree with each other and with the fp32 oracle."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _run(nproc, *args, timeout=600):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29631", os.path.join(HERE, "gpu_dist_worker.py"), *args]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
+    assert r.returncode == 0, f"worker failed:\n{r.stdout[-4000:]}\n{r.stderr[-4000:]}"
+    return r.stdout
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("case", ["dp2_library", "dp2_fused", "pp2", "fused_kernels"])
+def test_two_gpus(case):
+    out = _run(2, case)
+    assert "WORKER_OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 4, reason="needs 4 GPUs")
+@pytest.mark.parametrize("case", ["pp2dp2_library", "pp2dp2_fused"])
+def test_four_gpus(case):
+    out = _run(4, case)
+    assert "WORKER_OK" in out

@@ -338,8 +338,13 @@ class StageEngine:
         self.device, self.cfg, self.ops = device, cfg, ops
         self.streams = streams or Streams(device)
         self.counters = Counters()
-        self.units = [ZeroUnit(ly, gid, device=device, cfg=cfg, ops=ops, shard=shard, replicate=replicate, rank=rank,
-                               streams=self.streams, zero_level=zero_level, counters=self.counters, meta_init=meta_init)
+        cls = ZeroUnit
+        if cfg.collectives == "fused" and device.type == "cuda" and shard.size > 1 and replicate.size == 1:
+            from .fused import FusedZeroUnit
+
+            cls = FusedZeroUnit
+        self.units = [cls(ly, gid, device=device, cfg=cfg, ops=ops, shard=shard, replicate=replicate, rank=rank,
+                          streams=self.streams, zero_level=zero_level, counters=self.counters, meta_init=meta_init)
                       for ly, gid in zip(layers, gids)]
 
     def __len__(self):

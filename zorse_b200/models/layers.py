@@ -160,7 +160,11 @@ class TransformerBlock(Layer):
     # ---- sub-blocks ---------------------------------------------------------------
     def _attn_fwd(self, xin, resid, ctx, ops, sv):
         p, B, S = self.p, ctx["B"], ctx["S"]
-        qkv = ops.linear_fwd(xin, p["qkv_w"], p.get("qkv_b"))
+        ag = self.__dict__.pop("_ag", None)  # left by a fused ZeRO unit: gather the unit inside this GEMM
+        if ag is not None:
+            qkv = ops.linear_fwd_gather(xin, "qkv_w", ag, p.get("qkv_b"))
+        else:
+            qkv = ops.linear_fwd(xin, p["qkv_w"], p.get("qkv_b"))
         cs = self._rope(ops, S, xin.device)
         if cs is not None:
             ops.rope_(qkv, cs, S, self.Hq + self.Hkv, self.D)
@@ -375,6 +379,9 @@ class HeadLayer(Layer):
             n, st = xp, None
         if saved is not None:
             saved.update(xp=xp, n=n, st=st)
+        ag = self.__dict__.pop("_ag", None)
+        if ag is not None:
+            return ops.linear_fwd_gather(n, "head_w", ag, self.p.get("head_b"))
         return ops.linear_fwd(n, self.p["head_w"], self.p.get("head_b"))
 
     def forward(self, x, ctx, ops, saved=None):

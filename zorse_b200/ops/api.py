@@ -153,6 +153,14 @@ class Sm100Ops:
         y = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
         return self.k.gemm(x, w, y, bias=bias, addend=addend)
 
+    def linear_fwd_gather(self, x, name, ag, bias=None):
+        """Forward GEMM that also all-gathers the unit's parameters (see engine/fused.py)."""
+        off, shape = ag.layout[name]
+        y = torch.empty(x.shape[0], shape[0], dtype=x.dtype, device=x.device)
+        return self.k.ag_gemm(x, ag.full, off, shape, y, shard_ptrs=ag.shard_ptrs, R=ag.R, r=ag.r,
+                              shard_elems=ag.shard_n, chunk_bytes=ag.chunk_bytes, chunk_flags=ag.chunk_flags,
+                              epoch=ag.epoch, version_flags=ag.version_flags, need_version=ag.need_version, bias=bias)
+
     def linear_dgrad(self, dy, w, addend=None):
         dx = torch.empty(dy.shape[0], w.shape[1], dtype=dy.dtype, device=dy.device)
         return self.k.gemm(dy, w, dx, b_mn=True, addend=addend)

@@ -104,13 +104,11 @@ def _bf16(t: torch.Tensor, name: str) -> None:
 # --------------------------------------------------------------------------- GEMM
 def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          bias: Optional[torch.Tensor] = None, addend: Optional[torch.Tensor] = None, accumulate: bool = False,
-         act: Optional[str] = None, bn: int = 0, max_ctas: int = 0,
-         gate: Optional[tuple] = None) -> torch.Tensor:
+         act: Optional[str] = None, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
     """out[M,N] = A @ B^T (+bias) (+addend), or out += ... with accumulate.
 
     a: [M,K] (K-major) or [K,M] when a_mn; b: [N,K] (K-major) or [K,N] when b_mn.
-    out: bf16 or fp32 [M,N]. gate = (flags int32 tensor, epoch, rows_per_chunk) makes the
-    loader of B wait for chunk-arrival flags (all-gather fused GEMM).
+    out: bf16 or fp32 [M,N].
     """
     _bf16(a, "a"); _bf16(b, "b")
     M, N = out.shape
@@ -129,12 +127,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = Fa
         flags |= GEMM_GELU
     elif act == "relu":
         flags |= GEMM_RELU
-    gflags, gepoch, grows = (None, 0, 1) if gate is None else gate
     rc = lib().zb_gemm_bf16(_p(a), _p(b), _p(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
                             c_int(b.stride(0)), c_int(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)),
                             _p(bias), _p(addend), c_int(0 if addend is None else addend.stride(0)),
-                            c_int(flags), c_int(bn), c_int(max_ctas), _p(gflags), c_int(gepoch), c_int(grows),
-                            _p(status_word(a.device)), _stream())
+                            c_int(flags), c_int(bn), c_int(max_ctas), _p(status_word(a.device)), _stream())
     _check(rc, "gemm")
     return out
 
@@ -282,3 +278,54 @@ def flash_bwd(do, qkv, o, lse, B: int, S: int, Hq: int, Hkv: int, D: int, causal
     global _launches
     _launches += 2  # delta + finish kernels
     return dqkv
+
+
+# --------------------------------------------------------------------------- fused collectives
+def _ptr_array(ptrs):
+    arr = (c_void_p * len(ptrs))(*[c_void_p(int(x)) for x in ptrs])
+    return arr
+
+
+def ag_gemm(a: torch.Tensor, full: torch.Tensor, w_offset: int, w_shape, out: torch.Tensor, *, shard_ptrs, R: int,
+            r: int, shard_elems: int, chunk_bytes: int, chunk_flags: torch.Tensor, epoch: int,
+            version_flags: torch.Tensor, need_version: int, bias=None, addend=None) -> torch.Tensor:
+    """out = a @ W^T with W = full[w_offset : w_offset + N*K].view(N, K), while the same kernel
+    pulls the other ranks' shards of the unit into `full` (all-gather fused with the GEMM).
+    shard_ptrs: device addresses of every rank's bf16 shard (peer-mapped), by group rank."""
+    _bf16(a, "a")
+    N, K = w_shape
+    M = a.shape[0]
+    assert out.shape == (M, N) and a.shape[1] == K and out.dtype == torch.bfloat16
+    rc = lib().zb_ag_gemm_bf16(_p(a), _p(full), c_long(w_offset * 2), _p(out), c_int(M), c_int(N), c_int(K),
+                               c_int(a.stride(0)), c_int(out.stride(0)), _p(bias), _p(addend),
+                               c_int(0 if addend is None else addend.stride(0)), c_int(0), _ptr_array(shard_ptrs),
+                               c_int(R), c_int(r), c_long(shard_elems * 2), c_int(chunk_bytes), _p(chunk_flags),
+                               c_int(epoch), _p(version_flags), c_int(need_version), _p(status_word(a.device)),
+                               _stream())
+    _check(rc, "ag_gemm")
+    return out
+
+
+def rs_adam(grad_ptrs, flag_ptrs, R: int, r: int, shard_elems: int, master, m, v, p16, *, lr, beta1, beta2, eps,
+            weight_decay, step, grad_scale, grad_f32: bool, epoch: int, counter: torch.Tensor, max_blocks: int = 0,
+            wait_seconds: float = 2.0):
+    """Fused reduce-scatter + Adam: sums slice r of every rank's gradient bucket (peer loads)
+    and updates master/m/v/p16 in one pass. grad_ptrs / flag_ptrs: device addresses by group rank."""
+    rc = lib().zb_rs_adam(_ptr_array(grad_ptrs), _ptr_array(flag_ptrs), c_int(R), c_int(r), c_long(shard_elems),
+                          _p(master), _p(m), _p(v), _p(p16), c_float(lr), c_float(beta1), c_float(beta2), c_float(eps),
+                          c_float(weight_decay), c_int(step), c_float(grad_scale), c_int(int(grad_f32)), c_int(epoch),
+                          _p(counter), c_int(max_blocks), ctypes.c_double(wait_seconds),
+                          _p(status_word(master.device)), _stream())
+    _check(rc, "rs_adam")
+
+
+def wait_flags(flags: torch.Tensor, R: int, which: int, epoch: int, wait_seconds: float = 2.0):
+    """One-thread kernel that returns once flags[which*R + q] >= epoch for all q (bounded)."""
+    _check(lib().zb_wait_flags(_p(flags), c_int(R), c_int(which), c_int(epoch), ctypes.c_double(wait_seconds),
+                               _p(status_word(flags.device)), _stream()), "wait_flags")
+
+
+def peer_pull(src_ptr: int, dst: torch.Tensor, nbytes: int, max_blocks: int = 0):
+    """Copies nbytes from a peer-mapped device address into dst with plain peer loads."""
+    _check(lib().zb_peer_pull(c_void_p(int(src_ptr)), _p(dst), c_long(nbytes), c_int(max_blocks), _stream()),
+           "peer_pull")

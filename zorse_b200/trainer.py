@@ -50,6 +50,8 @@ class Trainer:
     def __init__(self, cfg: PipelineConfig, opt: TrainerOptions):
         if opt.offload_model_params and not opt.optimizer_in_backward:
             raise ValueError("--offload_model_params requires --optimizer_in_backwards")
+        if opt.collectives == "fused":
+            opt.optimizer_in_backward = True  # the fused reduce-scatter kernel applies Adam itself
         self.cfg, self.opt = cfg, opt
         self.device = G.dist_init(opt.backend)
         self.rank, self.world = G.rank(), G.world_size()
