@@ -1,0 +1,110 @@
+"""Checkpoint round trip / re-sharding and host-side failure detection (no GPU involved)."""
+import os
+import time
+
+import pytest
+import torch
+
+from dist_utils import run_workers
+from zorse_b200.config.training_config import parse_pipeline_dict
+from zorse_b200.utils.health import DictStore, Heartbeat, Watchdog
+from test_dist_cpu import PIPE_1x2, PIPE_2x1, tiny_cfg
+
+
+def _train_and_save(rank, world, cfg_dict, ckdir, steps):
+    from zorse_b200.ckpt.writer import save_checkpoint
+    from zorse_b200.trainer import Trainer, TrainerOptions
+
+    tr = Trainer(parse_pipeline_dict(cfg_dict), TrainerOptions(backend="gloo", schedule="layer_major"))
+    batch = tr.synthetic_batch()
+    for _ in range(steps):
+        tr.train_step_from_host(batch)
+    save_checkpoint(tr, ckdir, steps)
+    return tr.global_loss(tr.train_step_from_host(batch))
+
+
+def _load_and_step(rank, world, cfg_dict, ckdir, steps):
+    from zorse_b200.ckpt.reader import load_checkpoint
+    from zorse_b200.trainer import Trainer, TrainerOptions
+
+    tr = Trainer(parse_pipeline_dict(cfg_dict), TrainerOptions(backend="gloo", schedule="layer_major", seed=0))
+    assert load_checkpoint(tr, os.path.join(ckdir, f"step_{steps}")) == steps
+    batch = tr.synthetic_batch()
+    return tr.global_loss(tr.train_step_from_host(batch))
+
+
+def test_checkpoint_resume_and_reshard(tmp_path):
+    ck = str(tmp_path / "ck")
+    a = run_workers(2, _train_and_save, tiny_cfg(PIPE_2x1), ck, 2)
+    # same plan
+    b = run_workers(2, _load_and_step, tiny_cfg(PIPE_2x1), ck, 2)
+    assert abs(a[0] - b[0]) < 1e-5, (a, b)
+    # different plan: one stage, 2-way sharded
+    c = run_workers(2, _load_and_step, tiny_cfg(PIPE_1x2), ck, 2)
+    assert abs(a[0] - c[0]) < 1e-4, (a, c)
+
+
+def test_corrupt_checkpoint_is_detected(tmp_path):
+    from zorse_b200.ckpt.reader import CheckpointError, read_meta
+
+    ck = str(tmp_path / "ck")
+    run_workers(2, _train_and_save, tiny_cfg(PIPE_2x1), ck, 1)
+    d = os.path.join(ck, "step_1")
+    f = os.path.join(d, "stage0_rank0.bin")
+    with open(f, "r+b") as fh:
+        fh.truncate(os.path.getsize(f) // 2)
+    with pytest.raises(RuntimeError, match="truncated"):
+        run_workers(2, _load_and_step, tiny_cfg(PIPE_2x1), ck, 1, timeout=120)
+    os.remove(os.path.join(d, "meta.json"))
+    with pytest.raises(CheckpointError):
+        read_meta(d)
+
+
+def test_heartbeat_names_the_silent_rank():
+    now = [1000.0]
+    store = DictStore()
+    hbs = [Heartbeat(store, r, 3, clock=lambda: now[0]) for r in range(3)]
+    for h in hbs:
+        h.beat(0)
+    now[0] += 5
+    hbs[0].beat(1)
+    hbs[2].beat(1)       # rank 1 never reports step 1
+    now[0] += 5
+    assert hbs[0].stale_ranks(limit_s=8.0) == [1]
+    assert hbs[0].stale_ranks(limit_s=100.0, min_step=1) == [1]
+
+
+def test_watchdog_fires_on_a_stuck_step():
+    fired = []
+    w = Watchdog(0.3, on_timeout=lambda step, idle: fired.append((step, idle)), poll_s=0.05)
+    w.start()
+    w.beat(7)
+    time.sleep(0.15)
+    w.beat(8)
+    time.sleep(0.15)
+    assert not fired
+    time.sleep(0.5)
+    assert fired and fired[0][0] == 8
+    w.stop()
+
+
+def _rank_that_dies(rank, world):
+    """A rank that raises before joining a collective: the others see a bounded failure."""
+    import datetime
+
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    if rank == 1:
+        raise RuntimeError("injected host-side fault")
+    t = torch.ones(1)
+    try:
+        dist.all_reduce(t)
+    except Exception as e:  # the surviving rank gets an error, not a hang
+        return f"error: {type(e).__name__}"
+    return "no error"
+
+
+def test_peer_failure_ends_collective_with_error():
+    with pytest.raises(RuntimeError, match="injected host-side fault|rank 0 failed|exited"):
+        run_workers(2, _rank_that_dies, timeout=90)

@@ -1,0 +1,180 @@
+"""Config parsing/validation, static p2p plans, planner arithmetic, comm model, file formats."""
+import json
+import math
+import os
+
+import pytest
+from hypothesis import given, settings
+from hypothesis import strategies as st
+
+from zorse_b200.config import training_config as tc
+from zorse_b200.models import registry
+from zorse_b200.parallel.p2p_plan import create_static_comm_plans, interleave_owners
+from zorse_b200.planner import comm_model as cm
+from zorse_b200.planner.cluster import GPU, GPUGroup, ModelConfig, ModelLatencies
+from zorse_b200.planner.memory import group_memory_bytes
+from zorse_b200.planner.stage2 import PipelineOptimizer, distribute_layers, distribute_microbatches
+
+REF_EXAMPLE = {
+    "model_name": "deepspeedllama_tiny", "global_batch_size": 128, "microbatch_size": 2, "sequence_length": 512,
+    "vocab_size": 49152, "fused_optimizer": True, "interleave_degree": 1, "latency": 7721.375000533334,
+    "autocast_dtype": "float16", "reduce_dtype": "float32",
+    "pipeline_config": [{"gpu_ranks": [0, 3, 2, 1], "num_microbatches_per_rank": [18, 1, 28, 17],
+                         "layer_partition": [0, 22], "zero_config": [[0, 3, 2, 1]]}]}
+
+
+def test_reference_example_round_trip():
+    cfg = tc.parse_pipeline_dict(REF_EXAMPLE)
+    assert cfg.num_microbatches == 64 and cfg.stages[0].num_microbatches_per_rank == (18, 1, 28, 17)
+    assert cfg.gloo_batch_recv and cfg.alternate_nccl_gloo and not cfg.sync_after_recompute
+    again = tc.parse_pipeline_dict(json.loads(json.dumps(tc.to_dict(cfg))))
+    assert tc.to_dict(again) == tc.to_dict(cfg)
+    assert tc.to_dict(cfg)["latency"] == REF_EXAMPLE["latency"]
+
+
+@pytest.mark.parametrize("mutate,msg", [
+    (lambda d: d["pipeline_config"][0].update(layer_partition=[1, 22]), "starts at"),
+    (lambda d: d["pipeline_config"][0].update(num_microbatches_per_rank=[1, 1, 1, 1]), "microbatches"),
+    (lambda d: d["pipeline_config"][0].update(zero_config=[[0, 3], [2]]), "partition|sizes"),
+    (lambda d: d.update(global_batch_size=127), "multiple"),
+    (lambda d: d.update(autocast_dtype="int8"), "dtype"),
+    (lambda d: d.pop("model_name"), "required"),
+])
+def test_config_validation_errors(mutate, msg):
+    d = json.loads(json.dumps(REF_EXAMPLE))
+    mutate(d)
+    with pytest.raises(tc.ConfigError, match=msg):
+        tc.parse_pipeline_dict(d)
+
+
+def test_stage_sorting_gaps_and_even_split():
+    d = json.loads(json.dumps(REF_EXAMPLE))
+    d["split_microbatches_evenly"] = True
+    d["pipeline_config"] = [
+        {"gpu_ranks": [2, 3], "layer_partition": [10, 22], "zero_config": [[2], [3]]},
+        {"gpu_ranks": [0, 1], "layer_partition": [0, 10], "zero_config": [[0, 1]]}]
+    cfg = tc.parse_pipeline_dict(d)
+    assert [s.layer_partition for s in cfg.stages] == [(0, 10), (10, 22)]
+    assert cfg.stages[0].num_microbatches_per_rank == (32, 32)
+    assert cfg.stages[1].replicate_group_of(3) == (2, 3) and cfg.stages[1].shard_group_of(3) == (3,)
+    d["pipeline_config"][0]["layer_partition"] = [11, 22]
+    with pytest.raises(tc.ConfigError, match="contiguous"):
+        tc.parse_pipeline_dict(d)
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.lists(st.integers(0, 9), min_size=1, max_size=5).filter(lambda c: sum(c) > 0))
+def test_interleave_owners_counts(counts):
+    own = interleave_owners(counts)
+    assert len(own) == sum(counts)
+    assert [own.count(k) for k in range(len(counts))] == list(counts)
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 3), st.integers(1, 3), st.integers(1, 3), st.integers(2, 12), st.data())
+def test_static_plan_invariants(w0, w1, w2, M, data):
+    widths = [w0, w1, w2]
+    pipe, rank, bounds = [], 0, [0, 2, 3, 4]
+    for i, w in enumerate(widths):
+        ranks = list(range(rank, rank + w))
+        rank += w
+        cuts = sorted(data.draw(st.lists(st.integers(0, M), min_size=w - 1, max_size=w - 1)))
+        counts = [b - a for a, b in zip([0] + cuts, cuts + [M])]
+        pipe.append({"gpu_ranks": ranks, "num_microbatches_per_rank": counts, "layer_partition": [bounds[i], bounds[i + 1]],
+                     "zero_config": [ranks]})
+    cfg = tc.parse_pipeline_dict({"model_name": "tiny_llama", "global_batch_size": M, "microbatch_size": 1,
+                                  "sequence_length": 8, "pipeline_config": pipe})
+    plans = create_static_comm_plans(cfg)  # validates: each transfer once, mirrored, unique tags
+    assert sorted(plans) == list(range(rank))
+    for st_cfg in cfg.stages:
+        got = sorted(g for r in st_cfg.gpu_ranks for g in plans[r].stages[st_cfg.stage_id].microbatches)
+        assert got == list(range(M))
+
+
+@settings(max_examples=50, deadline=None)
+@given(st.integers(1, 200), st.lists(st.floats(0.5, 50.0), min_size=1, max_size=8))
+def test_distribution_sum_rules(total, lat):
+    m = distribute_microbatches(total, lat)
+    assert sum(m) == total and all(x >= 0 for x in m)
+    fastest, slowest = lat.index(min(lat)), lat.index(max(lat))
+    assert m[fastest] >= m[slowest]
+    L = distribute_layers(total, lat)
+    assert sum(L) == total and L[fastest] >= L[slowest]
+
+
+def _groups(n_groups, per_group, ag=1.0):
+    out, r = [], 0
+    for g in range(n_groups):
+        gp = [GPU("b200", r + i) for i in range(per_group)]
+        r += per_group
+        out.append(GPUGroup(g, gp, ag, ag, 0.05, 0.05))
+    return out
+
+
+def test_optimizer_latency_monotone_and_uneven_split():
+    model = ModelConfig("llama2_7b", 32, 4096, 202383360, 6738415616, 4096, 64)
+    lat = {"b200": ModelLatencies(2.0, 4.0)}
+    opt = PipelineOptimizer(_groups(4, 2), model, lat, 1)
+    res = opt.optimize()
+    assert res is not None and sum(s.num_layers for s in res.stages) == 32
+    slow = PipelineOptimizer(_groups(4, 2), model, {"b200": ModelLatencies(4.0, 8.0)}, 1).optimize()
+    assert slow.latency_ms > res.latency_ms
+    # a slower group gets fewer layers
+    groups = _groups(2, 4)
+    groups[1].gpus = [GPU("h100", 4 + i) for i in range(4)]
+    res2 = PipelineOptimizer(groups, model, {"b200": ModelLatencies(2.0, 4.0), "h100": ModelLatencies(4.0, 9.0)}, 1,
+                             max_interleave=1).optimize()
+    n = {s.group_id: s.num_layers for s in res2.stages}
+    assert n[0] > n[1] and n[0] + n[1] == 32
+    # interleaving keeps every layer exactly once and each group's total
+    st2 = opt.interleave(opt.generate_stage_configs()[0], 2)
+    assert [s.layer_partition[0] for s in st2] == sorted(s.layer_partition[0] for s in st2)
+    assert st2[-1].layer_partition[1] == 32 and len(st2) == 8
+
+
+def test_memory_model_and_comm_model():
+    one = group_memory_bytes([8], 2, 202383360, 1, 4096, 4096)
+    two = group_memory_bytes([4, 4], 2, 202383360, 1, 4096, 4096)
+    assert math.isclose(one, two)  # maxpair covers all 8 layers in both
+    assert group_memory_bytes([8], 4, 202383360, 1, 4096, 4096) < one
+    bw = [[0, 10.0], [10.0, 0]]
+    size = 1e9
+    assert math.isclose(cm.ring_collective_ms(size, bw), 0.5 * 1.0 / 10 * 1e3)
+    assert math.isclose(cm.ring_collective_ms_v2(size, bw), 1.15 * 0.5 / 10 * 1e3)
+    assert math.isclose(cm.switch_collective_ms(size, 2, 0.02, 700.0), 0.02 + 0.5 / 700 * 1e3)
+    assert cm.p2p_ms(5e6, 10.0, 0.004) == pytest.approx(4.0 * 0.9)
+    assert cm.p2p_ms(2e7, 10.0, 0.004) == pytest.approx(4.0 + 1.0)
+
+
+def test_model_registry_parameter_counts():
+    # per-layer counts published in the reference's data/model_stats.json
+    for name, per_layer in [("deepspeedllama_7b", 202383360), ("deepspeedllama_tiny", 51384320),
+                            ("deepspeedllama_3b", 123910400), ("deepspeedllama_13b", 317204480),
+                            ("deepspeedllama_65b", 809517056)]:
+        assert registry.get_model_stats(name)["parameters_per_layer"] == per_layer
+    assert registry.get_model_stats("deepspeedllama_7b", vocab=49152)["total_parameters"] == 6878924800
+    assert registry.get_config_for_model("deepspeedllama_13b") == (40, 5120, 40, 13824)
+    s = registry.get_spec("llama3.2_1b")
+    assert (s.n_kv, s.head_dim, s.vocab) == (8, 64, 128256)
+    with pytest.raises(ValueError, match="Unsupported model"):
+        registry.get_spec("nope")
+    layers = registry.build_stage_layers(registry.get_spec("tiny_llama"), 2, 4, 128)
+    assert [l.kind for l in layers] == ["block", "block", "head"]
+
+
+def test_planner_end_to_end(tmp_path):
+    from zorse_b200.planner.plan import export_config, plan
+
+    gl = [{"index": i, "name": "NVIDIA B200", "memory_total_mib": 183359, "id": f"gpu_{i}", "machine": "m0",
+           "global_rank": i} for i in range(8)]
+    data = {"machines": [{"machine": "m0", "num_gpus": 8, "machine_index": 0, "gpus": gl}], "gpu_list": gl,
+            "total_gpus": 8, "bandwidth": {"internode_bandwidth": {}, "intranode_bandwidth": {"0": 770.0},
+                                           "internode_latency": {}, "intranode_latency": {"0": 2e-5}},
+            "collective_fit": {"all_gather": {"2": {"alpha_ms": 0.03, "bandwidth_gbs": 650.0}},
+                               "reduce_scatter": {"2": {"alpha_ms": 0.03, "bandwidth_gbs": 650.0}}}}
+    res, tried = plan(data, "llama2_7b", global_batch_size=64, sequence_length=4096, ks=[4])
+    assert res is not None and len(res.stages) == 4 and [t["k"] for t in tried] == [4]
+    out = export_config(res, "llama2_7b", 64, 4096, 32000, "bfloat16", "float32", str(tmp_path / "plan.json"))
+    cfg = tc.parse_pipeline_config(str(tmp_path / "plan.json"))   # the trainer's reader accepts the planner's output
+    assert cfg.world_size == 8 and cfg.latency == pytest.approx(res.latency_ms)
+    assert all(len(s.gpu_ranks) == 2 for s in cfg.stages)

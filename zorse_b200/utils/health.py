@@ -1,0 +1,96 @@
+"""Failure detection on the host: per-step heartbeats and a watchdog.
+
+The reference has none (only collective timeouts, utils/comm.py:15, 113-114).  Here every
+rank publishes `(step, wall time)` to the rendezvous store after each step; `stale_ranks`
+names ranks whose heartbeat is older than a limit, and `Watchdog` is a thread that turns a
+step that exceeds its time limit into a diagnostic dump and a clean abort (`os._exit`)
+instead of a silent hang.  Device-side waits are bounded separately (kernel status word).
+Nothing here touches a GPU.
+"""
+from __future__ import annotations
+
+import faulthandler
+import os
+import sys
+import threading
+import time
+from typing import Callable, Optional
+
+
+class Heartbeat:
+    """Writes `hb/<rank>` = "step:time" into a key-value store (torch TCPStore/FileStore or any
+    object with set/get)."""
+
+    def __init__(self, store, rank: int, world: int, clock: Callable[[], float] = time.time):
+        self.store, self.rank, self.world, self.clock = store, rank, world, clock
+
+    def beat(self, step: int) -> None:
+        self.store.set(f"hb/{self.rank}", f"{step}:{self.clock():.3f}")
+
+    def read(self, rank: int):
+        try:
+            v = self.store.get(f"hb/{rank}")
+        except Exception:
+            return None
+        if isinstance(v, bytes):
+            v = v.decode()
+        if not v:
+            return None
+        s, t = v.split(":")
+        return int(s), float(t)
+
+    def stale_ranks(self, limit_s: float, min_step: Optional[int] = None) -> list[int]:
+        """Ranks with no heartbeat, one older than limit_s, or (if given) behind min_step."""
+        now, out = self.clock(), []
+        for r in range(self.world):
+            hb = self.read(r)
+            if hb is None or now - hb[1] > limit_s or (min_step is not None and hb[0] < min_step):
+                out.append(r)
+        return out
+
+
+class DictStore:
+    """In-process stand-in for a rendezvous store (tests)."""
+
+    def __init__(self):
+        self.d: dict = {}
+
+    def set(self, k, v):
+        self.d[k] = v
+
+    def get(self, k):
+        return self.d.get(k, "")
+
+
+class Watchdog(threading.Thread):
+    def __init__(self, timeout_s: float, rank: int = 0, on_timeout: Optional[Callable[[int, float], None]] = None,
+                 poll_s: float = 0.5):
+        super().__init__(daemon=True)
+        self.timeout_s, self.rank, self.poll_s = timeout_s, rank, poll_s
+        self.on_timeout = on_timeout or self._abort
+        self._last = time.monotonic()
+        self._step = -1
+        self._stop = threading.Event()
+        self.fired = False
+
+    def beat(self, step: int) -> None:
+        self._step = step
+        self._last = time.monotonic()
+
+    def stop(self) -> None:
+        self._stop.set()
+
+    def run(self) -> None:
+        while not self._stop.wait(self.poll_s):
+            idle = time.monotonic() - self._last
+            if idle > self.timeout_s:
+                self.fired = True
+                self.on_timeout(self._step, idle)
+                return
+
+    def _abort(self, step: int, idle: float) -> None:
+        sys.stderr.write(f"[watchdog] rank {self.rank}: no progress for {idle:.1f}s after step {step}; "
+                         f"dumping stacks and aborting\n")
+        faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
+        sys.stderr.flush()
+        os._exit(3)
