@@ -172,6 +172,15 @@ def main():
     tr.check_kernels()
     loss_val = tr.global_loss(loss)
 
+    # ---- exposed communication: one extra step with every compute-stream wait on comm bracketed ----
+    tr.measure_exposed_comm(True)
+    tr.train_step(inputs, targets)
+    exposed = torch.tensor([tr.exposed_comm_ms()], device=tr.device)
+    tr.measure_exposed_comm(False)
+    if world > 1:
+        dist.all_reduce(exposed, op=dist.ReduceOp.MAX)
+    exposed_ms = float(exposed.item())
+
     # ---- end to end through the public API: H2D of the inputs + D2H of the loss every step ----
     e2e = None
     if not args.skip_e2e:
@@ -207,6 +216,7 @@ def main():
                        "reduce_dtype": args.reduce_dtype, "collectives": args.collectives,
                        "l2": "per-step working set (>100 GB of parameters, optimizer state and activations) far exceeds the 126 MB L2; no flush needed"},
             "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches, "loss": loss_val,
+            "exposed_comm_ms_per_step": exposed_ms,
             "max_memory_allocated_gb_rank0": mem,
         }
         print(json.dumps(out))

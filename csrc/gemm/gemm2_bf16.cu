@@ -1,0 +1,321 @@
+// bf16 GEMM on CTA pairs: tcgen05.mma.cta_group::2 with a 256 x 256 output tile per pair.
+//
+// Two CTAs of a cluster (2,1,1) share one tile: each holds 128 rows of A and of the fp32
+// accumulators (its own tensor memory) and loads HALF of the B tile (128 of the 256 rows);
+// the MMA issued by the leader CTA reads A and B from both CTAs' shared memory.  Per k-block a
+// pair moves 64 KB for 256x256x64 MACs, 1.5x the arithmetic intensity of the single-CTA
+// 128x256 kernel, which is what the L2 -> SM path needs at tensor-core rate.
+//   * every TMA load is issued by the CTA that receives the data, WITHOUT cluster multicast;
+//     its mbarrier completion is routed to the leader's barrier (cta_group::2 form),
+//   * tcgen05.commit with cluster multicast hands stages / accumulators back to both CTAs,
+//   * warp roles per CTA: 0 = TMA producer, 1 = MMA issuer (leader only) + TMEM owner,
+//     2..5 = epilogue for the CTA's own 128 rows.
+// Operand layouts and epilogue options are those of gemm_bf16.cu.
+#include "../common/host.h"
+#include "../common/ptx.cuh"
+#include "gemm_common.cuh"
+
+namespace zb {
+
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.aligned;\nbarrier.cluster.wait.aligned;" ::: "memory");
+}
+// arrive on the barrier at the same shared-memory offset in CTA `cta` of the cluster
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+      "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}" ::"r"(smem_u32(bar)),
+      "r"(cta)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tmap, uint64_t* leader_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%3, %4}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(leader_bar) & PEER_BIT_MASK), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const void* tmap, uint64_t* leader_bar, int x, int y,
+                                                 int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%3, %4, %5}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(leader_bar) & PEER_BIT_MASK), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0),
+        "r"(0), "r"(0), "r"(0)
+      : "memory");
+}
+// arrives (once all MMAs issued so far are complete) on the barrier at this offset in BOTH CTAs
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(uint16_t(3))
+      : "memory");
+}
+
+struct Gemm2Cfg {
+  static constexpr int BM = 256;   // per pair; 128 per CTA
+  static constexpr int BN = 256;   // per pair; each CTA loads 128 rows of B
+  static constexpr int BK = 64;
+  static constexpr int A_BYTES = 128 * BK * 2;
+  static constexpr int B_BYTES = 128 * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+struct Gemm2Extra {
+  int a_3d, b_3d;  // MN-major operand fetched with one 3-D TMA box {64, BK, 2} instead of two 2-D boxes
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const GemmParams p, const Gemm2Extra ex) {
+  using Cfg = Gemm2Cfg;
+  constexpr int BK = Cfg::BK, STAGES = Cfg::STAGES, BN = Cfg::BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;                          // leader's copy is the one in use
+  uint64_t* empty = bars + STAGES;                // each CTA waits on its own
+  uint64_t* tmem_full = bars + 2 * STAGES;        // [2], each CTA waits on its own
+  uint64_t* tmem_empty = bars + 2 * STAGES + 2;   // [2], leader's copy, 8 arrivals
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();
+  const bool leader = cta == 0;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int tiles_m = (p.M + Cfg::BM - 1) / Cfg::BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  WaitCtx wctx{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 8);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // barriers of both CTAs are initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile % tiles_m) * Cfg::BM + int(cta) * 128;
+        const int n0 = (tile / tiles_m) * BN + int(cta) * 128;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, wctx, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          if (leader) mbar_expect_tx(&full[stage], 2 * Cfg::STAGE_BYTES);
+          if (!A_MN) {
+            tma_load_2d_pair(sa, &tmap_a, &full[stage], kb * BK, m0);
+          } else if (ex.a_3d) {
+            tma_load_3d_pair(sa, &tmap_a, &full[stage], 0, kb * BK, m0 >> 6);
+          } else {
+            tma_load_2d_pair(sa, &tmap_a, &full[stage], m0, kb * BK);
+            tma_load_2d_pair(sa + BK * 128, &tmap_a, &full[stage], m0 + 64, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(sb, &tmap_b, &full[stage], kb * BK, n0);
+          } else if (ex.b_3d) {
+            tma_load_3d_pair(sb, &tmap_b, &full[stage], 0, kb * BK, n0 >> 6);
+          } else {
+            tma_load_2d_pair(sb, &tmap_b, &full[stage], n0, kb * BK);
+            tma_load_2d_pair(sb + BK * 128, &tmap_b, &full[stage], n0 + 64, kb * BK);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(256, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+        const int buf = local & 1;
+        const uint32_t use = uint32_t(local >> 1);
+        if (!mbar_wait(&tmem_empty[buf], (use & 1) ^ 1, wctx, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + uint32_t(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, wctx, ST_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            uint64_t da = A_MN ? umma_desc_mnmajor(sa + kk * 16 * 128, BK * 128) : umma_desc_kmajor(sa + kk * 32);
+            uint64_t db = B_MN ? umma_desc_mnmajor(sb + kk * 16 * 128, BK * 128) : umma_desc_kmajor(sb + kk * 32);
+            umma_f16_ss_pair(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair(&tmem_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (own 128 rows) ------------------------------
+    const int q = warp & 3;
+    const EpilogueCfg ecfg = epilogue_cfg(p);
+    int local = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
+      const int m0 = (tile % tiles_m) * Cfg::BM + int(cta) * 128;
+      const int n0 = (tile / tiles_m) * BN;
+      const int buf = local & 1;
+      const uint32_t use = uint32_t(local >> 1);
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[buf], use & 1, wctx, ST_TIMEOUT_TMEM_FULL))) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * BN + c * 32), r);
+        tmem_wait_ld();
+        if (!row_ok) continue;
+        epilogue_store_chunk(p, ecfg, row, col0, r);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(&tmem_empty[buf], 0);
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  __syncwarp();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  cluster_sync_all();  // the leader's MMAs read the peer's shared memory: leave together
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// 3-D view of an MN-major operand stored [K rows, MN cols]: {64 within a block, K, MN/64 blocks}
+static int make_tmap_mn3d(CUtensorMap* out, const void* base, uint64_t krows, uint64_t mn, uint64_t ld) {
+  uint64_t dims[3] = {64, krows, mn / 64};
+  uint64_t strides[2] = {ld * 2, 128};
+  uint32_t box[3] = {64, 64, 2};
+  return make_tmap_nd_bf16(out, base, 3, dims, strides, box);
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_gemm2(const void* A, const void* B, const GemmParams& p, int lda, int ldb, int max_ctas,
+                        cudaStream_t stream) {
+  using Cfg = Gemm2Cfg;
+  CUtensorMap ta, tb;
+  Gemm2Extra ex = {0, 0};
+  int rc;
+  if (!A_MN) rc = make_tmap_2d_bf16(&ta, A, p.M, p.K, lda, 128, 64);
+  else if (p.M % 64 == 0) { rc = make_tmap_mn3d(&ta, A, p.K, p.M, lda); ex.a_3d = 1; }
+  else rc = make_tmap_2d_bf16(&ta, A, p.K, p.M, lda, 64, 64);
+  if (rc) return rc;
+  if (!B_MN) rc = make_tmap_2d_bf16(&tb, B, p.N, p.K, ldb, 128, 64);
+  else if (p.N % 64 == 0) { rc = make_tmap_mn3d(&tb, B, p.K, p.N, ldb); ex.b_3d = 1; }
+  else rc = make_tmap_2d_bf16(&tb, B, p.K, p.N, ldb, 64, 64);
+  if (rc) return rc;
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    ZB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    attr_set = true;
+  }
+  const int tiles = ((p.M + Cfg::BM - 1) / Cfg::BM) * ((p.N + Cfg::BN - 1) / Cfg::BN);
+  int pairs = num_sms() / 2;
+  if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  if (tiles < pairs) pairs = tiles;
+  kern<<<2 * pairs, 192, Cfg::SMEM_BYTES, stream>>>(ta, tb, p, ex);
+  ZB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace zb
+
+extern "C" int zb_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                             int a_mn_major, int b_mn_major, const void* bias, const void* addend, int ld_addend,
+                             int flags, int max_ctas, int* status, cudaStream_t stream) {
+  using namespace zb;
+  if (M <= 0 || N <= 0 || K <= 0) ZB_FAIL(-1, "gemm2: empty problem %d x %d x %d", M, N, K);
+  GemmParams p;
+  p.C = C;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.addend = static_cast<const __nv_bfloat16*>(addend);
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc; p.ld_addend = ld_addend;
+  p.flags = flags;
+  p.status = status;
+  p.gate_flags = nullptr;
+  p.gate_epoch = 0;
+  p.gate_base = 0; p.gate_row_bytes = 0; p.gate_shard_bytes = 1;
+  p.gate_chunk_bytes = 1; p.gate_cps = 1; p.gate_self = -1;
+  if (!a_mn_major && !b_mn_major) return launch_gemm2<false, false>(A, B, p, lda, ldb, max_ctas, stream);
+  if (!a_mn_major && b_mn_major) return launch_gemm2<false, true>(A, B, p, lda, ldb, max_ctas, stream);
+  if (a_mn_major && b_mn_major) return launch_gemm2<true, true>(A, B, p, lda, ldb, max_ctas, stream);
+  return launch_gemm2<true, false>(A, B, p, lda, ldb, max_ctas, stream);
+}

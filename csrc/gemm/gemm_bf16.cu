@@ -17,35 +17,9 @@
 // (models/llama_simple.py:206-221, models/llama_v2.py:222-229).
 #include "../common/host.h"
 #include "../common/ptx.cuh"
+#include "gemm_common.cuh"
 
 namespace zb {
-
-enum : int {
-  GEMM_OUT_F32 = 1,     // C is fp32 (else bf16)
-  GEMM_ACCUMULATE = 2,  // C += result (read-modify-write in C's dtype, fp32 add)
-  GEMM_GELU = 4,        // tanh-GELU applied after bias (forward of GPT-style MLPs)
-  GEMM_RELU = 8,
-};
-
-struct GemmParams {
-  void* C;
-  const __nv_bfloat16* bias;    // [N] or nullptr
-  const __nv_bfloat16* addend;  // [M, ld_addend] bf16 or nullptr (e.g. residual)
-  int M, N, K;
-  int ldc, ld_addend;
-  int flags;
-  int* status;
-  // optional arrival gating of B tiles (all-gather fused GEMM): B lives inside a flat
-  // unsharded parameter buffer that is being filled shard by shard, chunk by chunk. Before
-  // loading rows [n0, n_end] of B the producer waits until the flag of every chunk that
-  // overlaps bytes [gate_base + n0*row_bytes, gate_base + (n_end+1)*row_bytes) of the flat
-  // buffer is >= gate_epoch. Flag index of flat byte b: (b / shard_bytes) * cps +
-  // (b % shard_bytes) / chunk_bytes; the rank's own shard needs no wait. nullptr = off.
-  const int* gate_flags;
-  int gate_epoch;
-  long gate_base, gate_row_bytes, gate_shard_bytes;
-  int gate_chunk_bytes, gate_cps, gate_self;
-};
 
 // All-gather half of the fused kernel: four extra warps per CTA pull the peers' shards of
 // the unit into the local unsharded buffer with plain 16-byte peer loads, chunk by chunk,
@@ -75,12 +49,6 @@ struct GemmCfg {
   static constexpr int NUM_THREADS = 192;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
-
-__device__ __forceinline__ float gelu_tanh(float x) {
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  float u = k0 * (x + k1 * x * x * x);
-  return 0.5f * x * (1.f + tanhf(u));
-}
 
 template <int BN, bool A_MN, bool B_MN, bool FUSED_AG>
 __global__ void __launch_bounds__(FUSED_AG ? 320 : 192, 1)
@@ -224,11 +192,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp < 6) {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const bool out_f32 = (p.flags & GEMM_OUT_F32) != 0;
-    const bool accum = (p.flags & GEMM_ACCUMULATE) != 0;
-    const bool vec_ok = (p.ldc % 8 == 0) && (p.addend == nullptr || p.ld_addend % 8 == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.addend) & 15) == 0);
+    const EpilogueCfg ecfg = epilogue_cfg(p);
     int local = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int m0 = (tile % tiles_m) * BM;
@@ -247,79 +211,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * BN + c * 32), r);
         tmem_wait_ld();
         if (!row_ok) continue;
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-        const bool full_cols = (col0 + 32 <= p.N);
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (full_cols || col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
-        }
-        if (p.flags & GEMM_GELU) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
-        } else if (p.flags & GEMM_RELU) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
-        }
-        if (full_cols && vec_ok) {
-          if (p.addend != nullptr) {
-            const uint4* ap = reinterpret_cast<const uint4*>(p.addend + size_t(row) * p.ld_addend + col0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 a = ap[j];
-              float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z),
-                     f3 = unpack_bf16x2(a.w);
-              v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
-              v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
-            }
-          }
-          if (out_f32) {
-            float4* cp = reinterpret_cast<float4*>(static_cast<float*>(p.C) + size_t(row) * p.ldc + col0);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 o = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
-              if (accum) {
-                float4 old = cp[j];
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              cp[j] = o;
-            }
-          } else {
-            uint4* cp = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.C) + size_t(row) * p.ldc + col0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (accum) {
-                uint4 a = cp[j];
-                float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z),
-                       f3 = unpack_bf16x2(a.w);
-                v[j * 8 + 0] += f0.x; v[j * 8 + 1] += f0.y; v[j * 8 + 2] += f1.x; v[j * 8 + 3] += f1.y;
-                v[j * 8 + 4] += f2.x; v[j * 8 + 5] += f2.y; v[j * 8 + 6] += f3.x; v[j * 8 + 7] += f3.y;
-              }
-              uint4 o;
-              o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
-              o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
-              o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
-              o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
-              cp[j] = o;
-            }
-          }
-        } else {
-          for (int i = 0; i < 32; ++i) {
-            const int col = col0 + i;
-            if (col >= p.N) break;
-            float x = v[i];
-            if (p.addend != nullptr) x += __bfloat162float(p.addend[size_t(row) * p.ld_addend + col]);
-            if (out_f32) {
-              float* cp = static_cast<float*>(p.C) + size_t(row) * p.ldc + col;
-              *cp = accum ? (*cp + x) : x;
-            } else {
-              __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(p.C) + size_t(row) * p.ldc + col;
-              *cp = __float2bfloat16(accum ? (__bfloat162float(*cp) + x) : x);
-            }
-          }
-        }
+        epilogue_store_chunk(p, ecfg, row, col0, r);
       }
       tc_fence_before();
       __syncwarp();

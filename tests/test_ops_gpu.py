@@ -54,6 +54,26 @@ def test_gemm_layouts(k, M, N, K, a_mn, b_mn, bn):
     _close(out, want, atol=0.02 * math.sqrt(K), rtol=1e-2)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 256), (300, 520, 200), (1024, 1280, 4096), (4096, 1024, 512)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_pair_kernel(k, M, N, K, a_mn, b_mn):
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operand needs a 16-byte aligned row stride")
+    a = _rand(M, K, seed=1)
+    b = _rand(N, K, seed=2)
+    want = a.float() @ b.float().t()
+    ad = (a.t().contiguous() if a_mn else a).cuda()
+    bd = (b.t().contiguous() if b_mn else b).cuda()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    k.gemm(ad, bd, out, a_mn=a_mn, b_mn=b_mn, kernel="2cta")
+    k.check_status()
+    _close(out, want, atol=0.02 * math.sqrt(K), rtol=1e-2)
+    acc = torch.ones(M, N, dtype=torch.float32, device="cuda")
+    k.gemm(ad, bd, acc, a_mn=a_mn, b_mn=b_mn, kernel="2cta", accumulate=True)
+    k.check_status()
+    _close(acc, want + 1, atol=0.02 * math.sqrt(K), rtol=1e-2)
+
+
 def test_gemm_epilogues(k):
     M, N, K = 300, 520, 192
     a, b = _rand(M, K, seed=3), _rand(N, K, seed=4)
@@ -203,6 +223,8 @@ def test_adam(k, gdt):
 
 
 ATTN_CASES = [
+    (1, 300, 2, 1, 64, True, 0),
+    (1, 640, 1, 1, 128, True, 200),
     # B, S, Hq, Hkv, D, causal, window
     (1, 128, 1, 1, 128, True, 0),
     (1, 128, 1, 1, 64, True, 0),
@@ -215,13 +237,28 @@ ATTN_CASES = [
 ]
 
 
+@pytest.mark.parametrize("version", [1, 2])
 @pytest.mark.parametrize("B,S,Hq,Hkv,D,causal,window", ATTN_CASES)
-def test_flash_fwd(k, B, S, Hq, Hkv, D, causal, window):
+def test_flash_fwd(k, B, S, Hq, Hkv, D, causal, window, version):
     qkv = _rand(B * S, (Hq + 2 * Hkv) * D, seed=1)
     want = ref.attention(qkv.float(), B, S, Hq, Hkv, D, causal, window)
-    out, lse = k.flash_fwd(qkv.cuda(), B, S, Hq, Hkv, D, causal, window)
+    out, lse = k.flash_fwd(qkv.cuda(), B, S, Hq, Hkv, D, causal, window, version=version)
     k.check_status()
     _close(out, want, atol=2e-2, rtol=2e-2)
+    # log-sum-exp against the oracle's scores
+    x = qkv.float().reshape(B, S, Hq + 2 * Hkv, D)
+    q = x[:, :, :Hq].permute(0, 2, 1, 3)
+    kk = x[:, :, Hq:Hq + Hkv].permute(0, 2, 1, 3).repeat_interleave(Hq // Hkv, dim=1)
+    s = (q @ kk.transpose(-1, -2)) / math.sqrt(D)
+    i = torch.arange(S)[:, None]
+    j = torch.arange(S)[None, :]
+    mask = torch.ones(S, S, dtype=torch.bool)
+    if causal:
+        mask &= j <= i
+    if window:
+        mask &= (i - j) < window
+    want_lse = torch.logsumexp(s.masked_fill(~mask, float("-inf")), dim=-1)
+    _close(lse, want_lse, atol=2e-2, rtol=1e-2)
 
 
 @pytest.mark.parametrize("B,S,Hq,Hkv,D,causal,window", ATTN_CASES)

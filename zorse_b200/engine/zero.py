@@ -66,7 +66,39 @@ class Streams:
             self.copy = torch.cuda.Stream(device=device)
         else:
             self.comm = self.copy = None
-        self.exposed_events: list = []  # (start, end) pairs bracketing compute-stream waits on comm
+        self.measure_exposed = False
+        self.exposed_events: list = []  # (start, end) pairs bracketing compute-stream waits on comm / p2p
+
+    def wait_event(self, ev) -> None:
+        """Compute stream waits for `ev`; when measuring, the wait is bracketed by timing events so
+        the time the compute stream sat idle on communication can be summed up after the step."""
+        cur = torch.cuda.current_stream()
+        if not self.measure_exposed:
+            cur.wait_event(ev)
+            return
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(cur)
+        cur.wait_event(ev)
+        b.record(cur)
+        self.exposed_events.append((a, b))
+
+    def wait_stream(self, other) -> None:
+        cur = torch.cuda.current_stream()
+        if not self.measure_exposed:
+            cur.wait_stream(other)
+            return
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(cur)
+        cur.wait_stream(other)
+        b.record(cur)
+        self.exposed_events.append((a, b))
+
+    def exposed_ms(self, clear: bool = True) -> float:
+        """Sum of the bracketed waits (call after a device synchronisation)."""
+        t = sum(a.elapsed_time(b) for a, b in self.exposed_events)
+        if clear:
+            self.exposed_events.clear()
+        return t
 
 
 @dataclass
@@ -182,7 +214,7 @@ class ZeroUnit:
         """Makes the unsharded parameters available to the compute stream and binds the layer."""
         self.prefetch()
         if self.cuda and self.full_event is not None:
-            torch.cuda.current_stream().wait_event(self.full_event)
+            self.streams.wait_event(self.full_event)
             self.full_event = None
         self.layer.bind(self.full, self.grad)
 
@@ -365,7 +397,7 @@ class StageEngine:
         for u in self.units:
             u.finish_step()
         if self.device.type == "cuda":
-            torch.cuda.current_stream().wait_stream(self.streams.comm)
+            self.streams.wait_stream(self.streams.comm)
 
     def num_params(self) -> int:
         return sum(u.layer.num_params() for u in self.units)

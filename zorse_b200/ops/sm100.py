@@ -27,6 +27,8 @@ GEMM_ACCUMULATE = 2
 GEMM_GELU = 4
 GEMM_RELU = 8
 
+GEMM_KERNEL = os.environ.get("ZORSE_GEMM", "1cta")
+
 ACT_GELU_TANH = 0
 ACT_RELU = 1
 ACT_GELU_ERF = 2
@@ -104,11 +106,12 @@ def _bf16(t: torch.Tensor, name: str) -> None:
 # --------------------------------------------------------------------------- GEMM
 def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          bias: Optional[torch.Tensor] = None, addend: Optional[torch.Tensor] = None, accumulate: bool = False,
-         act: Optional[str] = None, bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
+         act: Optional[str] = None, bn: int = 0, max_ctas: int = 0, kernel: Optional[str] = None) -> torch.Tensor:
     """out[M,N] = A @ B^T (+bias) (+addend), or out += ... with accumulate.
 
     a: [M,K] (K-major) or [K,M] when a_mn; b: [N,K] (K-major) or [K,N] when b_mn.
-    out: bf16 or fp32 [M,N].
+    out: bf16 or fp32 [M,N]. kernel: "1cta" (128x{128,256} tile per CTA), "2cta" (256x256 tile per
+    CTA pair, tcgen05 cta_group::2) or None = GEMM_KERNEL default ("2cta" for M, N >= 256).
     """
     _bf16(a, "a"); _bf16(b, "b")
     M, N = out.shape
@@ -127,6 +130,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = Fa
         flags |= GEMM_GELU
     elif act == "relu":
         flags |= GEMM_RELU
+    kern = kernel or GEMM_KERNEL
+    if kern == "2cta" and bn == 0 and M >= 256 and N >= 256:
+        rc = lib().zb_gemm2_bf16(_p(a), _p(b), _p(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
+                                 c_int(b.stride(0)), c_int(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)),
+                                 _p(bias), _p(addend), c_int(0 if addend is None else addend.stride(0)),
+                                 c_int(flags), c_int(max_ctas), _p(status_word(a.device)), _stream())
+        _check(rc, "gemm2")
+        return out
     rc = lib().zb_gemm_bf16(_p(a), _p(b), _p(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
                             c_int(b.stride(0)), c_int(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)),
                             _p(bias), _p(addend), c_int(0 if addend is None else addend.stride(0)),
@@ -242,15 +253,21 @@ def adam_step(p, m, v, g, p16, *, lr, beta1, beta2, eps, weight_decay, step, gra
 
 
 # --------------------------------------------------------------------------- attention
+ATTN_FWD_VERSION = int(os.environ.get("ZORSE_ATTN_FWD", "2"))
+
+
 def flash_fwd(qkv, B: int, S: int, Hq: int, Hkv: int, D: int, causal: bool = True, window: int = 0,
-              scale: Optional[float] = None):
-    """qkv: packed [B*S, (Hq+2Hkv)*D]. Returns (out [B*S, Hq*D], lse [B, Hq, S])."""
+              scale: Optional[float] = None, version: Optional[int] = None):
+    """qkv: packed [B*S, (Hq+2Hkv)*D]. Returns (out [B*S, Hq*D], lse [B, Hq, S]).
+    version 2 (default): two query tiles per CTA, P kept in tensor memory; version 1: one
+    query tile per CTA, P staged through shared memory."""
     _bf16(qkv, "qkv")
     assert qkv.shape == (B * S, (Hq + 2 * Hkv) * D) and qkv.is_contiguous()
     out = torch.empty(B * S, Hq * D, dtype=qkv.dtype, device=qkv.device)
     lse = torch.empty(B, Hq, S, dtype=torch.float32, device=qkv.device)
     sc = (1.0 / math.sqrt(D)) if scale is None else scale
-    _check(lib().zb_flash_fwd(_p(qkv), _p(out), _p(lse), c_int(B), c_int(S), c_int(Hq), c_int(Hkv), c_int(D),
+    fn = lib().zb_flash_fwd2 if (version or ATTN_FWD_VERSION) == 2 else lib().zb_flash_fwd
+    _check(fn(_p(qkv), _p(out), _p(lse), c_int(B), c_int(S), c_int(Hq), c_int(Hkv), c_int(D),
                               c_int(int(causal)), c_int(window), c_float(sc), c_int(out.stride(0)),
                               _p(status_word(qkv.device)), _stream()), "flash_fwd")
     return out, lse

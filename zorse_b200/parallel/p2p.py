@@ -41,8 +41,9 @@ class Handle:
 class NcclP2P:
     KINDS = ("act", "grad")
 
-    def __init__(self, device: torch.device, timeout_s: float = 300.0):
+    def __init__(self, device: torch.device, timeout_s: float = 300.0, streams=None):
         self.device = device
+        self.streams = streams  # engine Streams: brackets receive waits for exposed-communication accounting
         self.rank = dist.get_rank()
         self.send_stream = torch.cuda.Stream(device=device)
         self.recv_stream = torch.cuda.Stream(device=device)
@@ -76,7 +77,10 @@ class NcclP2P:
         def wait():
             with torch.cuda.stream(self.recv_stream):
                 work.wait()
-            torch.cuda.current_stream().wait_stream(self.recv_stream)
+            if self.streams is not None:
+                self.streams.wait_stream(self.recv_stream)
+            else:
+                torch.cuda.current_stream().wait_stream(self.recv_stream)
             return buf
 
         return Handle(wait)
@@ -163,9 +167,9 @@ class LoopbackP2P:
         pass
 
 
-def make_transport(device: torch.device, use_gloo: bool = False, gloo_group=None):
+def make_transport(device: torch.device, use_gloo: bool = False, gloo_group=None, streams=None):
     if not (dist.is_available() and dist.is_initialized()):
         return LoopbackP2P(0, {})
     if device.type == "cuda" and not use_gloo:
-        return NcclP2P(device)
+        return NcclP2P(device, streams=streams)
     return GlooP2P(device, gloo_group)

@@ -1,0 +1,58 @@
+"""Runs ONE of this repository's kernels a few times on a small, larger-than-L2 case, for
+`ncu` captures (`ncu --set full --clock-control none -k regex:<name> -c 2 python -m
+zorse_b200.profiler.kernel_run <case>`).  Holds well under a few GB on the device.
+
+cases: gemm_fwd | gemm_dgrad | gemm_wgrad | flash_fwd1 | flash_fwd2 | flash_bwd | rmsnorm | adam | ce
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+
+def main(argv=None):
+    case = (argv or sys.argv[1:])[0]
+    reps = int((argv or sys.argv[1:])[1]) if len(argv or sys.argv[1:]) > 1 else 3
+    from zorse_b200.ops import sm100 as k
+
+    k.lib()
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *s: (torch.randn(*s, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    if case.startswith("gemm"):
+        M, N, K = 4096, 11008, 4096          # 34 + 90 + 90 MB
+        a, w, dy = rnd(M, K), rnd(N, K), rnd(M, N)
+        out, dx = torch.empty(M, N, device=dev, dtype=torch.bfloat16), torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+        gw = torch.zeros(N, K, device=dev, dtype=torch.bfloat16)
+        fn = {"gemm_fwd": lambda: k.gemm(a, w, out), "gemm_dgrad": lambda: k.gemm(dy, w, dx, b_mn=True),
+              "gemm_wgrad": lambda: k.gemm(dy, a, gw, a_mn=True, b_mn=True, accumulate=True)}[case]
+    elif case.startswith("flash"):
+        B, S, Hq, Hkv, D = 1, 4096, 32, 32, 128   # qkv 100 MB
+        qkv, do = rnd(B * S, (Hq + 2 * Hkv) * D), rnd(B * S, Hq * D)
+        out, lse = k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, 0)
+        fn = {"flash_fwd1": lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, 0, version=1),
+              "flash_fwd2": lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, 0, version=2),
+              "flash_bwd": lambda: k.flash_bwd(do, qkv, out, lse, B, S, Hq, Hkv, D, True, 0)}[case]
+    elif case == "rmsnorm":
+        x, w = rnd(32768, 4096), torch.ones(4096, device=dev, dtype=torch.bfloat16)
+        fn = lambda: k.norm_fwd(x, w, None, 1e-5, False)
+    elif case == "adam":
+        n = 64 * 1024 * 1024
+        p, m, v = (torch.zeros(n, device=dev) for _ in range(3))
+        gr, p16 = rnd(n), torch.empty(n, device=dev, dtype=torch.bfloat16)
+        fn = lambda: k.adam_step(p, m, v, gr, p16, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1)
+    elif case == "ce":
+        lg, tg = rnd(4096, 32000), torch.randint(0, 32000, (4096,), device=dev)
+        fn = lambda: k.cross_entropy(lg, tg, 1.0, dlogits=lg)
+    else:
+        raise SystemExit(__doc__)
+    for _ in range(reps):
+        fn()
+    torch.cuda.synchronize()
+    k.check_status()
+    print("ok", case)
+
+
+if __name__ == "__main__":
+    main()

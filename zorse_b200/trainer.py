@@ -70,7 +70,8 @@ class Trainer:
         self.streams = Streams(self.device)
         stage_groups = G.StageGroups.create_all(cfg.stages, self.rank)
         self.gloo_group = G.gloo_world_group() if (opt.gloo_p2p or self.device.type == "cuda") and G.is_dist() else None
-        self.transport = make_transport(self.device, use_gloo=opt.gloo_p2p, gloo_group=self.gloo_group)
+        self.transport = make_transport(self.device, use_gloo=opt.gloo_p2p, gloo_group=self.gloo_group,
+                                        streams=self.streams)
         plans = create_static_comm_plans(cfg)
         self.plan = plans[self.rank]
         offload_act = cfg.activation_offload if opt.activation_offload is None else opt.activation_offload
@@ -155,6 +156,16 @@ class Trainer:
             dist.all_reduce(t)
             v = t.cpu()
         return float(v[0])
+
+    def measure_exposed_comm(self, on: bool = True) -> None:
+        """Brackets every compute-stream wait on a collective or a p2p receive with timing events."""
+        self.streams.measure_exposed = on and self.device.type == "cuda"
+        self.streams.exposed_events.clear()
+
+    def exposed_comm_ms(self) -> float:
+        """Time the compute stream spent blocked on communication since the last call (ms)."""
+        self.synchronize()
+        return self.streams.exposed_ms() if self.device.type == "cuda" else 0.0
 
     def synchronize(self):
         if self.device.type == "cuda":
