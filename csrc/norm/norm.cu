@@ -281,3 +281,31 @@ int zb_colsum(const void* dy, int T, int N, int ld, float* part, void* out, int 
 }
 
 }  // extern "C"
+
+// Launch sequence of the norm backward with caller-provided scratch and partial-row count
+// (used by the allocation-free entry point in norm_bwd_noalloc.cu).
+namespace zb {
+int norm_bwd_with_scratch(const void* dy, const void* x, const void* w, const float* stats, const void* dres, void* dx,
+                          float* part_dw, float* part_db, int P, void* dw, void* db, int T, int H, int ln, int grad_f32,
+                          int accumulate, cudaStream_t stream) {
+  auto DY = static_cast<const __nv_bfloat16*>(dy);
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto W = static_cast<const __nv_bfloat16*>(w);
+  auto DR = static_cast<const __nv_bfloat16*>(dres);
+  auto DX = static_cast<__nv_bfloat16*>(dx);
+  if (ln) norm_bwd_kernel<true><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, part_db, T, H);
+  else norm_bwd_kernel<false><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, nullptr, T, H);
+  ZB_CUDA_OK(cudaGetLastError());
+  const int nb = (H + 255) / 256;
+  if (dw != nullptr) {
+    if (grad_f32) colsum_accumulate_kernel<float><<<nb, 256, 0, stream>>>(part_dw, P, H, static_cast<float*>(dw), accumulate);
+    else colsum_accumulate_kernel<__nv_bfloat16><<<nb, 256, 0, stream>>>(part_dw, P, H, static_cast<__nv_bfloat16*>(dw), accumulate);
+  }
+  if (ln && db != nullptr) {
+    if (grad_f32) colsum_accumulate_kernel<float><<<nb, 256, 0, stream>>>(part_db, P, H, static_cast<float*>(db), accumulate);
+    else colsum_accumulate_kernel<__nv_bfloat16><<<nb, 256, 0, stream>>>(part_db, P, H, static_cast<__nv_bfloat16*>(db), accumulate);
+  }
+  ZB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+}  // namespace zb
