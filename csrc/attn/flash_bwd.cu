@@ -54,7 +54,7 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
 }
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                  const AttnBwdParams p) {
@@ -100,12 +100,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       mbar_init(&qdo_empty[i], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 4);
+    mbar_init(dq_empty, 8);
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
@@ -114,7 +114,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       tma_prefetch_desc(&tmap_q);
@@ -141,7 +141,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0 && n_iters > 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, false, false);
@@ -195,8 +195,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
   } else {
     // ------------------------------ softmax-grad warps ------------------------------
-    const int t = threadIdx.x;  // row within the query tile (steps) / key tile (final write)
-    const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16);
+    // warps 0-3 take columns [0,64) of S / dP (and the first half of the dQ, dK, dV columns),
+    // warps 4-7 the other half; both sets cover TMEM lanes (= rows) 0..127
+    const int half = warp >> 2;
+    const int t = (warp & 3) * 32 + lane;  // row within the query tile (steps) / key tile (final write)
+    const uint32_t lane_addr = tmem_base + (uint32_t((warp & 3) * 32) << 16);
     const float LOG2E = 1.4426950408889634f;
     bool ok = true;
     for (int it = 0; it < n_iters; ++it) {
@@ -217,7 +220,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       uint8_t* prow = sP + t * 128;
       uint8_t* dsrow = sDS + t * 128;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t rs[32], rd[32];
         tmem_ld32(lane_addr + uint32_t(c * 32), rs);
         tmem_ld32(lane_addr + uint32_t(Cfg::DP_COL + c * 32), rd);
@@ -225,7 +228,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         float pv[32], dsv[32];
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          float pe = bwd_exp2(__uint_as_float(rs[k]) * p.scale_log2 - lse_r);
+          float pe = exp2f(fmaf(__uint_as_float(rs[k]), p.scale_log2, -lse_r));
           if (need_mask) {
             const int col = kv0 + c * 32 + k;
             const bool vis = row_ok && (col < p.S) && (!p.causal || col <= row) &&
@@ -258,7 +261,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       tc_fence_after();
       float* dq_row = p.dq_acc + (size_t(batch) * p.S + row) * (size_t(p.Hq) * D) + size_t(head) * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t r[32];
         tmem_ld32(lane_addr + uint32_t(c * 32), r);
         tmem_wait_ld();
@@ -284,7 +287,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       __nv_bfloat16* dst = p.dqkv + (size_t(batch) * p.S + krow) * width +
                            size_t(which == 0 ? (p.Hq + kv_head) : (p.Hq + p.Hkv + kv_head)) * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t r[32];
         if (n_iters > 0) {
           tmem_ld32(lane_addr + col0 + uint32_t(c * 32), r);
@@ -314,7 +317,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
@@ -388,7 +391,7 @@ static int launch_bwd(const __nv_bfloat16* qkv, const __nv_bfloat16* d_o, const 
     attr_set = true;
   }
   dim3 grid((p.S + 127) / 128, p.Hkv, p.B);
-  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  kern<<<grid, 320, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
   ZB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -206,24 +206,34 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       tc_fence_after();
       const bool need_mask = (p.causal && kv0 + BN - 1 > q0) || (p.window > 0 && kv0 < q0 + BM - p.window) ||
                              (kv0 + BN > p.S);
-      // pass 1: row maximum
-      float tmax = -INFINITY;
+      // pass 1: row maximum, four independent partial maxima per 64-column half
+      float tmax;
+      {
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int ch = 0; ch < BN / 32; ++ch) {
-        uint32_t r[32];
-        tmem_ld32(s_col + uint32_t(ch * 32), r);
-        tmem_wait_ld();
-        if (need_mask) {
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(s_col + uint32_t(half * 64), r0);
+          tmem_ld32(s_col + uint32_t(half * 64 + 32), r1);
+          tmem_wait_ld();
+          if (need_mask) {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            const int col = kv0 + ch * 32 + k;
-            const bool vis = (col < p.S) && (!p.causal || col <= row) && (p.window <= 0 || row - col < p.window);
-            tmax = fmaxf(tmax, vis ? __uint_as_float(r[k]) : -INFINITY);
+            for (int k = 0; k < 32; ++k) {
+              const int c0 = kv0 + half * 64 + k, c1 = c0 + 32;
+              const bool v0 = (c0 < p.S) && (!p.causal || c0 <= row) && (p.window <= 0 || row - c0 < p.window);
+              const bool v1 = (c1 < p.S) && (!p.causal || c1 <= row) && (p.window <= 0 || row - c1 < p.window);
+              mx[k & 1] = fmaxf(mx[k & 1], v0 ? __uint_as_float(r0[k]) : -INFINITY);
+              mx[2 + (k & 1)] = fmaxf(mx[2 + (k & 1)], v1 ? __uint_as_float(r1[k]) : -INFINITY);
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              mx[k & 1] = fmaxf(mx[k & 1], __uint_as_float(r0[k]));
+              mx[2 + (k & 1)] = fmaxf(mx[2 + (k & 1)], __uint_as_float(r1[k]));
+            }
           }
-        } else {
-#pragma unroll
-          for (int k = 0; k < 32; ++k) tmax = fmaxf(tmax, __uint_as_float(r[k]));
         }
+        tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       }
       // running maximum; O is rescaled only when it grew by more than 8 in log2 units
       if (i == 0) {
@@ -233,7 +243,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (__any_sync(0xffffffffu, need)) {
           float alpha = 1.f;
           if (need) {
-            alpha = (m_run == -INFINITY) ? 0.f : fwd2_exp2((m_run - tmax) * p.scale_log2);
+            alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - tmax) * p.scale_log2);
             m_run = tmax;
             l_run *= alpha;
           }
@@ -252,30 +262,36 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       const float m_eff = (m_run == -INFINITY) ? 0.f : m_run;
       const float neg_mc = -m_eff * p.scale_log2;
-      // pass 2: P = exp2(S*c - m*c), packed bf16 pairs written over the first 64 columns of S
-      float lsum = 0.f;
+      // pass 2: P = exp2(S*c - m*c), packed bf16 pairs written over the first 64 columns of S;
+      // four independent partial sums keep the dependent-add chains short
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int ch = 0; ch < BN / 32; ++ch) {
-        uint32_t r[32];
-        tmem_ld32(s_col + uint32_t(ch * 32), r);
+      for (int half = 0; half < 2; ++half) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(s_col + uint32_t(half * 64), r0);
+        tmem_ld32(s_col + uint32_t(half * 64 + 32), r1);
         tmem_wait_ld();
-        uint32_t pk[16];
+        uint32_t pk[32];
 #pragma unroll
         for (int k = 0; k < 32; k += 2) {
-          float e0 = fwd2_exp2(fmaf(__uint_as_float(r[k]), p.scale_log2, neg_mc));
-          float e1 = fwd2_exp2(fmaf(__uint_as_float(r[k + 1]), p.scale_log2, neg_mc));
+          float e0 = exp2f(fmaf(__uint_as_float(r0[k]), p.scale_log2, neg_mc));
+          float e1 = exp2f(fmaf(__uint_as_float(r0[k + 1]), p.scale_log2, neg_mc));
+          float e2 = exp2f(fmaf(__uint_as_float(r1[k]), p.scale_log2, neg_mc));
+          float e3 = exp2f(fmaf(__uint_as_float(r1[k + 1]), p.scale_log2, neg_mc));
           if (need_mask) {
-            const int col = kv0 + ch * 32 + k;
-            const bool v0 = (col < p.S) && (!p.causal || col <= row) && (p.window <= 0 || row - col < p.window);
-            const bool v1 = (col + 1 < p.S) && (!p.causal || col + 1 <= row) && (p.window <= 0 || row - col - 1 < p.window);
-            e0 = v0 ? e0 : 0.f;
-            e1 = v1 ? e1 : 0.f;
+            const int c0 = kv0 + half * 64 + k, c2 = c0 + 32;
+            e0 = ((c0 < p.S) && (!p.causal || c0 <= row) && (p.window <= 0 || row - c0 < p.window)) ? e0 : 0.f;
+            e1 = ((c0 + 1 < p.S) && (!p.causal || c0 + 1 <= row) && (p.window <= 0 || row - c0 - 1 < p.window)) ? e1 : 0.f;
+            e2 = ((c2 < p.S) && (!p.causal || c2 <= row) && (p.window <= 0 || row - c2 < p.window)) ? e2 : 0.f;
+            e3 = ((c2 + 1 < p.S) && (!p.causal || c2 + 1 <= row) && (p.window <= 0 || row - c2 - 1 < p.window)) ? e3 : 0.f;
           }
-          lsum += e0 + e1;
+          ls[0] += e0; ls[1] += e1; ls[2] += e2; ls[3] += e3;
           pk[k >> 1] = pack_bf16x2(e0, e1);
+          pk[16 + (k >> 1)] = pack_bf16x2(e2, e3);
         }
-        tmem_st16(s_col + uint32_t(ch * 16), pk);
+        tmem_st32(s_col + uint32_t(half * 32), pk);
       }
+      const float lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tmem_wait_st();
       l_run += lsum;
       tc_fence_before();

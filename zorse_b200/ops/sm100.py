@@ -27,7 +27,7 @@ GEMM_ACCUMULATE = 2
 GEMM_GELU = 4
 GEMM_RELU = 8
 
-GEMM_KERNEL = os.environ.get("ZORSE_GEMM", "1cta")
+GEMM_KERNEL = os.environ.get("ZORSE_GEMM", "2cta")
 
 ACT_GELU_TANH = 0
 ACT_RELU = 1
