@@ -206,32 +206,29 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       tc_fence_after();
       const bool need_mask = (p.causal && kv0 + BN - 1 > q0) || (p.window > 0 && kv0 < q0 + BM - p.window) ||
                              (kv0 + BN > p.S);
-      // pass 1: row maximum, four independent partial maxima per 64-column half
+      // pass 1: row maximum. All 128 columns are requested before the single wait, so the
+      // TMEM round trip is paid once; four independent partial maxima keep the chains short.
       float tmax;
       {
+        uint32_t r[4][32];
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) tmem_ld32(s_col + uint32_t(ch * 32), r[ch]);
+        tmem_wait_ld();
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (need_mask) {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t r0[32], r1[32];
-          tmem_ld32(s_col + uint32_t(half * 64), r0);
-          tmem_ld32(s_col + uint32_t(half * 64 + 32), r1);
-          tmem_wait_ld();
-          if (need_mask) {
+          for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
             for (int k = 0; k < 32; ++k) {
-              const int c0 = kv0 + half * 64 + k, c1 = c0 + 32;
-              const bool v0 = (c0 < p.S) && (!p.causal || c0 <= row) && (p.window <= 0 || row - c0 < p.window);
-              const bool v1 = (c1 < p.S) && (!p.causal || c1 <= row) && (p.window <= 0 || row - c1 < p.window);
-              mx[k & 1] = fmaxf(mx[k & 1], v0 ? __uint_as_float(r0[k]) : -INFINITY);
-              mx[2 + (k & 1)] = fmaxf(mx[2 + (k & 1)], v1 ? __uint_as_float(r1[k]) : -INFINITY);
+              const int col = kv0 + ch * 32 + k;
+              const bool vis = (col < p.S) && (!p.causal || col <= row) && (p.window <= 0 || row - col < p.window);
+              mx[ch] = fmaxf(mx[ch], vis ? __uint_as_float(r[ch][k]) : -INFINITY);
             }
-          } else {
+        } else {
 #pragma unroll
-            for (int k = 0; k < 32; ++k) {
-              mx[k & 1] = fmaxf(mx[k & 1], __uint_as_float(r0[k]));
-              mx[2 + (k & 1)] = fmaxf(mx[2 + (k & 1)], __uint_as_float(r1[k]));
-            }
-          }
+          for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+            for (int k = 0; k < 32; ++k) mx[ch] = fmaxf(mx[ch], __uint_as_float(r[ch][k]));
         }
         tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       }
@@ -262,34 +259,38 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       const float m_eff = (m_run == -INFINITY) ? 0.f : m_run;
       const float neg_mc = -m_eff * p.scale_log2;
-      // pass 2: P = exp2(S*c - m*c), packed bf16 pairs written over the first 64 columns of S;
-      // four independent partial sums keep the dependent-add chains short
+      // pass 2: P = exp2(S*c - m*c), packed bf16 pairs written over the first 64 columns of S.
+      // Chunk c+1 is requested before chunk c is processed, so only the first TMEM round trip is
+      // exposed; four independent partial sums keep the dependent-add chains short.
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t r0[32], r1[32];
-        tmem_ld32(s_col + uint32_t(half * 64), r0);
-        tmem_ld32(s_col + uint32_t(half * 64 + 32), r1);
+      {
+        uint32_t ra[32], rb[32];
+        tmem_ld32(s_col, ra);
         tmem_wait_ld();
-        uint32_t pk[32];
 #pragma unroll
-        for (int k = 0; k < 32; k += 2) {
-          float e0 = exp2f(fmaf(__uint_as_float(r0[k]), p.scale_log2, neg_mc));
-          float e1 = exp2f(fmaf(__uint_as_float(r0[k + 1]), p.scale_log2, neg_mc));
-          float e2 = exp2f(fmaf(__uint_as_float(r1[k]), p.scale_log2, neg_mc));
-          float e3 = exp2f(fmaf(__uint_as_float(r1[k + 1]), p.scale_log2, neg_mc));
-          if (need_mask) {
-            const int c0 = kv0 + half * 64 + k, c2 = c0 + 32;
-            e0 = ((c0 < p.S) && (!p.causal || c0 <= row) && (p.window <= 0 || row - c0 < p.window)) ? e0 : 0.f;
-            e1 = ((c0 + 1 < p.S) && (!p.causal || c0 + 1 <= row) && (p.window <= 0 || row - c0 - 1 < p.window)) ? e1 : 0.f;
-            e2 = ((c2 < p.S) && (!p.causal || c2 <= row) && (p.window <= 0 || row - c2 < p.window)) ? e2 : 0.f;
-            e3 = ((c2 + 1 < p.S) && (!p.causal || c2 + 1 <= row) && (p.window <= 0 || row - c2 - 1 < p.window)) ? e3 : 0.f;
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t (&cur)[32] = (ch & 1) ? rb : ra;
+          uint32_t (&nxt)[32] = (ch & 1) ? ra : rb;
+          if (ch + 1 < 4) tmem_ld32(s_col + uint32_t((ch + 1) * 32), nxt);
+          uint32_t pk[16];
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            float e0 = exp2f(fmaf(__uint_as_float(cur[k]), p.scale_log2, neg_mc));
+            float e1 = exp2f(fmaf(__uint_as_float(cur[k + 1]), p.scale_log2, neg_mc));
+            if (need_mask) {
+              const int c0 = kv0 + ch * 32 + k;
+              e0 = ((c0 < p.S) && (!p.causal || c0 <= row) && (p.window <= 0 || row - c0 < p.window)) ? e0 : 0.f;
+              e1 = ((c0 + 1 < p.S) && (!p.causal || c0 + 1 <= row) && (p.window <= 0 || row - c0 - 1 < p.window)) ? e1 : 0.f;
+            }
+            ls[(k >> 1) & 3] += e0 + e1;
+            pk[k >> 1] = pack_bf16x2(e0, e1);
           }
-          ls[0] += e0; ls[1] += e1; ls[2] += e2; ls[3] += e3;
-          pk[k >> 1] = pack_bf16x2(e0, e1);
-          pk[16 + (k >> 1)] = pack_bf16x2(e2, e3);
+          // chunk ch+1 (columns 32(ch+1)..) must have left TMEM before P overwrites columns
+          // [16 ch, 16 ch + 16): for ch >= 1 those columns belong to chunks already consumed,
+          // for ch == 0 they belong to chunk 0 itself
+          if (ch + 1 < 4) tmem_wait_ld();
+          tmem_st16(s_col + uint32_t(ch * 16), pk);
         }
-        tmem_st32(s_col + uint32_t(half * 32), pk);
       }
       const float lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tmem_wait_st();

@@ -253,14 +253,14 @@ def adam_step(p, m, v, g, p16, *, lr, beta1, beta2, eps, weight_decay, step, gra
 
 
 # --------------------------------------------------------------------------- attention
-ATTN_FWD_VERSION = int(os.environ.get("ZORSE_ATTN_FWD", "2"))
+ATTN_FWD_VERSION = int(os.environ.get("ZORSE_ATTN_FWD", "1"))
 
 
 def flash_fwd(qkv, B: int, S: int, Hq: int, Hkv: int, D: int, causal: bool = True, window: int = 0,
               scale: Optional[float] = None, version: Optional[int] = None):
     """qkv: packed [B*S, (Hq+2Hkv)*D]. Returns (out [B*S, Hq*D], lse [B, Hq, S]).
-    version 2 (default): two query tiles per CTA, P kept in tensor memory; version 1: one
-    query tile per CTA, P staged through shared memory."""
+    version 1 (default, the faster one as measured): one query tile per CTA, S double-buffered in
+    TMEM, P staged through shared memory; version 2: two query tiles per CTA, P kept in TMEM."""
     _bf16(qkv, "qkv")
     assert qkv.shape == (B * S, (Hq + 2 * Hkv) * D) and qkv.is_contiguous()
     out = torch.empty(B * S, Hq * D, dtype=qkv.dtype, device=qkv.device)
