@@ -7,6 +7,8 @@ uniform-random token ids and random-init weights, on N GPUs of one node.
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29500 bench.py --gpus 8 --steps 3 --warmup 3
 
+Default schedule: true 1F1B without activation recomputation (`--schedule zero2` runs the
+reference's ZeRO-2 pipeline schedule, which recomputes every layer in backward).
 Parallelism per N (total work fixed = strong scaling): 1 GPU: one stage; 2 GPUs: one stage x
 2-way ZeRO-3; 4 GPUs: 2 stages x 2-way ZeRO-3; 8 GPUs: 4 stages x 2-way ZeRO-3 (the named
 configuration).  Rank 0 prints ONE JSON line.  `value` is device-timed (CUDA events, max over
@@ -134,7 +136,7 @@ def main():
         args.warmup = 3
     schedule = args.schedule
     if schedule == "auto":
-        schedule = "1f1b" if args.gpus == 1 else "zero2"
+        schedule = "1f1b"
     cfg_dict, par = build_config(args.gpus, args.model, args.global_batch, args.microbatch, args.seq_len, args.vocab,
                                  args.reduce_dtype, schedule, args.layers)
     cfg = parse_pipeline_dict(cfg_dict)

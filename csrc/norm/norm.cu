@@ -109,18 +109,18 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 // dx = (dres) + rstd * (g - xhat * mean(g * xhat) [- mean(g)]) with g = dy * w.
 // Each CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ... and keeps its partial
 // dw (and db) in registers; partials go to part_dw[gridDim.x, H] (and part_db).
-template <bool LN>
-__global__ void __launch_bounds__(NORM_THREADS)
+template <bool LN, int MAXV>
+__global__ void __launch_bounds__(NORM_THREADS, MAXV <= 2 ? 2 : 1)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                 const __nv_bfloat16* __restrict__ w, const float* __restrict__ stats,
                 const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                 float* __restrict__ part_dw, float* __restrict__ part_db, int T, int H) {
   __shared__ float red[33];
   const int nchunk = H >> 3;
-  float aw[NORM_MAXV][8], ab[NORM_MAXV][8], wf[NORM_MAXV][8];
+  float aw[MAXV][8], ab[MAXV][8], wf[MAXV][8];
   const uint4* wr = reinterpret_cast<const uint4*>(w);
 #pragma unroll
-  for (int i = 0; i < NORM_MAXV; ++i) {
+  for (int i = 0; i < MAXV; ++i) {
     int c = threadIdx.x + i * NORM_THREADS;
 #pragma unroll
     for (int j = 0; j < 8; ++j) { aw[i][j] = 0.f; ab[i][j] = 0.f; wf[i][j] = 0.f; }
@@ -130,10 +130,10 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     const uint4* xr = reinterpret_cast<const uint4*>(x + size_t(row) * H);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + size_t(row) * H);
     const float mean = stats[2 * row], rstd = stats[2 * row + 1];
-    float xh[NORM_MAXV][8], g[NORM_MAXV][8];
+    float xh[MAXV][8], g[MAXV][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < NORM_MAXV; ++i) {
+    for (int i = 0; i < MAXV; ++i) {
       int c = threadIdx.x + i * NORM_THREADS;
       if (c < nchunk) {
         float xf[8], df[8];
@@ -156,7 +156,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     uint4* dxr = reinterpret_cast<uint4*>(dx + size_t(row) * H);
     const uint4* rr = reinterpret_cast<const uint4*>(dres ? dres + size_t(row) * H : nullptr);
 #pragma unroll
-    for (int i = 0; i < NORM_MAXV; ++i) {
+    for (int i = 0; i < MAXV; ++i) {
       int c = threadIdx.x + i * NORM_THREADS;
       if (c < nchunk) {
         float o[8], rf[8];
@@ -171,7 +171,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     }
   }
 #pragma unroll
-  for (int i = 0; i < NORM_MAXV; ++i) {
+  for (int i = 0; i < MAXV; ++i) {
     int c = threadIdx.x + i * NORM_THREADS;
     if (c < nchunk) {
       float4* pw = reinterpret_cast<float4*>(part_dw + size_t(blockIdx.x) * H + c * 8);
@@ -249,8 +249,14 @@ int zb_norm_bwd(const void* dy, const void* x, const void* w, const float* stats
   auto W = static_cast<const __nv_bfloat16*>(w);
   auto DR = static_cast<const __nv_bfloat16*>(dres);
   auto DX = static_cast<__nv_bfloat16*>(dx);
-  if (ln) norm_bwd_kernel<true><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, part_db, T, H);
-  else norm_bwd_kernel<false><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, nullptr, T, H);
+  // rows up to 4096 wide need two 16-byte chunks per thread: half the registers, two CTAs per SM
+  if (H <= NORM_THREADS * 2 * 8) {
+    if (ln) norm_bwd_kernel<true, 2><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, part_db, T, H);
+    else norm_bwd_kernel<false, 2><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, nullptr, T, H);
+  } else {
+    if (ln) norm_bwd_kernel<true, NORM_MAXV><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, part_db, T, H);
+    else norm_bwd_kernel<false, NORM_MAXV><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, nullptr, T, H);
+  }
   ZB_CUDA_OK(cudaGetLastError());
   const int nb = (H + 255) / 256;
   if (dw != nullptr) {
@@ -293,8 +299,14 @@ int norm_bwd_with_scratch(const void* dy, const void* x, const void* w, const fl
   auto W = static_cast<const __nv_bfloat16*>(w);
   auto DR = static_cast<const __nv_bfloat16*>(dres);
   auto DX = static_cast<__nv_bfloat16*>(dx);
-  if (ln) norm_bwd_kernel<true><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, part_db, T, H);
-  else norm_bwd_kernel<false><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, nullptr, T, H);
+  // rows up to 4096 wide need two 16-byte chunks per thread: half the registers, two CTAs per SM
+  if (H <= NORM_THREADS * 2 * 8) {
+    if (ln) norm_bwd_kernel<true, 2><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, part_db, T, H);
+    else norm_bwd_kernel<false, 2><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, nullptr, T, H);
+  } else {
+    if (ln) norm_bwd_kernel<true, NORM_MAXV><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, part_db, T, H);
+    else norm_bwd_kernel<false, NORM_MAXV><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, nullptr, T, H);
+  }
   ZB_CUDA_OK(cudaGetLastError());
   const int nb = (H + 255) / 256;
   if (dw != nullptr) {

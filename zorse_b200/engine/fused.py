@@ -29,7 +29,9 @@ import torch.distributed as dist
 from ..models.layers import Layer
 from .zero import ZeroUnit
 
-CHUNK_BYTES = 1 << 18
+# small chunks: every CTA copies one chunk at a time at 1/148 of the link rate, so a chunk is the
+# granularity at which weight rows become visible to the GEMM tiles waiting for them
+CHUNK_BYTES = 1 << 15
 
 
 @dataclass

@@ -110,7 +110,7 @@ def main(argv=None):
     symm.rendezvous(vflags, dist.group.WORLD)
     x = torch.randn(M, K, device=dev).to(torch.bfloat16)
     out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-    chunk = 1 << 18
+    chunk = 1 << 15
     cps = (sn * 2 + chunk - 1) // chunk
     cflags = torch.zeros(R * cps, dtype=torch.int32, device=dev)
     shard_ptrs = [int(hfull.buffer_ptrs[qq]) + qq * sn * 2 for qq in range(R)]
