@@ -119,6 +119,8 @@ def main():
     ap.add_argument("--recompute", default="auto", choices=["auto", "on", "off"])
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the JSON line says so)")
     ap.add_argument("--skip_e2e", action="store_true")
+    ap.add_argument("--stall_timeout", type=float, default=420.0,
+                    help="abort (non-zero exit) if no training step completes on the host for this many seconds")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -145,6 +147,23 @@ def main():
                                      collectives=args.collectives, activation_recompute=recompute,
                                      model_overrides={} if args.layers is None else {"layers": args.layers}))
     from zorse_b200.ops import sm100
+    from zorse_b200.utils.health import Watchdog
+
+    def _stalled(step, idle):
+        # a wedged collective must not hold the GPUs until somebody else's limit kills the job
+        sys.stderr.write(f"[bench] rank {tr.rank}: no step finished for {idle:.0f}s after step {step}; aborting\n")
+        if tr.rank == 0:
+            print(json.dumps({"metric": "tokens/s", "impl": "ours", "n_gpus": args.gpus,
+                              "error": f"stalled: no step finished for {idle:.0f}s (schedule {schedule})"}), flush=True)
+        os._exit(4)
+
+    dog = Watchdog(args.stall_timeout, rank=tr.rank, on_timeout=_stalled)
+    dog.start()
+    beats = [0]
+
+    def beat():
+        beats[0] += 1
+        dog.beat(beats[0])
 
     rank = tr.rank
     batch = tr.synthetic_batch()
@@ -154,6 +173,8 @@ def main():
     # ---- device-timed region -------------------------------------------------------------
     for _ in range(args.warmup):
         tr.train_step(inputs, targets)
+        tr.synchronize()
+        beat()
     tr.check_kernels()
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
     tr.synchronize(); tr.barrier()
@@ -166,6 +187,7 @@ def main():
         loss = tr.train_step(inputs, targets)
     b.record()
     tr.synchronize(); tr.barrier()
+    beat()
     launches = sm100.launch_count() - l0
     ms = torch.tensor([a.elapsed_time(b) / args.steps], device=tr.device)
     if world > 1:
@@ -182,6 +204,7 @@ def main():
     if world > 1:
         dist.all_reduce(exposed, op=dist.ReduceOp.MAX)
     exposed_ms = float(exposed.item())
+    beat()
 
     # ---- end to end through the public API: H2D of the inputs + D2H of the loss every step ----
     e2e = None
@@ -191,6 +214,7 @@ def main():
         t0 = time.perf_counter()
         for _ in range(args.steps):
             tr.train_step_from_host(batch)
+            beat()
         tr.synchronize(); tr.barrier()
         t = torch.tensor([(time.perf_counter() - t0) / args.steps * 1e3], device=tr.device)
         bts = torch.tensor([float(h2d_bytes), 4.0 if loss is not None else 0.0], device=tr.device)
@@ -200,6 +224,7 @@ def main():
         e2e = {"value": tokens_per_step / (float(t.item()) / 1e3), "unit": "tokens/s",
                "ms_per_step": float(t.item()), "h2d_bytes_per_step": int(bts[0].item()),
                "d2h_bytes_per_step": int(bts[1].item())}
+    dog.stop()
     sampler.stop_flag.set()
     sampler.join(timeout=2)
     mem = torch.cuda.max_memory_allocated() / 2**30

@@ -179,7 +179,9 @@ int zb_rs_adam(const void* const* grad_ptrs, int* const* flag_ptrs, int R, int r
   p.grad_scale = grad_scale;
   p.epoch = epoch; p.status = status; p.counter = counter;
   p.wait_ns = (unsigned long long)(wait_seconds * 1e9);
-  int blocks = num_sms() * 6;  // many resident warps: every iteration waits on NVLink-latency peer loads
+  // two CTAs per SM: the CTAs spin at their start until every peer has announced its bucket, so
+  // they must leave room on each SM for the kernels (NCCL p2p, GEMMs) the peers may still need
+  int blocks = num_sms() * 2;
   if (max_blocks > 0 && max_blocks < blocks) blocks = max_blocks;
   long need = (shard_n / (grad_f32 ? 4 : 8) + 255) / 256;
   if (need < blocks) blocks = int(need < 1 ? 1 : need);

@@ -260,15 +260,14 @@ def flash_fwd(qkv, B: int, S: int, Hq: int, Hkv: int, D: int, causal: bool = Tru
               scale: Optional[float] = None, version: Optional[int] = None):
     """qkv: packed [B*S, (Hq+2Hkv)*D]. Returns (out [B*S, Hq*D], lse [B, Hq, S]).
     version 1 (default, the faster one as measured): one query tile per CTA, S double-buffered in
-    TMEM, P staged through shared memory; version 2: two query tiles per CTA, P kept in TMEM;
-    version 3: version 1 with eight softmax warps (two threads per query row)."""
+    TMEM, P staged through shared memory; version 2: two query tiles per CTA, P kept in TMEM."""
     _bf16(qkv, "qkv")
     assert qkv.shape == (B * S, (Hq + 2 * Hkv) * D) and qkv.is_contiguous()
     out = torch.empty(B * S, Hq * D, dtype=qkv.dtype, device=qkv.device)
     lse = torch.empty(B, Hq, S, dtype=torch.float32, device=qkv.device)
     sc = (1.0 / math.sqrt(D)) if scale is None else scale
     ver = version or ATTN_FWD_VERSION
-    fn = {1: lib().zb_flash_fwd, 2: lib().zb_flash_fwd2, 3: lib().zb_flash_fwd3}[ver]
+    fn = {1: lib().zb_flash_fwd, 2: lib().zb_flash_fwd2}[ver]
     _check(fn(_p(qkv), _p(out), _p(lse), c_int(B), c_int(S), c_int(Hq), c_int(Hkv), c_int(D),
                               c_int(int(causal)), c_int(window), c_float(sc), c_int(out.stride(0)),
                               _p(status_word(qkv.device)), _stream()), "flash_fwd")

@@ -29,21 +29,14 @@ class OneFOneBSchedule(ScheduleBase):
         st.engine.prefetch_all()
         stage_pos = [s.stage_id for s in self.cfg.stages].index(st.stage_id)
         warm = min(len(self.cfg.stages) - stage_pos - 1, M)
-        frecv = {}
-        brecv = {}
-
-        def post_f(mbl):
-            if not st.is_first and mbl < M and mbl not in frecv:
-                frecv[mbl] = st.recv_fwd(mbl)
-
-        def post_b(mbl):
-            if not st.is_last and mbl < M and mbl not in brecv:
-                brecv[mbl] = st.recv_bwd(mbl)
+        # Receives are posted when they are needed, never ahead: torch serialises the p2p
+        # operations of one process group on each rank, so a receive posted one microbatch early
+        # would sit in front of this rank's own send of the current microbatch, and across four
+        # or more stages those extra "send waits for the next receive" edges close a cycle
+        # (stage 0's first backward would wait for a forward it runs only afterwards).
 
         def fwd(mbl):
-            post_f(mbl)
-            x = self._inp(st, inputs, mbl) if st.is_first else frecv.pop(mbl).wait()
-            post_f(mbl + 1)
+            x = self._inp(st, inputs, mbl) if st.is_first else st.recv_fwd(mbl).wait()
             for li in range(L):
                 units[li].acquire()
                 x = st.forward_layer(li, mbl, x, self._tgt(st, targets, mbl), self.recompute)
@@ -51,9 +44,7 @@ class OneFOneBSchedule(ScheduleBase):
                 st.send_fwd(mbl, x)
 
         def bwd(mbl):
-            post_b(mbl)
-            dy = None if st.is_last else brecv.pop(mbl).wait()
-            post_b(mbl + 1)
+            dy = None if st.is_last else st.recv_bwd(mbl).wait()
             for li in reversed(range(L)):
                 units[li].acquire()
                 units[li].grad_views()

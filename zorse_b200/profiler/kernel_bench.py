@@ -100,7 +100,7 @@ def bench_attn(k, peaks, rows):
             pairs = S * (S + 1) // 2
         fl_f = 4.0 * pairs * D * Hq * B
         t_o = time_fn(lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win))
-        for ver in (1, 2, 3):
+        for ver in (1, 2):
             t_v = time_fn(lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win, version=ver))
             rows.append({"op": f"flash fwd v{ver}", "shape": f"{name} S{S} Hq{Hq} Hkv{Hkv} D{D} win{win}", "ours_ms": t_v,
                          "lib_ms": None, "ours_tflops": fl_f / t_v / 1e9, "frac_of_peak": fl_f / t_v / 1e9 / peaks["bf16_tflops"]})
