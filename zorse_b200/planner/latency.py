@@ -81,3 +81,17 @@ def store(table: dict, model: str, gpu: str, seq: int, dtype: str, fwd_ms: list[
 
     table.setdefault(model, {}).setdefault(gpu, {}).setdefault(str(seq), {})[dtype] = [fit(fwd_ms), fit(bwd_ms),
                                                                                       list(fwd_ms), list(bwd_ms)]
+
+
+def head_and_embedding_ms(model: str, gpu: str, seq: int, mbs: int, vocab: int, **overrides) -> tuple[tuple, tuple]:
+    """Analytic (forward, backward) times per microbatch of the output head and of the embedding:
+    the head is two GEMM-sized passes (dgrad + wgrad) over [tokens, hidden] x [vocab, hidden] plus
+    a cross-entropy pass over the logits; the embedding is a gather / scatter of the activations."""
+    spec = registry.get_spec(model, vocab=vocab, **overrides)
+    tf = ANALYTIC_TFLOPS.get(gpu, 100.0) * 1e12
+    hbm = {"b200": 6.5e12}.get(gpu, 1.5e12)
+    T = mbs * seq
+    gemm = 2.0 * T * spec.hidden * (vocab or spec.vocab) / tf * 1e3
+    ce = 2.0 * T * (vocab or spec.vocab) * 2 / hbm * 1e3
+    emb = 2.0 * T * spec.hidden * 2 / hbm * 1e3
+    return (gemm + 0.5 * ce, 2.0 * gemm + 0.5 * ce), (emb, 2.0 * emb)

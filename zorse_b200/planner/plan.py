@@ -17,7 +17,7 @@ from ..models import registry
 from ..utils.metrics import clean_gpu_name
 from . import comm_model
 from .cluster import GPU, GPUGroup, ModelConfig, link_bandwidth, link_latency
-from .latency import load_model_compute_latencies_per_gpu, load_table
+from .latency import head_and_embedding_ms, load_model_compute_latencies_per_gpu, load_table
 from .partition import build_gpu_graph, partition
 from .stage2 import PipelineOptimizer, PlanResult
 
@@ -73,7 +73,8 @@ def microbatch_sizes(gbs: int) -> list[int]:
 def plan_partition(data: dict, pmap: dict, model_name: str, *, global_batch_size: int, sequence_length: int,
                    autocast_dtype: str, vocab_size: int, dtype_multiplier: float, optimizer_multiplier: float,
                    reserved_memory_gb: float, recompute: bool = True, measured_agrs: Optional[dict] = None,
-                   table: Optional[dict] = None, optimizer_gbs: float = 6000.0) -> Optional[PlanResult]:
+                   table: Optional[dict] = None, optimizer_gbs: float = 6000.0,
+                   microbatch_size: Optional[int] = None, compute_overhead: float = 1.075) -> Optional[PlanResult]:
     stats = registry.get_model_stats(model_name, vocab=vocab_size)
     model = ModelConfig(model_name, stats["num_layers"], stats["hidden_size"], stats["parameters_per_layer"],
                         stats["total_parameters"], sequence_length, global_batch_size, vocab_size)
@@ -89,7 +90,7 @@ def plan_partition(data: dict, pmap: dict, model_name: str, *, global_batch_size
             g.reduce_scatter_latency = comm_model.collective_ms(data, g.ranks, size, "reduce_scatter")
     groups = order_groups(data, groups)
     best = None
-    for mbs in microbatch_sizes(global_batch_size):
+    for mbs in ([microbatch_size] if microbatch_size else microbatch_sizes(global_batch_size)):
         act_bytes = mbs * sequence_length * model.hidden_size * comm_model.DTYPE_BYTES[autocast_dtype]
         for a, b in zip(groups, groups[1:]):
             bw, lat = inter_group_bandwidth(data, a, b)
@@ -98,11 +99,17 @@ def plan_partition(data: dict, pmap: dict, model_name: str, *, global_batch_size
             b.send_recv_latency_prev = t
         gpus = [x.identifier for g in groups for x in g.gpus]
         lat_tbl = load_model_compute_latencies_per_gpu(model_name, gpus, sequence_length, autocast_dtype, mbs, table)
+        # the layer profile times one block in a tight loop; a whole step also pays for launch gaps,
+        # allocator traffic and the small kernels between blocks (7.5 % on the B200 runs used to calibrate)
+        lat_tbl = {g: type(v)(v.forward * compute_overhead, v.backward * compute_overhead) for g, v in lat_tbl.items()}
         # optimizer: 28 bytes per parameter of HBM traffic on each rank's shard
         opt_ms = model.parameters_per_layer / max(min(len(g.gpus) for g in groups), 1) * 28 / (optimizer_gbs * 1e9) * 1e3
+        slowest = max(gpus, key=lambda g: lat_tbl[g].total)
+        head_ms, emb_ms = head_and_embedding_ms(model_name, slowest, sequence_length, mbs, vocab_size)
         res = PipelineOptimizer(groups, model, lat_tbl, mbs, dtype_multiplier=dtype_multiplier,
                                 optimizer_multiplier=optimizer_multiplier, reserved_memory_gb=reserved_memory_gb,
-                                recompute=recompute, optimizer_ms_per_layer=opt_ms).optimize()
+                                recompute=recompute, optimizer_ms_per_layer=opt_ms, head_ms=head_ms,
+                                embedding_ms=emb_ms).optimize()
         if res is None:
             if best is not None:
                 break   # larger microbatches only need more memory
@@ -124,7 +131,8 @@ def plan(data: dict, model_name: str, *, global_batch_size: int, sequence_length
          reduce_dtype: str = "float32", vocab_size: int = 32000, partition_algorithm: str = "min_k_cut_split",
          dtype_multiplier: float = 2.0, optimizer_multiplier: float = 12.0, reserved_memory_gb: float = 2.0,
          recompute: bool = True, measured_agrs: Optional[dict] = None, table: Optional[dict] = None,
-         ks: Optional[list[int]] = None) -> tuple[Optional[PlanResult], list[dict]]:
+         ks: Optional[list[int]] = None, microbatch_size: Optional[int] = None,
+         compute_overhead: float = 1.075) -> tuple[Optional[PlanResult], list[dict]]:
     G = build_gpu_graph(data)
     best, tried = None, []
     for k in (ks or candidate_ks(data)):
@@ -133,7 +141,7 @@ def plan(data: dict, model_name: str, *, global_batch_size: int, sequence_length
                              sequence_length=sequence_length, autocast_dtype=autocast_dtype, vocab_size=vocab_size,
                              dtype_multiplier=dtype_multiplier, optimizer_multiplier=optimizer_multiplier,
                              reserved_memory_gb=reserved_memory_gb, recompute=recompute, measured_agrs=measured_agrs,
-                             table=table)
+                             table=table, microbatch_size=microbatch_size, compute_overhead=compute_overhead)
         tried.append({"k": k, "latency_ms": None if res is None else res.latency_ms,
                       "microbatch_size": None if res is None else res.microbatch_size,
                       "interleave_degree": None if res is None else res.interleave_degree})

@@ -61,7 +61,8 @@ class PlanResult:
 class PipelineOptimizer:
     def __init__(self, groups: list[GPUGroup], model: ModelConfig, latencies: dict[str, ModelLatencies], microbatch_size: int,
                  *, dtype_multiplier: float = 2.0, optimizer_multiplier: float = 12.0, reserved_memory_gb: float = 2.0,
-                 recompute: bool = True, optimizer_ms_per_layer: float = 0.0, max_interleave: Optional[int] = None):
+                 recompute: bool = True, optimizer_ms_per_layer: float = 0.0, max_interleave: Optional[int] = None,
+                 head_ms: tuple = (0.0, 0.0), embedding_ms: tuple = (0.0, 0.0)):
         self.groups = list(groups)
         self.model = model
         self.lat = latencies
@@ -71,6 +72,11 @@ class PipelineOptimizer:
         self.recompute = recompute
         self.opt_ms = optimizer_ms_per_layer
         self.max_interleave = max_interleave
+        # (forward, backward) time per microbatch of the output head (final norm + vocabulary
+        # projection + loss) on the last stage and of the embedding on the first one; the
+        # reference's model treats the network as L identical blocks and leaves both out
+        self.head_ms = head_ms
+        self.embedding_ms = embedding_ms
 
     # ---- work split ------------------------------------------------------------------
     def microbatches_for_group(self, g: GPUGroup) -> list[int]:
@@ -139,7 +145,15 @@ class PipelineOptimizer:
                 bk = [(fi + bi) if self.recompute else bi for fi, bi in zip(ff, bb)]
                 bwd = max(max(max(x * n, sr) * m for x, m in zip(bk, s.num_microbatches_per_rank)),
                           (g.all_gather_latency + g.reduce_scatter_latency) * n)
-                tot += fwd + bwd + self.opt_ms * n
+                extra = 0.0
+                m_max = max(s.num_microbatches_per_rank)
+                if i == len(stages) - 1:
+                    hf, hb = self.head_ms
+                    extra += m_max * (hf + hb + (hf if self.recompute else 0.0))
+                if i == 0:
+                    ef, eb = self.embedding_ms
+                    extra += m_max * (ef + eb)
+                tot += fwd + bwd + self.opt_ms * n + extra
             steady = max(steady, tot)
         drain = 0.0
         for i, s in enumerate(reversed(stages[1:])):

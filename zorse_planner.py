@@ -33,6 +33,9 @@ def main(argv=None) -> int:
     ap.add_argument("--agrs_profile", default=None, help="JSON of measured AG/RS times per group (profiler output)")
     ap.add_argument("--no_recompute", action="store_true")
     ap.add_argument("--num_stages", type=int, default=None, help="only try this number of GPU groups")
+    ap.add_argument("--microbatch_size", type=int, default=None, help="plan for this microbatch size only (no sweep)")
+    ap.add_argument("--compute_overhead", type=float, default=1.075,
+                    help="whole-step time over the sum of profiled layer times (launch gaps, small kernels)")
     ap.add_argument("--draw", default=None, help="write a PNG of the partitioned GPU graph (needs matplotlib)")
     a = ap.parse_args(argv)
 
@@ -49,7 +52,7 @@ def main(argv=None) -> int:
                       partition_algorithm=a.partition_algorithm, dtype_multiplier=a.dtype_multiplier,
                       optimizer_multiplier=a.optimizer_multiplier, reserved_memory_gb=a.reserved_memory_gb,
                       recompute=not a.no_recompute, measured_agrs=measured,
-                      ks=[a.num_stages] if a.num_stages else None)
+                      ks=[a.num_stages] if a.num_stages else None, microbatch_size=a.microbatch_size, compute_overhead=a.compute_overhead)
     for t in tried:
         print(f"k={t['k']}: predicted {t['latency_ms']} ms (microbatch {t['microbatch_size']}, interleave {t['interleave_degree']})")
     if res is None:
