@@ -1,0 +1,138 @@
+"""Host-side tools: flags, metrics block, cluster collector (with a fake command runner),
+comm-model CLI, collective fit, latency table, trace post-processing."""
+import json
+import os
+import subprocess
+import sys
+import types
+import warnings
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_flags_accept_reference_command_line(tmp_path):
+    from zorse_b200.config.flags import parse_args_zorse
+    from zorse_b200.parallel.schedules import schedule_name_from_flags
+
+    cfg = {"model_name": "tiny_llama", "global_batch_size": 8, "microbatch_size": 2, "sequence_length": 128,
+           "autocast_dtype": "bfloat16", "reduce_dtype": "float32", "pipeline_config": []}
+    f = tmp_path / "c.json"
+    f.write_text(json.dumps(cfg))
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        a = parse_args_zorse(["--config_file", str(f), "--zero2_pipeline", "--gloo_p2p", "--optimizer_in_backwards",
+                              "--hybrid_shard", "--tt_pp", "2", "--iterations", "3"])
+    assert any("ignored" in str(x.message) for x in w)
+    import torch
+
+    assert a.seq_length == 128 and a.autocast_dtype == torch.bfloat16 and a.global_batch_size == 8
+    assert schedule_name_from_flags(a) == "zero2"
+    a.flashflex_pipeline = True
+    assert schedule_name_from_flags(a) == "flashflex"          # precedence flashflex > zero2
+    b = types.SimpleNamespace(two_stage_sync=True, sync_comm=True)
+    with pytest.raises(ValueError):
+        schedule_name_from_flags(b)
+    assert schedule_name_from_flags(types.SimpleNamespace(sync_comm=True)) == "no_overlap"
+    assert schedule_name_from_flags(types.SimpleNamespace()) == "layer_major"
+
+
+def test_metrics_block_and_mfu():
+    from zorse_b200.utils import metrics as m
+
+    assert m.clean_gpu_name("NVIDIA B200") == "b200"
+    assert m.clean_gpu_name("NVIDIA A100-SXM4-80GB") == "a100x80"
+    assert m.clean_gpu_name("NVIDIA H100 NVL") == "h100-nvl"
+    fl = m.compute_model_flops(6_738_415_616, 32, 4096, 4096, 64)
+    assert fl == pytest.approx(4.5 * (2 * 6_738_415_616 * 4096 + 4 * 32 * 4096 * 4096 ** 2) * 64)
+    mfu, tflops = m.compute_mfu(fl, 12000.0, ["b200"], "bfloat16")
+    assert 0 < mfu < 1 and tflops == pytest.approx(fl / 12.0 / 1e12)
+    per = m.per_gpu_mfu(fl, 12000.0, [3, 1], ["b200", "h100"], "bfloat16")
+    assert per[0] > per[1] * 0.5
+    s = m.format_summary(global_batch=64, seq=4096, step_ms=12000.0, flops_per_step=fl, gpu_names=["b200"],
+                         dtype="bfloat16", max_alloc_gb=[117.0], predicted_ms=12471.0, exposed_comm_ms=0.0, loss=1.5)
+    assert m.CSV_HEADER in s and "Throughput: 21845.3 tokens/s" in s and "measured/predicted" in s
+    assert s.splitlines()[-1].startswith("64,4096,117.00,117.00,12000.00,21845.33")
+
+
+def test_cluster_collector_with_fake_runner(tmp_path):
+    from zorse_b200.profiler import cluster as C
+
+    hostfile = tmp_path / "hostfile"
+    hostfile.write_text("nodeA,~/.ssh/k,/opt/conda.sh,env,~/repo,eth0\nnodeB,,,,~/repo,\n")
+    ms = C.read_machine_file(str(hostfile))
+    assert [m.hostname for m in ms] == ["nodeA", "nodeB"] and ms[0].socket_ifname == "eth0"
+    cmd = C.remote_command(ms[0], "nvidia-smi")
+    assert cmd[0] == "ssh" and "-i" in cmd and "conda activate env" in cmd[-1] and "NCCL_SOCKET_IFNAME=eth0" in cmd[-1]
+
+    def runner(cmd, **kw):
+        text = " ".join(cmd)
+        if "nvidia-smi" in text:
+            out = "0, NVIDIA B200, 183359 MiB\n1, NVIDIA B200, 183359 MiB\n" if "nodeA" in text else "0, NVIDIA H100 NVL, 95830 MiB\n"
+        elif "--intranode" in text:
+            out = "Bandwidth: 742.5 GB/s\nLatency: 0.000054 s\n"
+        else:
+            out = "Bandwidth: 11.2 GB/s\nLatency: 0.0036 s\n"
+        return types.SimpleNamespace(returncode=0, stdout=out, stderr="")
+
+    info = C.collect_cluster_info(ms, runner)
+    assert info["total_gpus"] == 3 and [g["global_rank"] for g in info["gpu_list"]] == [0, 1, 2]
+    assert info["gpu_list"][2]["name"] == "h100-nvl" and info["global_rank_map"]["2"]["machine"] == "nodeB"
+    bw = C.run_bandwidth_test(ms, info, runner)
+    assert bw["intranode_bandwidth"]["0"] == 742.5 and bw["intranode_bandwidth"]["1"] == 0.0
+    assert bw["internode_bandwidth"]["0"]["1"] == 11.2 and bw["internode_latency"]["0"]["1"] == 0.0036
+    info["bandwidth"] = bw
+    # the planner reads what the collector writes
+    from zorse_b200.planner.cluster import link_bandwidth
+    from zorse_b200.planner.partition import build_gpu_graph, partition
+
+    g = info["gpu_list"]
+    assert link_bandwidth(info, g[0], g[1]) == 742.5 and link_bandwidth(info, g[2], g[0]) == 11.2
+    G = build_gpu_graph(info)
+    for alg in ("min_k_cut_split", "min_k_cut_efficient", "clustering"):
+        pm = partition(G, 2, alg)
+        assert pm["gpu_0"] == pm["gpu_1"] != pm["gpu_2"], alg
+
+
+def test_collective_fit_and_latency_table(tmp_path):
+    from zorse_b200.planner import latency as L
+    from zorse_b200.profiler.collectives import fit_switch_model
+
+    R, alpha, bw = 4, 0.05, 600.0
+    sizes = [25e6, 100e6, 400e6]
+    times = [alpha + (R - 1) / R * s / 1e9 / bw * 1e3 for s in sizes]
+    fit = fit_switch_model(sizes, times, R)
+    assert fit["alpha_ms"] == pytest.approx(alpha, rel=1e-3) and fit["bandwidth_gbs"] == pytest.approx(bw, rel=1e-3)
+    tbl = {}
+    L.store(tbl, "llama2_7b", "b200", 4096, "bfloat16", [1.6, 3.4], [4.0, 7.6])
+    assert L.lookup(tbl, "llama2_7b", "b200", 4096, "bfloat16", 2).forward == 3.4      # measured value wins
+    assert L.lookup(tbl, "llama2_7b", "b200", 4096, "bfloat16", 4).forward == pytest.approx(1.8 * 4 - 0.2)  # linear model
+    assert L.lookup(tbl, "llama2_7b", "h100", 4096, "bfloat16", 1) is None
+    shipped = L.load_table()
+    assert L.lookup(shipped, "llama2_7b", "b200", 4096, "bfloat16", 1) is not None   # profile measured on a B200
+    a = L.analytic("llama2_7b", "b200", 4096, 1)
+    assert 0.5 < a.forward < 5.0
+
+
+def test_comm_model_cli_and_param_estimate():
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "comm_model.py"), "--cluster_info_file",
+                        os.path.join(ROOT, "data", "cluster_info_b200x8.json"), "--ranks", "0,1"],
+                       capture_output=True, text=True, cwd=ROOT)
+    assert r.returncode == 0 and "all_gather (best model)" in r.stdout
+    from zorse_b200.models.param_estimate import estimate
+
+    e = estimate("llama2_7b")
+    assert e["parameters_per_layer"] == 202383360 and e["total_parameters"] == 6738415616
+
+
+def test_trace_postprocessing(tmp_path):
+    from zorse_b200.utils.trace import extract_kernel_runtime, stream_busy_and_gaps
+
+    ev = [{"cat": "kernel", "ts": 0, "dur": 100, "args": {"stream": 7}}, {"cat": "kernel", "ts": 150, "dur": 50, "args": {"stream": 7}},
+          {"cat": "kernel", "ts": 20, "dur": 30, "args": {"stream": 9}}, {"cat": "cpu_op", "ts": 0, "dur": 999}]
+    f = tmp_path / "t.json"
+    f.write_text(json.dumps({"traceEvents": ev}))
+    assert extract_kernel_runtime(str(f), iterations=2) == pytest.approx(0.09)
+    s = stream_busy_and_gaps(str(f))
+    assert s[7]["busy_ms"] == pytest.approx(0.15) and s[7]["gap_ms"] == pytest.approx(0.05) and s[9]["kernels"] == 1
