@@ -68,3 +68,42 @@ def test_simulator_flags_order_mismatch():
     b = [Event("post_recv", 0, "act", 2), Event("wait_recv", 0, "act", 2), Event("post_recv", 0, "act", 0),
          Event("wait_recv", 0, "act", 0)]
     assert "order mismatch" in simulate({0: a, 1: b})
+
+
+def test_alternate_nccl_gloo_and_batched_gloo_receives():
+    """With a Gloo communicator present, equal-width boundaries stay on the primary transport and
+    mixed-width ones go through Gloo; Gloo receives of a ZeRO-2 pass are all posted up front."""
+    import torch
+
+    from zorse_b200.engine.zero import EngineConfig, Streams
+    from zorse_b200.ops.api import get_ops
+    from zorse_b200.parallel.groups import Group, StageGroups
+    from zorse_b200.parallel.p2p_plan import create_static_comm_plans
+    from zorse_b200.parallel.p2p_sim import RecordingTransport
+    from zorse_b200.parallel.schedules import build_schedule
+    from zorse_b200.parallel.stage import PipelineStage
+
+    pipe = [{"gpu_ranks": [0], "num_microbatches_per_rank": [4], "layer_partition": [0, 1], "zero_config": [[0]]},
+            {"gpu_ranks": [1, 2], "num_microbatches_per_rank": [2, 2], "layer_partition": [1, 2], "zero_config": [[1], [2]]},
+            {"gpu_ranks": [3, 4], "num_microbatches_per_rank": [2, 2], "layer_partition": [2, 3], "zero_config": [[3], [4]]}]
+    cfg = parse_pipeline_dict({"model_name": "tiny_llama", "global_batch_size": 4, "microbatch_size": 1, "sequence_length": 8,
+                               "vocab_size": 64, "autocast_dtype": "float32", "reduce_dtype": "float32", "pipeline_config": pipe})
+    plans = create_static_comm_plans(cfg)
+    g = torch.Generator().manual_seed(0)
+    data = {i: torch.randint(0, 64, (1, 8), generator=g) for i in range(4)}
+    rank = 1  # middle stage: previous boundary is 1 -> 2 ranks (mixed), next boundary 2 -> 2 (equal)
+    prim, gloo = RecordingTransport(rank), RecordingTransport(rank)
+    st_cfg = cfg.stages_of_rank(rank)[0]
+    st = PipelineStage(cfg, st_cfg, rank=rank, device=torch.device("cpu"), ops=get_ops("ref"),
+                       engine_cfg=EngineConfig(compute_dtype=torch.float32, reduce_dtype=torch.float32),
+                       groups=StageGroups(Group((rank,)), Group((rank,))), streams=Streams(torch.device("cpu")),
+                       pattern=plans[rank].stages[st_cfg.stage_id], transport=prim, gloo_transport=gloo,
+                       model_overrides={**OV, "layers": 3})
+    assert st.uses_gloo(False) and not st.uses_gloo(True)
+    build_schedule("zero2", [st], cfg).step(0, data, data)
+    assert {e.peer for e in gloo.events} == {0} and {e.peer for e in prim.events} <= {3, 4}
+    # forward: both Gloo receives are posted before the first one is waited for
+    fwd = [e.what for e in gloo.events if e.kind == "act"]
+    assert fwd[:3] == ["post_recv", "post_recv", "wait_recv"]
+    cfg.alternate_nccl_gloo = False
+    assert st.uses_gloo(True)

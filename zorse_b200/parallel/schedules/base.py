@@ -42,10 +42,10 @@ class ScheduleBase:
             st.loss_sum = None
         for st in self.stages:
             self.forward_stage(st, inputs, targets)
-            st.transport.flush()
+            st.flush()
         for st in reversed(self.stages):
             self.backward_stage(st, inputs, targets)
-            st.transport.flush()
+            st.flush()
         for st in self.stages:
             st.engine.optimizer_step()
             st.engine.finish_step()

@@ -65,7 +65,7 @@ class OneFOneBSchedule(ScheduleBase):
             for u in units:
                 u.grad_views()
                 u.reduce_grads()
-        st.transport.flush()
+        st.flush()
         st.engine.optimizer_step()
         st.engine.finish_step()
         st.stash.clear()

@@ -118,24 +118,48 @@ class PipelineStage:
     def act_shape(self):
         return (self.tokens, self.hidden)
 
-    def tp(self, kind_is_grad: bool = False):
-        return self.transport
+    def boundary_transport(self, towards_next: bool):
+        """Transport of the boundary to the next (or previous) stage.  With a Gloo communicator
+        present (`--gloo_p2p`) and `alternate_nccl_gloo` set, boundaries between stages of equal
+        width stay on NCCL and mixed-width boundaries (many-to-many routing) go through Gloo, as
+        the reference's ZeRO-2 schedule does (zorse_utils/pipeline_schedule_zero2.py:230-244);
+        without the option every boundary uses the Gloo communicator."""
+        if self.gloo_transport is None:
+            return self.transport
+        if not self.cfg.alternate_nccl_gloo:
+            return self.gloo_transport
+        stages = self.cfg.stages
+        pos = [s.stage_id for s in stages].index(self.stage_id)
+        other = pos + 1 if towards_next else pos - 1
+        if 0 <= other < len(stages) and len(stages[other].gpu_ranks) == len(self.st.gpu_ranks):
+            return self.transport
+        return self.gloo_transport
+
+    def uses_gloo(self, towards_next: bool) -> bool:
+        return self.gloo_transport is not None and self.boundary_transport(towards_next) is self.gloo_transport
+
+    def transports(self):
+        return [t for t in (self.transport, self.gloo_transport) if t is not None]
+
+    def flush(self) -> None:
+        for t in self.transports():
+            t.flush()
 
     def recv_fwd(self, mbl: int):
         src, tag = self.pattern.fwd_recv[mbl]
-        return self.transport.recv(self.act_shape(), self.act_dtype, src, tag, "act")
+        return self.boundary_transport(False).recv(self.act_shape(), self.act_dtype, src, tag, "act")
 
     def send_fwd(self, mbl: int, y: torch.Tensor):
         dst, tag = self.pattern.fwd_send[mbl]
-        return self.transport.send(y, dst, tag, "act")
+        return self.boundary_transport(True).send(y, dst, tag, "act")
 
     def recv_bwd(self, mbl: int):
         src, tag = self.pattern.bwd_recv[mbl]
-        return self.transport.recv(self.act_shape(), self.act_dtype, src, tag, "grad")
+        return self.boundary_transport(True).recv(self.act_shape(), self.act_dtype, src, tag, "grad")
 
     def send_bwd(self, mbl: int, dx: torch.Tensor):
         dst, tag = self.pattern.bwd_send[mbl]
-        return self.transport.send(dx, dst, tag, "grad")
+        return self.boundary_transport(False).send(dx, dst, tag, "grad")
 
     def add_loss(self, rows: torch.Tensor) -> None:
         v = rows.float().sum() * self.loss_scale

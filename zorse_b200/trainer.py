@@ -70,15 +70,20 @@ class Trainer:
         self.streams = Streams(self.device)
         stage_groups = G.StageGroups.create_all(cfg.stages, self.rank)
         self.gloo_group = G.gloo_world_group() if (opt.gloo_p2p or self.device.type == "cuda") and G.is_dist() else None
-        self.transport = make_transport(self.device, use_gloo=opt.gloo_p2p, gloo_group=self.gloo_group,
+        # --gloo_p2p on GPUs: keep an NCCL transport next to the Gloo one so that the ZeRO-2 schedule
+        # can alternate between them by stage width; on CPU ranks there is only Gloo
+        both = opt.gloo_p2p and self.device.type == "cuda" and G.is_dist()
+        self.transport = make_transport(self.device, use_gloo=opt.gloo_p2p and not both, gloo_group=self.gloo_group,
                                         streams=self.streams)
+        self.gloo_transport = GlooP2P(self.device, self.gloo_group) if both else None
         plans = create_static_comm_plans(cfg)
         self.plan = plans[self.rank]
         offload_act = cfg.activation_offload if opt.activation_offload is None else opt.activation_offload
         self.stages = [
             PipelineStage(cfg, st, rank=self.rank, device=self.device, ops=self.ops, engine_cfg=self.engine_cfg,
                           groups=stage_groups[st.stage_id], streams=self.streams, pattern=self.plan.stages[st.stage_id],
-                          transport=self.transport, activation_offload=bool(offload_act),
+                          transport=self.transport, gloo_transport=self.gloo_transport,
+                          activation_offload=bool(offload_act),
                           model_overrides=opt.model_overrides)
             for st in cfg.stages_of_rank(self.rank)]
         recompute = cfg.activation_recompute if opt.activation_recompute is None else opt.activation_recompute
