@@ -7,14 +7,15 @@
 //     dV += P^T dO        dK += dS^T Q                     (TMEM cols [256,256+D) / [256+D,256+2D))
 //     dQ = dS K           (reuses the S columns; added to an fp32 accumulator in global
 //                          memory with red.global.add.v4.f32, one row per thread)
-// Warps 0-3 turn S/dP into P and dS = P * (dP - delta) * scale in registers and write both
+// Warps 0-7 (0-3: key columns 0-63, 4-7: columns 64-127 of the tile; every warp covers 32 query
+// rows) turn S/dP into P and dS = P * (dP - delta) * scale in registers and write both
 // as bf16 into 128-byte-swizzled shared tiles whose layout serves as the K-major operand
 // of dS K and as the MN-major operand of P^T dO / dS^T Q.  dK and dV never leave TMEM
 // until the CTA is done, so no atomics are needed for them.
 //
 // Inputs: packed qkv[B*S, (Hq+2Hkv)*D], O and dO [B*S, Hq*D], LSE[B,Hq,S].
-// Outputs: dqkv (k and v parts written here, q part by zb_flash_bwd_finish from the fp32
-// accumulator).  Replaces the autograd of flash-attn 2 / SDPA used by the reference
+// Outputs: dqkv (k and v parts written here, q part by attn_dq_finish_kernel from the fp32
+// accumulator).  Warp 8 = TMA producer, warp 9 = MMA issuer and TMEM owner.  Replaces the autograd of flash-attn 2 / SDPA used by the reference
 // (models/llama_simple.py:396-416).
 #include "../common/host.h"
 #include "../common/ptx.cuh"
@@ -43,11 +44,6 @@ struct AttnBwdCfg {
   static constexpr int DP_COL = 128, DV_COL = 256, DK_COL = 256 + D;
 };
 
-__device__ __forceinline__ float bwd_exp2(float x) {
-  float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
@@ -74,9 +70,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint64_t* qdo_full = bars + 1;       // QS
   uint64_t* qdo_empty = qdo_full + 2;  // QS
   uint64_t* sdp_full = qdo_empty + 2;  // 1
-  uint64_t* pds_full = sdp_full + 1;   // 1 (4 arrivals)
+  uint64_t* pds_full = sdp_full + 1;   // 1 (8 arrivals)
   uint64_t* dq_full = pds_full + 1;    // 1
-  uint64_t* dq_empty = dq_full + 1;    // 1 (4 arrivals)
+  uint64_t* dq_empty = dq_full + 1;    // 1 (8 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 

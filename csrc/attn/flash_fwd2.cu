@@ -36,12 +36,6 @@ struct AttnFwd2Cfg {
   static constexpr int THREADS = 352;
 };
 
-__device__ __forceinline__ float fwd2_exp2(float x) {
-  float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 template <int D>
 __global__ void __launch_bounds__(352, 1)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,

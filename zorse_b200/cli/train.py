@@ -10,7 +10,7 @@ import torch
 import torch.distributed as dist
 
 from ..config.flags import parse_args_zorse
-from ..config.training_config import dtype_to_str, parse_pipeline_config
+from ..config.training_config import parse_pipeline_config
 from ..models import registry
 from ..parallel import groups as G
 from ..parallel.schedules import schedule_name_from_flags

@@ -21,7 +21,6 @@ sharded.  Replaces the NCCL calls at reference utils/patch.py:500-501, 585-589.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -142,7 +142,6 @@ class ZeroUnit:
         self.full: Optional[torch.Tensor] = None
         self.full_event = None
         self.grad: Optional[torch.Tensor] = None
-        self.grad_ready_event = None
         self.update_event = None
         # ---- offload ----------------------------------------------------------------
         self.host_master = self.host_p = None

@@ -9,7 +9,7 @@ the benchmark configurations name (`llama3.2_1b`, `llama2_7b`, `mistral_7b`, `op
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field, replace
+from dataclasses import dataclass, replace
 from typing import Optional
 
 from .layers import EmbeddingLayer, HeadLayer, Layer, NoOpLayer, PatchEmbeddingLayer, TransformerBlock

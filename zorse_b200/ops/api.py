@@ -11,9 +11,6 @@ are 2-D `[tokens, features]`.
 """
 from __future__ import annotations
 
-import math
-from typing import Optional
-
 import torch
 
 from . import ref

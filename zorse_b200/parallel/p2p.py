@@ -17,7 +17,6 @@
 from __future__ import annotations
 
 import datetime
-from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -19,7 +19,7 @@ its operations, and can be decided without any GPU:
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Optional
 
 import torch

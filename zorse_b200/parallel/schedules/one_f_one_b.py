@@ -9,7 +9,6 @@ backward microbatch.  By default activations are kept (no recompute): at most
 """
 from __future__ import annotations
 
-from ..stage import PipelineStage
 from .base import ScheduleBase
 
 

@@ -11,7 +11,7 @@ from typing import Optional
 
 import torch
 
-from ..config.training_config import PipelineConfig, StageConfig, dtype_from_str
+from ..config.training_config import PipelineConfig, StageConfig
 from ..engine.zero import EngineConfig, StageEngine, Streams
 from ..models import registry
 from .groups import StageGroups

@@ -10,8 +10,7 @@ bandwidth of all-gather / reduce-scatter on the NVSwitch domain, and a `units` n
 from __future__ import annotations
 
 import json
-from dataclasses import dataclass, field
-from typing import Optional
+from dataclasses import dataclass
 
 
 @dataclass(frozen=True)

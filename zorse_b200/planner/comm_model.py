@@ -10,7 +10,7 @@ Two families:
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import Sequence
 
 from .cluster import link_bandwidth
 

@@ -10,8 +10,6 @@ back to contiguous blocks of equal size in rank order.
 """
 from __future__ import annotations
 
-from typing import Optional
-
 import networkx as nx
 
 from .cluster import link_bandwidth
@@ -114,7 +112,6 @@ def spectral_partition(G: nx.Graph, k: int, seed: int = 0) -> dict:
         return {n: 0 for n in G.nodes}
     if _uniform(G):
         return contiguous_blocks(G, k)
-    import numpy as np
     from sklearn.cluster import SpectralClustering
 
     nodes = list(G.nodes)

@@ -17,7 +17,7 @@ from ..models import registry
 from ..utils.metrics import clean_gpu_name
 from . import comm_model
 from .cluster import GPU, GPUGroup, ModelConfig, link_bandwidth, link_latency
-from .latency import head_and_embedding_ms, load_model_compute_latencies_per_gpu, load_table
+from .latency import head_and_embedding_ms, load_model_compute_latencies_per_gpu
 from .partition import build_gpu_graph, partition
 from .stage2 import PipelineOptimizer, PlanResult
 

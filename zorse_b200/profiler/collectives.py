@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import statistics
 import time
-from typing import Optional, Sequence
+from typing import Sequence
 
 import torch
 import torch.distributed as dist

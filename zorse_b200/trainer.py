@@ -12,7 +12,6 @@ schedule -> loop over `schedule.step`.
 """
 from __future__ import annotations
 
-import time
 from dataclasses import dataclass, field
 from typing import Optional
 
@@ -90,7 +89,6 @@ class Trainer:
         name = cfg.schedule or opt.schedule
         self.schedule = build_schedule(name, self.stages, cfg, recompute=recompute, pipeline_log=opt.pipeline_log)
         self.step_idx = 0
-        self._dev_batch = None
 
     # ------------------------------------------------------------------ data
     def synthetic_batch(self, seed: Optional[int] = None, pin: bool = True) -> dict:
