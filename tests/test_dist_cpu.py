@@ -90,6 +90,31 @@ def test_uneven_microbatches_per_rank():
     _check(res, cfg)
 
 
+@pytest.mark.parametrize("schedule,oib", [("layer_major", False), ("zero2", True)])
+def test_uneven_parameter_shards(schedule, oib):
+    """Rank 0 owns about 70 % of every unit: broadcast-per-owner gather and reduce-per-owner
+    reduction must give the same training as equal shards."""
+    pipe = [dict(PIPE_1x2[0], shard_ratio=[0.7, 0.3])]
+    cfg = tiny_cfg(pipe)
+    res = run_workers(2, _worker, cfg, {"schedule": schedule, "optimizer_in_backward": oib}, 2)
+    _check(res, cfg)
+
+
+def test_shard_bounds():
+    from zorse_b200.engine.zero import shard_bounds
+    from zorse_b200.models.layers import ALIGN
+
+    n = 64 * ALIGN
+    assert shard_bounds(n, 4) == [0, n // 4, n // 2, 3 * n // 4, n]
+    b = shard_bounds(n, 3, [2, 1, 1])
+    assert b[0] == 0 and b[-1] == n and all(x % ALIGN == 0 for x in b)
+    assert b[1] == n // 2 and b[2] == 3 * n // 4
+    tiny = shard_bounds(4 * ALIGN, 4, [1000, 1, 1, 1])      # every rank keeps at least one block
+    assert all(tiny[i + 1] - tiny[i] >= ALIGN for i in range(4))
+    with pytest.raises(ValueError):
+        shard_bounds(n, 2, [1.0])
+
+
 def test_offload_params():
     cfg = tiny_cfg(PIPE_1x2)
     res = run_workers(2, _worker, cfg, {"schedule": "zero2", "optimizer_in_backward": True,

@@ -25,16 +25,25 @@ def read_meta(directory: str) -> dict:
     return meta
 
 
+def _bounds(unit: dict) -> list[int]:
+    """Element offsets of the saved shards (files written before unequal shards existed carry
+    only the common shard size)."""
+    if "shard_offsets" in unit:
+        return list(unit["shard_offsets"])
+    return [i * unit["shard_numel"] for i in range(len(unit["shard_ranks"]) + 1)]
+
+
 def _file_offsets(meta: dict) -> dict:
     """(stage, rank) -> {gid: byte offset of the unit's (master, m, v) block in that file}."""
     out: dict = {}
     for stage in sorted({u["stage"] for u in meta["units"]}):
         units = [u for u in meta["units"] if u["stage"] == stage]
-        for r in units[0]["shard_ranks"]:
+        for idx, r in enumerate(units[0]["shard_ranks"]):
             off, table = 0, {}
             for u in units:
                 table[u["gid"]] = off
-                off += 3 * u["shard_numel"] * 4
+                bd = _bounds(u)
+                off += 3 * (bd[idx + 1] - bd[idx]) * 4
             out[(stage, r)] = table
     return out
 
@@ -42,18 +51,19 @@ def _file_offsets(meta: dict) -> dict:
 def read_range(directory: str, meta: dict, offsets: dict, unit: dict, which: int, lo: int, hi: int) -> torch.Tensor:
     """Elements [lo, hi) of the padded flat tensor `which` (0 master, 1 m, 2 v) of a saved unit."""
     out = torch.zeros(hi - lo, dtype=torch.float32)
-    sn = unit["shard_numel"]
+    bd = _bounds(unit)
     for idx, r in enumerate(unit["shard_ranks"]):
-        a, b = max(lo, idx * sn), min(hi, (idx + 1) * sn)
+        s0, sn = bd[idx], bd[idx + 1] - bd[idx]
+        a, b = max(lo, s0), min(hi, s0 + sn)
         if a >= b:
             continue
         path = os.path.join(directory, f"stage{unit['stage']}_rank{r}.bin")
         if not os.path.exists(path):
             raise CheckpointError(f"missing shard file {path}")
-        need = offsets[(unit["stage"], r)][unit["gid"]] + (which * sn + (b - idx * sn)) * 4
+        need = offsets[(unit["stage"], r)][unit["gid"]] + (which * sn + (b - s0)) * 4
         if os.path.getsize(path) < need:
             raise CheckpointError(f"{path} is truncated ({os.path.getsize(path)} bytes, need {need})")
-        start = offsets[(unit["stage"], r)][unit["gid"]] + (which * sn + (a - idx * sn)) * 4
+        start = offsets[(unit["stage"], r)][unit["gid"]] + (which * sn + (a - s0)) * 4
         arr = np.fromfile(path, dtype="<f4", count=b - a, offset=start)
         out[a - lo:b - lo] = torch.from_numpy(arr.copy())
     return out
@@ -74,7 +84,7 @@ def load_checkpoint(trainer, directory: str) -> int:
             su = by_gid[u.gid]
             if su["numel"] != u.layer.layout()[1]:
                 raise CheckpointError(f"unit {u.gid}: {su['numel']} elements saved, model has {u.layer.layout()[1]}")
-            lo, hi = u.r * u.shard_n, (u.r + 1) * u.shard_n
+            lo, hi = u.lo, u.hi
             parts = []
             for which in range(3):
                 t = torch.zeros(u.shard_n, dtype=torch.float32)

@@ -2,8 +2,8 @@
 
 Layout: `<dir>/step_<n>/meta.json` + one flat binary per (stage, rank) `stage<s>_rank<r>.bin`.
 `meta.json` holds the training config, the step, seeds, dtypes and, per stage, the unit table:
-global unit id, kind, unpadded and padded element counts, shard-group ranks and each rank's
-element range.  A rank file is the concatenation, per unit in table order, of the fp32 master
+global unit id, kind, unpadded and padded element counts, shard-group ranks and the element
+offsets of their shards (equal or, with `shard_ratio`, unequal).  A rank file is the concatenation, per unit in table order, of the fp32 master
 shard, Adam m and v shards (little-endian float32).  Files are written to a temporary name,
 fsynced and renamed, `meta.json` last, so a directory with a `meta.json` is complete.
 """
@@ -36,7 +36,7 @@ def unit_table(trainer) -> list[dict]:
         for u in st.engine.units:
             out.append({"stage": st.stage_id, "gid": u.gid, "kind": u.layer.kind, "numel": u.layer.layout()[1],
                         "padded": u.n, "shard_ranks": list(u.shard_group.ranks), "shard_numel": u.shard_n,
-                        "step_count": u.step_count})
+                        "shard_offsets": list(u.offs), "step_count": u.step_count})
     return out
 
 

@@ -8,8 +8,10 @@ stage, and `zero_config` lists the shard groups of a stage (more than one group 
 hybrid shard: reduce-scatter inside a group, all-reduce across groups).
 
 Additions over the reference format (all optional, defaults keep reference behaviour):
-`zero_level` per stage (2 or 3), `reduce_dtype`, `schedule`, `activation_recompute`,
-`activation_offload`, `grad_norm_compat`.
+`zero_level` per stage (2 or 3), `shard_ratio` per stage (relative parameter-shard sizes of
+the ranks of a shard group, e.g. by GPU memory; the reference's dormant `split_uneven` /
+`shard_ratio` state, utils/patch.py:308-441), `reduce_dtype`, `schedule`,
+`activation_recompute`, `activation_offload`, `grad_norm_compat`.
 """
 from __future__ import annotations
 
@@ -49,6 +51,7 @@ class StageConfig:
     zero_config: tuple[tuple[int, ...], ...]
     num_microbatches_per_rank: tuple[int, ...]
     zero_level: int = 3
+    shard_ratio: Optional[tuple[float, ...]] = None   # one entry per rank of a shard group
 
     @property
     def num_microbatches(self) -> int:
@@ -94,6 +97,9 @@ class StageConfig:
             raise ConfigError(f"{s}: shard groups of different sizes {self.zero_config}")
         if self.zero_level not in (2, 3):
             raise ConfigError(f"{s}: zero_level must be 2 or 3")
+        if self.shard_ratio is not None:
+            if len(self.shard_ratio) != len(self.zero_config[0]) or any(x <= 0 for x in self.shard_ratio):
+                raise ConfigError(f"{s}: shard_ratio needs one positive entry per rank of a shard group")
 
 
 @dataclass
@@ -197,7 +203,8 @@ def parse_pipeline_dict(d: dict[str, Any]) -> PipelineConfig:
         stages.append(StageConfig(
             stage_id=i, gpu_ranks=ranks, layer_partition=(int(s["layer_partition"][0]), int(s["layer_partition"][1])),
             microbatch_size=mbs, zero_config=tuple(tuple(int(r) for r in g) for g in zc),
-            num_microbatches_per_rank=per_rank, zero_level=int(s.get("zero_level", d.get("zero_level", 3)))))
+            num_microbatches_per_rank=per_rank, zero_level=int(s.get("zero_level", d.get("zero_level", 3))),
+            shard_ratio=tuple(float(x) for x in s["shard_ratio"]) if s.get("shard_ratio") else None))
     known = {"model_name", "global_batch_size", "microbatch_size", "sequence_length", "pipeline_config", "vocab_size",
              "fused_optimizer", "interleave_degree", "latency", "autocast_dtype", "reduce_dtype",
              "split_microbatches_evenly", "skip_compute_sync", "interleave_stage_sync", "gloo_batch_recv",
@@ -236,7 +243,8 @@ def to_dict(cfg: PipelineConfig) -> dict[str, Any]:
         "pipeline_config": [
             {"gpu_ranks": list(s.gpu_ranks), "num_microbatches_per_rank": list(s.num_microbatches_per_rank),
              "layer_partition": list(s.layer_partition), "zero_config": [list(g) for g in s.zero_config],
-             **({"zero_level": s.zero_level} if s.zero_level != 3 else {})}
+             **({"zero_level": s.zero_level} if s.zero_level != 3 else {}),
+             **({"shard_ratio": list(s.shard_ratio)} if s.shard_ratio else {})}
             for s in cfg.stages],
     }
     if cfg.split_microbatches_evenly:

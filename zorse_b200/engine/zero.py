@@ -17,9 +17,12 @@ with a small state machine per unit that the pipeline schedules drive directly:
                              copied on a dedicated copy stream (:61-73, :1159-1187)
 
 Per shard group of size R the flat buffer is padded to a multiple of R*ALIGN elements and
-rank r owns elements [r*n/R, (r+1)*n/R).  Collectives run on a side stream; the compute
-stream waits on a per-unit event, never on the whole stream (patch.py:873-879).
-On CPU (gloo) everything is synchronous.
+rank r owns elements [r*n/R, (r+1)*n/R).  With `shard_ratios` the ranks own unequal,
+ALIGN-rounded ranges instead (the reference's dormant uneven-shard path,
+utils/patch.py:308-441, 470-498, 244-275): the gather becomes one broadcast per owner and
+the reduce-scatter one reduce per owner, both of which every backend supports for unequal
+sizes.  Collectives run on a side stream; the compute stream waits on a per-unit event,
+never on the whole stream (patch.py:873-879).  On CPU (gloo) everything is synchronous.
 """
 from __future__ import annotations
 
@@ -31,6 +34,28 @@ import torch.distributed as dist
 
 from ..models.layers import ALIGN, Layer
 from ..parallel.groups import Group
+
+
+def shard_bounds(n: int, R: int, ratios=None) -> list[int]:
+    """Element offsets [o_0 = 0, ..., o_R = n] of the R shards of a flat buffer of n elements
+    (n a multiple of R*ALIGN).  Without ratios the shards are equal; with ratios rank q gets
+    about ratios[q] / sum(ratios) of the buffer, rounded to ALIGN elements, the last rank the
+    remainder; every rank keeps at least one ALIGN block."""
+    if ratios is None:
+        return [q * (n // R) for q in range(R + 1)]
+    if len(ratios) != R or any(x <= 0 for x in ratios):
+        raise ValueError(f"shard_ratios needs {R} positive entries, got {list(ratios)}")
+    blocks = n // ALIGN
+    tot = float(sum(ratios))
+    offs, acc = [0], 0.0
+    for q in range(R - 1):
+        acc += ratios[q] / tot
+        b = int(round(acc * blocks))
+        b = max(b, offs[-1] // ALIGN + 1)          # at least one block for rank q
+        b = min(b, blocks - (R - 1 - q))            # and one for every later rank
+        offs.append(b * ALIGN)
+    offs.append(n)
+    return offs
 
 
 @dataclass
@@ -114,7 +139,7 @@ class Counters:
 class ZeroUnit:
     def __init__(self, layer: Layer, gid: int, *, device: torch.device, cfg: EngineConfig, ops, shard: Group,
                  replicate: Group, rank: int, streams: Streams, zero_level: Optional[int] = None,
-                 counters: Optional[Counters] = None, meta_init: bool = False):
+                 counters: Optional[Counters] = None, meta_init: bool = False, shard_ratios=None):
         self.layer, self.gid, self.device, self.cfg, self.ops = layer, gid, device, cfg, ops
         self.shard_group, self.rep_group, self.rank, self.streams = shard, replicate, rank, streams
         self.zero_level = zero_level or cfg.zero_level
@@ -124,11 +149,14 @@ class ZeroUnit:
         _, raw = layer.layout()
         q = self.R * ALIGN
         self.n = (raw + q - 1) // q * q
-        self.shard_n = self.n // self.R
+        self.offs = shard_bounds(self.n, self.R, shard_ratios if self.R > 1 else None)
+        self.uneven = len({self.offs[q + 1] - self.offs[q] for q in range(self.R)}) > 1
+        self.lo, self.hi = self.offs[self.r], self.offs[self.r + 1]
+        self.shard_n = self.hi - self.lo
         self.cuda = device.type == "cuda"
         self.step_count = 0
         # ---- persistent state ------------------------------------------------------
-        lo, hi = self.r * self.shard_n, (self.r + 1) * self.shard_n
+        lo, hi = self.lo, self.hi
         full32 = torch.empty(self.n, dtype=torch.float32, device=device)
         if not meta_init:
             layer.init_flat(full32, cfg.seed * 1000003 + gid)
@@ -198,16 +226,35 @@ class ZeroUnit:
             with torch.cuda.stream(self.streams.comm):
                 if self.update_event is not None:
                     self.streams.comm.wait_event(self.update_event)
-                dist.all_gather_into_tensor(full, self.p_shard, group=self.shard_group.pg)
+                self._gather_into(full, self.p_shard)
                 ev = torch.cuda.Event()
                 ev.record(self.streams.comm)
             full.record_stream(self.streams.comm)
             self.full_event = ev
         else:
-            dist.all_gather_into_tensor(full, self.p_shard, group=self.shard_group.pg)
+            self._gather_into(full, self.p_shard)
         self.full = full
         if self.host_p is not None:
             self.p_shard = None  # the device copy of an offloaded shard lives only for the gather
+
+    def _gather_into(self, full: torch.Tensor, shard: torch.Tensor) -> None:
+        pg = self.shard_group.pg
+        if not self.uneven:
+            dist.all_gather_into_tensor(full, shard, group=pg)
+            return
+        full[self.lo:self.hi].copy_(shard)
+        for q, owner in enumerate(self.shard_group.ranks):
+            dist.broadcast(full[self.offs[q]:self.offs[q + 1]], src=owner, group=pg)
+
+    def _reduce_scatter(self, g_full: torch.Tensor) -> torch.Tensor:
+        pg = self.shard_group.pg
+        if not self.uneven:
+            g_sh = torch.empty(self.shard_n, dtype=g_full.dtype, device=self.device)
+            dist.reduce_scatter_tensor(g_sh, g_full, group=pg)
+            return g_sh
+        for q, owner in enumerate(self.shard_group.ranks):
+            dist.reduce(g_full[self.offs[q]:self.offs[q + 1]], dst=owner, group=pg)
+        return g_full[self.lo:self.hi]
 
     def acquire(self) -> None:
         """Makes the unsharded parameters available to the compute stream and binds the layer."""
@@ -267,8 +314,7 @@ class ZeroUnit:
 
         def work():
             if self.R > 1:
-                g_sh = torch.empty(self.shard_n, dtype=g_full.dtype, device=self.device)
-                dist.reduce_scatter_tensor(g_sh, g_full, group=self.shard_group.pg)
+                g_sh = self._reduce_scatter(g_full)
                 self.counters.reduce_scatters += 1
             else:
                 g_sh = g_full
@@ -340,7 +386,7 @@ class ZeroUnit:
         if self.R == 1:
             return mine.clone()
         out = torch.empty(self.n, dtype=torch.float32, device=self.device)
-        dist.all_gather_into_tensor(out, mine.contiguous(), group=self.shard_group.pg)
+        self._gather_into(out, mine.contiguous())
         return out
 
     def state_tensors(self) -> dict[str, torch.Tensor]:
@@ -365,17 +411,19 @@ class StageEngine:
 
     def __init__(self, layers: list[Layer], gids: list[int], *, device, cfg: EngineConfig, ops, shard: Group,
                  replicate: Group, rank: int, streams: Optional[Streams] = None, zero_level: Optional[int] = None,
-                 meta_init: bool = False):
+                 meta_init: bool = False, shard_ratios=None):
         self.device, self.cfg, self.ops = device, cfg, ops
         self.streams = streams or Streams(device)
         self.counters = Counters()
         cls = ZeroUnit
-        if cfg.collectives == "fused" and device.type == "cuda" and shard.size > 1 and replicate.size == 1:
+        if (cfg.collectives == "fused" and device.type == "cuda" and shard.size > 1 and replicate.size == 1
+                and shard_ratios is None):
             from .fused import FusedZeroUnit
 
             cls = FusedZeroUnit
         self.units = [cls(ly, gid, device=device, cfg=cfg, ops=ops, shard=shard, replicate=replicate, rank=rank,
-                          streams=self.streams, zero_level=zero_level, counters=self.counters, meta_init=meta_init)
+                          streams=self.streams, zero_level=zero_level, counters=self.counters, meta_init=meta_init,
+                          shard_ratios=shard_ratios)
                       for ly, gid in zip(layers, gids)]
 
     def __len__(self):

@@ -57,6 +57,7 @@ def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
         raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
     if verbose:
         print(r.stderr)
+    obj.with_suffix(".log").write_text(f"==== {src.relative_to(CSRC)}\n{r.stderr}")
     return r.stderr
 
 
@@ -75,8 +76,11 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             futs = [ex.submit(_compile_one, nvcc, s, o, verbose) for s, o in jobs]
-            logs = [f.result() for f in futs]
-        (OUT_DIR / "ptxas.log").write_text("\n".join(logs))
+            for f in futs:
+                f.result()
+        # registers / spills / shared memory of every kernel, one section per source file
+        (OUT_DIR / "ptxas.log").write_text("\n".join(o.with_suffix(".log").read_text() for o in objs
+                                                      if o.with_suffix(".log").exists()))
     if jobs or not LIB.exists():
         cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"]
         r = subprocess.run(cmd, capture_output=True, text=True)

@@ -85,7 +85,7 @@ class PipelineStage:
                 for i in range(len(self.layers))]
         self.engine = StageEngine(self.layers, gids, device=device, cfg=engine_cfg, ops=ops, shard=groups.shard,
                                   replicate=groups.replicate, rank=rank, streams=streams, zero_level=st.zero_level,
-                                  meta_init=False)
+                                  meta_init=False, shard_ratios=st.shard_ratio)
         self.pattern = pattern
         self.transport = transport
         self.gloo_transport = gloo_transport
