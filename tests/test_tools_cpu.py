@@ -136,3 +136,18 @@ def test_trace_postprocessing(tmp_path):
     assert extract_kernel_runtime(str(f), iterations=2) == pytest.approx(0.09)
     s = stream_busy_and_gaps(str(f))
     assert s[7]["busy_ms"] == pytest.approx(0.15) and s[7]["gap_ms"] == pytest.approx(0.05) and s[9]["kernels"] == 1
+
+
+def test_attn_trace_decode_and_phase_stats():
+    from zorse_b200.profiler.attn_trace import decode, format_summary, phase_stats, summarize
+
+    words = [(100 << 8) | 1, (150 << 8) | 2, (400 << 8) | 3, (900 << 8) | 4, (1300 << 8) | 5, (2000 << 8) | 1,
+             (2040 << 8) | 2, 0, 0]
+    ev = decode(words)
+    assert ev[0] == (100, "s_ready") and ev[-1] == (2040, "s_loaded") and len(ev) == 7
+    st = phase_stats(ev)
+    assert st["s_ready->s_loaded"] == {"n": 2, "mean": 45.0, "max": 50, "min": 40, "total": 90}
+    assert st["p_half1->s_ready"]["total"] == 700
+    summ = summarize([[words, [0, 0, 0]]], 0)
+    assert list(summ) == [0] and summ[0]["span"] == 1940
+    assert "p_half1->s_ready" in format_summary(summ)

@@ -256,22 +256,42 @@ def adam_step(p, m, v, g, p16, *, lr, beta1, beta2, eps, weight_decay, step, gra
 ATTN_FWD_VERSION = int(os.environ.get("ZORSE_ATTN_FWD", "1"))
 
 
+ATTN_FWD4_FLAGS = int(os.environ.get("ZORSE_ATTN_FWD4_FLAGS", "0"))
+
+
 def flash_fwd(qkv, B: int, S: int, Hq: int, Hkv: int, D: int, causal: bool = True, window: int = 0,
-              scale: Optional[float] = None, version: Optional[int] = None):
+              scale: Optional[float] = None, version: Optional[int] = None, flags: Optional[int] = None,
+              trace: Optional[torch.Tensor] = None, trace_ctas: int = 0):
     """qkv: packed [B*S, (Hq+2Hkv)*D]. Returns (out [B*S, Hq*D], lse [B, Hq, S]).
     version 1 (default, the faster one as measured): one query tile per CTA, S double-buffered in
-    TMEM, P staged through shared memory; version 2: two query tiles per CTA, P kept in TMEM."""
+    TMEM, P staged through shared memory; version 2: two query tiles per CTA, P kept in TMEM;
+    version 4: two query tiles, one MMA issuer, score rows in registers (`flags` bit 0: two-wide
+    fp32 math; `trace`: zeroed int64 buffer from `flash_fwd4_trace_buffer` for a phase timeline)."""
     _bf16(qkv, "qkv")
     assert qkv.shape == (B * S, (Hq + 2 * Hkv) * D) and qkv.is_contiguous()
     out = torch.empty(B * S, Hq * D, dtype=qkv.dtype, device=qkv.device)
     lse = torch.empty(B, Hq, S, dtype=torch.float32, device=qkv.device)
     sc = (1.0 / math.sqrt(D)) if scale is None else scale
     ver = version or ATTN_FWD_VERSION
+    if ver == 4:
+        fl = ATTN_FWD4_FLAGS if flags is None else flags
+        _check(lib().zb_flash_fwd4(_p(qkv), _p(out), _p(lse), c_int(B), c_int(S), c_int(Hq), c_int(Hkv), c_int(D),
+                                   c_int(int(causal)), c_int(window), c_float(sc), c_int(out.stride(0)),
+                                   _p(status_word(qkv.device)), c_int(fl), _p(trace),
+                                   c_int(trace_ctas if trace is not None else 0), _stream()), "flash_fwd4")
+        return out, lse
     fn = {1: lib().zb_flash_fwd, 2: lib().zb_flash_fwd2}[ver]
     _check(fn(_p(qkv), _p(out), _p(lse), c_int(B), c_int(S), c_int(Hq), c_int(Hkv), c_int(D),
                               c_int(int(causal)), c_int(window), c_float(sc), c_int(out.stride(0)),
                               _p(status_word(qkv.device)), _stream()), "flash_fwd")
     return out, lse
+
+
+def flash_fwd4_trace_buffer(device, ctas: int) -> torch.Tensor:
+    """Zeroed event buffer [ctas, warps, events] for `flash_fwd(version=4, trace=...)`; an event is
+    (clock64 << 8) | code, 0 = unused slot."""
+    w, e = lib().zb_flash_fwd4_trace_warps(), lib().zb_flash_fwd4_trace_events()
+    return torch.zeros(ctas, w, e, dtype=torch.int64, device=device)
 
 
 _attn_scratch: dict = {}
