@@ -19,19 +19,9 @@
 // (models/llama_simple.py:396-416).
 #include "../common/host.h"
 #include "../common/ptx.cuh"
+#include "attn_bwd_common.h"
 
 namespace zb {
-
-struct AttnBwdParams {
-  const float* lse;
-  const float* delta;
-  float* dq_acc;          // [B*S, Hq*D] fp32, zero on entry
-  __nv_bfloat16* dqkv;    // [B*S, (Hq+2Hkv)*D]
-  int B, S, Hq, Hkv;
-  int window, causal;
-  float scale, scale_log2;
-  int* status;
-};
 
 template <int D>
 struct AttnBwdCfg {
@@ -363,6 +353,27 @@ __global__ void attn_dq_finish_kernel(float* __restrict__ dq_acc, __nv_bfloat16*
   }
 }
 
+int attn_bwd_delta(const __nv_bfloat16* o, const __nv_bfloat16* d_o, float* delta, int B, int S, int Hq, int D,
+                   cudaStream_t stream) {
+  const long warps = long(B) * S * Hq;
+  const int threads = 256;
+  const long blocks = (warps * 32 + threads - 1) / threads;
+  attn_delta_kernel<<<(unsigned)blocks, threads, 0, stream>>>(o, d_o, delta, B, S, Hq, D);
+  ZB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int attn_bwd_finish_dq(float* dq_acc, __nv_bfloat16* dqkv, int B, int S, int Hq, int Hkv, int D, cudaStream_t stream) {
+  const long T = long(B) * S;
+  const int qw = Hq * D, width = (Hq + 2 * Hkv) * D;
+  long blocks = (T * (qw / 8) + 255) / 256;
+  long cap = long(num_sms()) * 16;
+  if (blocks > cap) blocks = cap;
+  attn_dq_finish_kernel<<<(unsigned)blocks, 256, 0, stream>>>(dq_acc, dqkv, T, qw, width);
+  ZB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 static int make_head_tmap_bwd(CUtensorMap* out, const __nv_bfloat16* base, int B, int S, int heads, int D, int width) {
   uint64_t dims[4] = {uint64_t(D), uint64_t(heads), uint64_t(S), uint64_t(B)};
   uint64_t strides[3] = {uint64_t(D) * 2, uint64_t(width) * 2, uint64_t(width) * 2 * uint64_t(S)};
@@ -407,13 +418,7 @@ int zb_flash_bwd(const void* d_o, const void* qkv, const void* o, const float* l
   auto DO = static_cast<const __nv_bfloat16*>(d_o);
   auto O = static_cast<const __nv_bfloat16*>(o);
   auto QKV = static_cast<const __nv_bfloat16*>(qkv);
-  {
-    const long warps = long(B) * S * Hq;
-    const int threads = 256;
-    const long blocks = (warps * 32 + threads - 1) / threads;
-    attn_delta_kernel<<<(unsigned)blocks, threads, 0, stream>>>(O, DO, delta, B, S, Hq, D);
-    ZB_CUDA_OK(cudaGetLastError());
-  }
+  if (int rc = attn_bwd_delta(O, DO, delta, B, S, Hq, D, stream)) return rc;
   AttnBwdParams p;
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
   p.dqkv = static_cast<__nv_bfloat16*>(dqkv);
@@ -424,16 +429,7 @@ int zb_flash_bwd(const void* d_o, const void* qkv, const void* o, const float* l
   p.status = status;
   int rc = (D == 128) ? launch_bwd<128>(QKV, DO, p, stream) : launch_bwd<64>(QKV, DO, p, stream);
   if (rc) return rc;
-  {
-    const long T = long(B) * S;
-    const int qw = Hq * D, width = (Hq + 2 * Hkv) * D;
-    long blocks = (T * (qw / 8) + 255) / 256;
-    long cap = long(num_sms()) * 16;
-    if (blocks > cap) blocks = cap;
-    attn_dq_finish_kernel<<<(unsigned)blocks, 256, 0, stream>>>(dq_acc, p.dqkv, T, qw, width);
-    ZB_CUDA_OK(cudaGetLastError());
-  }
-  return 0;
+  return attn_bwd_finish_dq(dq_acc, p.dqkv, B, S, Hq, Hkv, D, stream);
 }
 
 }  // extern "C"

@@ -287,6 +287,33 @@ def flash_fwd(qkv, B: int, S: int, Hq: int, Hkv: int, D: int, causal: bool = Tru
     return out, lse
 
 
+_attn_scratch2: dict = {}
+
+
+def _flash_bwd2(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale, trace, trace_ctas):
+    key = (qkv.device.index, B, S, Hq, D)
+    if key not in _attn_scratch2:
+        n = lib().zb_flash_bwd2_stats_floats(c_int(B), c_int(S), c_int(Hq))
+        # zeroed once: the kernels never write the padding of the statistics rows
+        _attn_scratch2[key] = (torch.zeros(n, dtype=torch.float32, device=qkv.device),
+                               torch.zeros(B * S * Hq * D, dtype=torch.float32, device=qkv.device))
+    stats, dq_acc = _attn_scratch2[key]
+    dqkv = torch.empty_like(qkv)
+    sc = (1.0 / math.sqrt(D)) if scale is None else scale
+    _check(lib().zb_flash_bwd2(_p(do), _p(qkv), _p(o), _p(lse), _p(dqkv), _p(stats), _p(dq_acc), c_int(B), c_int(S),
+                               c_int(Hq), c_int(Hkv), c_int(D), c_int(int(causal)), c_int(window), c_float(sc),
+                               _p(status_word(qkv.device)), _p(trace), c_int(trace_ctas if trace is not None else 0),
+                               _stream()), "flash_bwd2")
+    global _launches
+    _launches += 2  # statistics + finish kernels
+    return dqkv
+
+
+def flash_bwd2_trace_buffer(device, ctas: int) -> torch.Tensor:
+    w, e = lib().zb_flash_bwd2_trace_warps(), lib().zb_flash_bwd2_trace_events()
+    return torch.zeros(ctas, w, e, dtype=torch.int64, device=device)
+
+
 def flash_fwd4_trace_buffer(device, ctas: int) -> torch.Tensor:
     """Zeroed event buffer [ctas, warps, events] for `flash_fwd(version=4, trace=...)`; an event is
     (clock64 << 8) | code, 0 = unused slot."""
@@ -297,12 +324,21 @@ def flash_fwd4_trace_buffer(device, ctas: int) -> torch.Tensor:
 _attn_scratch: dict = {}
 
 
+ATTN_BWD_VERSION = int(os.environ.get("ZORSE_ATTN_BWD", "1"))
+
+
 def flash_bwd(do, qkv, o, lse, B: int, S: int, Hq: int, Hkv: int, D: int, causal: bool = True, window: int = 0,
-              scale: Optional[float] = None):
+              scale: Optional[float] = None, version: Optional[int] = None, trace: Optional[torch.Tensor] = None,
+              trace_ctas: int = 0):
     """Returns dqkv packed like qkv. Scratch (fp32 dQ accumulator, delta) is cached per shape
-    and device; the accumulator is left zeroed by the kernel that converts it to bf16."""
+    and device; the accumulator is left zeroed by the kernel that converts it to bf16.
+    version 1 (default): scores with queries on the TMEM lanes, P and dS staged through shared
+    memory; version 2: transposed scores, P^T / dS^T consumed from tensor memory, two Q/dO stages
+    (`trace`: zeroed buffer from `flash_bwd2_trace_buffer`)."""
     _bf16(do, "do"); _bf16(qkv, "qkv")
     assert do.is_contiguous() and qkv.is_contiguous() and o.is_contiguous()
+    if (version or ATTN_BWD_VERSION) == 2:
+        return _flash_bwd2(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale, trace, trace_ctas)
     key = (qkv.device.index, B, S, Hq, D)
     if key not in _attn_scratch:
         _attn_scratch[key] = (torch.empty(B * Hq * S, dtype=torch.float32, device=qkv.device),

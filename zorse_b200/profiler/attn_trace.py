@@ -1,7 +1,8 @@
-"""Phase timeline of the attention forward kernel (version 4) from its in-kernel event trace.
+"""Phase timeline of the attention kernels that carry an in-kernel event trace (forward version 4,
+backward version 2).
 
-    python -m zorse_b200.profiler.attn_trace [--S 4096 --heads 32 --kv_heads 32 --D 128] [--ctas 8]
-                                             [--flags 0] [--cta 0] [--out FILE.json]
+    python -m zorse_b200.profiler.attn_trace [--kernel fwd4|bwd2] [--S 4096 --heads 32 --kv_heads 32 --D 128]
+                                             [--ctas 8] [--flags 0] [--cta 0] [--out FILE.json]
 
 The kernel's first `--ctas` CTAs record (clock64, code) pairs per warp at phase boundaries.  For
 one CTA this tool prints, per role, the mean / max number of SM clocks between consecutive
@@ -11,6 +12,7 @@ boundaries, i.e. where a key tile's time goes:
                    -> second P half stored -> (waiting for the next S)
     MMA issuer:    what it waited for (V tile, P halves, K tile) and when it issued
     TMA producer:  slot free -> loads issued
+(backward: S^T ready -> P^T stored -> dP^T ready -> dS^T stored -> dQ ready -> dQ drained.)
 
 Decoding and the summary are plain Python (`decode`, `phase_stats`) and are unit-tested on CPU.
 """
@@ -25,14 +27,20 @@ CODES = {1: "s_ready", 2: "s_loaded", 3: "max_done", 4: "p_half0", 5: "p_half1",
          21: "mma_qk_issued", 32: "tma_slot_free", 33: "tma_issued"}
 
 
-def decode(words) -> list[tuple[int, str]]:
+BWD_CODES = {1: "s_ready", 2: "p_done", 3: "dp_ready", 4: "ds_done", 5: "dq_ready", 6: "dq_drained",
+             16: "mma_qdo_ready", 17: "mma_pds_ready", 18: "mma_def_issued", 19: "mma_a_issued", 20: "mma_dq_empty",
+             21: "mma_b_issued", 32: "tma_stage_free", 33: "tma_issued"}
+
+
+def decode(words, codes=None) -> list[tuple[int, str]]:
     """One warp's event words -> [(clock, name)], unused (zero) slots dropped."""
+    codes = CODES if codes is None else codes
     out = []
     for w in words:
         w = int(w)
         if w == 0:
             continue
-        out.append(((w >> 8) & ((1 << 55) - 1), CODES.get(w & 0xFF, f"code{w & 0xFF}")))
+        out.append(((w >> 8) & ((1 << 55) - 1), codes.get(w & 0xFF, f"code{w & 0xFF}")))
     return out
 
 
@@ -45,11 +53,11 @@ def phase_stats(events: list[tuple[int, str]]) -> dict[str, dict]:
             for k, v in acc.items()}
 
 
-def summarize(trace, cta: int) -> dict:
+def summarize(trace, cta: int, codes=None) -> dict:
     """trace: [ctas, warps, events] integer array-like (host). Returns {warp: {span, phases}}."""
     res = {}
     for w in range(len(trace[cta])):
-        ev = decode(trace[cta][w])
+        ev = decode(trace[cta][w], codes)
         if not ev:
             continue
         res[w] = {"events": len(ev), "span": ev[-1][0] - ev[0][0], "first": ev[0][0], "phases": phase_stats(ev)}
@@ -69,6 +77,7 @@ def format_summary(summary: dict) -> str:
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="fwd4", choices=["fwd4", "bwd2"])
     ap.add_argument("--S", type=int, default=4096)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv_heads", type=int, default=32)
@@ -86,20 +95,31 @@ def main(argv=None):
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(0)
     qkv = (torch.randn(a.S, (a.heads + 2 * a.kv_heads) * a.D, device=dev, generator=g) * 0.5).to(torch.bfloat16)
-    for _ in range(2):
-        k.flash_fwd(qkv, 1, a.S, a.heads, a.kv_heads, a.D, True, a.window, version=4, flags=a.flags)
-    buf = k.flash_fwd4_trace_buffer(dev, a.ctas)
-    k.flash_fwd(qkv, 1, a.S, a.heads, a.kv_heads, a.D, True, a.window, version=4, flags=a.flags, trace=buf,
-                trace_ctas=a.ctas)
+    codes = CODES
+    if a.kernel == "fwd4":
+        for _ in range(2):
+            k.flash_fwd(qkv, 1, a.S, a.heads, a.kv_heads, a.D, True, a.window, version=4, flags=a.flags)
+        buf = k.flash_fwd4_trace_buffer(dev, a.ctas)
+        k.flash_fwd(qkv, 1, a.S, a.heads, a.kv_heads, a.D, True, a.window, version=4, flags=a.flags, trace=buf,
+                    trace_ctas=a.ctas)
+    else:
+        codes = BWD_CODES
+        do = (torch.randn(a.S, a.heads * a.D, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+        out, lse = k.flash_fwd(qkv, 1, a.S, a.heads, a.kv_heads, a.D, True, a.window)
+        for _ in range(2):
+            k.flash_bwd(do, qkv, out, lse, 1, a.S, a.heads, a.kv_heads, a.D, True, a.window, version=2)
+        buf = k.flash_bwd2_trace_buffer(dev, a.ctas)
+        k.flash_bwd(do, qkv, out, lse, 1, a.S, a.heads, a.kv_heads, a.D, True, a.window, version=2, trace=buf,
+                    trace_ctas=a.ctas)
     torch.cuda.synchronize()
     k.check_status()
     host = buf.cpu().tolist()
-    summ = summarize(host, a.cta)
+    summ = summarize(host, a.cta, codes)
     print(format_summary(summ))
     if a.out:
         with open(a.out, "w") as f:
             json.dump({"args": vars(a), "cta": a.cta, "summary": summ,
-                       "events": {w: decode(host[a.cta][w]) for w in range(len(host[a.cta]))}}, f)
+                       "events": {w: decode(host[a.cta][w], codes) for w in range(len(host[a.cta]))}}, f)
 
 
 if __name__ == "__main__":

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import statistics
 from pathlib import Path
 
@@ -99,9 +100,10 @@ def bench_attn(k, peaks, rows):
             pairs = S * (S + 1) // 2
         fl_f = 4.0 * pairs * D * Hq * B
         t_o = time_fn(lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win))
-        for ver in (1, 2):
-            t_v = time_fn(lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win, version=ver))
-            rows.append({"op": f"flash fwd v{ver}", "shape": f"{name} S{S} Hq{Hq} Hkv{Hkv} D{D} win{win}", "ours_ms": t_v,
+        cand = os.environ.get("ZORSE_BENCH_CANDIDATES") == "1"   # kernels not yet validated on hardware
+        for ver, fl in [(1, 0), (2, 0)] + ([(4, 0), (4, 1)] if cand else []):
+            t_v = time_fn(lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win, version=ver, flags=fl))
+            rows.append({"op": f"flash fwd v{ver}" + ("p" if fl else ""), "shape": f"{name} S{S} Hq{Hq} Hkv{Hkv} D{D} win{win}", "ours_ms": t_v,
                          "lib_ms": None, "ours_tflops": fl_f / t_v / 1e9, "frac_of_peak": fl_f / t_v / 1e9 / peaks["bf16_tflops"]})
         t_l = None
         if not win:
@@ -124,6 +126,11 @@ def bench_attn(k, peaks, rows):
                     t_lb = time_fn(lambda: torch.autograd.grad(og, (qg, kg, vg), dog, retain_graph=True))
                 except Exception:
                     t_lb = None
+            if cand:
+                t_b2 = time_fn(lambda: k.flash_bwd(do, qkv, out, lse, B, S, Hq, Hkv, D, True, win, version=2))
+                rows.append({"op": "flash bwd v2", "shape": f"{name} S{S} Hq{Hq} Hkv{Hkv} D{D} win{win}", "ours_ms": t_b2,
+                             "lib_ms": None, "ours_tflops": 2.5 * fl_f / t_b2 / 1e9,
+                             "frac_of_peak": 2.5 * fl_f / t_b2 / 1e9 / peaks["bf16_tflops"]})
             rows.append({"op": "flash bwd", "shape": f"{name} S{S} Hq{Hq} Hkv{Hkv} D{D} win{win}", "ours_ms": t_b,
                          "lib_ms": t_lb, "ours_tflops": 2.5 * fl_f / t_b / 1e9,
                          "lib_tflops": None if t_lb is None else 2.5 * fl_f / t_lb / 1e9,
