@@ -46,3 +46,35 @@ def test_registry_lists_every_reference_family():
     for prefix in ("deepspeedllama_", "deepspeedllamav2_", "deepspeedmistral_", "deepspeedgpt_", "toygpt", "opt_",
                    "deepspeedbert_", "deepspeedvit_"):
         assert any(n.startswith(prefix) for n in names), prefix
+
+
+def test_model_stats_file_matches_registry():
+    """data/model_stats.json is generated from the registry (python -m zorse_b200.models.registry)."""
+    import json
+    from pathlib import Path
+
+    from zorse_b200.models import registry
+
+    path = Path(__file__).resolve().parents[1] / "data" / "model_stats.json"
+    table = json.loads(path.read_text())
+    assert sorted(table) == registry.list_models()
+    for name in ("llama2_7b", "deepspeedgpt_1.3b", "opt_13b", "deepspeedbert_large", "deepspeedvit_g"):
+        assert table[name] == registry.get_model_stats(name)
+    # figure quoted by the reference's own table for a Llama-7B block
+    assert table["deepspeedllama_7b"]["parameters_per_layer"] == 202383360
+
+
+def test_example_files_parse():
+    import json
+    from pathlib import Path
+
+    from zorse_b200.config.training_config import parse_pipeline_config
+    from zorse_b200.profiler.cluster import read_machine_file
+
+    ex = Path(__file__).resolve().parents[1] / "example"
+    cfg = parse_pipeline_config(ex / "training_config.json")
+    assert cfg.model_name == "llama2_7b" and len(cfg.stages) == 4 and cfg.num_microbatches == 64
+    info = json.loads((ex / "cluster_info.json").read_text())
+    assert info["total_gpus"] == 8
+    hosts = read_machine_file(str(ex / "hostfile"))
+    assert len(hosts) == 1 and hosts[0].local

@@ -214,3 +214,22 @@ def get_model_stats(name: str, **overrides) -> dict:
     s = get_spec(name, **overrides)
     return {"hidden_size": s.hidden, "num_layers": s.layers, "parameters_per_layer": params_per_block(s),
             "total_parameters": total_params(s)}
+
+
+def write_model_stats(path: str) -> dict:
+    """Writes the statistics of every registered model as JSON (the layout of the reference's
+    data/model_stats.json: model -> hidden_size, num_layers, parameters_per_layer,
+    total_parameters)."""
+    import json
+
+    table = {name: get_model_stats(name) for name in list_models()}
+    with open(path, "w") as f:
+        json.dump(table, f, indent=2)
+    return table
+
+
+if __name__ == "__main__":
+    import sys
+
+    out = sys.argv[1] if len(sys.argv) > 1 else "data/model_stats.json"
+    print(f"{len(write_model_stats(out))} models -> {out}")
