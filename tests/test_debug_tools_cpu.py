@@ -1,0 +1,120 @@
+"""Debug aids: stream-order checker (vector clocks), deterministic replay, named ranges."""
+import pytest
+import torch
+
+from zorse_b200.utils import ranges
+from zorse_b200.utils.stream_check import StreamOrderChecker, StreamOrderError
+
+
+def test_read_after_event_wait_is_ordered():
+    c = StreamOrderChecker()
+    c.wrote("full", "comm")
+    c.record("ev", "comm")
+    assert not c.read("full", "compute", "before the wait")       # the race
+    c.wait_event("compute", "ev")
+    assert c.read("full", "compute", "after the wait")
+    assert len(c.violations) == 1 and "comm" in str(c.violations[0])
+
+
+def test_event_recorded_before_the_write_does_not_cover_it():
+    c = StreamOrderChecker()
+    c.record("early", "comm")
+    c.wrote("grad", "comm")
+    c.wait_event("compute", "early")
+    assert not c.read("grad", "compute")
+
+
+def test_ordering_is_transitive_and_same_stream_is_free():
+    c = StreamOrderChecker()
+    c.wrote("act", "compute")
+    assert c.read("act", "compute")                 # program order on one stream
+    c.wait_stream("copy", "compute")                # copy stream waits for compute ...
+    c.wrote("host", "copy")
+    c.record("done", "copy")
+    c.wait_event("other", "done")                   # ... a third stream waits for the copy
+    assert c.read("host", "other") and c.read("act", "other")
+
+
+def test_missing_wait_stream_is_the_reference_bug_class():
+    """Activation copied to the host on a side stream that never waited for the compute stream."""
+    c = StreamOrderChecker(strict=True)
+    c.wrote(("stash_src", 1), "compute")
+    with pytest.raises(StreamOrderError, match="without having waited"):
+        c.read(("stash_src", 1), "copy", "D2H copy")
+    c.wait_stream("copy", "compute")
+    assert c.read(("stash_src", 1), "copy")
+
+
+def test_host_synchronize_orders_everything():
+    c = StreamOrderChecker()
+    c.wrote("x", "comm")
+    c._clock("compute")
+    c.synchronize()
+    assert c.read("x", "compute")
+    assert "no violation" in c.report()
+
+
+def test_module_hooks_are_noops_when_inactive():
+    from zorse_b200.utils import stream_check as SC
+
+    assert SC.active() is None
+    SC.wrote("k", "s")          # must not touch torch.cuda on a CPU box
+    SC.read("k", "s")
+
+
+def _tiny_trainer():
+    from zorse_b200.config.training_config import parse_pipeline_dict
+    from zorse_b200.trainer import Trainer, TrainerOptions
+
+    cfg = parse_pipeline_dict({
+        "model_name": "tiny_llama", "global_batch_size": 4, "microbatch_size": 2, "sequence_length": 16,
+        "vocab_size": 128, "autocast_dtype": "float32", "reduce_dtype": "float32",
+        "pipeline_config": [{"gpu_ranks": [0], "num_microbatches_per_rank": [2], "layer_partition": [0, 4],
+                             "zero_config": [[0]]}]})
+    tr = Trainer(cfg, TrainerOptions(schedule="layer_major", ops="ref"))
+    batch = tr.synthetic_batch()
+    inputs, targets, _ = tr.to_device(batch)
+    return tr, inputs, targets
+
+
+def test_replay_is_bit_identical_on_the_oracle_backend():
+    from zorse_b200.utils.replay import replay_check
+
+    tr, inputs, targets = _tiny_trainer()
+    rep = replay_check(tr, inputs, targets)
+    assert rep["identical"] and rep["differing_units"] == [] and rep["loss"][0] == rep["loss"][1]
+    assert tr.step_idx == 1
+
+
+def test_replay_reports_the_unit_that_differs():
+    from zorse_b200.utils.replay import replay_check
+
+    tr, inputs, targets = _tiny_trainer()
+    orig = tr.ops.adam_step
+    calls = {"n": 0}
+
+    def noisy(master, *a, **kw):
+        orig(master, *a, **kw)
+        calls["n"] += 1
+        if calls["n"] == len(tr.stages[0].engine.units) + 2:     # second unit of the second run
+            master.add_(1e-3)
+
+    tr.ops.adam_step = noisy
+    rep = replay_check(tr, inputs, targets, tolerance=1e-6)
+    assert not rep["identical"] and not rep["within_tolerance"]
+    assert len(rep["differing_units"]) == 1 and rep["differing_units"][0]["max_abs_diff"] > 5e-4
+
+
+def test_ranges_name_every_engine_phase():
+    tr, inputs, targets = _tiny_trainer()
+    log: list = []
+    ranges.enable(True)
+    ranges.capture(log)
+    try:
+        tr.train_step(inputs, targets)
+    finally:
+        ranges.capture(None)
+        ranges.enable(False)
+    seen = set(log)
+    assert {"fwd.embedding", "fwd.block", "fwd.head", "bwd.block", "bwd.head", "recompute.block"} <= seen
+    assert ranges.phase("x").__class__.__name__ == "_Null"

@@ -34,6 +34,15 @@ def main(argv=None) -> int:
         activation_recompute=False if args.no_recompute else None,
         activation_offload=True if args.offload_activations_to_host else None, lr=args.lr, seed=args.seed,
         backend=args.backend, pipeline_log=plog)
+    if args.nvtx:
+        from ..utils import ranges
+
+        ranges.enable()
+    checker = None
+    if args.check_streams and torch.cuda.is_available():
+        from ..utils import stream_check
+
+        checker = stream_check.install()
     tr = Trainer(cfg, opt)
     log.info(f"rank {tr.rank}/{tr.world} on {tr.device}; schedule {tr.schedule.name}; ops {tr.ops.name}; "
              f"stages {[s.stage_id for s in tr.stages]}", leader_only=False)
@@ -50,6 +59,13 @@ def main(argv=None) -> int:
     batch = tr.synthetic_batch()
     inputs, targets, _ = tr.to_device(batch)
     cuda = tr.device.type == "cuda"
+    if args.replay_check:
+        from ..utils.replay import replay_check
+
+        rep = replay_check(tr, inputs, targets)
+        log.info(f"replay check: identical={rep['identical']} loss={rep['loss']} "
+                 f"differing units={[(d['gid'], d['kind'], d['max_abs_diff']) for d in rep['differing_units']]}",
+                 leader_only=False)
     total = args.warmup_iterations + args.iterations
     start = end = None
     iter_ms = []
@@ -85,6 +101,11 @@ def main(argv=None) -> int:
         tr.check_kernels()
         if watchdog:
             watchdog.beat(step)
+        if step == args.warmup_iterations - 3:
+            # same point as the reference (zorse.py:170-172): three steps before the timed region
+            mem = metrics.memory_stats(tr.device)
+            log.info("memory: " + ", ".join(f"{k}={v:.2f}" if isinstance(v, float) else f"{k}={v}" for k, v in mem.items()),
+                     leader_only=False)
         iter_ms.append(ms)
         log.info(f"Iteration {step} Time {ms:.2f} ms" + (f" loss {float(loss):.4f}" if loss is not None else ""))
         if prof is not None and step == args.warmup_iterations - 1:
@@ -126,6 +147,8 @@ def main(argv=None) -> int:
                                      flops_per_step=flops, gpu_names=names, dtype=cfg.autocast_dtype,
                                      max_alloc_gb=[float(o[1]) for o in outs], predicted_ms=cfg.latency, loss=gl,
                                      flashflex_ga=args.flashflex_ga))
+    if checker is not None:
+        log.info(checker.report(), leader_only=False)
     if watchdog:
         watchdog.stop()
     if G.is_dist():

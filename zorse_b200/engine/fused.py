@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 from ..models.layers import Layer
+from ..utils.ranges import phase
 from .zero import ZeroUnit
 
 # small chunks: every CTA copies one chunk at a time at 1/148 of the link rate, so a chunk is the
@@ -147,7 +148,7 @@ class FusedZeroUnit(ZeroUnit):
         k = self.ops.k
         cur = torch.cuda.current_stream()
         self.streams.comm.wait_stream(cur)
-        with torch.cuda.stream(self.streams.comm):
+        with phase("zero.rs_adam_fused"), torch.cuda.stream(self.streams.comm):
             k.rs_adam(self.grad_ptrs, self.flag_ptrs, self.R, self.r, self.shard_n, self.master, self.m, self.v,
                       self.p_shard, lr=a.lr, beta1=a.beta1, beta2=a.beta2, eps=a.eps, weight_decay=a.weight_decay,
                       step=self.step_count, grad_scale=gscale, grad_f32=self.cfg.reduce_dtype == torch.float32,

@@ -34,6 +34,8 @@ import torch.distributed as dist
 
 from ..models.layers import ALIGN, Layer
 from ..parallel.groups import Group
+from ..utils import stream_check as SC
+from ..utils.ranges import phase
 
 
 def shard_bounds(n: int, R: int, ratios=None) -> list[int]:
@@ -197,7 +199,7 @@ class ZeroUnit:
         if self.cuda:
             self.p_shard = torch.empty(self.shard_n, dtype=self.cfg.compute_dtype, device=self.device)
             self.streams.copy.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(self.streams.copy):
+            with phase("offload.h2d_shard"), torch.cuda.stream(self.streams.copy):
                 self.p_shard.copy_(self.host_p, non_blocking=True)
             self.p_shard.record_stream(self.streams.copy)
             self.streams.comm.wait_stream(self.streams.copy)
@@ -223,10 +225,12 @@ class ZeroUnit:
         if self.cuda:
             cur = torch.cuda.current_stream()
             self.streams.comm.wait_stream(cur)
-            with torch.cuda.stream(self.streams.comm):
+            with phase("zero.all_gather"), torch.cuda.stream(self.streams.comm):
                 if self.update_event is not None:
                     self.streams.comm.wait_event(self.update_event)
+                SC.read(("shard", id(self)), label="all-gather of the bf16 shard")
                 self._gather_into(full, self.p_shard)
+                SC.wrote(("full", id(self)))
                 ev = torch.cuda.Event()
                 ev.record(self.streams.comm)
             full.record_stream(self.streams.comm)
@@ -260,8 +264,11 @@ class ZeroUnit:
         """Makes the unsharded parameters available to the compute stream and binds the layer."""
         self.prefetch()
         if self.cuda and self.full_event is not None:
-            self.streams.wait_event(self.full_event)
+            with phase("zero.wait_params"):
+                self.streams.wait_event(self.full_event)
             self.full_event = None
+        if self.cuda:
+            SC.read(("full", id(self)), label="layer compute on gathered parameters")
         self.layer.bind(self.full, self.grad)
 
     def release(self, force: bool = False) -> None:
@@ -281,6 +288,8 @@ class ZeroUnit:
     def grad_views(self) -> None:
         if self.grad is None:
             self.grad = torch.zeros(self.n, dtype=self.cfg.reduce_dtype, device=self.device)
+        if self.cuda:
+            SC.wrote(("grad", id(self)))   # backward kernels on the current stream accumulate into it
         self.layer.bind(self.full, self.grad)
 
     def _adam(self, g: torch.Tensor, grad_scale: float):
@@ -331,8 +340,11 @@ class ZeroUnit:
         if self.cuda:
             cur = torch.cuda.current_stream()
             self.streams.comm.wait_stream(cur)
-            with torch.cuda.stream(self.streams.comm):
+            with phase("zero.reduce_scatter"), torch.cuda.stream(self.streams.comm):
+                SC.read(("grad", id(self)), label="reduce-scatter of the gradient bucket")
                 g_sh = work()
+                if self.cfg.optimizer_in_backward:
+                    SC.wrote(("shard", id(self)))
                 ev = torch.cuda.Event()
                 ev.record(self.streams.comm)
             g_full.record_stream(self.streams.comm)
@@ -363,7 +375,9 @@ class ZeroUnit:
             cur = torch.cuda.current_stream()
             if self.update_event is not None:
                 cur.wait_event(self.update_event)
-            self._adam(g, getattr(self, 'grad_shard_scale', 1.0))
+            with phase("zero.adam"):
+                self._adam(g, getattr(self, 'grad_shard_scale', 1.0))
+            SC.wrote(("shard", id(self)))
             ev = torch.cuda.Event()
             ev.record(cur)
             self.update_event = ev

@@ -21,6 +21,8 @@ import datetime
 import torch
 import torch.distributed as dist
 
+from ..utils import stream_check as SC
+
 
 class Handle:
     """Result of an asynchronous transfer. wait() returns the received tensor (None for sends)."""
@@ -57,8 +59,10 @@ class NcclP2P:
 
     def send(self, t: torch.Tensor, dst: int, tag: int, kind: str = "act") -> Handle:
         cur = torch.cuda.current_stream()
+        SC.wrote(("p2p_src", id(t)), cur)
         self.send_stream.wait_stream(cur)
         with torch.cuda.stream(self.send_stream):
+            SC.read(("p2p_src", id(t)), label="NCCL send of a tensor the compute stream produced")
             work = dist.isend(t, dst, group=self._group(kind, self.rank, dst))
         t.record_stream(self.send_stream)
         self.bytes_sent += t.numel() * t.element_size()
@@ -76,10 +80,12 @@ class NcclP2P:
         def wait():
             with torch.cuda.stream(self.recv_stream):
                 work.wait()
+                SC.wrote(("p2p_dst", id(buf)))
             if self.streams is not None:
                 self.streams.wait_stream(self.recv_stream)
             else:
                 torch.cuda.current_stream().wait_stream(self.recv_stream)
+            SC.read(("p2p_dst", id(buf)), label="compute on a received tensor")
             return buf
 
         return Handle(wait)

@@ -15,6 +15,8 @@ from ..config.training_config import PipelineConfig, StageConfig
 from ..engine.zero import EngineConfig, StageEngine, Streams
 from ..models import registry
 from .groups import StageGroups
+from ..utils import stream_check as SC
+from ..utils.ranges import phase
 from .p2p_plan import StageCommPattern
 
 
@@ -38,9 +40,12 @@ class ActivationStash:
         pk = (tuple(t.shape), t.dtype)
         free = self._pool.setdefault(pk, [])
         host = free.pop() if free else torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+        SC.wrote(("stash_src", id(t)))
         self.copy_stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.copy_stream):
+            SC.read(("stash_src", id(t)), label="D2H copy of an activation the compute stream produced")
             host.copy_(t, non_blocking=True)
+            SC.wrote(("stash_host", key))
             ev = torch.cuda.Event()
             ev.record(self.copy_stream)
         t.record_stream(self.copy_stream)
@@ -54,10 +59,13 @@ class ActivationStash:
         host, ev = v
         with torch.cuda.stream(self.copy_stream):
             self.copy_stream.wait_event(ev)
+            SC.read(("stash_host", key), label="H2D copy of a parked activation")
             dev = host.to(self.device, non_blocking=True)
+            SC.wrote(("stash_dev", id(dev)))
             done = torch.cuda.Event()
             done.record(self.copy_stream)
         torch.cuda.current_stream().wait_event(done)
+        SC.read(("stash_dev", id(dev)), label="compute on a restored activation")
         dev.record_stream(torch.cuda.current_stream())
         self.h2d_bytes += host.numel() * host.element_size()
         if pop:
@@ -147,19 +155,23 @@ class PipelineStage:
 
     def recv_fwd(self, mbl: int):
         src, tag = self.pattern.fwd_recv[mbl]
-        return self.boundary_transport(False).recv(self.act_shape(), self.act_dtype, src, tag, "act")
+        with phase("p2p.recv_act"):
+            return self.boundary_transport(False).recv(self.act_shape(), self.act_dtype, src, tag, "act")
 
     def send_fwd(self, mbl: int, y: torch.Tensor):
         dst, tag = self.pattern.fwd_send[mbl]
-        return self.boundary_transport(True).send(y, dst, tag, "act")
+        with phase("p2p.send_act"):
+            return self.boundary_transport(True).send(y, dst, tag, "act")
 
     def recv_bwd(self, mbl: int):
         src, tag = self.pattern.bwd_recv[mbl]
-        return self.boundary_transport(True).recv(self.act_shape(), self.act_dtype, src, tag, "grad")
+        with phase("p2p.recv_grad"):
+            return self.boundary_transport(True).recv(self.act_shape(), self.act_dtype, src, tag, "grad")
 
     def send_bwd(self, mbl: int, dx: torch.Tensor):
         dst, tag = self.pattern.bwd_send[mbl]
-        return self.boundary_transport(False).send(dx, dst, tag, "grad")
+        with phase("p2p.send_grad"):
+            return self.boundary_transport(False).send(dx, dst, tag, "grad")
 
     def add_loss(self, rows: torch.Tensor) -> None:
         v = rows.float().sum() * self.loss_scale
@@ -170,13 +182,14 @@ class PipelineStage:
         """Runs layer li on microbatch mbl. With recompute only the layer input is stashed."""
         layer = self.layers[li]
         c = self.ctx(mbl, targets if layer.kind == "head" else None)
-        if recompute:
-            self.stash.put((li, mbl), x)
-            y = layer.forward(x, c, self.ops, None)
-        else:
-            sv: dict = {}
-            y = layer.forward(x, c, self.ops, sv)
-            self.saved[(li, mbl)] = sv
+        with phase("fwd." + layer.kind):
+            if recompute:
+                self.stash.put((li, mbl), x)
+                y = layer.forward(x, c, self.ops, None)
+            else:
+                sv: dict = {}
+                y = layer.forward(x, c, self.ops, sv)
+                self.saved[(li, mbl)] = sv
         if layer.kind == "head":
             if want_loss:
                 self.add_loss(y)
@@ -189,7 +202,9 @@ class PipelineStage:
         if recompute:
             x = self.stash.get((li, mbl))
             sv: dict = {}
-            layer.forward(x, c, self.ops, sv)
+            with phase("recompute." + layer.kind):
+                layer.forward(x, c, self.ops, sv)
         else:
             sv = self.saved.pop((li, mbl))
-        return layer.backward(dy, c, self.ops, sv)
+        with phase("bwd." + layer.kind):
+            return layer.backward(dy, c, self.ops, sv)
