@@ -108,9 +108,13 @@ def test_gemm_large_vs_fp32(k):
     _close(out, want, atol=0.15, rtol=1e-2)
 
 
-@pytest.mark.parametrize("T,H", [(5, 512), (300, 4096), (64, 2048), (33, 5120)])
+CANDIDATES = os.environ.get("ZORSE_TEST_CANDIDATES") == "1"   # kernel versions not yet validated on hardware
+
+
+@pytest.mark.parametrize("bwd_version", [1] + ([2] if CANDIDATES else []))
+@pytest.mark.parametrize("T,H", [(5, 512), (300, 4096), (64, 2048), (33, 5120), (1000, 4096)])
 @pytest.mark.parametrize("ln", [False, True])
-def test_norm(k, T, H, ln):
+def test_norm(k, T, H, ln, bwd_version):
     x, w, b = _rand(T, H, seed=1), (_rand(H, seed=2) * 0.1 + 1).to(torch.bfloat16), _rand(H, seed=3, scale=0.1)
     dy, dres = _rand(T, H, seed=4), _rand(T, H, seed=5)
     xr = x.float().requires_grad_(True)
@@ -126,7 +130,8 @@ def test_norm(k, T, H, ln):
     for gdt in (torch.float32, torch.bfloat16):
         dw = torch.ones(H, dtype=gdt, device="cuda")
         db = torch.ones(H, dtype=gdt, device="cuda")
-        dx = k.norm_bwd(dy.cuda(), x.cuda(), w.cuda(), stats, dres.cuda(), dw, db if ln else None, ln)
+        dx = k.norm_bwd(dy.cuda(), x.cuda(), w.cuda(), stats, dres.cuda(), dw, db if ln else None, ln,
+                        version=bwd_version)
         _close(dx, xr.grad + dres.float(), atol=5e-2, rtol=2e-2)
         tol = 0.02 * math.sqrt(T) + (0.3 if gdt == torch.bfloat16 else 0)
         _close(dw, wr.grad + 1, atol=tol, rtol=2e-2)
@@ -239,7 +244,7 @@ ATTN_CASES = [
 
 
 # (version, flags); kernel versions that have not yet passed on hardware join the matrix only on request
-FWD_VERSIONS = [(1, 0), (2, 0)] + ([(4, 0), (4, 1)] if os.environ.get("ZORSE_TEST_CANDIDATES") == "1" else [])
+FWD_VERSIONS = [(1, 0), (2, 0)] + ([(4, 0), (4, 1)] if CANDIDATES else [])
 
 
 @pytest.mark.parametrize("version,flags", FWD_VERSIONS)
@@ -266,7 +271,7 @@ def test_flash_fwd(k, B, S, Hq, Hkv, D, causal, window, version, flags):
     _close(lse, want_lse, atol=2e-2, rtol=1e-2)
 
 
-BWD_VERSIONS = [1] + ([2] if os.environ.get("ZORSE_TEST_CANDIDATES") == "1" else [])
+BWD_VERSIONS = [1] + ([2] if CANDIDATES else [])
 
 
 @pytest.mark.parametrize("version", BWD_VERSIONS)

@@ -157,15 +157,20 @@ def norm_fwd(x, w, b, eps: float, layernorm: bool):
     return y, stats
 
 
-def norm_bwd(dy, x, w, stats, dres, dw, db, layernorm: bool, accumulate: bool = True):
-    """Returns dx (+dres). dw/db: gradient slots (fp32 or bf16) accumulated into."""
+NORM_BWD_VERSION = int(os.environ.get("ZORSE_NORM_BWD", "1"))
+
+
+def norm_bwd(dy, x, w, stats, dres, dw, db, layernorm: bool, accumulate: bool = True, version: Optional[int] = None):
+    """Returns dx (+dres). dw/db: gradient slots (fp32 or bf16) accumulated into.
+    version 2: next-row prefetch, one barrier per row, parallel column reduction."""
     T, H = x.shape
     dx = torch.empty_like(x)
     P = lib().zb_norm_partial_rows(c_int(T))
     part_dw = torch.empty(P, H, dtype=torch.float32, device=x.device)
     part_db = torch.empty(P, H, dtype=torch.float32, device=x.device) if (layernorm and db is not None) else None
     gf32 = int(dw.dtype == torch.float32)
-    _check(lib().zb_norm_bwd(_p(dy), _p(x), _p(w), _p(stats), _p(dres), _p(dx), _p(part_dw), _p(part_db),
+    fn = lib().zb_norm_bwd2 if (version or NORM_BWD_VERSION) == 2 else lib().zb_norm_bwd
+    _check(fn(_p(dy), _p(x), _p(w), _p(stats), _p(dres), _p(dx), _p(part_dw), _p(part_db),
                              _p(dw), _p(db), c_int(T), c_int(H), c_int(int(layernorm)), c_int(gf32),
                              c_int(int(accumulate)), _stream()), "norm_bwd")
     return dx
