@@ -11,7 +11,7 @@ def visualize_partition(G, partition_map=None, path="gpu_graph.png") -> bool:
         matplotlib.use("Agg")
         import matplotlib.pyplot as plt
         import networkx as nx
-    except Exception:
+    except ImportError:
         return False
     pos = nx.spring_layout(G, seed=0, weight="weight")
     colors = [partition_map.get(n, 0) for n in G.nodes] if partition_map else "tab:blue"

@@ -30,7 +30,7 @@ class Heartbeat:
     def read(self, rank: int):
         try:
             v = self.store.get(f"hb/{rank}")
-        except Exception:
+        except (KeyError, RuntimeError, TimeoutError):   # key never written / store gone
             return None
         if isinstance(v, bytes):
             v = v.decode()

@@ -42,7 +42,7 @@ def measured_peak_tflops() -> Optional[float]:
     if f.exists():
         try:
             return float(json.loads(f.read_text())["bf16_tflops_sustained"])
-        except Exception:
+        except (OSError, ValueError, KeyError, TypeError):
             return None
     return None
 
