@@ -75,12 +75,14 @@ enum : int {
   TR_TMA_SLOT_FREE = 32, TR_TMA_ISSUED = 33,
 };
 
-template <int D, bool TRACE, bool PACKED>
+template <int D, bool TRACE, int MODE>
 __global__ void __launch_bounds__(32 * FWD4_WARPS, 1)
 flash_fwd4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const AttnFwd4Params p) {
   using Cfg = AttnFwd4Cfg<D>;
   constexpr int BM = 128, BN = 128, NSLOT = Cfg::NSLOT, DB = D / 64, BLK = 128 * 128;
+  constexpr bool PACKED = MODE >= 1;   // two-wide fp32 fma / add, three-input maximum
+  constexpr bool POLY = MODE >= 2;     // every fourth exponential on the fma pipe instead of MUFU
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                               // two tiles
@@ -387,7 +389,9 @@ flash_fwd4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             x0 = fmaf(__uint_as_float(r[k]), scale, neg_mc);
             x1 = fmaf(__uint_as_float(r[k + 1]), scale, neg_mc);
           }
-          const float e0 = exp2f(x0), e1 = exp2f(x1);
+          // with POLY keys 3, 7, 11, ... of the tile take the polynomial, the other three quarters MUFU
+          const float e0 = exp2f(x0);
+          const float e1 = (POLY && (k & 2)) ? exp2_poly3(x1) : exp2f(x1);
           const int a = ((k >> 1) & 3) * 2;
           if (PACKED) {
             fadd2(ls[a], ls[a + 1], ls[a], ls[a + 1], e0, e1);
@@ -472,7 +476,7 @@ static int make_head_tmap4(CUtensorMap* out, const __nv_bfloat16* base, int B, i
   return make_tmap_nd_bf16(out, base, 4, dims, strides, box);
 }
 
-template <int D, bool TRACE, bool PACKED>
+template <int D, bool TRACE, int MODE>
 static int launch_fwd4(const __nv_bfloat16* qkv, int width, const AttnFwd4Params& p, cudaStream_t stream) {
   using Cfg = AttnFwd4Cfg<D>;
   CUtensorMap tq, tk, tv;
@@ -480,7 +484,7 @@ static int launch_fwd4(const __nv_bfloat16* qkv, int width, const AttnFwd4Params
   if ((rc = make_head_tmap4(&tq, qkv, p.B, p.S, p.Hq, D, width))) return rc;
   if ((rc = make_head_tmap4(&tk, qkv + size_t(p.Hq) * D, p.B, p.S, p.Hkv, D, width))) return rc;
   if ((rc = make_head_tmap4(&tv, qkv + size_t(p.Hq + p.Hkv) * D, p.B, p.S, p.Hkv, D, width))) return rc;
-  auto kern = flash_fwd4_kernel<D, TRACE, PACKED>;
+  auto kern = flash_fwd4_kernel<D, TRACE, MODE>;
   static bool attr_set = false;
   if (!attr_set) {
     ZB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
@@ -497,7 +501,8 @@ static int launch_fwd4(const __nv_bfloat16* qkv, int width, const AttnFwd4Params
 extern "C" int zb_flash_fwd4_trace_events() { return zb::FWD4_TRACE_EV; }
 extern "C" int zb_flash_fwd4_trace_warps() { return zb::FWD4_WARPS; }
 
-// flags bit 0: two-wide fp32 fma / add and three-input maximum in the softmax.
+// flags: 0 = scalar softmax math, 1 = two-wide fp32 fma / add and three-input maximum,
+// 2 = as 1 and a quarter of the exponentials as a polynomial on the fma pipe.
 // trace: nullptr, or a zeroed device buffer of trace_ctas * zb_flash_fwd4_trace_warps() * zb_flash_fwd4_trace_events() 64-bit words.
 extern "C" int zb_flash_fwd4(const void* qkv, void* out, float* lse, int B, int S, int Hq, int Hkv, int D,
                              int causal, int window, float softmax_scale, int ldo, int* status, int flags,
@@ -518,14 +523,20 @@ extern "C" int zb_flash_fwd4(const void* qkv, void* out, float* lse, int B, int 
   const int width = (Hq + 2 * Hkv) * D;
   auto Q = static_cast<const __nv_bfloat16*>(qkv);
   const bool tr = trace != nullptr && trace_ctas > 0;
-  const bool pk = (flags & 1) != 0;
-  if (D == 128) {
-    if (tr) return pk ? launch_fwd4<128, true, true>(Q, width, p, stream) : launch_fwd4<128, true, false>(Q, width, p, stream);
-    return pk ? launch_fwd4<128, false, true>(Q, width, p, stream) : launch_fwd4<128, false, false>(Q, width, p, stream);
-  }
-  if (D == 64) {
-    if (tr) return pk ? launch_fwd4<64, true, true>(Q, width, p, stream) : launch_fwd4<64, true, false>(Q, width, p, stream);
-    return pk ? launch_fwd4<64, false, true>(Q, width, p, stream) : launch_fwd4<64, false, false>(Q, width, p, stream);
-  }
+  const int mode = flags < 0 ? 0 : (flags > 2 ? 2 : flags);
+#define ZB_FWD4_DISPATCH(DD)                                                                                  \
+  do {                                                                                                        \
+    if (tr) {                                                                                                 \
+      if (mode == 0) return launch_fwd4<DD, true, 0>(Q, width, p, stream);                                    \
+      if (mode == 1) return launch_fwd4<DD, true, 1>(Q, width, p, stream);                                    \
+      return launch_fwd4<DD, true, 2>(Q, width, p, stream);                                                   \
+    }                                                                                                         \
+    if (mode == 0) return launch_fwd4<DD, false, 0>(Q, width, p, stream);                                     \
+    if (mode == 1) return launch_fwd4<DD, false, 1>(Q, width, p, stream);                                     \
+    return launch_fwd4<DD, false, 2>(Q, width, p, stream);                                                    \
+  } while (0)
+  if (D == 128) ZB_FWD4_DISPATCH(128);
+  if (D == 64) ZB_FWD4_DISPATCH(64);
+#undef ZB_FWD4_DISPATCH
   ZB_FAIL(-1, "attention: head dim %d unsupported (64 or 128)", D);
 }

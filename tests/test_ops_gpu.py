@@ -244,7 +244,7 @@ ATTN_CASES = [
 
 
 # (version, flags); kernel versions that have not yet passed on hardware join the matrix only on request
-FWD_VERSIONS = [(1, 0), (2, 0)] + ([(4, 0), (4, 1)] if CANDIDATES else [])
+FWD_VERSIONS = [(1, 0), (2, 0)] + ([(4, 0), (4, 1), (4, 2)] if CANDIDATES else [])
 
 
 @pytest.mark.parametrize("version,flags", FWD_VERSIONS)

@@ -151,3 +151,29 @@ def test_attn_trace_decode_and_phase_stats():
     summ = summarize([[words, [0, 0, 0]]], 0)
     assert list(summ) == [0] and summ[0]["span"] == 1940
     assert "p_half1->s_ready" in format_summary(summ)
+
+
+def test_exp2_polynomial_matches_exp2_in_fp32_emulation():
+    """The fma-pipe exponential of the attention candidate (csrc/common/ptx.cuh exp2_poly3),
+    re-stated in numpy float32: relative error far below a bf16 ulp, exact zero below 2^-126."""
+    import numpy as np
+
+    c = np.array([0.9999280571937561, 0.6932610273361206, 0.2426111102104187, 0.05517158284783363], np.float32)
+    magic = np.float32(12582912.0)
+
+    def emu(x):
+        x = x.astype(np.float32)
+        xc = np.maximum(x, np.float32(-126.0))
+        t = (xc + magic).astype(np.float32)
+        f = (xc - (t - magic)).astype(np.float32)
+        p = (c[3] * f + c[2]).astype(np.float32)
+        p = (p * f + c[1]).astype(np.float32)
+        p = (p * f + c[0]).astype(np.float32)
+        r = (p.view(np.int32) + (t.view(np.int32) << np.int32(23))).view(np.float32)
+        return np.where(x < -126.0, np.float32(0), r)
+
+    x = np.random.default_rng(0).uniform(-60, 9, 200_000).astype(np.float32)
+    rel = np.abs(emu(x) - np.exp2(x.astype(np.float64))) / np.exp2(x.astype(np.float64))
+    assert rel.max() < 1e-4
+    assert emu(np.array([-np.inf, -1e9, -127.0]))[0] == 0 and emu(np.array([-127.0]))[0] == 0
+    assert abs(emu(np.array([0.0]))[0] - 1.0) < 1e-4 and abs(emu(np.array([8.0]))[0] - 256.0) < 0.03

@@ -270,8 +270,8 @@ def flash_fwd(qkv, B: int, S: int, Hq: int, Hkv: int, D: int, causal: bool = Tru
     """qkv: packed [B*S, (Hq+2Hkv)*D]. Returns (out [B*S, Hq*D], lse [B, Hq, S]).
     version 1 (default, the faster one as measured): one query tile per CTA, S double-buffered in
     TMEM, P staged through shared memory; version 2: two query tiles per CTA, P kept in TMEM;
-    version 4: two query tiles, one MMA issuer, score rows in registers (`flags` bit 0: two-wide
-    fp32 math; `trace`: zeroed int64 buffer from `flash_fwd4_trace_buffer` for a phase timeline)."""
+    version 4: two query tiles, one MMA issuer, score rows in registers (`flags` 1: two-wide
+    fp32 math, 2: also a quarter of the exponentials as a polynomial on the fma pipe; `trace`: zeroed int64 buffer from `flash_fwd4_trace_buffer` for a phase timeline)."""
     _bf16(qkv, "qkv")
     assert qkv.shape == (B * S, (Hq + 2 * Hkv) * D) and qkv.is_contiguous()
     out = torch.empty(B * S, Hq * D, dtype=qkv.dtype, device=qkv.device)

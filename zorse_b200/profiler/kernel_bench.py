@@ -101,9 +101,9 @@ def bench_attn(k, peaks, rows):
         fl_f = 4.0 * pairs * D * Hq * B
         t_o = time_fn(lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win))
         cand = os.environ.get("ZORSE_BENCH_CANDIDATES") == "1"   # kernels not yet validated on hardware
-        for ver, fl in [(1, 0), (2, 0)] + ([(4, 0), (4, 1)] if cand else []):
+        for ver, fl in [(1, 0), (2, 0)] + ([(4, 0), (4, 1), (4, 2)] if cand else []):
             t_v = time_fn(lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win, version=ver, flags=fl))
-            rows.append({"op": f"flash fwd v{ver}" + ("p" if fl else ""), "shape": f"{name} S{S} Hq{Hq} Hkv{Hkv} D{D} win{win}", "ours_ms": t_v,
+            rows.append({"op": f"flash fwd v{ver}" + (f" mode{fl}" if fl else ""), "shape": f"{name} S{S} Hq{Hq} Hkv{Hkv} D{D} win{win}", "ours_ms": t_v,
                          "lib_ms": None, "ours_tflops": fl_f / t_v / 1e9, "frac_of_peak": fl_f / t_v / 1e9 / peaks["bf16_tflops"]})
         t_l = None
         if not win:

@@ -2,7 +2,7 @@
 `ncu` captures (`ncu --set full --clock-control none -k regex:<name> -c 2 python -m
 zorse_b200.profiler.kernel_run <case>`).  Holds well under a few GB on the device.
 
-cases: gemm_fwd | gemm_dgrad | gemm_wgrad | flash_fwd1 | flash_fwd2 | flash_fwd4 | flash_fwd4p | flash_bwd | flash_bwd2 |
+cases: gemm_fwd | gemm_dgrad | gemm_wgrad | flash_fwd1 | flash_fwd2 | flash_fwd4 | flash_fwd4p | flash_fwd4q | flash_bwd | flash_bwd2 |
        rmsnorm | adam | ce
 """
 from __future__ import annotations
@@ -36,6 +36,7 @@ def main(argv=None):
               "flash_fwd2": lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, 0, version=2),
               "flash_fwd4": lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, 0, version=4, flags=0),
               "flash_fwd4p": lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, 0, version=4, flags=1),
+              "flash_fwd4q": lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, 0, version=4, flags=2),
               "flash_bwd": lambda: k.flash_bwd(do, qkv, out, lse, B, S, Hq, Hkv, D, True, 0, version=1),
               "flash_bwd2": lambda: k.flash_bwd(do, qkv, out, lse, B, S, Hq, Hkv, D, True, 0, version=2)}[case]
     elif case == "rmsnorm":
