@@ -141,3 +141,33 @@ def test_interleaved_stages_three_ranks():
     cfg = tiny_cfg(pipe)
     res = run_workers(3, _worker, cfg, {"schedule": "layer_major"}, 2)
     _check(res, cfg)
+
+
+def test_trainer_cli_end_to_end(tmp_path):
+    """`zorse.py` under torchrun on two gloo ranks: flags of the reference plus the debug aids,
+    summary block with the CSV header scripts parse, checkpoint written and resumable."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = tiny_cfg(PIPE_2x1, fused_optimizer=True)
+    cfg_file = tmp_path / "training_config.json"
+    cfg_file.write_text(json.dumps(cfg))
+    ck = tmp_path / "ck"
+    base = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+            "127.0.0.1", "--master-port", "29877", os.path.join(root, "zorse.py"), "--config_file", str(cfg_file),
+            "--backend", "gloo", "--ops", "ref", "--iterations", "2", "--warmup_iterations", "3", "--skip_profile"]
+    env = dict(os.environ, PYTHONPATH=root)
+    r = subprocess.run(base + ["--zero2_pipeline", "--optimizer_in_backwards", "--replay_check", "--nvtx",
+                               "--checkpoint_dir", str(ck), "--checkpoint_every", "5"],
+                       capture_output=True, text=True, timeout=300, env=env, cwd=root)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-3000:]
+    assert "replay check: identical=True" in out
+    assert "Throughput:" in out and "Batch Size,Seq_Len,Min_Allocated,Max_Allocated,Latency,Throughput" in out
+    assert (ck / "step_5" / "meta.json").exists()
+    r2 = subprocess.run(base + ["--resume", str(ck / "step_5")], capture_output=True, text=True, timeout=300,
+                        env=env, cwd=root)
+    assert r2.returncode == 0, (r2.stdout + r2.stderr)[-3000:]

@@ -67,19 +67,13 @@ def main(argv=None) -> int:
                  f"differing units={[(d['gid'], d['kind'], d['max_abs_diff']) for d in rep['differing_units']]}",
                  leader_only=False)
     total = args.warmup_iterations + args.iterations
-    start = end = None
     iter_ms = []
     prof = None
-    t0 = time.perf_counter()
     loss = None
     for step in range(total):
         if step == args.warmup_iterations:
             tr.synchronize()
             tr.barrier()
-            if cuda:
-                start = torch.cuda.Event(enable_timing=True)
-                start.record()
-            t0 = time.perf_counter()
         if (not args.skip_profile and args.trace_dir and prof is None
                 and step == args.warmup_iterations - args.profiling_iterations and args.profiling_iterations > 0):
             from ..utils.trace import profiler_context
@@ -115,13 +109,10 @@ def main(argv=None) -> int:
             from ..ckpt.writer import save_checkpoint
 
             save_checkpoint(tr, args.checkpoint_dir, step + 1)
-    if cuda:
-        end = torch.cuda.Event(enable_timing=True)
-        end.record()
-        torch.cuda.synchronize()
-        avg_ms = start.elapsed_time(end) / max(args.iterations, 1) if start is not None else 0.0
-    else:
-        avg_ms = (time.perf_counter() - t0) * 1e3 / max(args.iterations, 1)
+    # mean of the timed iterations (each one is bracketed by events / a host clock and a device
+    # synchronisation above), so checkpoint writes and logging between steps are not counted
+    timed = iter_ms[args.warmup_iterations:]
+    avg_ms = sum(timed) / len(timed) if timed else 0.0
     tr.barrier()
     # max over ranks, memory and GPU names over the host-side group
     t = torch.tensor([avg_ms, metrics.memory_stats(tr.device)["max_allocated_gb"]], dtype=torch.float64)
