@@ -118,3 +118,26 @@ def test_ranges_name_every_engine_phase():
     seen = set(log)
     assert {"fwd.embedding", "fwd.block", "fwd.head", "bwd.block", "bwd.head", "recompute.block"} <= seen
     assert ranges.phase("x").__class__.__name__ == "_Null"
+
+
+def test_shift_labels_training_matches_autograd():
+    """Next-token targets with an ignored last position: loss and gradients of the explicit
+    backward equal autograd's (ignored rows contribute zero loss and zero gradient)."""
+    from zorse_b200.config.training_config import parse_pipeline_dict
+    from zorse_b200.trainer import Trainer, TrainerOptions
+    from zorse_b200.utils.oracle import OracleTrainer
+
+    d = {"model_name": "tiny_llama", "global_batch_size": 4, "microbatch_size": 2, "sequence_length": 16,
+         "vocab_size": 128, "autocast_dtype": "float32", "reduce_dtype": "float32",
+         "pipeline_config": [{"gpu_ranks": [0], "num_microbatches_per_rank": [2], "layer_partition": [0, 4],
+                              "zero_config": [[0]]}]}
+    cfg = parse_pipeline_dict(d)
+    tr = Trainer(cfg, TrainerOptions(schedule="layer_major", ops="ref", shift_labels=True))
+    batch = tr.synthetic_batch()
+    assert torch.equal(batch["targets"][..., :-1], batch["inputs"][..., 1:]) and (batch["targets"][..., -1] == -100).all()
+    orc = OracleTrainer(cfg)
+    want = [orc.step(batch) for _ in range(2)]
+    got = [tr.train_step_from_host(batch) for _ in range(2)]
+    assert all(abs(a - b) < 2e-4 for a, b in zip(got, want)), (got, want)
+    for u, f in zip(tr.stages[0].engine.units, orc.flats):
+        assert (u.full_master()[: f.numel()] - f.detach()).abs().max() < 5e-4

@@ -207,6 +207,22 @@ def test_cross_entropy(k, T, V):
     _close(d, lr.grad, atol=2e-3, rtol=2e-2)
 
 
+def test_cross_entropy_ignored_rows(k):
+    """Rows whose target is the ignore index (-100) give zero loss and a zero gradient row."""
+    T, V = 64, 1000
+    logits = _rand(T, V, seed=3, scale=2.0)
+    tg = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(3))
+    tg[::4] = -100
+    lr = logits.float().requires_grad_(True)
+    rows = torch.nn.functional.cross_entropy(lr, tg, reduction="none", ignore_index=-100)
+    rows.sum().backward()
+    d = torch.empty_like(logits, device="cuda")
+    got = k.cross_entropy(logits.cuda(), tg.cuda(), 1.0, dlogits=d)
+    _close(got, rows.detach(), atol=2e-3, rtol=1e-3)
+    _close(d, lr.grad, atol=2e-3, rtol=2e-2)
+    assert float(d[::4].float().abs().max()) == 0.0 and float(got[::4].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("gdt", [torch.float32, torch.bfloat16])
 def test_adam(k, gdt):
     n = 100_003

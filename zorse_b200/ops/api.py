@@ -123,7 +123,10 @@ class RefOps:
         if not want_grad:
             return rows, None
         p = torch.softmax(lf, dim=-1)
-        p[torch.arange(lf.shape[0], device=lf.device), targets] -= 1.0
+        keep = targets != -100                      # ignored positions: zero loss, zero gradient
+        idx = torch.arange(lf.shape[0], device=lf.device)
+        p[idx[keep], targets[keep]] -= 1.0
+        p[~keep] = 0.0
         return rows, (p * grad_scale).to(logits.dtype)
 
     def adam_step(self, p, m, v, g, p16, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,

@@ -43,6 +43,7 @@ class TrainerOptions:
     backend: Optional[str] = None          # torch.distributed backend override ("gloo" forces CPU)
     model_overrides: dict = field(default_factory=dict)
     pipeline_log: object = None
+    shift_labels: bool = False             # synthetic targets = next token of the inputs (last position ignored)
 
 
 class Trainer:
@@ -105,6 +106,10 @@ class Trainer:
         else:
             x = torch.randint(0, cfg.vocab_size, (M, B, S), generator=g)
             y = torch.randint(0, cfg.vocab_size, (M, B, S), generator=g)
+            if self.opt.shift_labels:
+                from .utils.data import shift_labels
+
+                y = shift_labels(x)
         if pin and self.device.type == "cuda":
             x, y = x.pin_memory(), y.pin_memory()
         return {"inputs": x, "targets": y}
