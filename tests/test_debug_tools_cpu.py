@@ -141,3 +141,21 @@ def test_shift_labels_training_matches_autograd():
     assert all(abs(a - b) < 2e-4 for a, b in zip(got, want)), (got, want)
     for u, f in zip(tr.stages[0].engine.units, orc.flats):
         assert (u.full_master()[: f.numel()] - f.detach()).abs().max() < 5e-4
+
+
+def test_canary_detects_writes_outside_a_guarded_buffer():
+    from zorse_b200.utils import canary
+
+    canary.reset()
+    alloc = lambda k, dt: torch.zeros(k, dtype=dt)
+    assert canary.guarded(10, torch.float32, alloc, "plain").numel() == 10      # off: plain allocation
+    buf = canary.guarded(100, torch.bfloat16, alloc, "unit 3 gradients", force=True)
+    assert buf.numel() == 100 and buf.data_ptr() % 16 == 0
+    buf.fill_(1.0)                              # writes inside the payload are fine
+    assert canary.check_all() == []
+    raw = buf._base
+    raw[canary.guard_elems(torch.bfloat16) + 100] = 7.0      # first element after the payload
+    assert canary.check_all(raise_on_error=False) == ["unit 3 gradients (band after the buffer)"]
+    with pytest.raises(canary.CanaryError, match="unit 3 gradients"):
+        canary.check_all()
+    canary.reset()

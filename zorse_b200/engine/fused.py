@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 from ..models.layers import Layer
+from ..utils import canary
 from ..utils.ranges import phase
 from .zero import ZeroUnit
 
@@ -66,20 +67,33 @@ class FusedZeroUnit(ZeroUnit):
         pg = self.shard_group.pg
         dev = self.device
         R, r, n, sn = self.R, self.r, self.n, self.shard_n
-        self.full_sym = symm.empty(n, dtype=torch.bfloat16, device=dev)
-        self.grad_sym = symm.empty(n, dtype=self.cfg.reduce_dtype, device=dev)
-        self.flags_sym = symm.empty(64, dtype=torch.int32, device=dev)
+        # debug (ZORSE_DEBUG_CANARY=1): guard bands around the peer-visible buffers; every rank shifts
+        # its payload by the same number of bytes inside the symmetric allocation
+        guard = canary.enabled()
+        gd = lambda dt: canary.guard_elems(dt) if guard else 0
+        raw_full = symm.empty(n + 2 * gd(torch.bfloat16), dtype=torch.bfloat16, device=dev)
+        raw_grad = symm.empty(n + 2 * gd(self.cfg.reduce_dtype), dtype=self.cfg.reduce_dtype, device=dev)
+        raw_flag = symm.empty(64 + 2 * gd(torch.int32), dtype=torch.int32, device=dev)
+        if guard:
+            self.full_sym = canary.register(f"unit {gid} parameters (rank {self.rank})", raw_full, n)
+            self.grad_sym = canary.register(f"unit {gid} gradients (rank {self.rank})", raw_grad, n)
+            self.flags_sym = canary.register(f"unit {gid} flags (rank {self.rank})", raw_flag, 64)
+        else:
+            self.full_sym, self.grad_sym, self.flags_sym = raw_full, raw_grad, raw_flag
+        off_full = gd(torch.bfloat16) * 2
+        off_grad = gd(self.cfg.reduce_dtype) * raw_grad.element_size()
+        off_flag = gd(torch.int32) * 4
         self.full_sym.zero_()
         self.grad_sym.zero_()
         self.flags_sym.zero_()
         self.full_sym[r * sn:(r + 1) * sn].copy_(self.p_shard)
         torch.cuda.synchronize()
-        h_full = symm.rendezvous(self.full_sym, pg)
-        h_grad = symm.rendezvous(self.grad_sym, pg)
-        h_flag = symm.rendezvous(self.flags_sym, pg)
-        self.shard_ptrs = [int(h_full.buffer_ptrs[q]) + q * sn * 2 for q in range(R)]
-        self.grad_ptrs = [int(h_grad.buffer_ptrs[q]) for q in range(R)]
-        self.flag_ptrs = [int(h_flag.buffer_ptrs[q]) for q in range(R)]
+        h_full = symm.rendezvous(raw_full, pg)
+        h_grad = symm.rendezvous(raw_grad, pg)
+        h_flag = symm.rendezvous(raw_flag, pg)
+        self.shard_ptrs = [int(h_full.buffer_ptrs[q]) + off_full + q * sn * 2 for q in range(R)]
+        self.grad_ptrs = [int(h_grad.buffer_ptrs[q]) + off_grad for q in range(R)]
+        self.flag_ptrs = [int(h_flag.buffer_ptrs[q]) + off_flag for q in range(R)]
         self._handles = (h_full, h_grad, h_flag)
         self.p_shard = self.full_sym[r * sn:(r + 1) * sn]
         self.full = self.full_sym

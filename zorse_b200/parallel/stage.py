@@ -15,6 +15,7 @@ from ..config.training_config import PipelineConfig, StageConfig
 from ..engine.zero import EngineConfig, StageEngine, Streams
 from ..models import registry
 from .groups import StageGroups
+from ..utils import canary
 from ..utils import stream_check as SC
 from ..utils.ranges import phase
 from .p2p_plan import StageCommPattern
@@ -39,7 +40,9 @@ class ActivationStash:
             return
         pk = (tuple(t.shape), t.dtype)
         free = self._pool.setdefault(pk, [])
-        host = free.pop() if free else torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+        host = free.pop() if free else canary.guarded(
+            t.numel(), t.dtype, lambda k, dt: torch.empty(k, dtype=dt, device="cpu", pin_memory=True),
+            f"pinned activation buffer {tuple(t.shape)}").view(t.shape)
         SC.wrote(("stash_src", id(t)))
         self.copy_stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.copy_stream):

@@ -26,6 +26,7 @@ from .parallel.p2p import GlooP2P, make_transport
 from .parallel.p2p_plan import create_static_comm_plans
 from .parallel.schedules import build_schedule
 from .parallel.stage import PipelineStage
+from .utils import canary
 
 
 @dataclass
@@ -140,6 +141,9 @@ class Trainer:
         the mean loss as a device scalar (None on ranks without the last stage)."""
         loss = self.schedule.step(self.step_idx, inputs, targets)
         self.step_idx += 1
+        if canary.enabled():
+            self.synchronize()
+            canary.check_all()     # raises if a guard band next to a raw-pointer buffer changed
         return loss
 
     def train_step_from_host(self, batch: dict) -> Optional[float]:
