@@ -183,9 +183,19 @@ def main():
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     loss = None
+    done = []
     for _ in range(args.steps):
         loss = tr.train_step(inputs, targets)
+        ev = torch.cuda.Event()
+        ev.record()
+        done.append(ev)
     b.record()
+    # host-side progress beats while the queued steps drain (event queries only; the timed
+    # region on the device is untouched), so a long --steps run is not mistaken for a stall
+    for ev in done:
+        while not ev.query():
+            time.sleep(0.05)
+        beat()
     tr.synchronize(); tr.barrier()
     beat()
     launches = sm100.launch_count() - l0
