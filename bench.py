@@ -178,7 +178,8 @@ def main():
     tr.check_kernels()
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
     tr.synchronize(); tr.barrier()
-    sampler.start()
+    if tr.rank == 0:
+        sampler.start()   # one sampler (rank 0's GPU) is enough; eight would fork 40 nvidia-smi per second
     l0 = sm100.launch_count()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
@@ -236,7 +237,8 @@ def main():
                "d2h_bytes_per_step": int(bts[1].item())}
     dog.stop()
     sampler.stop_flag.set()
-    sampler.join(timeout=2)
+    if tr.rank == 0:
+        sampler.join(timeout=2)
     mem = torch.cuda.max_memory_allocated() / 2**30
 
     if rank == 0:
