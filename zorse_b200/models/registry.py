@@ -4,7 +4,8 @@ Covers the families of the reference registry (models/hub.py:25-84, 535-671): Ll
 both of its styles (`deepspeedllama_*`, `deepspeedllamav2_*`), Mistral, GPT
 (`deepspeedgpt_*`, `toygpt*`), OPT, BERT and ViT, under the same names, plus the models
 the benchmark configurations name (`llama3.2_1b`, `llama2_7b`, `mistral_7b`, `opt_13b`,
-`tiny_llama`).  Unlike the reference every family here can be split into pipeline stages:
+`tiny_llama`) and the names of the reference's HF whole-model wrappers (`llama_*`, `gpt_*`,
+`bert_*`, `vit_*`, `opt_*`, `mistral_*`; models/llama.py, gpt.py, bert.py, vit.py, opt.py, mistral.py).  Unlike the reference every family here can be split into pipeline stages:
 `build_stage_layers` returns `[embedding?] + blocks[start:end] + [head?]`.
 """
 from __future__ import annotations
@@ -125,6 +126,32 @@ for _n, (_L, _H, _h, _F) in {"default": (12, 768, 12, 3072), "1b": (24, 1824, 32
                               "h": (32, 1280, 16, 5120), "g_small": (6, 1664, 16, 8192), "g": (48, 1664, 16, 8192),
                               "e_small": (6, 1792, 16, 15360), "e": (56, 1792, 16, 15360)}.items():
     _reg(_vit(f"deepspeedvit_{_n}", _L, _H, _h, _F))
+
+
+# ---- names of the reference's whole-model wrappers (models/llama.py, gpt.py, bert.py, vit.py,
+# mistral.py): HF-config models at named sizes that the reference can only profile or run on a
+# single stage.  Same dimensions here, and like every other entry they can be pipelined.
+for _n, (_L, _H, _h) in {"1b": (24, 1536, 32), "2b": (24, 2176, 32), "3b": (24, 2688, 32), "4b": (24, 3136, 32),
+                          "5b": (24, 3520, 32), "6.7b": (32, 4096, 32), "13b": (40, 5120, 40), "33b": (60, 6656, 52),
+                          "65b": (80, 8192, 64)}.items():
+    _reg(_llama(f"llama_{_n}", _L, _H, _h, 4 * _H, vocab=49152))      # FFN = 4 x hidden (models/llama.py:49-50)
+for _n, (_L, _H, _h) in {"85m": (12, 768, 12), "300m": (24, 1024, 16), "1b": (24, 1824, 32), "1b_1l": (1, 1824, 32),
+                          "1.3b": (24, 2048, 128), "2b": (24, 2560, 32), "2.7b": (32, 2560, 80), "3b": (24, 3328, 32),
+                          "4b": (24, 3648, 32), "5b": (24, 4096, 32), "6b": (32, 4096, 32), "6.7b": (32, 4096, 128),
+                          "10b": (36, 4680, 36), "20b": (44, 6144, 48), "25b": (46, 6656, 52), "30b": (48, 7168, 56),
+                          "35b": (53, 7424, 58), "40b": (54, 7808, 61), "45b": (56, 8192, 64), "50b": (58, 8448, 66),
+                          "55b": (61, 8704, 68), "60b": (62, 8960, 70), "65b": (64, 9216, 72)}.items():
+    # OpenAI-GPT style (post-LN); `gpt_13b` of the reference (5140 / 128 heads) is not a valid shape and is left out
+    _reg(_gpt(f"gpt_{_n}", _L, _H, _h, pre_norm=False, vocab=49152))
+for _n, (_L, _H, _h, _F) in {"110m": (12, 768, 12, 0), "330m": (24, 1024, 16, 0), "1b": (24, 1824, 32, 0),
+                              "2b": (24, 2560, 32, 0), "3b": (24, 3172, 32, 0), "4b": (24, 3648, 32, 0),
+                              "5b": (24, 4096, 32, 0), "large": (24, 1024, 16, 4096), "xlarge": (36, 1536, 24, 6144)}.items():
+    _reg(replace(_bert(f"bert_{_n}", _L, _H, _h), ffn=_F or 4 * _H, vocab=49152))
+for _n, (_L, _H, _h, _F) in {"default": (12, 768, 12, 0), "1b": (24, 1824, 32, 0), "2b": (24, 2560, 32, 0),
+                              "3b": (24, 3172, 32, 0), "4b": (24, 3648, 32, 0), "5b": (24, 4096, 32, 0),
+                              "g": (48, 1664, 16, 8192), "e": (56, 1792, 16, 15360)}.items():
+    _reg(replace(_vit(f"vit_{_n}", _L, _H, _h, _F or 4 * _H), image=224, classes=2))   # HF ViTConfig defaults
+_reg(replace(_llama("mistral_toy", 5, 4096, 32, 14336, kv_heads=8, window=4096, vocab=49152), family="mistral"))
 
 
 def list_models() -> list[str]:
