@@ -177,3 +177,13 @@ def test_exp2_polynomial_matches_exp2_in_fp32_emulation():
     assert rel.max() < 1e-4
     assert emu(np.array([-np.inf, -1e9, -127.0]))[0] == 0 and emu(np.array([-127.0]))[0] == 0
     assert abs(emu(np.array([0.0]))[0] - 1.0) < 1e-4 and abs(emu(np.array([8.0]))[0] - 256.0) < 0.03
+
+
+def test_latency_probe_derivations():
+    from zorse_b200.profiler.sm100_latency import NAMES, derive
+
+    med = {n: 0 for n in NAMES.values()}
+    med.update({"mma_8": 900, "mma_32": 900 + 24 * 64, "ex2_1024_1warp_per_sched": 8192 + 1024})
+    d = derive(med)
+    assert d["clocks_per_mma_128x128x16"] == 64.0 and d["mma_fixed_latency"] == 900 - 8 * 64
+    assert d["ex2_clocks_per_op_1warp_per_sched"] == 9.0
