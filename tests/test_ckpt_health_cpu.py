@@ -120,3 +120,25 @@ def _rank_that_dies(rank, world):
 def test_peer_failure_ends_collective_with_error():
     with pytest.raises(RuntimeError, match="injected host-side fault|rank 0 failed|exited"):
         run_workers(2, _rank_that_dies, timeout=90)
+
+
+def test_cli_watchdog_names_the_rank_that_stopped(tmp_path):
+    """Two gloo ranks under torchrun; rank 1 stops joining before step 2 (host-side fault
+    injection). Rank 0's next receive never completes, its watchdog fires, reads the heartbeat
+    store and names rank 1 before aborting."""
+    import json
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg_file = tmp_path / "cfg.json"
+    cfg_file.write_text(json.dumps(tiny_cfg(PIPE_2x1, fused_optimizer=True)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29911", os.path.join(root, "zorse.py"), "--config_file", str(cfg_file),
+           "--backend", "gloo", "--ops", "ref", "--iterations", "3", "--warmup_iterations", "3", "--skip_profile",
+           "--heartbeat_timeout", "6", "--inject_fault", "1:2:stall"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=dict(os.environ, PYTHONPATH=root), cwd=root)
+    out = r.stdout + r.stderr
+    assert r.returncode != 0
+    assert "[watchdog] rank 0: no progress" in out, out[-3000:]
+    assert "ranks behind or silent: [1]" in out, out[-3000:]

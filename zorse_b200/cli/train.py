@@ -50,11 +50,29 @@ def main(argv=None) -> int:
         from ..ckpt.reader import load_checkpoint
 
         load_checkpoint(tr, args.resume)
-    watchdog = None
-    if args.heartbeat_timeout > 0:
-        from ..utils.health import Watchdog
+    from ..utils.health import maybe_inject, parse_fault
 
-        watchdog = Watchdog(args.heartbeat_timeout, rank=tr.rank)
+    fault = parse_fault(args.inject_fault)
+    watchdog = heartbeat = None
+    if args.heartbeat_timeout > 0:
+        import faulthandler
+
+        from ..utils.health import Watchdog, tcp_heartbeat
+
+        heartbeat = tcp_heartbeat(tr.rank, tr.world)
+
+        def stuck(step, idle):
+            # name the ranks whose heartbeat is older than ours before giving up
+            msg = f"[watchdog] rank {tr.rank}: no progress for {idle:.1f}s after step {step}"
+            if heartbeat is not None:
+                behind = [r for r in heartbeat.stale_ranks(args.heartbeat_timeout, min_step=step) if r != tr.rank]
+                msg += f"; ranks behind or silent: {behind}"
+            sys.stderr.write(msg + "; dumping stacks and aborting\n")
+            faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
+            sys.stderr.flush()
+            os._exit(3)
+
+        watchdog = Watchdog(args.heartbeat_timeout, rank=tr.rank, on_timeout=stuck)
         watchdog.start()
     batch = tr.synthetic_batch()
     inputs, targets, _ = tr.to_device(batch)
@@ -71,6 +89,7 @@ def main(argv=None) -> int:
     prof = None
     loss = None
     for step in range(total):
+        maybe_inject(fault, tr.rank, step, keepalive=watchdog.beat if watchdog else None)
         if step == args.warmup_iterations:
             tr.synchronize()
             tr.barrier()
@@ -95,6 +114,8 @@ def main(argv=None) -> int:
         tr.check_kernels()
         if watchdog:
             watchdog.beat(step)
+        if heartbeat is not None:
+            heartbeat.beat(step)
         if step == args.warmup_iterations - 3:
             # same point as the reference (zorse.py:170-172): three steps before the timed region
             mem = metrics.memory_stats(tr.device)

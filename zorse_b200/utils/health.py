@@ -29,6 +29,9 @@ class Heartbeat:
 
     def read(self, rank: int):
         try:
+            check = getattr(self.store, "check", None)     # TCPStore.get blocks on a missing key
+            if check is not None and not check([f"hb/{rank}"]):
+                return None
             v = self.store.get(f"hb/{rank}")
         except (KeyError, RuntimeError, TimeoutError):   # key never written / store gone
             return None
@@ -94,3 +97,46 @@ class Watchdog(threading.Thread):
         faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
         sys.stderr.flush()
         os._exit(3)
+
+
+def tcp_heartbeat(rank: int, world: int, port_offset: int = 23, timeout_s: float = 60.0) -> Optional[Heartbeat]:
+    """Heartbeat over a TCPStore next to the rendezvous port (rank 0 hosts it). None for one rank."""
+    if world <= 1:
+        return None
+    import datetime
+
+    from torch.distributed import TCPStore
+
+    host = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    port = int(os.environ.get("MASTER_PORT", "29500")) + port_offset
+    store = TCPStore(host, port, world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=timeout_s),
+                     wait_for_workers=False)
+    return Heartbeat(store, rank, world)
+
+
+def parse_fault(spec: Optional[str]):
+    """`rank:step:kind` with kind in stall | raise | exit -> (rank, step, kind); host-side fault
+    injection for failure-detection tests (nothing on the device is made to fault)."""
+    if not spec:
+        return None
+    r, s, kind = spec.split(":")
+    if kind not in ("stall", "raise", "exit"):
+        raise ValueError(f"unknown fault kind {kind!r}")
+    return int(r), int(s), kind
+
+
+def maybe_inject(fault, rank: int, step: int, keepalive: Optional[Callable[[int], None]] = None) -> None:
+    """Called between steps, with none of this rank's kernels or collectives in flight.
+    `keepalive` (the local watchdog's beat) is called while a stalled rank sleeps, so that the
+    stalled rank itself stays silent towards its peers without aborting on its own."""
+    if fault is None or fault[0] != rank or fault[1] != step:
+        return
+    kind = fault[2]
+    if kind == "raise":
+        raise RuntimeError(f"injected failure on rank {rank} before step {step}")
+    if kind == "exit":
+        os._exit(17)
+    while True:          # stall: this rank never joins the next step
+        time.sleep(1.0)
+        if keepalive is not None:
+            keepalive(step - 1)
