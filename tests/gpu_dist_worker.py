@@ -11,7 +11,9 @@ from zorse_b200.trainer import Trainer, TrainerOptions
 def cfg_for(case, world):
     if case.startswith("dp2"):
         pipe = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [3, 1], "layer_partition": [0, 4], "zero_config": [[0, 1]]}]
-    elif case == "pp2":
+        if case == "dp2_uneven_library":
+            pipe[0]["shard_ratio"] = [0.7, 0.3]
+    elif case.startswith("pp2_") or case == "pp2":
         pipe = [{"gpu_ranks": [0], "num_microbatches_per_rank": [4], "layer_partition": [0, 2], "zero_config": [[0]]},
                 {"gpu_ranks": [1], "num_microbatches_per_rank": [4], "layer_partition": [2, 4], "zero_config": [[1]]}]
     else:
@@ -25,9 +27,9 @@ def cfg_for(case, world):
 def train_case(case):
     fused = case.endswith("fused")
     cfg = cfg_for(case, int(dist.get_world_size()) if dist.is_initialized() else 1)
-    sched = "zero2" if "pp" in case else "layer_major"
+    sched = "1f1b" if "1f1b" in case else ("zero2" if "pp" in case else "layer_major")
     tr = Trainer(cfg, TrainerOptions(schedule=sched, ops="sm100", collectives="fused" if fused else "library",
-                                     optimizer_in_backward=True, lr=1e-3))
+                                     optimizer_in_backward=sched != "1f1b", lr=1e-3))
     batch = tr.synthetic_batch()
     losses = []
     for _ in range(3):
@@ -120,8 +122,9 @@ def main():
     else:
         losses, masters, tr = train_case(case)
         # same job with the other collectives mode must land on the same parameters
-        if case.endswith("fused"):
-            l2, m2, _ = train_case(case.replace("fused", "library"))
+        other = {"dp2_uneven_library": "dp2_library", "pp2_1f1b": "pp2", "pp2dp2_1f1b_library": "pp2dp2_library"}.get(case)
+        if case.endswith("fused") or other:
+            l2, m2, _ = train_case(other or case.replace("fused", "library"))
             for a, b in zip(losses, l2):
                 assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (losses, l2)
             for gid in masters:

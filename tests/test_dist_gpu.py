@@ -33,6 +33,22 @@ def test_two_gpus(case):
     assert "WORKER_OK" in out
 
 
+CANDIDATES = os.environ.get("ZORSE_TEST_CANDIDATES") == "1"   # paths that have not yet run on hardware
+
+
+@pytest.mark.skipif(_ngpu() < 2 or not CANDIDATES, reason="needs 2 GPUs and ZORSE_TEST_CANDIDATES=1")
+@pytest.mark.parametrize("case", ["dp2_uneven_library", "pp2_1f1b"])
+def test_two_gpus_candidates(case):
+    out = _run(2, case, timeout=300)
+    assert "WORKER_OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 4 or not CANDIDATES, reason="needs 4 GPUs and ZORSE_TEST_CANDIDATES=1")
+def test_four_gpus_1f1b():
+    out = _run(4, "pp2dp2_1f1b_library", timeout=300)
+    assert "WORKER_OK" in out
+
+
 @pytest.mark.skipif(_ngpu() < 4, reason="needs 4 GPUs")
 @pytest.mark.parametrize("case", ["pp2dp2_library", "pp2dp2_fused"])
 def test_four_gpus(case):
