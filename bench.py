@@ -44,11 +44,27 @@ def parallel_plan(n: int, layers: int):
     raise SystemExit(f"bench.py supports 1, 2, 4 or 8 GPUs, got {n}")
 
 
-def build_config(n, model, gbs, mbs, seq, vocab, reduce_dtype, schedule, layers_override=None):
+def interleave_plan(stages, layers: int, v: int):
+    """Splits the layer range into v chunks per rank group: stage k = chunk k of the model on the
+    rank group k mod P (for the interleaved 1F1B schedule)."""
+    P = len(stages)
+    per, rem = divmod(layers, P * v)
+    out, a = [], 0
+    for k in range(P * v):
+        b = a + per + (1 if k < rem else 0)
+        out.append((stages[k % P][0], a, b))
+        a = b
+    return out
+
+
+def build_config(n, model, gbs, mbs, seq, vocab, reduce_dtype, schedule, layers_override=None, interleave=1):
     from zorse_b200.models import registry
 
     spec = registry.get_spec(model, layers=layers_override)
     stages, par = parallel_plan(n, spec.layers)
+    if interleave > 1 and len(stages) > 1:
+        stages = interleave_plan(stages, spec.layers, interleave)
+        par += f"-v{interleave}"
     M = gbs // mbs
     pipe = []
     for ranks, a, b in stages:
@@ -118,6 +134,8 @@ def main():
     ap.add_argument("--optimizer_in_backward", action="store_true")
     ap.add_argument("--recompute", default="auto", choices=["auto", "on", "off"])
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the JSON line says so)")
+    ap.add_argument("--interleave", type=int, default=1,
+                    help="model chunks per rank group (>1 selects the interleaved 1F1B schedule on 4 and 8 GPUs)")
     ap.add_argument("--skip_e2e", action="store_true")
     ap.add_argument("--stall_timeout", type=float, default=420.0,
                     help="abort (non-zero exit) if no training step completes on the host for this many seconds")
@@ -138,9 +156,9 @@ def main():
         args.warmup = 3
     schedule = args.schedule
     if schedule == "auto":
-        schedule = "1f1b"
+        schedule = "1f1b_interleaved" if (args.interleave > 1 and args.gpus >= 4) else "1f1b"
     cfg_dict, par = build_config(args.gpus, args.model, args.global_batch, args.microbatch, args.seq_len, args.vocab,
-                                 args.reduce_dtype, schedule, args.layers)
+                                 args.reduce_dtype, schedule, args.layers, args.interleave)
     cfg = parse_pipeline_dict(cfg_dict)
     recompute = None if args.recompute == "auto" else (args.recompute == "on")
     tr = Trainer(cfg, TrainerOptions(schedule=schedule, ops="sm100", optimizer_in_backward=args.optimizer_in_backward,

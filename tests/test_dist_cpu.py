@@ -171,3 +171,28 @@ def test_trainer_cli_end_to_end(tmp_path):
     r2 = subprocess.run(base + ["--resume", str(ck / "step_5")], capture_output=True, text=True, timeout=300,
                         env=env, cwd=root)
     assert r2.returncode == 0, (r2.stdout + r2.stderr)[-3000:]
+
+
+def _interleaved_pipe(P, v, width, M):
+    pipe = []
+    for k in range(P * v):
+        ranks = list(range((k % P) * width, (k % P + 1) * width))
+        pipe.append({"gpu_ranks": ranks, "num_microbatches_per_rank": [M // width] * width,
+                     "layer_partition": [k, k + 1], "zero_config": [ranks]})
+    return pipe
+
+
+@pytest.mark.parametrize("P,v,width,M", [(2, 2, 1, 4), (2, 2, 2, 8)])
+def test_interleaved_1f1b(P, v, width, M):
+    """Two model chunks per rank (stages g and g + P): same training as the oracle."""
+    cfg = tiny_cfg(_interleaved_pipe(P, v, width, M), gbs=M, mbs=1)
+    res = run_workers(P * width, _worker, cfg, {"schedule": "1f1b_interleaved"}, 2)
+    _check(res, cfg)
+
+
+def test_interleaved_1f1b_rejects_bad_plans():
+    from zorse_b200.parallel.p2p_sim import record_programs
+
+    cfg = parse_pipeline_dict(tiny_cfg(_interleaved_pipe(2, 2, 1, 3), gbs=3, mbs=1))   # 3 microbatches, 2 groups
+    with pytest.raises(ValueError, match="multiple of 2 rank groups"):
+        record_programs(cfg, "1f1b_interleaved")

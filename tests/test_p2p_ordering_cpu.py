@@ -107,3 +107,20 @@ def test_alternate_nccl_gloo_and_batched_gloo_receives():
     assert fwd[:3] == ["post_recv", "post_recv", "wait_recv"]
     cfg.alternate_nccl_gloo = False
     assert st.uses_gloo(True)
+
+
+@pytest.mark.parametrize("P,v,width,M", [(2, 2, 1, 4), (4, 2, 1, 8), (4, 2, 2, 16), (4, 4, 1, 8), (3, 2, 1, 6), (8, 2, 1, 16)])
+def test_interleaved_1f1b_ordering_is_deadlock_free(P, v, width, M):
+    """v chunks per rank group, including the wrap-around transfers from the last group back to
+    the first, under the same serialised-group semantics."""
+    pipe = []
+    for k in range(P * v):
+        ranks = list(range((k % P) * width, (k % P + 1) * width))
+        pipe.append({"gpu_ranks": ranks, "num_microbatches_per_rank": [M // width] * width,
+                     "layer_partition": [k, k + 1], "zero_config": [[q] for q in ranks]})
+    cfg = parse_pipeline_dict({"model_name": "tiny_llama", "global_batch_size": M, "microbatch_size": 1,
+                               "sequence_length": 8, "vocab_size": 64, "autocast_dtype": "float32",
+                               "reduce_dtype": "float32", "pipeline_config": pipe})
+    progs = record_programs(cfg, "1f1b_interleaved", model_overrides={**OV, "layers": P * v})
+    assert simulate(progs) is None
+    assert simulate(progs, serialize_within_group=False) is None

@@ -2,6 +2,7 @@
 (precedence flashflex > zero2 > two-stage-sync > sync-comm > default, reference zorse.py:245-262)."""
 from .base import ScheduleBase
 from .flashflex import FlashflexSchedule
+from .interleaved import InterleavedOneFOneBSchedule
 from .layer_major import LayerMajorSchedule
 from .no_overlap import NoOverlapSchedule
 from .one_f_one_b import OneFOneBSchedule
@@ -15,6 +16,7 @@ SCHEDULES = {
     "zero2": Zero2Schedule, "zero2_pipeline": Zero2Schedule,
     "flashflex": FlashflexSchedule, "flashflex_pipeline": FlashflexSchedule,
     "1f1b": OneFOneBSchedule, "one_f_one_b": OneFOneBSchedule,
+    "1f1b_interleaved": InterleavedOneFOneBSchedule, "interleaved_1f1b": InterleavedOneFOneBSchedule,
 }
 
 
