@@ -41,4 +41,7 @@ def schedule_name_from_flags(args) -> str:
 def build_schedule(name: str, stages, cfg, **kw) -> ScheduleBase:
     if name not in SCHEDULES:
         raise ValueError(f"unknown schedule {name!r}; known: {sorted(set(SCHEDULES))}")
-    return SCHEDULES[name](stages, cfg, **kw)
+    cls = SCHEDULES[name]
+    if cls is OneFOneBSchedule and len(stages) > 1:
+        cls = InterleavedOneFOneBSchedule   # several chunks per rank: the planner's interleaved plans
+    return cls(stages, cfg, **kw)
