@@ -99,8 +99,10 @@ flash_fwd4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_pairs = (p.S + 2 * BM - 1) / (2 * BM);
-  const int pair = n_pairs - 1 - int(blockIdx.x);  // heavy (late) tiles first
-  const int head = blockIdx.y, batch = blockIdx.z;
+  // grid = (heads, query pairs, batch): CTAs are dispatched x-fastest, so every head's heaviest
+  // (latest) pair starts first and the light ones fill the tail of the last wave
+  const int pair = n_pairs - 1 - int(blockIdx.y);
+  const int head = blockIdx.x, batch = blockIdx.z;
   const int kv_head = head / (p.Hq / p.Hkv);
   const int n_kv = (p.S + BN - 1) / BN;
   int lo[2], hi[2];
@@ -490,7 +492,7 @@ static int launch_fwd4(const __nv_bfloat16* qkv, int width, const AttnFwd4Params
     ZB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     attr_set = true;
   }
-  dim3 grid((p.S + 255) / 256, p.Hq, p.B);
+  dim3 grid(p.Hq, (p.S + 255) / 256, p.B);
   kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, p);
   ZB_CUDA_OK(cudaGetLastError());
   return 0;
