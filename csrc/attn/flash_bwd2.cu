@@ -81,7 +81,9 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int jt = blockIdx.x, kv_head = blockIdx.y, batch = blockIdx.z;
+  // grid = (kv heads, key tiles, batch): x-fastest dispatch starts every head's heaviest key tile
+  // (tile 0 sees all query tiles under a causal mask) before any light one
+  const int jt = blockIdx.y, kv_head = blockIdx.x, batch = blockIdx.z;
   const int kv0 = jt * BN;
   const int rep = p.Hq / p.Hkv;
   const int n_qt = (p.S + BM - 1) / BM;
@@ -450,7 +452,7 @@ static int launch_bwd2(const __nv_bfloat16* qkv, const __nv_bfloat16* d_o, const
     ZB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     attr_set = true;
   }
-  dim3 grid((p.S + 127) / 128, p.Hkv, p.B);
+  dim3 grid(p.Hkv, (p.S + 127) / 128, p.B);
   kern<<<grid, 32 * BWD2_WARPS, Cfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p, stats, s_pad, trace, trace_ctas);
   ZB_CUDA_OK(cudaGetLastError());
   return 0;
