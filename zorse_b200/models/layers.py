@@ -43,6 +43,8 @@ class Layer:
     def __init__(self):
         self.p: dict[str, torch.Tensor] = {}
         self.g: dict[str, torch.Tensor] = {}
+        self._bound_p = self._bound_g = None      # flat buffers the views in p / g were cut from
+        self._layout_cache = None
 
     # -- parameters ---------------------------------------------------------------
     def param_specs(self) -> list[ParamSpec]:
@@ -50,25 +52,29 @@ class Layer:
 
     def layout(self) -> tuple[dict[str, tuple[int, tuple]], int]:
         """name -> (offset, shape) inside the flat buffer, and the total (unpadded) length."""
-        off, out = 0, {}
-        for s in self.param_specs():
-            out[s.name] = (off, s.shape)
-            off += (s.numel + ALIGN - 1) // ALIGN * ALIGN
-        return out, off
+        if self._layout_cache is None:
+            off, out = 0, {}
+            for s in self.param_specs():
+                out[s.name] = (off, s.shape)
+                off += (s.numel + ALIGN - 1) // ALIGN * ALIGN
+            self._layout_cache = (out, off)
+        return self._layout_cache
 
     def num_params(self) -> int:
         return sum(s.numel for s in self.param_specs())
 
     def bind(self, flat_params: Optional[torch.Tensor], flat_grads: Optional[torch.Tensor]) -> None:
+        """Cuts the per-parameter views out of the flat buffers. Schedules call this for every
+        (layer, microbatch); the views are rebuilt only when a different buffer object arrives."""
         lay, _ = self.layout()
-        if flat_params is not None:
-            self.p = {n: flat_params[o:o + math.prod(sh)].view(sh) for n, (o, sh) in lay.items()}
-        else:
-            self.p = {}
-        if flat_grads is not None:
-            self.g = {n: flat_grads[o:o + math.prod(sh)].view(sh) for n, (o, sh) in lay.items()}
-        else:
-            self.g = {}
+        if flat_params is not self._bound_p:
+            self.p = ({} if flat_params is None else
+                      {n: flat_params[o:o + math.prod(sh)].view(sh) for n, (o, sh) in lay.items()})
+            self._bound_p = flat_params
+        if flat_grads is not self._bound_g:
+            self.g = ({} if flat_grads is None else
+                      {n: flat_grads[o:o + math.prod(sh)].view(sh) for n, (o, sh) in lay.items()})
+            self._bound_g = flat_grads
 
     def init_flat(self, flat: torch.Tensor, seed: int) -> None:
         """Fills `flat` (any float dtype) deterministically from `seed` with a generator on
