@@ -40,21 +40,24 @@ struct RsAdamParams {
 template <typename GT> struct GradVec;
 template <> struct GradVec<float> {
   static constexpr int N = 4;
-  static __device__ __forceinline__ void load(const float* p, float* f) {
-    uint4 u = ld_v4_relaxed_sys(p);
+  static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
     f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
   }
+  static __device__ __forceinline__ void load(const float* p, float* f) { unpack(ld_v4_relaxed_sys(p), f); }
 };
 template <> struct GradVec<__nv_bfloat16> {
   static constexpr int N = 8;
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
-    uint4 u = ld_v4_relaxed_sys(p);
+  static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
     float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
     f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
   }
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) { unpack(ld_v4_relaxed_sys(p), f); }
 };
 
-template <typename GT>
+// EARLY = false: the measured kernel (peer loads one after another, then the optimizer state).
+// EARLY = true (candidate, selected with zb_set_rs_adam_variant(1)): the optimizer state and all
+// R slices are requested before anything is consumed, so one NVLink round trip covers them all.
+template <typename GT, bool EARLY>
 __global__ void __launch_bounds__(256)
 rs_adam_kernel(const RsAdamParams p) {
   constexpr int N = GradVec<GT>::N;
@@ -79,20 +82,42 @@ rs_adam_kernel(const RsAdamParams p) {
   const long lo = long(p.r) * p.shard_n;
   for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < nvec; i += long(gridDim.x) * blockDim.x) {
     float g[N];
-#pragma unroll
-    for (int k = 0; k < N; ++k) g[k] = 0.f;
-    for (int q = 0; q < p.R; ++q) {
-      float t[N];
-      GradVec<GT>::load(static_cast<const GT*>(p.grad[q]) + lo + i * N, t);
-#pragma unroll
-      for (int k = 0; k < N; ++k) g[k] += t[k];
-    }
     float pm[N], mm[N], vv[N];
 #pragma unroll
-    for (int k = 0; k < N; k += 4) {
-      *reinterpret_cast<float4*>(pm + k) = *reinterpret_cast<const float4*>(p.master + i * N + k);
-      *reinterpret_cast<float4*>(mm + k) = *reinterpret_cast<const float4*>(p.m + i * N + k);
-      *reinterpret_cast<float4*>(vv + k) = *reinterpret_cast<const float4*>(p.v + i * N + k);
+    for (int k = 0; k < N; ++k) g[k] = 0.f;
+    if (EARLY) {
+#pragma unroll
+      for (int k = 0; k < N; k += 4) {
+        *reinterpret_cast<float4*>(pm + k) = *reinterpret_cast<const float4*>(p.master + i * N + k);
+        *reinterpret_cast<float4*>(mm + k) = *reinterpret_cast<const float4*>(p.m + i * N + k);
+        *reinterpret_cast<float4*>(vv + k) = *reinterpret_cast<const float4*>(p.v + i * N + k);
+      }
+      uint4 raw[MAX_R];
+#pragma unroll
+      for (int q = 0; q < MAX_R; ++q)
+        if (q < p.R) raw[q] = ld_v4_relaxed_sys(static_cast<const GT*>(p.grad[q]) + lo + i * N);
+#pragma unroll
+      for (int q = 0; q < MAX_R; ++q) {     // same rank order as the other variant: same sum
+        if (q < p.R) {
+          float t[N];
+          GradVec<GT>::unpack(raw[q], t);
+#pragma unroll
+          for (int k = 0; k < N; ++k) g[k] += t[k];
+        }
+      }
+    } else {
+      for (int q = 0; q < p.R; ++q) {
+        float t[N];
+        GradVec<GT>::load(static_cast<const GT*>(p.grad[q]) + lo + i * N, t);
+#pragma unroll
+        for (int k = 0; k < N; ++k) g[k] += t[k];
+      }
+#pragma unroll
+      for (int k = 0; k < N; k += 4) {
+        *reinterpret_cast<float4*>(pm + k) = *reinterpret_cast<const float4*>(p.master + i * N + k);
+        *reinterpret_cast<float4*>(mm + k) = *reinterpret_cast<const float4*>(p.m + i * N + k);
+        *reinterpret_cast<float4*>(vv + k) = *reinterpret_cast<const float4*>(p.v + i * N + k);
+      }
     }
 #pragma unroll
     for (int k = 0; k < N; ++k) {
@@ -158,7 +183,12 @@ peer_pull_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long n1
 
 }  // namespace zb
 
+static int g_rs_adam_variant = 0;
+
 extern "C" {
+
+// 0 = measured kernel, 1 = candidate that requests the optimizer state and all R slices up front.
+void zb_set_rs_adam_variant(int v) { g_rs_adam_variant = v; }
 
 // grad_ptrs / flag_ptrs: host arrays of R device pointers (peer-mapped), ordered by rank in
 // the shard group. counter: a zeroed device int owned by the caller.
@@ -185,8 +215,13 @@ int zb_rs_adam(const void* const* grad_ptrs, int* const* flag_ptrs, int R, int r
   if (max_blocks > 0 && max_blocks < blocks) blocks = max_blocks;
   long need = (shard_n / (grad_f32 ? 4 : 8) + 255) / 256;
   if (need < blocks) blocks = int(need < 1 ? 1 : need);
-  if (grad_f32) rs_adam_kernel<float><<<blocks, 256, 0, stream>>>(p);
-  else rs_adam_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(p);
+  if (g_rs_adam_variant == 1) {
+    if (grad_f32) rs_adam_kernel<float, true><<<blocks, 256, 0, stream>>>(p);
+    else rs_adam_kernel<__nv_bfloat16, true><<<blocks, 256, 0, stream>>>(p);
+  } else {
+    if (grad_f32) rs_adam_kernel<float, false><<<blocks, 256, 0, stream>>>(p);
+    else rs_adam_kernel<__nv_bfloat16, false><<<blocks, 256, 0, stream>>>(p);
+  }
   ZB_CUDA_OK(cudaGetLastError());
   return 0;
 }

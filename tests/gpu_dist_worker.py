@@ -42,13 +42,14 @@ def train_case(case):
     return losses, masters, tr
 
 
-def fused_kernels():
+def fused_kernels(variant: int = 0):
     """rs_adam and ag_gemm against NCCL + the standalone kernels on identical inputs."""
     import torch.distributed._symmetric_memory as symm
     from zorse_b200.ops import sm100 as k
 
     rank, R = dist.get_rank(), dist.get_world_size()
     dev = torch.device("cuda", rank)
+    k.set_rs_adam_variant(variant)
     g = torch.Generator(device=dev).manual_seed(123 + rank)
     sn = 8 * 64 * 1031
     n = sn * R
@@ -117,8 +118,8 @@ def main():
     from zorse_b200.parallel.groups import dist_init
 
     dist_init()
-    if case == "fused_kernels":
-        fused_kernels()
+    if case.startswith("fused_kernels"):
+        fused_kernels(1 if case.endswith("_v1") else 0)
     else:
         losses, masters, tr = train_case(case)
         # same job with the other collectives mode must land on the same parameters

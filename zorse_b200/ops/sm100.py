@@ -52,6 +52,8 @@ def lib():
             _build.build()
         _lib = ctypes.CDLL(str(_LIB_PATH))
         _lib.zb_last_error.restype = ctypes.c_char_p
+        if os.environ.get("ZORSE_RS_ADAM_VARIANT", "0") != "0":      # candidate, see csrc/comm/rs_adam.cu
+            _lib.zb_set_rs_adam_variant(c_int(int(os.environ["ZORSE_RS_ADAM_VARIANT"])))
     return _lib
 
 
@@ -396,6 +398,11 @@ def rs_adam(grad_ptrs, flag_ptrs, R: int, r: int, shard_elems: int, master, m, v
                           _p(counter), c_int(max_blocks), ctypes.c_double(wait_seconds),
                           _p(status_word(master.device)), _stream())
     _check(rc, "rs_adam")
+
+
+def set_rs_adam_variant(variant: int) -> None:
+    """0: measured kernel; 1: candidate that requests the optimizer state and all slices up front."""
+    lib().zb_set_rs_adam_variant(c_int(variant))
 
 
 def wait_flags(flags: torch.Tensor, R: int, which: int, epoch: int, wait_seconds: float = 2.0):

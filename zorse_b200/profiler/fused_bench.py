@@ -48,6 +48,7 @@ def main(argv=None):
     ap.add_argument("--out", default=None)
     ap.add_argument("--params", type=int, default=202_383_360)
     ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--rs_adam_variant", type=int, default=0, help="1 = early-load candidate of the rs_adam kernel")
     a = ap.parse_args(argv)
     import torch.distributed._symmetric_memory as symm
 
@@ -56,6 +57,7 @@ def main(argv=None):
     from zorse_b200.profiler.kernel_bench import _peaks
 
     dev = dist_init()
+    k.set_rs_adam_variant(a.rs_adam_variant)
     rank, R = dist.get_rank(), dist.get_world_size()
     peaks = _peaks()
     q = 64 * R
