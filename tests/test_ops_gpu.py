@@ -125,7 +125,7 @@ def test_norm(k, T, H, ln, bwd_version):
     else:
         yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
     yr.backward(dy.float())
-    y, stats = k.norm_fwd(x.cuda(), w.cuda(), b.cuda() if ln else None, 1e-5, ln)
+    y, stats = k.norm_fwd(x.cuda(), w.cuda(), b.cuda() if ln else None, 1e-5, ln, version=bwd_version)
     _close(y, yr.detach(), atol=2e-2, rtol=1e-2)
     for gdt in (torch.float32, torch.bfloat16):
         dw = torch.ones(H, dtype=gdt, device="cuda")

@@ -149,13 +149,18 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = Fa
 
 
 # --------------------------------------------------------------------------- norms
-def norm_fwd(x, w, b, eps: float, layernorm: bool):
+NORM_FWD_VERSION = int(os.environ.get("ZORSE_NORM_FWD", "1"))
+
+
+def norm_fwd(x, w, b, eps: float, layernorm: bool, version: Optional[int] = None):
+    """version 1: one CTA per row; version 2 (candidate): one warp per row, no block barriers."""
     _bf16(x, "x")
     T, H = x.shape
     y = torch.empty_like(x)
     stats = torch.empty(T, 2, dtype=torch.float32, device=x.device)
-    _check(lib().zb_norm_fwd(_p(x), _p(w), _p(b), _p(y), _p(stats), c_int(T), c_int(H), c_float(eps),
-                             c_int(int(layernorm)), _stream()), "norm_fwd")
+    fn = lib().zb_norm_fwd2 if (version or NORM_FWD_VERSION) == 2 else lib().zb_norm_fwd
+    _check(fn(_p(x), _p(w), _p(b), _p(y), _p(stats), c_int(T), c_int(H), c_float(eps),
+              c_int(int(layernorm)), _stream()), "norm_fwd")
     return y, stats
 
 

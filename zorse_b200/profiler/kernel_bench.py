@@ -157,6 +157,8 @@ def bench_elementwise(k, peaks, rows):
     add("rmsnorm bwd", f"T{T} H{H}", time_fn(lambda: k.norm_bwd(dy, x, w, st, None, gw, None, False, version=1)), None,
         3 * T * H * 2)
     if os.environ.get("ZORSE_BENCH_CANDIDATES") == "1":
+        add("rmsnorm fwd v2", f"T{T} H{H}", time_fn(lambda: k.norm_fwd(x, w, None, 1e-5, False, version=2)), None,
+            2 * T * H * 2)
         add("rmsnorm bwd v2", f"T{T} H{H}", time_fn(lambda: k.norm_bwd(dy, x, w, st, None, gw, None, False, version=2)),
             None, 3 * T * H * 2)
     gu = torch.randn(T, 2 * Fd, device="cuda", dtype=torch.bfloat16)
