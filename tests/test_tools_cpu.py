@@ -187,3 +187,22 @@ def test_latency_probe_derivations():
     d = derive(med)
     assert d["clocks_per_mma_128x128x16"] == 64.0 and d["mma_fixed_latency"] == 900 - 8 * 64
     assert d["ex2_clocks_per_op_1warp_per_sched"] == 9.0
+
+
+def test_perf_check_flags_regressions(tmp_path):
+    import json
+
+    from zorse_b200.profiler import perf_check
+
+    base = json.loads(perf_check.DEFAULT.read_text())
+    assert len(base["kernels"]) > 40 and "gemm fwd 2cta | 7b qkv M4096 N12288 K4096" in base["kernels"]
+    k0, k1 = list(base["kernels"])[:2]
+    rows = [{"op": k0.split(" | ")[0], "shape": k0.split(" | ")[1], "ours_ms": base["kernels"][k0]["ours_ms"] * 1.25},
+            {"op": k1.split(" | ")[0], "shape": k1.split(" | ")[1], "ours_ms": base["kernels"][k1]["ours_ms"] * 1.02},
+            {"op": "new kernel", "shape": "x", "ours_ms": 1.0}]
+    res = perf_check.compare(rows, base, 0.10)
+    assert [s[0] for s in res["slower"]] == [k0] and res["same"] == 1 and res["unknown"] == ["new kernel | x"]
+    f = tmp_path / "new.json"
+    f.write_text(json.dumps({"rows": rows}))
+    assert perf_check.main([str(f)]) == 1
+    assert perf_check.main([str(f), "--tolerance", "0.5"]) == 0
