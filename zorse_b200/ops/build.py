@@ -57,7 +57,9 @@ def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
         raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
     if verbose:
         print(r.stderr)
-    obj.with_suffix(".log").write_text(f"==== {src.relative_to(CSRC)}\n{r.stderr}")
+    # compile times change from run to run; leaving them out keeps the tracked summary stable
+    kept = "\n".join(ln for ln in r.stderr.splitlines() if "Compile time" not in ln)
+    obj.with_suffix(".log").write_text(f"==== {src.relative_to(CSRC)}\n{kept}\n")
     return r.stderr
 
 
