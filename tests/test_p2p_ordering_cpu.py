@@ -103,7 +103,7 @@ def test_alternate_nccl_gloo_and_batched_gloo_receives():
     build_schedule("zero2", [st], cfg).step(0, data, data)
     assert {e.peer for e in gloo.events} == {0} and {e.peer for e in prim.events} <= {3, 4}
     # forward: both Gloo receives are posted before the first one is waited for
-    fwd = [e.what for e in gloo.events if e.kind == "act"]
+    fwd = [e.what for e in gloo.events if e.kind.startswith("act")]
     assert fwd[:3] == ["post_recv", "post_recv", "wait_recv"]
     cfg.alternate_nccl_gloo = False
     assert st.uses_gloo(True)
@@ -124,3 +124,53 @@ def test_interleaved_1f1b_ordering_is_deadlock_free(P, v, width, M):
     progs = record_programs(cfg, "1f1b_interleaved", model_overrides={**OV, "layers": P * v})
     assert simulate(progs) is None
     assert simulate(progs, serialize_within_group=False) is None
+
+
+def _irregular_cfg(widths, counts):
+    pipe, rank = [], 0
+    for s, (w, c) in enumerate(zip(widths, counts)):
+        ranks = list(range(rank, rank + w))
+        rank += w
+        pipe.append({"gpu_ranks": ranks, "num_microbatches_per_rank": c, "layer_partition": [s, s + 1],
+                     "zero_config": [[q] for q in ranks]})
+    M = sum(counts[0])
+    return parse_pipeline_dict({"model_name": "tiny_llama", "global_batch_size": M, "microbatch_size": 1,
+                                "sequence_length": 8, "vocab_size": 64, "autocast_dtype": "float32",
+                                "reduce_dtype": "float32", "pipeline_config": pipe})
+
+
+IRREGULAR = [
+    ([2, 2, 2], [[5, 5], [2, 8], [7, 3]]),                 # equal widths, uneven counts
+    ([1, 2, 2], [[11], [8, 3], [4, 7]]),
+    ([1, 1, 1, 2, 1], [[12], [12], [12], [7, 5], [12]]),
+    ([3, 1, 3, 1, 1, 3], [[5, 7, 0], [12], [10, 0, 2], [12], [12], [0, 6, 6]]),   # ranks without microbatches
+    ([1, 3, 1, 2], [[6], [2, 1, 3], [6], [0, 6]]),
+]
+
+
+@pytest.mark.parametrize("schedule", ["layer_major", "no_overlap", "two_stage_sync", "zero2", "flashflex", "1f1b"])
+@pytest.mark.parametrize("widths,counts", IRREGULAR)
+def test_irregular_routing_is_deadlock_free(schedule, widths, counts):
+    """Mixed stage widths and uneven microbatch counts (heterogeneous data parallelism): the classic
+    1F1B order and one-ahead receives on four shared groups deadlock on several of these; the planned
+    1F1B order and the parity-split groups do not."""
+    cfg = _irregular_cfg(widths, counts)
+    progs = record_programs(cfg, schedule, model_overrides={**OV, "layers": len(widths)})
+    assert simulate(progs) is None
+    assert simulate(progs, serialize_within_group=False) is None
+
+
+def test_planned_1f1b_order_equals_the_classic_one_on_a_regular_chain():
+    from zorse_b200.parallel.p2p_plan import is_regular, plan_1f1b_order
+
+    cfg = chain_cfg(4, 8)
+    assert is_regular(cfg)
+    order = plan_1f1b_order(cfg)
+    for pos in range(4):
+        warm = 4 - pos - 1
+        classic = [("F", i) for i in range(warm)]
+        for i in range(8 - warm):
+            classic += [("F", warm + i), ("B", i)]
+        classic += [("B", i) for i in range(8 - warm, 8)]
+        assert order[pos] == classic
+    assert not is_regular(_irregular_cfg(*IRREGULAR[0]))

@@ -40,9 +40,10 @@ class Handle:
 
 
 class NcclP2P:
-    KINDS = ("act", "grad")
-
-    def __init__(self, device: torch.device, timeout_s: float = 300.0, streams=None):
+    def __init__(self, device: torch.device, timeout_s: float = 300.0, streams=None, split_parity: bool = False):
+        # kinds of traffic, each with an "up" and a "down" group; with split_parity the boundaries of even
+        # and odd index get their own groups (needed for irregular routing, see PipelineStage)
+        self.KINDS = ("act0", "act1", "grad0", "grad1") if split_parity else ("act", "grad")
         self.device = device
         self.streams = streams  # engine Streams: brackets receive waits for exposed-communication accounting
         self.rank = dist.get_rank()
@@ -172,9 +173,10 @@ class LoopbackP2P:
         pass
 
 
-def make_transport(device: torch.device, use_gloo: bool = False, gloo_group=None, streams=None):
+def make_transport(device: torch.device, use_gloo: bool = False, gloo_group=None, streams=None,
+                   split_parity: bool = False):
     if not (dist.is_available() and dist.is_initialized()):
         return LoopbackP2P(0, {})
     if device.type == "cuda" and not use_gloo:
-        return NcclP2P(device, streams=streams)
+        return NcclP2P(device, streams=streams, split_parity=split_parity)
     return GlooP2P(device, gloo_group)

@@ -132,3 +132,87 @@ def validate_static_comm_plans(cfg, plans: dict[int, RankCommPlan]) -> None:
     expect = 2 * M * (len(cfg.stages) - 1)
     if len(sends) != expect:
         raise AssertionError(f"{len(sends)} transfers planned, expected {expect}")
+
+
+def is_regular(cfg) -> bool:
+    """True when every stage has the same width and every rank the same number of microbatches:
+    microbatch g then sits on rank `g % width` of every stage and all ranks of a column see the
+    same sequence of microbatches (the case the classic 1F1B order and one-ahead receives assume)."""
+    widths = {len(s.gpu_ranks) for s in cfg.stages}
+    counts = {c for s in cfg.stages for c in s.num_microbatches_per_rank}
+    return len(widths) == 1 and len(counts) == 1
+
+
+def plan_1f1b_order(cfg, f_cost: float = 1.0, b_cost: float = 2.0) -> dict[int, list[tuple[str, int]]]:
+    """Per rank, the order of forward ("F") and backward ("B") passes over its local microbatches
+    for a one-forward-one-backward schedule on ANY static routing (mixed stage widths, uneven
+    microbatch counts).
+
+    With many-to-many routing the ranks of a stage see different subsequences of the global
+    microbatch order, and the classic rule (P - s - 1 warm-up forwards, then strict alternation)
+    can make a rank wait for a gradient whose forward depends on an activation that same rank
+    would only produce later.  The order is therefore taken from a list-scheduling run of the
+    whole pipeline with unit costs (forward 1, backward 2 per layer): at every step the pass
+    that can start earliest is placed, backward before forward on ties, at most `P - s` forwards
+    in flight per rank (raised only if nothing could be placed).  Every rank computes the same
+    plan from the config alone; issuing passes in this order cannot deadlock because the run
+    itself is one valid execution.  Ranks host one stage each."""
+    stages = cfg.stages
+    P, M = len(stages), cfg.num_microbatches
+    owners = [stage_owners(s) for s in stages]
+    stage_of: dict[int, int] = {}
+    for si, s in enumerate(stages):
+        for r in s.gpu_ranks:
+            if r in stage_of:
+                raise ValueError("plan_1f1b_order: a rank hosts several stages")
+            stage_of[r] = si
+    local = {r: [g for g in range(M) if owners[si][g] == r] for r, si in stage_of.items()}
+    nf = {r: 0 for r in stage_of}
+    nb = {r: 0 for r in stage_of}
+    free = {r: 0.0 for r in stage_of}
+    order: dict[int, list] = {r: [] for r in stage_of}
+    act_ready = [[0.0 if si == 0 else None for _ in range(M)] for si in range(P)]
+    grad_ready = [[None] * M for _ in range(P)]
+    extra = 0
+    remaining = sum(len(v) for v in local.values())
+    while remaining:
+        best = None
+        for r in sorted(stage_of):
+            si = stage_of[r]
+            if nb[r] < nf[r]:
+                ready = grad_ready[si][local[r][nb[r]]]
+                if ready is not None:
+                    cand = (max(free[r], ready), 0, r, "B")
+                    best = cand if best is None or cand < best else best
+            if nf[r] < len(local[r]) and nf[r] - nb[r] < P - si + extra:
+                ready = act_ready[si][local[r][nf[r]]]
+                if ready is not None:
+                    cand = (max(free[r], ready), 1, r, "F")
+                    best = cand if best is None or cand < best else best
+        if best is None:
+            extra += 1          # every rank is at its in-flight limit: allow one more forward
+            if extra > M:
+                raise RuntimeError("plan_1f1b_order: no pass can be placed (inconsistent routing)")
+            continue
+        start, _, r, op = best
+        si = stage_of[r]
+        n_layers = stages[si].num_layers
+        if op == "F":
+            g = local[r][nf[r]]
+            end = start + f_cost * n_layers
+            if si + 1 < P:
+                act_ready[si + 1][g] = end
+            else:
+                grad_ready[si][g] = end       # the last stage can turn around at once
+            order[r].append(("F", nf[r]))
+            nf[r] += 1
+        else:
+            g = local[r][nb[r]]
+            end = start + b_cost * n_layers
+            if si > 0:
+                grad_ready[si - 1][g] = end
+            order[r].append(("B", nb[r]))
+            nb[r] += 1
+            remaining -= 1
+        free[r] = end
+    return order

@@ -67,14 +67,18 @@ class InterleavedOneFOneBSchedule(ScheduleBase):
             st, mbl = sts[chunk_of(k, False)], mb_of(k)
             units = st.engine.units
             dy = None if st.is_last else st.recv_bwd(mbl).wait()
+            last, asynchronous = mbl == M - 1, st.device.type == "cuda"   # see one_f_one_b.py
             for li in reversed(range(len(st.layers))):
                 units[li].acquire()
                 units[li].grad_views()
                 dy = st.backward_layer(li, mbl, dy, self._tgt(st, targets, mbl), self.recompute)
-                if mbl == M - 1:
+                if last and asynchronous:
                     units[li].reduce_grads()
             if not st.is_first:
                 st.send_bwd(mbl, dy)
+            if last and not asynchronous:
+                for li in reversed(range(len(st.layers))):
+                    units[li].reduce_grads()
 
         for k in range(warm):
             fwd(k)

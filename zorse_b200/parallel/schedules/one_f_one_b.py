@@ -9,12 +9,21 @@ backward microbatch.  By default activations are kept (no recompute): at most
 """
 from __future__ import annotations
 
+from ..p2p_plan import is_regular, plan_1f1b_order
 from .base import ScheduleBase
 
 
 class OneFOneBSchedule(ScheduleBase):
     name = "1f1b"
     recompute_default = False
+
+    def __init__(self, stages, cfg, **kw):
+        super().__init__(stages, cfg, **kw)
+        # mixed stage widths or uneven microbatch counts: the classic warm-up / alternate / drain
+        # order can deadlock there (see p2p_plan.plan_1f1b_order), so take the order from the plan
+        self.order = None
+        if len(self.stages) == 1 and not is_regular(cfg):
+            self.order = plan_1f1b_order(cfg)[self.stages[0].rank]
 
     def step(self, step_idx, inputs, targets):
         if len(self.stages) != 1:
@@ -44,22 +53,35 @@ class OneFOneBSchedule(ScheduleBase):
 
         def bwd(mbl):
             dy = None if st.is_last else st.recv_bwd(mbl).wait()
+            # On CUDA the reduction of a layer is queued on the communication stream as soon as its last
+            # backward is issued and overlaps the rest of that backward.  Host-blocking collectives (gloo)
+            # must wait until this microbatch's gradient has been sent upstream: a rank that finishes early
+            # would otherwise sit in the collective while upstream stages still need that gradient to
+            # produce the forwards its peers are waiting for.
+            last, asynchronous = mbl == M - 1, st.device.type == "cuda"
             for li in reversed(range(L)):
                 units[li].acquire()
                 units[li].grad_views()
                 dy = st.backward_layer(li, mbl, dy, self._tgt(st, targets, mbl), self.recompute)
-                if mbl == M - 1:
+                if last and asynchronous:
                     units[li].reduce_grads()
             if not st.is_first:
                 st.send_bwd(mbl, dy)
+            if last and not asynchronous:
+                for li in reversed(range(L)):
+                    units[li].reduce_grads()
 
-        for i in range(warm):
-            fwd(i)
-        for i in range(M - warm):
-            fwd(warm + i)
-            bwd(i)
-        for i in range(M - warm, M):
-            bwd(i)
+        if self.order is not None:
+            for op, i in self.order:
+                (fwd if op == "F" else bwd)(i)
+        else:
+            for i in range(warm):
+                fwd(i)
+            for i in range(M - warm):
+                fwd(warm + i)
+                bwd(i)
+            for i in range(M - warm, M):
+                bwd(i)
         if M == 0:
             for u in units:
                 u.grad_views()

@@ -18,7 +18,7 @@ from .groups import StageGroups
 from ..utils import canary
 from ..utils import stream_check as SC
 from ..utils.ranges import phase
-from .p2p_plan import StageCommPattern
+from .p2p_plan import StageCommPattern, is_regular
 
 
 class ActivationStash:
@@ -98,6 +98,11 @@ class PipelineStage:
                                   replicate=groups.replicate, rank=rank, streams=streams, zero_level=st.zero_level,
                                   meta_init=False, shard_ratios=st.shard_ratio)
         self.pattern = pattern
+        # irregular routing (mixed widths / uneven counts): traffic of even and odd stage boundaries goes
+        # through different process groups, so that a rank's receives (boundary b - 1) and sends (boundary b)
+        # never share a serialised queue; regular plans keep the four groups they were measured with
+        self.split_parity = not is_regular(cfg)
+        self.pos = [s.stage_id for s in cfg.stages].index(st.stage_id)
         self.transport = transport
         self.gloo_transport = gloo_transport
         self.microbatches = list(pattern.microbatches)  # global ids, increasing
@@ -156,25 +161,31 @@ class PipelineStage:
         for t in self.transports():
             t.flush()
 
+    def _kind(self, base: str, towards_next: bool) -> str:
+        if not self.split_parity:
+            return base
+        boundary = self.pos if towards_next else self.pos - 1
+        return f"{base}{boundary & 1}"
+
     def recv_fwd(self, mbl: int):
         src, tag = self.pattern.fwd_recv[mbl]
         with phase("p2p.recv_act"):
-            return self.boundary_transport(False).recv(self.act_shape(), self.act_dtype, src, tag, "act")
+            return self.boundary_transport(False).recv(self.act_shape(), self.act_dtype, src, tag, self._kind("act", False))
 
     def send_fwd(self, mbl: int, y: torch.Tensor):
         dst, tag = self.pattern.fwd_send[mbl]
         with phase("p2p.send_act"):
-            return self.boundary_transport(True).send(y, dst, tag, "act")
+            return self.boundary_transport(True).send(y, dst, tag, self._kind("act", True))
 
     def recv_bwd(self, mbl: int):
         src, tag = self.pattern.bwd_recv[mbl]
         with phase("p2p.recv_grad"):
-            return self.boundary_transport(True).recv(self.act_shape(), self.act_dtype, src, tag, "grad")
+            return self.boundary_transport(True).recv(self.act_shape(), self.act_dtype, src, tag, self._kind("grad", True))
 
     def send_bwd(self, mbl: int, dx: torch.Tensor):
         dst, tag = self.pattern.bwd_send[mbl]
         with phase("p2p.send_grad"):
-            return self.boundary_transport(False).send(dx, dst, tag, "grad")
+            return self.boundary_transport(False).send(dx, dst, tag, self._kind("grad", False))
 
     def add_loss(self, rows: torch.Tensor) -> None:
         v = rows.float().sum() * self.loss_scale

@@ -23,7 +23,7 @@ from .engine.zero import AdamConfig, EngineConfig, Streams
 from .ops.api import default_ops_for, get_ops
 from .parallel import groups as G
 from .parallel.p2p import GlooP2P, make_transport
-from .parallel.p2p_plan import create_static_comm_plans
+from .parallel.p2p_plan import create_static_comm_plans, is_regular
 from .parallel.schedules import build_schedule
 from .parallel.stage import PipelineStage
 from .utils import canary
@@ -75,7 +75,7 @@ class Trainer:
         # can alternate between them by stage width; on CPU ranks there is only Gloo
         both = opt.gloo_p2p and self.device.type == "cuda" and G.is_dist()
         self.transport = make_transport(self.device, use_gloo=opt.gloo_p2p and not both, gloo_group=self.gloo_group,
-                                        streams=self.streams)
+                                        streams=self.streams, split_parity=not is_regular(cfg))
         self.gloo_transport = GlooP2P(self.device, self.gloo_group) if both else None
         plans = create_static_comm_plans(cfg)
         self.plan = plans[self.rank]
