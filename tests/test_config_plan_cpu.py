@@ -212,3 +212,30 @@ def test_bench_plans_are_valid_configs_and_deadlock_free():
                        text=True, timeout=120, cwd=root)
     line = json.loads(r.stdout.strip().splitlines()[-1])
     assert r.returncode == 0 and line["impl"] == "reference" and "unavailable" in line
+
+
+def test_planner_lists_gpus_it_leaves_without_a_stage():
+    """One fast GPU next to very slow ones on another machine: the slow group may get no layer;
+    its ranks are then declared idle instead of silently missing from the config."""
+    from zorse_b200.planner.plan import export_config, plan
+
+    def gpu(rank, name, mem, machine, idx):
+        return {"index": idx, "name": name, "memory_total_mib": mem, "id": f"gpu_{rank}", "machine": machine,
+                "global_rank": rank}
+
+    gl = [gpu(0, "p40", 23040, "m0", 0), gpu(1, "l4", 23034, "m0", 1), gpu(2, "b200", 183359, "m0", 2),
+          gpu(3, "p40", 23040, "m1", 0)]
+    data = {"machines": [{"machine": "m0", "num_gpus": 3, "gpus": gl[:3], "machine_index": 0},
+                         {"machine": "m1", "num_gpus": 1, "gpus": gl[3:], "machine_index": 1}],
+            "total_gpus": 4, "gpu_list": gl,
+            "global_rank_map": {str(g["global_rank"]): {"machine": g["machine"], "local_rank": g["index"],
+                                                        "machine_index": int(g["machine"][1])} for g in gl},
+            "bandwidth": {"intranode_bandwidth": {"0": 25.0, "1": 25.0}, "intranode_latency": {"0": 1e-4, "1": 1e-4},
+                          "internode_bandwidth": {"0": {"1": 1.0}, "1": {"0": 1.0}},
+                          "internode_latency": {"0": {"1": 1e-3}, "1": {"0": 1e-3}}}}
+    best, _ = plan(data, "opt_1b", global_batch_size=32, sequence_length=1024)
+    d = export_config(best, "opt_1b", 32, 1024, 32000, "bfloat16", "float32", total_ranks=4)
+    cfg = parse_pipeline_dict(d)
+    assert cfg.world_size == 4
+    named = {r for s in cfg.stages for r in s.gpu_ranks}
+    assert named | set(cfg.unused_ranks) == {0, 1, 2, 3} and not (named & set(cfg.unused_ranks))

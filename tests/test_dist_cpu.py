@@ -196,3 +196,17 @@ def test_interleaved_1f1b_rejects_bad_plans():
     cfg = parse_pipeline_dict(tiny_cfg(_interleaved_pipe(2, 2, 1, 3), gbs=3, mbs=1))   # 3 microbatches, 2 groups
     with pytest.raises(ValueError, match="multiple of 2 rank groups"):
         record_programs(cfg, "1f1b_interleaved")
+
+
+def test_idle_rank_left_out_by_the_planner():
+    """A plan that gives a slow GPU no stage: that rank still joins the job (groups, barriers, loss
+    reduction) and idles; the other ranks train as the oracle does."""
+    pipe = [{"gpu_ranks": [0], "num_microbatches_per_rank": [4], "layer_partition": [0, 2], "zero_config": [[0]]},
+            {"gpu_ranks": [2], "num_microbatches_per_rank": [4], "layer_partition": [2, 4], "zero_config": [[2]]}]
+    cfg = tiny_cfg(pipe, unused_ranks=[1])
+    assert parse_pipeline_dict(cfg).world_size == 3
+    res = run_workers(3, _worker, cfg, {"schedule": "zero2"}, 2)
+    assert res[1]["params"] == {} and res[1]["counters"] == []
+    _check(res, cfg)
+    with pytest.raises(ValueError, match="0 .. world_size - 1"):
+        parse_pipeline_dict(tiny_cfg(pipe))            # rank 1 missing and not declared idle

@@ -150,7 +150,7 @@ def main(argv=None) -> int:
     else:
         outs, names = [t], [gpu]
     step_ms = max(float(o[0]) for o in outs)
-    spec = tr.stages[0].spec
+    spec = tr.spec
     flops = metrics.compute_model_flops(registry.total_params(spec, cfg.sequence_length), spec.layers, spec.hidden,
                                         cfg.sequence_length, cfg.global_batch_size, recompute=tr.schedule.recompute)
     gl = tr.global_loss(loss)

@@ -126,6 +126,7 @@ class PipelineConfig:
     activation_recompute: Optional[bool] = None
     activation_offload: Optional[bool] = None
     grad_norm_compat: str = "mean"
+    unused_ranks: tuple[int, ...] = ()   # ranks of the job that own no stage (the planner may leave a slow GPU out)
     extra: dict = field(default_factory=dict)
 
     @property
@@ -138,7 +139,7 @@ class PipelineConfig:
 
     @property
     def world_size(self) -> int:
-        return len({r for s in self.stages for r in s.gpu_ranks})
+        return len({r for s in self.stages for r in s.gpu_ranks} | set(self.unused_ranks))
 
     @property
     def gpu_groups(self) -> list[tuple[int, ...]]:
@@ -167,6 +168,11 @@ class PipelineConfig:
                 raise ConfigError(f"stage {s.stage_id}: {s.num_microbatches} microbatches, expected "
                                   f"{self.num_microbatches} (= global_batch_size / microbatch_size)")
         check_contiguous([s.layer_partition for s in self.stages])
+        named = {r for s in self.stages for r in s.gpu_ranks}
+        if named & set(self.unused_ranks):
+            raise ConfigError(f"unused_ranks {sorted(named & set(self.unused_ranks))} also own stages")
+        if sorted(named | set(self.unused_ranks)) != list(range(len(named) + len(self.unused_ranks))):
+            raise ConfigError("the ranks named by the stages and by unused_ranks must be 0 .. world_size - 1")
 
 
 def check_contiguous(parts: Sequence[tuple[int, int]]) -> None:
@@ -209,7 +215,7 @@ def parse_pipeline_dict(d: dict[str, Any]) -> PipelineConfig:
              "fused_optimizer", "interleave_degree", "latency", "autocast_dtype", "reduce_dtype",
              "split_microbatches_evenly", "skip_compute_sync", "interleave_stage_sync", "gloo_batch_recv",
              "alternate_nccl_gloo", "large_model_init", "schedule", "activation_recompute", "activation_offload",
-             "grad_norm_compat", "zero_level"}
+             "grad_norm_compat", "zero_level", "unused_ranks"}
     cfg = PipelineConfig(
         model_name=str(d["model_name"]), global_batch_size=gbs, microbatch_size=mbs,
         sequence_length=int(d["sequence_length"]), stages=stages, vocab_size=int(d.get("vocab_size", 49152)),
@@ -222,6 +228,7 @@ def parse_pipeline_dict(d: dict[str, Any]) -> PipelineConfig:
         large_model_init=bool(d.get("large_model_init", False)), schedule=d.get("schedule"),
         activation_recompute=d.get("activation_recompute"), activation_offload=d.get("activation_offload"),
         grad_norm_compat=str(d.get("grad_norm_compat", "mean")),
+        unused_ranks=tuple(int(r) for r in d.get("unused_ranks", ())),
         extra={k: v for k, v in d.items() if k not in known})
     cfg.validate()
     return cfg
@@ -247,6 +254,8 @@ def to_dict(cfg: PipelineConfig) -> dict[str, Any]:
              **({"shard_ratio": list(s.shard_ratio)} if s.shard_ratio else {})}
             for s in cfg.stages],
     }
+    if cfg.unused_ranks:
+        d["unused_ranks"] = list(cfg.unused_ranks)
     if cfg.split_microbatches_evenly:
         d["split_microbatches_evenly"] = True
     if cfg.sync_after_recompute:

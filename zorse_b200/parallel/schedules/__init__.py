@@ -42,6 +42,8 @@ def build_schedule(name: str, stages, cfg, **kw) -> ScheduleBase:
     if name not in SCHEDULES:
         raise ValueError(f"unknown schedule {name!r}; known: {sorted(set(SCHEDULES))}")
     cls = SCHEDULES[name]
+    if not stages:
+        cls = ScheduleBase                  # a rank the plan leaves idle: every step is empty
     if cls is OneFOneBSchedule and len(stages) > 1:
         cls = InterleavedOneFOneBSchedule   # several chunks per rank: the planner's interleaved plans
     return cls(stages, cfg, **kw)

@@ -151,8 +151,13 @@ def plan(data: dict, model_name: str, *, global_batch_size: int, sequence_length
 
 
 def export_config(res: PlanResult, model_name: str, global_batch_size: int, sequence_length: int, vocab_size: int,
-                  autocast_dtype: str, reduce_dtype: str, path: Optional[str] = None) -> dict:
-    """The training_config.json the trainer reads (reference zorse_planner.py:616-647)."""
+                  autocast_dtype: str, reduce_dtype: str, path: Optional[str] = None,
+                  total_ranks: Optional[int] = None) -> dict:
+    """The training_config.json the trainer reads (reference zorse_planner.py:616-647).  A group of
+    GPUs that is too slow to be given a single layer owns no stage; with `total_ranks` such ranks are
+    listed under `unused_ranks` so that a job launched on every GPU of the cluster file still starts
+    (the reference drops them silently, zorse_optimizer/optimizer.py:153-170, and its trainer then
+    cannot match the launched world size)."""
     d = {
         "model_name": model_name, "global_batch_size": global_batch_size, "microbatch_size": res.microbatch_size,
         "sequence_length": sequence_length, "vocab_size": vocab_size, "fused_optimizer": True,
@@ -162,6 +167,11 @@ def export_config(res: PlanResult, model_name: str, global_batch_size: int, sequ
                              "layer_partition": list(s.layer_partition), "zero_config": [list(s.gpu_ranks)]}
                             for s in res.stages],
     }
+    if total_ranks is not None:
+        used = {r for s in res.stages for r in s.gpu_ranks}
+        idle = [r for r in range(total_ranks) if r not in used]
+        if idle:
+            d["unused_ranks"] = idle
     if path:
         with open(path, "w") as f:
             json.dump(d, f, indent=4)

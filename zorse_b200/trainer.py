@@ -20,6 +20,7 @@ import torch.distributed as dist
 
 from .config.training_config import PipelineConfig, dtype_from_str
 from .engine.zero import AdamConfig, EngineConfig, Streams
+from .models import registry
 from .ops.api import default_ops_for, get_ops
 from .parallel import groups as G
 from .parallel.p2p import GlooP2P, make_transport
@@ -78,7 +79,7 @@ class Trainer:
                                         streams=self.streams, split_parity=not is_regular(cfg))
         self.gloo_transport = GlooP2P(self.device, self.gloo_group) if both else None
         plans = create_static_comm_plans(cfg)
-        self.plan = plans[self.rank]
+        self.plan = plans.get(self.rank)     # None on a rank the plan leaves idle
         offload_act = cfg.activation_offload if opt.activation_offload is None else opt.activation_offload
         self.stages = [
             PipelineStage(cfg, st, rank=self.rank, device=self.device, ops=self.ops, engine_cfg=self.engine_cfg,
@@ -87,6 +88,8 @@ class Trainer:
                           activation_offload=bool(offload_act),
                           model_overrides=opt.model_overrides)
             for st in cfg.stages_of_rank(self.rank)]
+        self.spec = (self.stages[0].spec if self.stages else
+                     registry.get_spec(cfg.model_name, vocab=cfg.vocab_size, **(opt.model_overrides or {})))
         recompute = cfg.activation_recompute if opt.activation_recompute is None else opt.activation_recompute
         name = cfg.schedule or opt.schedule
         self.schedule = build_schedule(name, self.stages, cfg, recompute=recompute, pipeline_log=opt.pipeline_log)
@@ -100,7 +103,7 @@ class Trainer:
         cfg = self.cfg
         g = torch.Generator().manual_seed(cfg_seed(self.opt.seed if seed is None else seed))
         M, B, S = cfg.num_microbatches, cfg.microbatch_size, cfg.sequence_length
-        spec = self.stages[0].spec
+        spec = self.spec
         if spec.family == "vit":
             x = torch.randn(M, B, 3, spec.image, spec.image, generator=g)
             y = torch.randint(0, spec.classes, (M, B), generator=g)

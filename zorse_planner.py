@@ -59,7 +59,9 @@ def main(argv=None) -> int:
         print("no plan fits in memory", file=sys.stderr)
         return 1
     cfg = export_config(res, a.model_name, a.global_batch_size, a.sequence_length, a.vocab_size, a.autocast_dtype,
-                        a.reduce_dtype, a.output_file)
+                        a.reduce_dtype, a.output_file, total_ranks=int(data.get("total_gpus", 0)) or None)
+    if cfg.get("unused_ranks"):
+        print(f"ranks {cfg['unused_ranks']} own no stage (too slow to be given a layer); they idle during training")
     print(f"best: {len(res.stages)} stages, microbatch {res.microbatch_size}, interleave {res.interleave_degree}, "
           f"predicted {res.latency_ms:.2f} ms -> {a.output_file}")
     if a.draw:
