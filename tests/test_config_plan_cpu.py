@@ -217,6 +217,7 @@ def test_bench_plans_are_valid_configs_and_deadlock_free():
 def test_planner_lists_gpus_it_leaves_without_a_stage():
     """One fast GPU next to very slow ones on another machine: the slow group may get no layer;
     its ranks are then declared idle instead of silently missing from the config."""
+    from zorse_b200.config.training_config import parse_pipeline_dict
     from zorse_b200.planner.plan import export_config, plan
 
     def gpu(rank, name, mem, machine, idx):
