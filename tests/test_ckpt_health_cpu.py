@@ -142,3 +142,51 @@ def test_cli_watchdog_names_the_rank_that_stopped(tmp_path):
     assert r.returncode != 0
     assert "[watchdog] rank 0: no progress" in out, out[-3000:]
     assert "ranks behind or silent: [1]" in out, out[-3000:]
+
+
+def test_read_range_against_synthetic_shard_files(tmp_path):
+    """Property check of the re-sharding reader: units with random padded sizes and random (equal
+    or unequal) shard boundaries, files filled so that element i of tensor `which` of unit u holds
+    u * 1e6 + which * 1e5 + i; any range read back must reproduce exactly those values."""
+    import random
+
+    import numpy as np
+
+    from zorse_b200.ckpt.reader import _file_offsets, read_range
+
+    rng = random.Random(0)
+    for trial in range(20):
+        d = tmp_path / f"t{trial}"
+        d.mkdir()
+        R = rng.randint(1, 4)
+        ranks = rng.sample(range(16), R)
+        units = []
+        for gid in range(rng.randint(1, 5)):
+            n = rng.randint(R, 40) * 8
+            if rng.random() < 0.5:
+                cuts = sorted(rng.sample(range(8, n, 8), R - 1)) if R > 1 and n // 8 > R else [n * (i + 1) // R // 8 * 8 for i in range(R - 1)]
+                offs = [0] + cuts + [n]
+                unit = {"stage": 0, "gid": gid, "numel": n - rng.randint(0, 7), "padded": n, "shard_ranks": ranks,
+                        "shard_numel": max(b - a for a, b in zip(offs, offs[1:])), "shard_offsets": offs}
+            else:
+                n = (n // (8 * R)) * 8 * R or 8 * R
+                unit = {"stage": 0, "gid": gid, "numel": n, "padded": n, "shard_ranks": ranks, "shard_numel": n // R}
+            units.append(unit)
+        meta = {"format_version": 1, "units": units}
+        for idx, r in enumerate(ranks):
+            blob = []
+            for u in units:
+                bd = u.get("shard_offsets") or [i * u["shard_numel"] for i in range(R + 1)]
+                lo, hi = bd[idx], bd[idx + 1]
+                for which in range(3):
+                    blob.append((u["gid"] * 1e6 + which * 1e5 + np.arange(lo, hi)).astype("<f4").tobytes())
+            (d / f"stage0_rank{r}.bin").write_bytes(b"".join(blob))
+        offsets = _file_offsets(meta)
+        for u in units:
+            for _ in range(6):
+                a = rng.randint(0, u["padded"] - 1)
+                b = rng.randint(a + 1, u["padded"])
+                which = rng.randint(0, 2)
+                got = read_range(str(d), meta, offsets, u, which, a, b)
+                want = torch.from_numpy((u["gid"] * 1e6 + which * 1e5 + np.arange(a, b)).astype("float32"))
+                assert torch.equal(got, want), (trial, u, which, a, b)
