@@ -240,3 +240,18 @@ def test_planner_lists_gpus_it_leaves_without_a_stage():
     assert cfg.world_size == 4
     named = {r for s in cfg.stages for r in s.gpu_ranks}
     assert named | set(cfg.unused_ranks) == {0, 1, 2, 3} and not (named & set(cfg.unused_ranks))
+
+
+@settings(max_examples=200, deadline=None)
+@given(st.integers(1, 8), st.integers(1, 64), st.lists(st.floats(0.01, 100.0), min_size=8, max_size=8))
+def test_shard_bounds_properties(R, blocks_per_rank, ratios):
+    """Any positive ratios: offsets start at 0, end at n, are aligned, strictly increasing (every
+    rank keeps at least one block), and equal ratios give equal shards."""
+    from zorse_b200.engine.zero import shard_bounds
+    from zorse_b200.models.layers import ALIGN
+
+    n = R * blocks_per_rank * ALIGN
+    b = shard_bounds(n, R, ratios[:R])
+    assert b[0] == 0 and b[-1] == n and len(b) == R + 1
+    assert all(x % ALIGN == 0 for x in b) and all(y > x for x, y in zip(b, b[1:]))
+    assert shard_bounds(n, R, [1.0] * R) == shard_bounds(n, R)
