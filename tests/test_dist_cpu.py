@@ -210,3 +210,15 @@ def test_idle_rank_left_out_by_the_planner():
     _check(res, cfg)
     with pytest.raises(ValueError, match="0 .. world_size - 1"):
         parse_pipeline_dict(tiny_cfg(pipe))            # rank 1 missing and not declared idle
+
+
+@pytest.mark.parametrize("schedule", ["zero2", "1f1b"])
+def test_rank_without_microbatches_joins_reductions_in_peer_order(schedule):
+    """Stage 0 has two replicas of which one runs no microbatch at all (a very slow GPU): it must
+    still take part in every gradient all-reduce, in the same layer order as its peer."""
+    pipe = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [0, 4], "layer_partition": [0, 1], "zero_config": [[0], [1]]},
+            {"gpu_ranks": [2], "num_microbatches_per_rank": [4], "layer_partition": [1, 2], "zero_config": [[2]]},
+            {"gpu_ranks": [3, 4], "num_microbatches_per_rank": [3, 1], "layer_partition": [2, 4], "zero_config": [[3], [4]]}]
+    cfg = tiny_cfg(pipe, gbs=8, mbs=2)
+    res = run_workers(5, _worker, cfg, {"schedule": schedule}, 2)
+    _check(res, cfg)

@@ -88,8 +88,10 @@ class InterleavedOneFOneBSchedule(ScheduleBase):
         for k in range(T - warm, T):
             bwd(k)
         if M == 0:
-            for st in sts:
-                for u in st.engine.units:
+            # no microbatches: join the reductions in the order the peers reach them (chunks from the
+            # last to the first, layers from the last to the first)
+            for st in reversed(sts):
+                for u in reversed(st.engine.units):
                     u.grad_views()
                     u.reduce_grads()
         loss = None

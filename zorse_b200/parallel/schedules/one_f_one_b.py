@@ -83,7 +83,9 @@ class OneFOneBSchedule(ScheduleBase):
             for i in range(M - warm, M):
                 bwd(i)
         if M == 0:
-            for u in units:
+            # a rank without microbatches still joins every reduction, in the order its peers use
+            # (last layer first)
+            for u in reversed(units):
                 u.grad_views()
                 u.reduce_grads()
         st.flush()

@@ -95,7 +95,9 @@ class Zero2Schedule(ScheduleBase):
                     self._ev("log_backward_send", st, 0, mbl)
                     st.send_bwd(mbl, dy)
         if M == 0:
-            for u in units:
+            # a rank without microbatches still joins every reduction, in the order its peers use
+            # (last layer first)
+            for u in reversed(units):
                 u.grad_views()
                 u.reduce_grads()
         if held:
