@@ -222,3 +222,15 @@ def test_rank_without_microbatches_joins_reductions_in_peer_order(schedule):
     cfg = tiny_cfg(pipe, gbs=8, mbs=2)
     res = run_workers(5, _worker, cfg, {"schedule": schedule}, 2)
     _check(res, cfg)
+
+
+@pytest.mark.parametrize("schedule", ["layer_major", "zero2"])
+def test_consecutive_stages_on_the_same_ranks(schedule):
+    """Two stages on one rank group (an interleaved plan with a single group): a microbatch's next
+    owner can be the sending rank itself; such hand-offs stay local instead of going through a
+    transport that cannot send to itself."""
+    pipe = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [1, 3], "layer_partition": [0, 2], "zero_config": [[0, 1]]},
+            {"gpu_ranks": [0, 1], "num_microbatches_per_rank": [1, 3], "layer_partition": [2, 4], "zero_config": [[0, 1]]}]
+    cfg = tiny_cfg(pipe, gbs=8, mbs=2)
+    res = run_workers(2, _worker, cfg, {"schedule": schedule, "optimizer_in_backward": True}, 2)
+    _check(res, cfg)

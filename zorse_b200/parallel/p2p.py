@@ -151,6 +151,28 @@ class GlooP2P:
         self._pending.clear()
 
 
+class LocalMailbox:
+    """Hand-off between two stages of the same rank (a plan may put consecutive stages on one rank
+    group, so a microbatch's next owner can be the rank itself).  Neither NCCL nor Gloo sends to the
+    calling rank; the tensor simply stays where it is: producer and consumer both run on the rank's
+    compute stream, in program order."""
+
+    def __init__(self):
+        self.box: dict = {}
+
+    def send(self, t, tag: int) -> Handle:
+        self.box[tag] = t
+        return Handle(lambda: None)
+
+    def recv(self, tag: int) -> Handle:
+        def wait():
+            if tag not in self.box:
+                raise RuntimeError(f"local hand-off {tag} is received before it was sent (schedule order)")
+            return self.box.pop(tag)
+
+        return Handle(wait)
+
+
 class LoopbackP2P:
     """Mailbox shared by simulated ranks of one process: {(src, dst, tag): tensor}."""
 

@@ -164,13 +164,17 @@ def record_programs(cfg, schedule_name: str, model_overrides: Optional[dict] = N
     g = torch.Generator().manual_seed(0)
     M, B, S = cfg.num_microbatches, cfg.microbatch_size, cfg.sequence_length
     inputs = {i: torch.randint(0, cfg.vocab_size, (B, S), generator=g) for i in range(M)}
+    from .p2p import LocalMailbox
+
     for r in sorted(plans):
         tp = RecordingTransport(r)
+        box = LocalMailbox()
         ecfg = EngineConfig(compute_dtype=torch.float32, reduce_dtype=torch.float32)
         streams = Streams(dev)
         stages = [PipelineStage(cfg, st, rank=r, device=dev, ops=ops, engine_cfg=ecfg,
                                 groups=StageGroups(Group((r,)), Group((r,))), streams=streams,
-                                pattern=plans[r].stages[st.stage_id], transport=tp, model_overrides=model_overrides)
+                                pattern=plans[r].stages[st.stage_id], transport=tp, model_overrides=model_overrides,
+                                local_mailbox=box)
                   for st in cfg.stages_of_rank(r)]
         sched = build_schedule(schedule_name, stages, cfg, **schedule_kw)
         sched.step(0, inputs, inputs)

@@ -18,6 +18,7 @@ from .groups import StageGroups
 from ..utils import canary
 from ..utils import stream_check as SC
 from ..utils.ranges import phase
+from .p2p import LocalMailbox
 from .p2p_plan import StageCommPattern, is_regular
 
 
@@ -83,7 +84,8 @@ class ActivationStash:
 class PipelineStage:
     def __init__(self, cfg: PipelineConfig, st: StageConfig, *, rank: int, device: torch.device, ops,
                  engine_cfg: EngineConfig, groups: StageGroups, streams: Streams, pattern: StageCommPattern,
-                 transport, gloo_transport=None, activation_offload: bool = False, model_overrides: Optional[dict] = None):
+                 transport, gloo_transport=None, activation_offload: bool = False, model_overrides: Optional[dict] = None,
+                 local_mailbox=None):
         self.cfg, self.st, self.rank, self.device, self.ops = cfg, st, rank, device, ops
         self.stage_id = st.stage_id
         self.num_stages = len(cfg.stages)
@@ -105,6 +107,7 @@ class PipelineStage:
         self.pos = [s.stage_id for s in cfg.stages].index(st.stage_id)
         self.transport = transport
         self.gloo_transport = gloo_transport
+        self.local = local_mailbox if local_mailbox is not None else LocalMailbox()
         self.microbatches = list(pattern.microbatches)  # global ids, increasing
         self.M = len(self.microbatches)
         self.B, self.S, self.hidden = cfg.microbatch_size, cfg.sequence_length, self.spec.hidden
@@ -169,21 +172,29 @@ class PipelineStage:
 
     def recv_fwd(self, mbl: int):
         src, tag = self.pattern.fwd_recv[mbl]
+        if src == self.rank:
+            return self.local.recv(tag)
         with phase("p2p.recv_act"):
             return self.boundary_transport(False).recv(self.act_shape(), self.act_dtype, src, tag, self._kind("act", False))
 
     def send_fwd(self, mbl: int, y: torch.Tensor):
         dst, tag = self.pattern.fwd_send[mbl]
+        if dst == self.rank:
+            return self.local.send(y, tag)
         with phase("p2p.send_act"):
             return self.boundary_transport(True).send(y, dst, tag, self._kind("act", True))
 
     def recv_bwd(self, mbl: int):
         src, tag = self.pattern.bwd_recv[mbl]
+        if src == self.rank:
+            return self.local.recv(tag)
         with phase("p2p.recv_grad"):
             return self.boundary_transport(True).recv(self.act_shape(), self.act_dtype, src, tag, self._kind("grad", True))
 
     def send_bwd(self, mbl: int, dx: torch.Tensor):
         dst, tag = self.pattern.bwd_send[mbl]
+        if dst == self.rank:
+            return self.local.send(dx, tag)
         with phase("p2p.send_grad"):
             return self.boundary_transport(False).send(dx, dst, tag, self._kind("grad", False))
 

@@ -23,7 +23,7 @@ from .engine.zero import AdamConfig, EngineConfig, Streams
 from .models import registry
 from .ops.api import default_ops_for, get_ops
 from .parallel import groups as G
-from .parallel.p2p import GlooP2P, make_transport
+from .parallel.p2p import GlooP2P, LocalMailbox, make_transport
 from .parallel.p2p_plan import create_static_comm_plans, is_regular
 from .parallel.schedules import build_schedule
 from .parallel.stage import PipelineStage
@@ -81,12 +81,13 @@ class Trainer:
         plans = create_static_comm_plans(cfg)
         self.plan = plans.get(self.rank)     # None on a rank the plan leaves idle
         offload_act = cfg.activation_offload if opt.activation_offload is None else opt.activation_offload
+        mailbox = LocalMailbox()     # hand-offs between two stages of this rank never touch a transport
         self.stages = [
             PipelineStage(cfg, st, rank=self.rank, device=self.device, ops=self.ops, engine_cfg=self.engine_cfg,
                           groups=stage_groups[st.stage_id], streams=self.streams, pattern=self.plan.stages[st.stage_id],
                           transport=self.transport, gloo_transport=self.gloo_transport,
                           activation_offload=bool(offload_act),
-                          model_overrides=opt.model_overrides)
+                          model_overrides=opt.model_overrides, local_mailbox=mailbox)
             for st in cfg.stages_of_rank(self.rank)]
         self.spec = (self.stages[0].spec if self.stages else
                      registry.get_spec(cfg.model_name, vocab=cfg.vocab_size, **(opt.model_overrides or {})))
