@@ -174,3 +174,40 @@ def test_planned_1f1b_order_equals_the_classic_one_on_a_regular_chain():
         classic += [("B", i) for i in range(8 - warm, 8)]
         assert order[pos] == classic
     assert not is_regular(_irregular_cfg(*IRREGULAR[0]))
+
+
+def test_planned_1f1b_order_properties_on_random_plans():
+    """For random widths and microbatch counts (zeros included): every rank's order contains each
+    of its microbatches once forward and once backward, both in increasing order, forward first,
+    and never more than P - s (+ slack) forwards in flight."""
+    import random
+
+    from zorse_b200.parallel.p2p_plan import plan_1f1b_order
+
+    rng = random.Random(0)
+    for _ in range(150):
+        P = rng.randint(1, 7)
+        widths = [rng.randint(1, 4) for _ in range(P)]
+        M = rng.randint(1, 14)
+        counts = []
+        for w in widths:
+            cuts = sorted(rng.randint(0, M) for _ in range(w - 1))
+            counts.append([b - a for a, b in zip([0] + cuts, cuts + [M])])
+        cfg = _irregular_cfg(widths, counts)
+        order = plan_1f1b_order(cfg)
+        for s, st in enumerate(cfg.stages):
+            for r, n in zip(st.gpu_ranks, st.num_microbatches_per_rank):
+                ops = order[r]
+                assert [i for op, i in ops if op == "F"] == list(range(n))
+                assert [i for op, i in ops if op == "B"] == list(range(n))
+                inflight = peak = 0
+                seen_f = set()
+                for op, i in ops:
+                    if op == "F":
+                        seen_f.add(i)
+                        inflight += 1
+                    else:
+                        assert i in seen_f
+                        inflight -= 1
+                    peak = max(peak, inflight)
+                assert peak <= P - s + M
