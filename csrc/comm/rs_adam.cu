@@ -25,6 +25,8 @@ constexpr int MAX_R = 8;
 
 struct RsAdamParams {
   const void* grad[MAX_R];  // bucket base of every rank of the group (own one included)
+  const void* grad_mc;      // NVLS variants: the buckets' multicast address (one load returns the sum over all ranks)
+  __nv_bfloat16* p16_mc;    // push variant: multicast address of this rank's shard inside the unsharded buffers
   int* flags[MAX_R];        // flag block of every rank: [3][R] ints (ready, done, version)
   int R, r;
   long shard_n;             // elements per shard
@@ -54,13 +56,52 @@ template <> struct GradVec<__nv_bfloat16> {
   static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) { unpack(ld_v4_relaxed_sys(p), f); }
 };
 
-// EARLY = false: the measured kernel (peer loads one after another, then the optimizer state).
-// EARLY = true (candidate, selected with zb_set_rs_adam_variant(1)): the optimizer state and all
+// In-switch reduction: one multimem.ld_reduce on the multicast address of the buckets returns the
+// sum over all ranks of the group (NVSwitch adds the R copies; bf16 inputs are accumulated in fp32
+// and returned as bf16), so 1/R of the bytes of the peer-load variants arrive at this GPU.
+template <typename GT> struct NvlsVec;
+template <> struct NvlsVec<float> {
+  static __device__ __forceinline__ uint4 load(const void* mc) {
+    uint4 u;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(mc) : "memory");
+    return u;
+  }
+};
+template <> struct NvlsVec<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 load(const void* mc) {
+    uint4 u;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(mc) : "memory");
+    return u;
+  }
+};
+
+__device__ __forceinline__ void multimem_st_v4(void* mc, const uint4& u) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(u.x), "r"(u.y), "r"(u.z),
+               "r"(u.w)
+               : "memory");
+}
+__device__ __forceinline__ void multimem_st_v2(void* mc, const uint2& u) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc), "r"(u.x), "r"(u.y) : "memory");
+}
+
+enum : int { RS_PLAIN = 0, RS_EARLY = 1, RS_NVLS = 2, RS_NVLS_PUSH = 3 };
+
+// MODE = RS_PLAIN: the measured kernel (peer loads one after another, then the optimizer state).
+// MODE = RS_EARLY (candidate, selected with zb_set_rs_adam_variant(1)): the optimizer state and all
 // R slices are requested before anything is consumed, so one NVLink round trip covers them all.
-template <typename GT, bool EARLY>
+// MODE = RS_NVLS (candidate, zb_rs_adam_nvls): the slice is reduced inside NVSwitch.
+// MODE = RS_NVLS_PUSH (candidate, zb_rs_adam_nvls with p16_mc): as RS_NVLS, and the refreshed bf16
+// shard is stored through the multicast address of the unsharded parameter buffers, so it lands in
+// every rank's copy (this rank's included) and the next step needs no all-gather: reduce-scatter,
+// optimizer and all-gather are this one kernel.  Safe because a rank announces `ready` only after
+// its last use of the unit's parameters in the step; `version` tells the peers that the shard arrived.
+template <typename GT, int MODE>
 __global__ void __launch_bounds__(256)
 rs_adam_kernel(const RsAdamParams p) {
   constexpr int N = GradVec<GT>::N;
+  constexpr bool EARLY = MODE == RS_EARLY;
   __shared__ int s_ok;
   // 1. announce that this rank's bucket is complete (the launch is stream-ordered after the
   //    last wgrad kernel of the unit), then wait for everybody else's announcement.
@@ -85,7 +126,15 @@ rs_adam_kernel(const RsAdamParams p) {
     float pm[N], mm[N], vv[N];
 #pragma unroll
     for (int k = 0; k < N; ++k) g[k] = 0.f;
-    if (EARLY) {
+    if (MODE == RS_NVLS || MODE == RS_NVLS_PUSH) {
+#pragma unroll
+      for (int k = 0; k < N; k += 4) {
+        *reinterpret_cast<float4*>(pm + k) = *reinterpret_cast<const float4*>(p.master + i * N + k);
+        *reinterpret_cast<float4*>(mm + k) = *reinterpret_cast<const float4*>(p.m + i * N + k);
+        *reinterpret_cast<float4*>(vv + k) = *reinterpret_cast<const float4*>(p.v + i * N + k);
+      }
+      GradVec<GT>::unpack(NvlsVec<GT>::load(static_cast<const GT*>(p.grad_mc) + lo + i * N), g);
+    } else if (EARLY) {
 #pragma unroll
       for (int k = 0; k < N; k += 4) {
         *reinterpret_cast<float4*>(pm + k) = *reinterpret_cast<const float4*>(p.master + i * N + k);
@@ -137,9 +186,12 @@ rs_adam_kernel(const RsAdamParams p) {
       uint4 u;
       u.x = pack_bf16x2(pm[0], pm[1]); u.y = pack_bf16x2(pm[2], pm[3]);
       u.z = pack_bf16x2(pm[4], pm[5]); u.w = pack_bf16x2(pm[6], pm[7]);
-      *reinterpret_cast<uint4*>(p.p16 + i * N) = u;
+      if (MODE == RS_NVLS_PUSH) multimem_st_v4(p.p16_mc + i * N, u);
+      else *reinterpret_cast<uint4*>(p.p16 + i * N) = u;
     } else {
-      *reinterpret_cast<uint2*>(p.p16 + i * N) = make_uint2(pack_bf16x2(pm[0], pm[1]), pack_bf16x2(pm[2], pm[3]));
+      const uint2 u = make_uint2(pack_bf16x2(pm[0], pm[1]), pack_bf16x2(pm[2], pm[3]));
+      if (MODE == RS_NVLS_PUSH) multimem_st_v2(p.p16_mc + i * N, u);
+      else *reinterpret_cast<uint2*>(p.p16 + i * N) = u;
     }
   }
 
@@ -185,22 +237,18 @@ peer_pull_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long n1
 
 static int g_rs_adam_variant = 0;
 
-extern "C" {
-
-// 0 = measured kernel, 1 = candidate that requests the optimizer state and all R slices up front.
-void zb_set_rs_adam_variant(int v) { g_rs_adam_variant = v; }
-
-// grad_ptrs / flag_ptrs: host arrays of R device pointers (peer-mapped), ordered by rank in
-// the shard group. counter: a zeroed device int owned by the caller.
-int zb_rs_adam(const void* const* grad_ptrs, int* const* flag_ptrs, int R, int r, long shard_n, float* master,
-               float* m, float* v, void* p16, float lr, float beta1, float beta2, float eps, float weight_decay,
-               int step, float grad_scale, int grad_f32, int epoch, unsigned int* counter, int max_blocks,
-               double wait_seconds, int* status, cudaStream_t stream) {
+static int rs_adam_launch(const void* const* grad_ptrs, const void* grad_mc, void* p16_mc, int* const* flag_ptrs, int R, int r,
+                          long shard_n, float* master, float* m, float* v, void* p16, float lr, float beta1,
+                          float beta2, float eps, float weight_decay, int step, float grad_scale, int grad_f32,
+                          int epoch, unsigned int* counter, int max_blocks, double wait_seconds, int* status,
+                          cudaStream_t stream) {
   using namespace zb;
   if (R < 1 || R > MAX_R) ZB_FAIL(-1, "rs_adam: group size %d unsupported (1..%d)", R, MAX_R);
   if (shard_n % 8 != 0) ZB_FAIL(-1, "rs_adam: shard size %ld not a multiple of 8", shard_n);
   RsAdamParams p;
-  for (int i = 0; i < R; ++i) { p.grad[i] = grad_ptrs[i]; p.flags[i] = flag_ptrs[i]; }
+  for (int i = 0; i < R; ++i) { p.grad[i] = grad_ptrs ? grad_ptrs[i] : nullptr; p.flags[i] = flag_ptrs[i]; }
+  p.grad_mc = grad_mc;
+  p.p16_mc = static_cast<__nv_bfloat16*>(p16_mc);
   p.R = R; p.r = r; p.shard_n = shard_n;
   p.master = master; p.m = m; p.v = v; p.p16 = static_cast<__nv_bfloat16*>(p16);
   p.lr = lr; p.beta1 = beta1; p.beta2 = beta2; p.eps = eps; p.weight_decay = weight_decay;
@@ -215,15 +263,54 @@ int zb_rs_adam(const void* const* grad_ptrs, int* const* flag_ptrs, int R, int r
   if (max_blocks > 0 && max_blocks < blocks) blocks = max_blocks;
   long need = (shard_n / (grad_f32 ? 4 : 8) + 255) / 256;
   if (need < blocks) blocks = int(need < 1 ? 1 : need);
-  if (g_rs_adam_variant == 1) {
-    if (grad_f32) rs_adam_kernel<float, true><<<blocks, 256, 0, stream>>>(p);
-    else rs_adam_kernel<__nv_bfloat16, true><<<blocks, 256, 0, stream>>>(p);
+  if (grad_mc != nullptr && p16_mc != nullptr) {
+    if (grad_f32) rs_adam_kernel<float, RS_NVLS_PUSH><<<blocks, 256, 0, stream>>>(p);
+    else rs_adam_kernel<__nv_bfloat16, RS_NVLS_PUSH><<<blocks, 256, 0, stream>>>(p);
+  } else if (grad_mc != nullptr) {
+    if (grad_f32) rs_adam_kernel<float, RS_NVLS><<<blocks, 256, 0, stream>>>(p);
+    else rs_adam_kernel<__nv_bfloat16, RS_NVLS><<<blocks, 256, 0, stream>>>(p);
+  } else if (g_rs_adam_variant == 1) {
+    if (grad_f32) rs_adam_kernel<float, RS_EARLY><<<blocks, 256, 0, stream>>>(p);
+    else rs_adam_kernel<__nv_bfloat16, RS_EARLY><<<blocks, 256, 0, stream>>>(p);
   } else {
-    if (grad_f32) rs_adam_kernel<float, false><<<blocks, 256, 0, stream>>>(p);
-    else rs_adam_kernel<__nv_bfloat16, false><<<blocks, 256, 0, stream>>>(p);
+    if (grad_f32) rs_adam_kernel<float, RS_PLAIN><<<blocks, 256, 0, stream>>>(p);
+    else rs_adam_kernel<__nv_bfloat16, RS_PLAIN><<<blocks, 256, 0, stream>>>(p);
   }
   ZB_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+extern "C" {
+
+// 0 = measured kernel, 1 = candidate that requests the optimizer state and all R slices up front.
+void zb_set_rs_adam_variant(int v) { g_rs_adam_variant = v; }
+
+// grad_ptrs / flag_ptrs: host arrays of R device pointers (peer-mapped), ordered by rank in
+// the shard group. counter: a zeroed device int owned by the caller.
+int zb_rs_adam(const void* const* grad_ptrs, int* const* flag_ptrs, int R, int r, long shard_n, float* master,
+               float* m, float* v, void* p16, float lr, float beta1, float beta2, float eps, float weight_decay,
+               int step, float grad_scale, int grad_f32, int epoch, unsigned int* counter, int max_blocks,
+               double wait_seconds, int* status, cudaStream_t stream) {
+  return rs_adam_launch(grad_ptrs, nullptr, nullptr, flag_ptrs, R, r, shard_n, master, m, v, p16, lr, beta1, beta2, eps,
+                        weight_decay, step, grad_scale, grad_f32, epoch, counter, max_blocks, wait_seconds, status,
+                        stream);
+}
+
+// Same update with the gradient slice reduced inside NVSwitch: grad_mc is the multicast address
+// of the group's buckets (every rank's bucket bound at the same offset of one multicast object).
+// The summation order is the switch's, so results can differ from zb_rs_adam in the last bit.
+// p16_mc (optional): multicast address of this rank's shard inside the group's unsharded parameter
+// buffers; when given, the refreshed bf16 shard is stored there (reaching every rank) instead of p16.
+int zb_rs_adam_nvls(const void* grad_mc, void* p16_mc, int* const* flag_ptrs, int R, int r, long shard_n, float* master, float* m,
+                    float* v, void* p16, float lr, float beta1, float beta2, float eps, float weight_decay, int step,
+                    float grad_scale, int grad_f32, int epoch, unsigned int* counter, int max_blocks,
+                    double wait_seconds, int* status, cudaStream_t stream) {
+  if (grad_mc == nullptr || (reinterpret_cast<uintptr_t>(grad_mc) & 15))
+    ZB_FAIL(-1, "rs_adam_nvls: no multicast address for the gradient buckets (or not 16-byte aligned)");
+  if (reinterpret_cast<uintptr_t>(p16_mc) & 15) ZB_FAIL(-1, "rs_adam_nvls: parameter multicast address not 16-byte aligned");
+  return rs_adam_launch(nullptr, grad_mc, p16_mc, flag_ptrs, R, r, shard_n, master, m, v, p16, lr, beta1, beta2, eps,
+                        weight_decay, step, grad_scale, grad_f32, epoch, counter, max_blocks, wait_seconds, status,
+                        stream);
 }
 
 int zb_wait_flags(const int* flags, int R, int which, int epoch, double wait_seconds, int* status,

@@ -72,8 +72,32 @@ def fused_kernels(variant: int = 0):
         k.adam_step(rm, rmm, rv, ref_g, rp16, step=1, grad_scale=0.5, **hyper)
         counter = torch.zeros(1, dtype=torch.int32, device=dev)
         dist.barrier()
-        k.rs_adam([int(x) for x in hg.buffer_ptrs], [int(x) for x in hf.buffer_ptrs], R, rank, sn, master, m, v, p16,
-                  step=1, grad_scale=0.5, grad_f32=gdt == torch.float32, epoch=1, counter=counter, **hyper)
+        kw = dict(step=1, grad_scale=0.5, grad_f32=gdt == torch.float32, epoch=1, counter=counter, **hyper)
+        if variant in (2, 3):
+            mc = int(getattr(hg, "multicast_ptr", 0) or 0)
+            if mc == 0:
+                print("no NVLS multicast for this group: in-switch variant not exercised")
+                return
+            full = hfp = None
+            if variant == 3:     # the new shard goes to every rank's unsharded buffer from inside the kernel
+                full = symm.empty(n, dtype=torch.bfloat16, device=dev)
+                full.zero_()
+                torch.cuda.synchronize()
+                hfp = symm.rendezvous(full, dist.group.WORLD)
+            k.rs_adam_nvls(mc, [int(x) for x in hf.buffer_ptrs], R, rank, sn, master, m, v, p16,
+                           p16_mc=0 if full is None else int(hfp.multicast_ptr) + rank * sn * 2, **kw)
+            if full is not None:
+                k.wait_flags(flags, R, 2, 1)          # every owner's version flag: its shard has arrived here
+                torch.cuda.synchronize()
+                k.check_status()
+                want = torch.empty(n, dtype=torch.bfloat16, device=dev)
+                dist.all_gather_into_tensor(want, rp16)
+                err = (full.float() - want.float()).abs().max().item()
+                assert err < 4e-2, f"pushed parameters differ from the gathered reference by {err}"
+                p16.copy_(full[rank * sn:(rank + 1) * sn])
+        else:
+            k.rs_adam([int(x) for x in hg.buffer_ptrs], [int(x) for x in hf.buffer_ptrs], R, rank, sn, master, m, v,
+                      p16, **kw)
         k.wait_flags(flags, R, 1, 1)
         torch.cuda.synchronize()
         k.check_status()
@@ -119,7 +143,7 @@ def main():
 
     dist_init()
     if case.startswith("fused_kernels"):
-        fused_kernels(1 if case.endswith("_v1") else 0)
+        fused_kernels(int(case[-1]) if case[-2:] in ("v1", "v2", "v3") else 0)
     else:
         losses, masters, tr = train_case(case)
         # same job with the other collectives mode must land on the same parameters

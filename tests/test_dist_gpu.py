@@ -17,8 +17,8 @@ def _ngpu():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-def _run(nproc, *args, timeout=600):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+def _run(nproc, *args, timeout=600, **extra_env):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT, **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", "29631", os.path.join(HERE, "gpu_dist_worker.py"), *args]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
@@ -37,9 +37,19 @@ CANDIDATES = os.environ.get("ZORSE_TEST_CANDIDATES") == "1"   # paths that have 
 
 
 @pytest.mark.skipif(_ngpu() < 2 or not CANDIDATES, reason="needs 2 GPUs and ZORSE_TEST_CANDIDATES=1")
-@pytest.mark.parametrize("case", ["dp2_uneven_library", "pp2_1f1b", "fused_kernels_v1"])
+@pytest.mark.parametrize("case", ["dp2_uneven_library", "pp2_1f1b", "fused_kernels_v1", "fused_kernels_v2",
+                                  "fused_kernels_v3"])
 def test_two_gpus_candidates(case):
     out = _run(2, case, timeout=300)
+    assert "WORKER_OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2 or not CANDIDATES, reason="needs 2 GPUs and ZORSE_TEST_CANDIDATES=1")
+@pytest.mark.parametrize("variant", ["2", "3"])
+def test_two_gpus_nvls_training(variant):
+    """Fused collectives with the in-switch reduction (2) and with the parameter push that replaces
+    the all-gather (3) must land on the parameters of the library-collectives run."""
+    out = _run(2, "dp2_fused", timeout=300, ZORSE_RS_ADAM_VARIANT=variant)
     assert "WORKER_OK" in out
 
 

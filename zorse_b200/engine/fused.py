@@ -20,6 +20,7 @@ sharded.  Replaces the NCCL calls at reference utils/patch.py:500-501, 585-589.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -33,6 +34,10 @@ from .zero import ZeroUnit
 # small chunks: every CTA copies one chunk at a time at 1/148 of the link rate, so a chunk is the
 # granularity at which weight rows become visible to the GEMM tiles waiting for them
 CHUNK_BYTES = 1 << 15
+# candidates of the reduce-scatter + Adam kernel that use NVSwitch multicast (csrc/comm/rs_adam.cu):
+# 2 = gradient slice summed inside the switch; 3 = as 2, and the refreshed bf16 shard is stored through
+# the multicast address of the unsharded buffers, so that no all-gather follows an update at all
+RS_ADAM_MODE = int(os.environ.get("ZORSE_RS_ADAM_VARIANT", "0"))
 
 
 @dataclass
@@ -95,6 +100,17 @@ class FusedZeroUnit(ZeroUnit):
         self.grad_ptrs = [int(h_grad.buffer_ptrs[q]) + off_grad for q in range(R)]
         self.flag_ptrs = [int(h_flag.buffer_ptrs[q]) + off_flag for q in range(R)]
         self._handles = (h_full, h_grad, h_flag)
+        self.grad_mc = self.shard_mc = 0
+        self.pushed_version = -1      # update whose shards the peers stored into this rank's buffer
+        if RS_ADAM_MODE in (2, 3):
+            mc_g = int(getattr(h_grad, "multicast_ptr", 0) or 0)
+            mc_f = int(getattr(h_full, "multicast_ptr", 0) or 0)
+            if mc_g == 0 or mc_f == 0:
+                raise RuntimeError("ZORSE_RS_ADAM_VARIANT=2/3 needs NVLS multicast, which this group's symmetric "
+                                   "memory does not provide")
+            self.grad_mc = mc_g + off_grad
+            if RS_ADAM_MODE == 3:
+                self.shard_mc = mc_f + off_full + r * sn * 2
         self.p_shard = self.full_sym[r * sn:(r + 1) * sn]
         self.full = self.full_sym
         self.cps = (sn * 2 + CHUNK_BYTES - 1) // CHUNK_BYTES
@@ -120,6 +136,12 @@ class FusedZeroUnit(ZeroUnit):
         if self.gathered_version == self.updates:
             return
         k = self.ops.k
+        if self.pushed_version == self.updates:
+            # every owner stored its refreshed shard into this rank's buffer from inside its optimizer
+            # kernel; what is left of the all-gather is the wait for their version flags
+            k.wait_flags(self.flags_sym, self.R, 2, self.updates)
+            self.gathered_version = self.updates
+            return
         self.gather_epoch += 1
         self.counters.all_gathers += 1
         lay, _ = self.layer.layout()
@@ -163,10 +185,17 @@ class FusedZeroUnit(ZeroUnit):
         cur = torch.cuda.current_stream()
         self.streams.comm.wait_stream(cur)
         with phase("zero.rs_adam_fused"), torch.cuda.stream(self.streams.comm):
-            k.rs_adam(self.grad_ptrs, self.flag_ptrs, self.R, self.r, self.shard_n, self.master, self.m, self.v,
-                      self.p_shard, lr=a.lr, beta1=a.beta1, beta2=a.beta2, eps=a.eps, weight_decay=a.weight_decay,
+            kw = dict(lr=a.lr, beta1=a.beta1, beta2=a.beta2, eps=a.eps, weight_decay=a.weight_decay,
                       step=self.step_count, grad_scale=gscale, grad_f32=self.cfg.reduce_dtype == torch.float32,
                       epoch=self.updates, counter=self.counter)
+            if self.grad_mc:
+                k.rs_adam_nvls(self.grad_mc, self.flag_ptrs, self.R, self.r, self.shard_n, self.master, self.m,
+                               self.v, self.p_shard, p16_mc=self.shard_mc, **kw)
+                if self.shard_mc:
+                    self.pushed_version = self.updates
+            else:
+                k.rs_adam(self.grad_ptrs, self.flag_ptrs, self.R, self.r, self.shard_n, self.master, self.m, self.v,
+                          self.p_shard, **kw)
             # the bucket may be cleared once every peer has read its slice of it
             k.wait_flags(self.flags_sym, self.R, 1, self.updates)
             self.grad_sym.zero_()
@@ -185,4 +214,4 @@ class FusedZeroUnit(ZeroUnit):
     def _after_update(self):
         self.full_sym[self.r * self.shard_n:(self.r + 1) * self.shard_n].copy_(self.master.to(torch.bfloat16))
         dist.barrier(group=self.shard_group.pg)
-        self.gathered_version = -1
+        self.gathered_version = self.pushed_version = -1

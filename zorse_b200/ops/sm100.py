@@ -405,6 +405,21 @@ def rs_adam(grad_ptrs, flag_ptrs, R: int, r: int, shard_elems: int, master, m, v
     _check(rc, "rs_adam")
 
 
+def rs_adam_nvls(grad_mc: int, flag_ptrs, R: int, r: int, shard_elems: int, master, m, v, p16, *, lr, beta1, beta2, eps,
+                 weight_decay, step, grad_scale, grad_f32: bool, epoch: int, counter: torch.Tensor,
+                 max_blocks: int = 0, wait_seconds: float = 2.0, p16_mc: int = 0):
+    """rs_adam with the gradient slice summed inside NVSwitch: grad_mc is the multicast address of the
+    group's gradient buckets (candidate; the switch's summation order, not the rank order).  With
+    p16_mc (multicast address of this rank's shard inside the unsharded parameter buffers) the new
+    bf16 shard is stored to every rank's buffer at once and p16 is left untouched."""
+    rc = lib().zb_rs_adam_nvls(c_void_p(int(grad_mc)), c_void_p(int(p16_mc)), _ptr_array(flag_ptrs), c_int(R), c_int(r), c_long(shard_elems),
+                               _p(master), _p(m), _p(v), _p(p16), c_float(lr), c_float(beta1), c_float(beta2),
+                               c_float(eps), c_float(weight_decay), c_int(step), c_float(grad_scale),
+                               c_int(int(grad_f32)), c_int(epoch), _p(counter), c_int(max_blocks),
+                               ctypes.c_double(wait_seconds), _p(status_word(master.device)), _stream())
+    _check(rc, "rs_adam_nvls")
+
+
 def set_rs_adam_variant(variant: int) -> None:
     """0: measured kernel; 1: candidate that requests the optimizer state and all slices up front."""
     lib().zb_set_rs_adam_variant(c_int(variant))

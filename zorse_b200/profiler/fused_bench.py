@@ -48,7 +48,7 @@ def main(argv=None):
     ap.add_argument("--out", default=None)
     ap.add_argument("--params", type=int, default=202_383_360)
     ap.add_argument("--tokens", type=int, default=4096)
-    ap.add_argument("--rs_adam_variant", type=int, default=0, help="1 = early-load candidate of the rs_adam kernel")
+    ap.add_argument("--rs_adam_variant", type=int, default=0, help="1 = early-load candidate of the rs_adam kernel, 2 = in-switch (NVLS) reduction candidate")
     a = ap.parse_args(argv)
     import torch.distributed._symmetric_memory as symm
 
@@ -80,11 +80,19 @@ def main(argv=None):
         g_sh = torch.empty(sn, dtype=gdt, device=dev)
         epoch = [0]
 
+        mc = int(getattr(hg, "multicast_ptr", 0) or 0)
+        if a.rs_adam_variant == 2 and mc == 0:
+            raise SystemExit("--rs_adam_variant 2 needs NVLS multicast; this group's symmetric memory has none")
+
         def fused():
             epoch[0] += 1
-            k.rs_adam([int(x) for x in hg.buffer_ptrs], [int(x) for x in hf.buffer_ptrs], R, rank, sn, master, m, v, p16,
-                      step=epoch[0], grad_scale=1.0, grad_f32=gdt == torch.float32, epoch=epoch[0], counter=counter,
+            kw = dict(step=epoch[0], grad_scale=1.0, grad_f32=gdt == torch.float32, epoch=epoch[0], counter=counter,
                       **hyper)
+            if a.rs_adam_variant == 2:
+                k.rs_adam_nvls(mc, [int(x) for x in hf.buffer_ptrs], R, rank, sn, master, m, v, p16, **kw)
+            else:
+                k.rs_adam([int(x) for x in hg.buffer_ptrs], [int(x) for x in hf.buffer_ptrs], R, rank, sn, master, m,
+                          v, p16, **kw)
             k.wait_flags(flags, R, 1, epoch[0])
 
         def library():
