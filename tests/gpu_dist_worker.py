@@ -9,7 +9,14 @@ from zorse_b200.trainer import Trainer, TrainerOptions
 
 
 def cfg_for(case, world):
-    if case.startswith("dp2"):
+    tp = 1
+    if case.startswith("tp2"):
+        # one lane (2 GPUs) or two ZeRO lanes (4 GPUs) of two tensor-parallel processes each
+        tp = 2
+        pipe = ([{"gpu_ranks": [0], "num_microbatches_per_rank": [4], "layer_partition": [0, 4], "zero_config": [[0]]}]
+                if world == 2 else
+                [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [3, 1], "layer_partition": [0, 4], "zero_config": [[0, 1]]}])
+    elif case.startswith("dp2"):
         pipe = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [3, 1], "layer_partition": [0, 4], "zero_config": [[0, 1]]}]
         if case == "dp2_uneven_library":
             pipe[0]["shard_ratio"] = [0.7, 0.3]
@@ -21,7 +28,7 @@ def cfg_for(case, world):
                 {"gpu_ranks": [2, 3], "num_microbatches_per_rank": [2, 2], "layer_partition": [2, 4], "zero_config": [[2, 3]]}]
     return parse_pipeline_dict({"model_name": "tiny_llama", "global_batch_size": 8, "microbatch_size": 2,
                                 "sequence_length": 256, "vocab_size": 2048, "autocast_dtype": "bfloat16",
-                                "reduce_dtype": "float32", "pipeline_config": pipe})
+                                "reduce_dtype": "float32", "pipeline_config": pipe, "tensor_parallel_size": tp})
 
 
 def train_case(case):
@@ -147,12 +154,13 @@ def main():
     else:
         losses, masters, tr = train_case(case)
         # same job with the other collectives mode must land on the same parameters
-        other = {"dp2_uneven_library": "dp2_library", "pp2_1f1b": "pp2", "pp2dp2_1f1b_library": "pp2dp2_library"}.get(case)
+        other = {"dp2_uneven_library": "dp2_library", "pp2_1f1b": "pp2", "pp2dp2_1f1b_library": "pp2dp2_library",
+                 "tp2_library": "dp2_library" if dist.get_world_size() == 2 else "pp2dp2_library"}.get(case)
         if case.endswith("fused") or other:
             l2, m2, _ = train_case(other or case.replace("fused", "library"))
             for a, b in zip(losses, l2):
                 assert abs(a - b) < 2e-2 * max(1.0, abs(b)), (losses, l2)
-            for gid in masters:
+            for gid in ({} if case.startswith("tp2") else masters):     # tensor-parallel slices have their own layout
                 err = (masters[gid] - m2[gid]).abs().max().item()
                 assert err < 5e-3, f"unit {gid}: fused vs library parameter difference {err}"
         assert losses[-1] < losses[0], losses

@@ -59,6 +59,19 @@ def test_four_gpus_1f1b():
     assert "WORKER_OK" in out
 
 
+@pytest.mark.skipif(_ngpu() < 2 or not CANDIDATES, reason="needs 2 GPUs and ZORSE_TEST_CANDIDATES=1")
+def test_tensor_parallel_two_gpus():
+    """One lane of two tensor-parallel processes trains like two data-parallel ranks on the same batch."""
+    out = _run(2, "tp2_library", timeout=300)
+    assert "WORKER_OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 4 or not CANDIDATES, reason="needs 4 GPUs and ZORSE_TEST_CANDIDATES=1")
+def test_tensor_parallel_four_gpus():
+    out = _run(4, "tp2_library", timeout=300)
+    assert "WORKER_OK" in out
+
+
 @pytest.mark.skipif(_ngpu() < 4, reason="needs 4 GPUs")
 @pytest.mark.parametrize("case", ["pp2dp2_library", "pp2dp2_fused"])
 def test_four_gpus(case):

@@ -1,0 +1,161 @@
+"""Tensor parallelism with sequence-parallel activations on CPU ranks (gloo): every combination with
+pipeline stages and ZeRO data parallelism must reproduce the single-process oracle (same loss, same
+parameters after two steps, once the slices are put back together)."""
+import pytest
+import torch
+
+from dist_utils import run_workers
+from test_dist_cpu import _oracle, tiny_cfg
+from zorse_b200.config.training_config import ConfigError, parse_pipeline_dict, to_dict
+
+
+def _worker(rank, world, cfg_dict, opts, steps):
+    from zorse_b200.trainer import Trainer, TrainerOptions
+
+    cfg = parse_pipeline_dict(cfg_dict)
+    tr = Trainer(cfg, TrainerOptions(backend="gloo", **opts))
+    batch = tr.synthetic_batch()
+    losses = [tr.global_loss(tr.train_step_from_host(batch)) for _ in range(steps)]
+    params = {u.gid: u.full_master()[: u.layer.layout()[1]].clone() for st in tr.stages for u in st.engine.units}
+    return {"losses": losses, "params": params, "tp_index": tr.tp_index, "lane": tr.lane,
+            "all_reduces": [c.all_reduces for c in tr.counters()]}
+
+
+def _check_tp(results, cfg_dict, steps=2, ptol=5e-4):
+    from zorse_b200.models import registry
+
+    cfg = parse_pipeline_dict(cfg_dict)
+    tp = cfg.tensor_parallel_size
+    spec = registry.get_spec(cfg.model_name, vocab=cfg.vocab_size)
+    want_losses, want_params = _oracle(cfg_dict, steps)
+    for res in results:
+        for a, b in zip(res["losses"], want_losses):
+            assert abs(a - b) < 2e-4, (res["losses"], want_losses)
+    # put the slices of every block back together, lane by lane
+    lanes = sorted({r["lane"] for r in results})
+    for lane in lanes:
+        mine = sorted((r for r in results if r["lane"] == lane), key=lambda r: r["tp_index"])
+        assert [r["tp_index"] for r in mine] == list(range(tp))
+        for gid in mine[0]["params"]:
+            if 1 <= gid <= spec.layers:
+                whole = torch.zeros_like(want_params[gid])
+                for r in mine:
+                    registry.make_block(spec, tp, r["tp_index"]).store_into_whole(r["params"][gid], whole)
+                got = [whole]
+            else:
+                got = [r["params"][gid] for r in mine]     # embedding / head: every process holds all of it
+            for g in got:
+                err = (g - want_params[gid][: g.numel()]).abs().max().item()
+                assert err < ptol, f"lane {lane} unit {gid}: max param error {err}"
+
+
+ONE_LANE = [{"gpu_ranks": [0], "num_microbatches_per_rank": [4], "layer_partition": [0, 4], "zero_config": [[0]]}]
+TWO_STAGES = [{"gpu_ranks": [0], "num_microbatches_per_rank": [4], "layer_partition": [0, 2], "zero_config": [[0]]},
+              {"gpu_ranks": [1], "num_microbatches_per_rank": [4], "layer_partition": [2, 4], "zero_config": [[1]]}]
+TWO_DP = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [2, 2], "layer_partition": [0, 4], "zero_config": [[0, 1]]}]
+
+
+@pytest.mark.parametrize("schedule,recompute", [("layer_major", None), ("1f1b", False), ("zero2", None)])
+def test_tp2_one_lane(schedule, recompute):
+    cfg = tiny_cfg(ONE_LANE, tensor_parallel_size=2)
+    res = run_workers(2, _worker, cfg, {"schedule": schedule, "activation_recompute": recompute}, 2)
+    _check_tp(res, cfg)
+    assert all(n > 0 for r in res for n in r["all_reduces"])      # norm / embedding / head gradients summed over the lane
+
+
+@pytest.mark.parametrize("schedule", ["layer_major", "1f1b"])
+def test_tp2_two_stages(schedule):
+    """2 stages x tp 2 = 4 processes; process l*2+t sends its rows to process (l+1)*2+t."""
+    cfg = tiny_cfg(TWO_STAGES, tensor_parallel_size=2)
+    res = run_workers(4, _worker, cfg, {"schedule": schedule}, 2)
+    _check_tp(res, cfg)
+
+
+@pytest.mark.parametrize("schedule,oib", [("layer_major", False), ("zero2", True)])
+def test_tp2_two_way_zero(schedule, oib):
+    """ZeRO shard groups connect the processes that hold the same slice: {0, 2} and {1, 3}."""
+    cfg = tiny_cfg(TWO_DP, tensor_parallel_size=2)
+    res = run_workers(4, _worker, cfg, {"schedule": schedule, "optimizer_in_backward": oib}, 2)
+    _check_tp(res, cfg)
+
+
+def test_tp_config_round_trip_and_errors():
+    cfg = parse_pipeline_dict(tiny_cfg(TWO_STAGES, tensor_parallel_size=4))
+    assert cfg.num_lanes == 2 and cfg.world_size == 8
+    assert to_dict(cfg)["tensor_parallel_size"] == 4
+    assert "tensor_parallel_size" not in to_dict(parse_pipeline_dict(tiny_cfg(TWO_STAGES)))
+    with pytest.raises(ConfigError):
+        parse_pipeline_dict(tiny_cfg(TWO_STAGES, tensor_parallel_size=0))
+
+
+def test_slices_tile_the_unsplit_block():
+    """take_slice / put_slice are inverse, the slices of all processes cover every parameter exactly once,
+    and replicated parameters are the ones reported for the lane-wide gradient sum."""
+    from zorse_b200.models import registry
+
+    spec = registry.get_spec("tiny_llama", vocab=512)
+    whole = registry.make_block(spec)
+    _, n = whole.layout()
+    ref = torch.arange(n, dtype=torch.float32)
+    back = torch.full((n,), -1.0)
+    tp = 2
+    for t in range(tp):
+        blk = registry.make_block(spec, tp, t)
+        flat = torch.empty(blk.layout()[1])
+        blk.load_from_whole(flat, ref)
+        blk.store_into_whole(flat, back)
+        rep = blk.tp_replicated_ranges()
+        lay, _ = blk.layout()
+        assert {o for o, _ in rep} == {lay["norm1_w"][0], lay["norm2_w"][0]}
+        assert blk.num_params() < whole.num_params()
+    lay, _ = whole.layout()
+    for name, (o, sh) in lay.items():
+        k = 1
+        for d in sh:
+            k *= d
+        assert torch.equal(back[o:o + k], ref[o:o + k]), name
+
+
+def test_checkpoint_across_tensor_parallel_widths(tmp_path):
+    """Saved with tp 2: resumes with tp 2, with tp 1 on two pipeline stages (blocks put back together
+    from their slices) and with tp 1 on two ZeRO ranks; saved with tp 1: resumes with tp 2."""
+    from test_ckpt_health_cpu import _load_and_step, _train_and_save
+    from test_dist_cpu import PIPE_1x2, PIPE_2x1
+
+    ck = str(tmp_path / "ck")
+    a = run_workers(2, _train_and_save, tiny_cfg(ONE_LANE, tensor_parallel_size=2), ck, 2)
+    b = run_workers(2, _load_and_step, tiny_cfg(ONE_LANE, tensor_parallel_size=2), ck, 2)
+    assert abs(a[0] - b[0]) < 1e-5, (a, b)
+    c = run_workers(2, _load_and_step, tiny_cfg(PIPE_2x1), ck, 2)
+    assert abs(a[0] - c[0]) < 1e-4, (a, c)
+    d = run_workers(2, _load_and_step, tiny_cfg(PIPE_1x2), ck, 2)
+    assert abs(a[0] - d[0]) < 1e-4, (a, d)
+    ck1 = str(tmp_path / "ck1")
+    e = run_workers(2, _train_and_save, tiny_cfg(PIPE_1x2), ck1, 2)
+    f = run_workers(4, _load_and_step, tiny_cfg(TWO_DP, tensor_parallel_size=2), ck1, 2)
+    assert abs(e[0] - f[0]) < 1e-4, (e, f)
+
+
+def test_parallel_dims_layout_and_training():
+    """The four sizes give a valid config whose numbering inverts, and a 2 (shard) x 2 (tp) job from it
+    trains like the oracle."""
+    from zorse_b200.parallel.mesh import ParallelDims
+
+    dims = ParallelDims(dp_replicate=2, dp_shard=2, tp=2, pp=3)
+    assert dims.world_size == 24
+    d = dims.training_config("tiny_llama", 4, 16, 2, 32, vocab_size=512)
+    cfg = parse_pipeline_dict(d)
+    assert cfg.world_size == 24 and len(cfg.stages) == 3
+    assert cfg.stages[1].zero_config == ((4, 5), (6, 7))
+    seen = set()
+    for p in range(dims.world_size):
+        c = dims.coordinates(p)
+        assert p in dims.processes_of_lane(dims.lane(c["pp"], c["dp_replicate"], c["dp_shard"]))
+        seen.add(tuple(c.values()))
+    assert len(seen) == 24
+    with pytest.raises(ValueError):
+        ParallelDims(tp=0)
+    small = ParallelDims(dp_shard=2, tp=2).training_config("tiny_llama", 4, 8, 2, 32, vocab_size=512,
+                                                           autocast_dtype="float32", reduce_dtype="float32")
+    res = run_workers(4, _worker, small, {"schedule": "layer_major"}, 2)
+    _check_tp(res, small)

@@ -1,6 +1,8 @@
 """Checkpoint reader with re-sharding: a checkpoint written under one plan (stage split, DP
-width) can be loaded under another, because every unit is addressed by its global id and
-each rank reads the element ranges of the saved shards that overlap its new shard."""
+width, tensor-parallel width) can be loaded under another, because every unit is addressed by its
+global id and each rank reads the element ranges of the saved shards that overlap its new shard.
+When the tensor-parallel width changes, a block is first put back together from its saved slices
+and then cut for the new width."""
 from __future__ import annotations
 
 import json
@@ -36,8 +38,8 @@ def _bounds(unit: dict) -> list[int]:
 def _file_offsets(meta: dict) -> dict:
     """(stage, rank) -> {gid: byte offset of the unit's (master, m, v) block in that file}."""
     out: dict = {}
-    for stage in sorted({u["stage"] for u in meta["units"]}):
-        units = [u for u in meta["units"] if u["stage"] == stage]
+    for stage, tpi in sorted({(u["stage"], u.get("tp_index", 0)) for u in meta["units"]}):
+        units = [u for u in meta["units"] if u["stage"] == stage and u.get("tp_index", 0) == tpi]
         for idx, r in enumerate(units[0]["shard_ranks"]):
             off, table = 0, {}
             for u in units:
@@ -69,28 +71,58 @@ def read_range(directory: str, meta: dict, offsets: dict, unit: dict, which: int
     return out
 
 
+def _whole_block(directory, meta, offsets, saved: dict, gid: int, which: int, spec, saved_tp: int) -> torch.Tensor:
+    """State tensor `which` of block `gid` as the unsplit block lays it out, rebuilt from the saved slices."""
+    from ..models import registry
+
+    n = registry.make_block(spec).layout()[1]
+    if saved_tp == 1:
+        su = saved[(gid, 0)]
+        return read_range(directory, meta, offsets, su, which, 0, su["padded"])[:n].clone()
+    whole = torch.zeros(n, dtype=torch.float32)
+    for t in range(saved_tp):
+        su = saved[(gid, t)]
+        flat = read_range(directory, meta, offsets, su, which, 0, su["padded"])
+        registry.make_block(spec, saved_tp, t).store_into_whole(flat[:su["numel"]], whole)
+    return whole
+
+
 def load_checkpoint(trainer, directory: str) -> int:
     """Loads master weights and Adam state into the trainer's units; returns the saved step."""
     meta = read_meta(directory)
     saved_model = meta["training_config"]["model_name"]
     if saved_model != trainer.cfg.model_name:
         raise CheckpointError(f"checkpoint is for {saved_model}, job trains {trainer.cfg.model_name}")
-    by_gid = {u["gid"]: u for u in meta["units"]}
+    saved = {(u["gid"], u.get("tp_index", 0)): u for u in meta["units"]}
+    saved_tp = int(meta.get("tensor_parallel_size", 1))
+    now_tp, now_t = trainer.cfg.tensor_parallel_size, getattr(trainer, "tp_index", 0)
     offsets = _file_offsets(meta)
     for st in trainer.stages:
         for u in st.engine.units:
-            if u.gid not in by_gid:
+            if (u.gid, 0) not in saved:
                 raise CheckpointError(f"checkpoint has no unit {u.gid}")
-            su = by_gid[u.gid]
-            if su["numel"] != u.layer.layout()[1]:
-                raise CheckpointError(f"unit {u.gid}: {su['numel']} elements saved, model has {u.layer.layout()[1]}")
             lo, hi = u.lo, u.hi
+            recut = u.layer.kind == "block" and saved_tp != now_tp
+            # layers that are not cut (embedding, head) are whole in every slice: read slice 0's copy
+            su = saved[(u.gid, now_t if saved_tp == now_tp else 0)]
+            if not recut and su["numel"] != u.layer.layout()[1]:
+                raise CheckpointError(f"unit {u.gid}: {su['numel']} elements saved, model has {u.layer.layout()[1]}")
             parts = []
             for which in range(3):
                 t = torch.zeros(u.shard_n, dtype=torch.float32)
-                a, b = lo, min(hi, su["padded"])
-                if a < b:
-                    t[: b - a] = read_range(directory, meta, offsets, su, which, a, b)
+                if recut:
+                    whole = _whole_block(directory, meta, offsets, saved, u.gid, which, trainer.spec, saved_tp)
+                    if now_tp == 1:
+                        mine = whole
+                    else:
+                        mine = torch.zeros(u.layer.layout()[1], dtype=torch.float32)
+                        u.layer.load_from_whole(mine, whole)
+                    seg = mine[lo:min(hi, mine.numel())]
+                    t[: seg.numel()] = seg
+                else:
+                    a, b = lo, min(hi, su["padded"])
+                    if a < b:
+                        t[: b - a] = read_range(directory, meta, offsets, su, which, a, b)
                 parts.append(t.to(u.device))
             u.load_state(parts[0], parts[1], parts[2], su.get("step_count", meta["step"]))
     trainer.step_idx = meta["step"]

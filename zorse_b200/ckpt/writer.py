@@ -3,7 +3,8 @@
 Layout: `<dir>/step_<n>/meta.json` + one flat binary per (stage, rank) `stage<s>_rank<r>.bin`.
 `meta.json` holds the training config, the step, seeds, dtypes and, per stage, the unit table:
 global unit id, kind, unpadded and padded element counts, shard-group ranks and the element
-offsets of their shards (equal or, with `shard_ratio`, unequal).  A rank file is the concatenation, per unit in table order, of the fp32 master
+offsets of their shards (equal or, with `shard_ratio`, unequal) and, with tensor parallelism, which
+slice of the layer the entry is (`tp_index`; ranks are process ranks).  A rank file is the concatenation, per unit in table order, of the fp32 master
 shard, Adam m and v shards (little-endian float32).  Files are written to a temporary name,
 fsynced and renamed, `meta.json` last, so a directory with a `meta.json` is complete.
 """
@@ -36,7 +37,8 @@ def unit_table(trainer) -> list[dict]:
         for u in st.engine.units:
             out.append({"stage": st.stage_id, "gid": u.gid, "kind": u.layer.kind, "numel": u.layer.layout()[1],
                         "padded": u.n, "shard_ranks": list(u.shard_group.ranks), "shard_numel": u.shard_n,
-                        "shard_offsets": list(u.offs), "step_count": u.step_count})
+                        "shard_offsets": list(u.offs), "step_count": u.step_count,
+                        "tp_index": getattr(trainer, "tp_index", 0)})
     return out
 
 
@@ -64,12 +66,14 @@ def save_checkpoint(trainer, directory: str, step: int) -> str:
         seen, units = set(), []
         for tb in tables:
             for e in tb or []:
-                if (e["stage"], e["gid"]) not in seen:
-                    seen.add((e["stage"], e["gid"]))
+                key = (e["stage"], e["gid"], e.get("tp_index", 0))
+                if key not in seen:
+                    seen.add(key)
                     units.append(e)
         meta = {"format_version": FORMAT_VERSION, "step": step, "seed": trainer.opt.seed,
                 "training_config": to_dict(trainer.cfg), "compute_dtype": trainer.cfg.autocast_dtype,
-                "world_size": trainer.world, "units": sorted(units, key=lambda e: (e["stage"], e["gid"]))}
+                "world_size": trainer.world, "tensor_parallel_size": trainer.cfg.tensor_parallel_size,
+                "units": sorted(units, key=lambda e: (e["stage"], e["gid"], e.get("tp_index", 0)))}
         _atomic_write(os.path.join(d, "meta.json"), json.dumps(meta, indent=1).encode())
     trainer.barrier()
     return d

@@ -11,7 +11,10 @@ Additions over the reference format (all optional, defaults keep reference behav
 `zero_level` per stage (2 or 3), `shard_ratio` per stage (relative parameter-shard sizes of
 the ranks of a shard group, e.g. by GPU memory; the reference's dormant `split_uneven` /
 `shard_ratio` state, utils/patch.py:308-441), `reduce_dtype`, `schedule`,
-`activation_recompute`, `activation_offload`, `grad_norm_compat`.
+`activation_recompute`, `activation_offload`, `grad_norm_compat`, and `tensor_parallel_size`
+(tp, default 1).  With tp > 1 every rank number in the file names a *lane* of tp consecutive
+processes (lane l = ranks l*tp .. l*tp + tp - 1, which hold the tensor-parallel slices of the
+lane's layers); the job then has tp times as many processes as the file names lanes.
 """
 from __future__ import annotations
 
@@ -127,6 +130,7 @@ class PipelineConfig:
     activation_offload: Optional[bool] = None
     grad_norm_compat: str = "mean"
     unused_ranks: tuple[int, ...] = ()   # ranks of the job that own no stage (the planner may leave a slow GPU out)
+    tensor_parallel_size: int = 1        # processes per rank number of this file (see the module docstring)
     extra: dict = field(default_factory=dict)
 
     @property
@@ -138,8 +142,12 @@ class PipelineConfig:
         return max(s.layer_partition[1] for s in self.stages)
 
     @property
-    def world_size(self) -> int:
+    def num_lanes(self) -> int:
         return len({r for s in self.stages for r in s.gpu_ranks} | set(self.unused_ranks))
+
+    @property
+    def world_size(self) -> int:
+        return self.num_lanes * self.tensor_parallel_size
 
     @property
     def gpu_groups(self) -> list[tuple[int, ...]]:
@@ -162,6 +170,8 @@ class PipelineConfig:
             raise ConfigError("autocast_dtype / reduce_dtype must be one of " + ", ".join(DTYPE_NAMES))
         if not self.stages:
             raise ConfigError("pipeline_config is empty")
+        if self.tensor_parallel_size < 1:
+            raise ConfigError("tensor_parallel_size must be at least 1")
         for s in self.stages:
             s.validate()
             if s.num_microbatches != self.num_microbatches:
@@ -215,7 +225,7 @@ def parse_pipeline_dict(d: dict[str, Any]) -> PipelineConfig:
              "fused_optimizer", "interleave_degree", "latency", "autocast_dtype", "reduce_dtype",
              "split_microbatches_evenly", "skip_compute_sync", "interleave_stage_sync", "gloo_batch_recv",
              "alternate_nccl_gloo", "large_model_init", "schedule", "activation_recompute", "activation_offload",
-             "grad_norm_compat", "zero_level", "unused_ranks"}
+             "grad_norm_compat", "zero_level", "unused_ranks", "tensor_parallel_size"}
     cfg = PipelineConfig(
         model_name=str(d["model_name"]), global_batch_size=gbs, microbatch_size=mbs,
         sequence_length=int(d["sequence_length"]), stages=stages, vocab_size=int(d.get("vocab_size", 49152)),
@@ -229,6 +239,7 @@ def parse_pipeline_dict(d: dict[str, Any]) -> PipelineConfig:
         activation_recompute=d.get("activation_recompute"), activation_offload=d.get("activation_offload"),
         grad_norm_compat=str(d.get("grad_norm_compat", "mean")),
         unused_ranks=tuple(int(r) for r in d.get("unused_ranks", ())),
+        tensor_parallel_size=int(d.get("tensor_parallel_size", 1)),
         extra={k: v for k, v in d.items() if k not in known})
     cfg.validate()
     return cfg
@@ -256,6 +267,8 @@ def to_dict(cfg: PipelineConfig) -> dict[str, Any]:
     }
     if cfg.unused_ranks:
         d["unused_ranks"] = list(cfg.unused_ranks)
+    if cfg.tensor_parallel_size != 1:
+        d["tensor_parallel_size"] = cfg.tensor_parallel_size
     if cfg.split_microbatches_evenly:
         d["split_microbatches_evenly"] = True
     if cfg.sync_after_recompute:

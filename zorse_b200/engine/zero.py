@@ -141,8 +141,12 @@ class Counters:
 class ZeroUnit:
     def __init__(self, layer: Layer, gid: int, *, device: torch.device, cfg: EngineConfig, ops, shard: Group,
                  replicate: Group, rank: int, streams: Streams, zero_level: Optional[int] = None,
-                 counters: Optional[Counters] = None, meta_init: bool = False, shard_ratios=None):
+                 counters: Optional[Counters] = None, meta_init: bool = False, shard_ratios=None,
+                 tp_group: Optional[Group] = None):
         self.layer, self.gid, self.device, self.cfg, self.ops = layer, gid, device, cfg, ops
+        # tensor-parallel lane of this rank: gradients of parameters every process of the lane holds
+        # whole (norm weights, embedding, head, ...) are summed over it before the data-parallel reduction
+        self.tp_group = tp_group if tp_group is not None and tp_group.size > 1 else None
         self.shard_group, self.rep_group, self.rank, self.streams = shard, replicate, rank, streams
         self.zero_level = zero_level or cfg.zero_level
         self.counters = counters or Counters()
@@ -322,6 +326,12 @@ class ZeroUnit:
             gscale /= self.rep_group.size
 
         def work():
+            if self.tp_group is not None:
+                from ..models.tp_layers import replicated_ranges
+
+                for o, k in replicated_ranges(self.layer):
+                    dist.all_reduce(g_full[o:o + k], group=self.tp_group.pg)
+                    self.counters.all_reduces += 1
             if self.R > 1:
                 g_sh = self._reduce_scatter(g_full)
                 self.counters.reduce_scatters += 1
@@ -425,19 +435,22 @@ class StageEngine:
 
     def __init__(self, layers: list[Layer], gids: list[int], *, device, cfg: EngineConfig, ops, shard: Group,
                  replicate: Group, rank: int, streams: Optional[Streams] = None, zero_level: Optional[int] = None,
-                 meta_init: bool = False, shard_ratios=None):
+                 meta_init: bool = False, shard_ratios=None, tp_group: Optional[Group] = None):
         self.device, self.cfg, self.ops = device, cfg, ops
         self.streams = streams or Streams(device)
         self.counters = Counters()
         cls = ZeroUnit
-        if (cfg.collectives == "fused" and device.type == "cuda" and shard.size > 1 and replicate.size == 1
+        kw = {}
+        if tp_group is not None and tp_group.size > 1:
+            kw["tp_group"] = tp_group     # the fused unit does not cover tensor-parallel lanes
+        elif (cfg.collectives == "fused" and device.type == "cuda" and shard.size > 1 and replicate.size == 1
                 and shard_ratios is None):
             from .fused import FusedZeroUnit
 
             cls = FusedZeroUnit
         self.units = [cls(ly, gid, device=device, cfg=cfg, ops=ops, shard=shard, replicate=replicate, rank=rank,
                           streams=self.streams, zero_level=zero_level, counters=self.counters, meta_init=meta_init,
-                          shard_ratios=shard_ratios)
+                          shard_ratios=shard_ratios, **kw)
                       for ly, gid in zip(layers, gids)]
 
     def __len__(self):

@@ -178,39 +178,57 @@ def get_config_for_model(name: str):
     return s.layers, s.hidden, s.heads, s.ffn
 
 
-def make_block(spec: ModelSpec) -> TransformerBlock:
-    return TransformerBlock(spec.hidden, spec.heads, spec.n_kv, spec.ffn, norm=spec.norm, pre_norm=spec.pre_norm,
-                            act=spec.act, bias=spec.bias, rope_theta=spec.rope_theta, causal=spec.causal,
-                            window=spec.window, eps=spec.eps, init_std=spec.init_std)
+def _tp_kw(tp: int, tp_index: int) -> dict:
+    return {} if tp == 1 else {"tp": tp, "tp_index": tp_index}
 
 
-def make_embedding(spec: ModelSpec, seq_len: int) -> Layer:
+def make_block(spec: ModelSpec, tp: int = 1, tp_index: int = 0) -> TransformerBlock:
+    """One transformer block; with tp > 1 slice `tp_index` of it (models/tp_layers.py)."""
+    cls = TransformerBlock
+    if tp > 1:
+        from .tp_layers import TPTransformerBlock as cls
+    return cls(spec.hidden, spec.heads, spec.n_kv, spec.ffn, norm=spec.norm, pre_norm=spec.pre_norm,
+               act=spec.act, bias=spec.bias, rope_theta=spec.rope_theta, causal=spec.causal,
+               window=spec.window, eps=spec.eps, init_std=spec.init_std, **_tp_kw(tp, tp_index))
+
+
+def make_embedding(spec: ModelSpec, seq_len: int, tp: int = 1, tp_index: int = 0) -> Layer:
     if spec.family == "vit":
+        if tp > 1:
+            raise NotImplementedError("tensor parallelism does not cover the ViT patch embedding")
         return PatchEmbeddingLayer(spec.image, spec.patch, 3, spec.hidden, spec.init_std)
     maxpos = max(spec.max_positions, seq_len) if spec.max_positions else 0
-    return EmbeddingLayer(spec.vocab, spec.hidden, max_positions=maxpos, pos_offset=spec.pos_offset,
-                          post_norm=spec.embed_norm, eps=spec.eps, init_std=spec.init_std)
+    cls = EmbeddingLayer
+    if tp > 1:
+        from .tp_layers import SPEmbeddingLayer as cls
+    return cls(spec.vocab, spec.hidden, max_positions=maxpos, pos_offset=spec.pos_offset,
+               post_norm=spec.embed_norm, eps=spec.eps, init_std=spec.init_std, **_tp_kw(tp, tp_index))
 
 
-def make_head(spec: ModelSpec) -> HeadLayer:
+def make_head(spec: ModelSpec, tp: int = 1, tp_index: int = 0) -> HeadLayer:
     out = spec.classes if spec.family == "vit" else spec.vocab
-    return HeadLayer(spec.hidden, out, norm=spec.head_norm, eps=spec.eps, pool=spec.pool, init_std=spec.init_std)
+    cls = HeadLayer
+    if tp > 1:
+        from .tp_layers import SPHeadLayer as cls
+    return cls(spec.hidden, out, norm=spec.head_norm, eps=spec.eps, pool=spec.pool, init_std=spec.init_std,
+               **_tp_kw(tp, tp_index))
 
 
 def build_stage_layers(spec: ModelSpec, layer_start: int, layer_end: int, seq_len: int,
-                       insert_noop: bool = False) -> list[Layer]:
+                       insert_noop: bool = False, tp: int = 1, tp_index: int = 0) -> list[Layer]:
     """Layers of the pipeline stage owning blocks [layer_start, layer_end): the first stage
-    also owns the embedding, the last one the final norm + head (+ loss)."""
+    also owns the embedding, the last one the final norm + head (+ loss).  With tp > 1 the
+    layers are this process's tensor-parallel slices."""
     if not (0 <= layer_start < layer_end <= spec.layers):
         raise ValueError(f"bad layer range [{layer_start},{layer_end}) for {spec.name} with {spec.layers} layers")
     out: list[Layer] = []
     if layer_start == 0:
-        out.append(make_embedding(spec, seq_len))
-    out += [make_block(spec) for _ in range(layer_start, layer_end)]
+        out.append(make_embedding(spec, seq_len, tp, tp_index))
+    out += [make_block(spec, tp, tp_index) for _ in range(layer_start, layer_end)]
     if insert_noop:
         out.append(NoOpLayer())
     if layer_end == spec.layers:
-        out.append(make_head(spec))
+        out.append(make_head(spec, tp, tp_index))
     return out
 
 

@@ -116,19 +116,32 @@ class GroupCache:
 class StageGroups:
     shard: Group
     replicate: Group
+    tp: Optional[Group] = None   # the tensor-parallel group of this rank's lane (None when tp = 1)
 
     @staticmethod
-    def create_all(stages, my_rank: int, cache: Optional[GroupCache] = None) -> dict[int, "StageGroups"]:
+    def create_all(stages, my_rank: int, cache: Optional[GroupCache] = None, tp: int = 1) -> dict[int, "StageGroups"]:
         """Creates every stage's groups on every rank (same order everywhere) and returns, per
-        stage id this rank belongs to, its own shard / replicate groups."""
+        stage id this rank belongs to, its own shard / replicate groups.  With tensor parallelism
+        the stage configs name lanes; process `l * tp + t` holds slice t of lane l, its shard and
+        replicate groups connect the processes with the same t, its tensor-parallel group the tp
+        processes of the lane.  `my_rank` and the ranks of the returned groups are process ranks."""
         cache = cache or GroupCache()
         mine: dict[int, StageGroups] = {}
-        for st in stages:
-            shard_groups = [cache.get(g) for g in st.zero_config]
-            width = len(st.zero_config[0])
-            rep_groups = [cache.get(tuple(g[j] for g in st.zero_config)) for j in range(width)]
-            if my_rank in st.gpu_ranks:
-                sg = next(g for g in shard_groups if my_rank in g.ranks)
-                rg = next(g for g in rep_groups if my_rank in g.ranks)
-                mine[st.stage_id] = StageGroups(sg, rg)
+        tp_group = None
+        if tp > 1:
+            lanes = sorted({r for st in stages for r in st.gpu_ranks})
+            for lane in lanes:
+                g = cache.get(tuple(lane * tp + i for i in range(tp)))
+                if my_rank in g.ranks:
+                    tp_group = g
+        for t in range(tp):
+            for st in stages:
+                phys = lambda ranks: tuple(r * tp + t for r in ranks)
+                shard_groups = [cache.get(phys(g)) for g in st.zero_config]
+                width = len(st.zero_config[0])
+                rep_groups = [cache.get(phys(tuple(g[j] for g in st.zero_config))) for j in range(width)]
+                if my_rank % tp == t and my_rank // tp in st.gpu_ranks:
+                    sg = next(g for g in shard_groups if my_rank in g.ranks)
+                    rg = next(g for g in rep_groups if my_rank in g.ranks)
+                    mine[st.stage_id] = StageGroups(sg, rg, tp_group)
         return mine

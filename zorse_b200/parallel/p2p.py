@@ -195,6 +195,27 @@ class LoopbackP2P:
         pass
 
 
+class LaneTransport:
+    """With tensor parallelism the plan numbers lanes, and slice t of lane a talks to slice t of lane b:
+    this wrapper turns lane numbers into process ranks (lane * tp + t) for the transport under it."""
+
+    def __init__(self, inner, tp: int, index: int):
+        self.inner, self.tp, self.index = inner, tp, index
+
+    def send(self, t, dst, tag, kind="act"):
+        return self.inner.send(t, dst * self.tp + self.index, tag, kind)
+
+    def recv(self, shape, dtype, src, tag, kind="act"):
+        return self.inner.recv(shape, dtype, src * self.tp + self.index, tag, kind)
+
+    def flush(self):
+        self.inner.flush()
+
+    @property
+    def bytes_sent(self):
+        return self.inner.bytes_sent
+
+
 def make_transport(device: torch.device, use_gloo: bool = False, gloo_group=None, streams=None,
                    split_parity: bool = False):
     if not (dist.is_available() and dist.is_initialized()):

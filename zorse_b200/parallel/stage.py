@@ -85,20 +85,31 @@ class PipelineStage:
     def __init__(self, cfg: PipelineConfig, st: StageConfig, *, rank: int, device: torch.device, ops,
                  engine_cfg: EngineConfig, groups: StageGroups, streams: Streams, pattern: StageCommPattern,
                  transport, gloo_transport=None, activation_offload: bool = False, model_overrides: Optional[dict] = None,
-                 local_mailbox=None):
+                 local_mailbox=None, process_rank: Optional[int] = None):
+        # `rank` is the number the config and the p2p plan know this process by (its lane with tensor
+        # parallelism); `process_rank` its rank in torch.distributed, which the groups are made of
         self.cfg, self.st, self.rank, self.device, self.ops = cfg, st, rank, device, ops
+        process_rank = rank if process_rank is None else process_rank
+        self.tp = None
+        tp_size, tp_index = cfg.tensor_parallel_size, 0
+        if tp_size > 1:
+            from ..models.tp_layers import TPComm
+
+            tp_index = groups.tp.index_of(process_rank)
+            self.tp = TPComm(groups.tp.pg, tp_size, tp_index)
         self.stage_id = st.stage_id
         self.num_stages = len(cfg.stages)
         self.is_first = st.layer_partition[0] == 0
         self.spec = registry.get_spec(cfg.model_name, vocab=cfg.vocab_size, **(model_overrides or {}))
         self.is_last = st.layer_partition[1] == self.spec.layers
         self.layers = registry.build_stage_layers(self.spec, st.layer_partition[0], st.layer_partition[1],
-                                                  cfg.sequence_length)
+                                                  cfg.sequence_length, tp=tp_size, tp_index=tp_index)
         gids = [registry.global_layer_index(self.spec, st.layer_partition[0], i, self.layers)
                 for i in range(len(self.layers))]
         self.engine = StageEngine(self.layers, gids, device=device, cfg=engine_cfg, ops=ops, shard=groups.shard,
-                                  replicate=groups.replicate, rank=rank, streams=streams, zero_level=st.zero_level,
-                                  meta_init=False, shard_ratios=st.shard_ratio)
+                                  replicate=groups.replicate, rank=process_rank, streams=streams,
+                                  zero_level=st.zero_level, meta_init=False, shard_ratios=st.shard_ratio,
+                                  tp_group=groups.tp)
         self.pattern = pattern
         # irregular routing (mixed widths / uneven counts): traffic of even and odd stage boundaries goes
         # through different process groups, so that a rank's receives (boundary b - 1) and sends (boundary b)
@@ -115,6 +126,8 @@ class PipelineStage:
         if self.spec.family == "vit":
             self.S = self.layers[0].tokens_per_image() if self.is_first else (self.spec.image // self.spec.patch) ** 2 + 1
             self.tokens = self.B * self.S
+        if self.tokens % tp_size:
+            raise ValueError(f"{self.tokens} tokens per microbatch do not split over {tp_size} tensor-parallel processes")
         self.act_dtype = engine_cfg.compute_dtype
         self.stash = ActivationStash(device, activation_offload, streams.copy)
         self.saved: dict = {}
@@ -130,12 +143,16 @@ class PipelineStage:
     # -- helpers ----------------------------------------------------------------------
     def ctx(self, mbl: int, targets=None) -> dict:
         c = {"B": self.B, "S": self.S, "loss_scale": self.loss_scale}
+        if self.tp is not None:
+            c["tp"] = self.tp
         if targets is not None:
             c["targets"] = targets
         return c
 
     def act_shape(self):
-        return (self.tokens, self.hidden)
+        """Rows of a stage-boundary message: with tensor parallelism every process of a lane sends and
+        receives only its own rows."""
+        return (self.tokens // self.cfg.tensor_parallel_size, self.hidden)
 
     def boundary_transport(self, towards_next: bool):
         """Transport of the boundary to the next (or previous) stage.  With a Gloo communicator

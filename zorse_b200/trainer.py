@@ -23,7 +23,7 @@ from .engine.zero import AdamConfig, EngineConfig, Streams
 from .models import registry
 from .ops.api import default_ops_for, get_ops
 from .parallel import groups as G
-from .parallel.p2p import GlooP2P, LocalMailbox, make_transport
+from .parallel.p2p import GlooP2P, LaneTransport, LocalMailbox, make_transport
 from .parallel.p2p_plan import create_static_comm_plans, is_regular
 from .parallel.schedules import build_schedule
 from .parallel.stage import PipelineStage
@@ -70,7 +70,13 @@ class Trainer:
             collectives=opt.collectives, grad_divide_by_group=cfg.grad_norm_compat == "reference",
             adam=AdamConfig(lr=opt.lr), seed=opt.seed)
         self.streams = Streams(self.device)
-        stage_groups = G.StageGroups.create_all(cfg.stages, self.rank)
+        # tensor parallelism: the config numbers lanes of tp processes; everything that follows the plan
+        # (stages, microbatches, p2p peers) uses the lane number, the groups use process ranks
+        tp = cfg.tensor_parallel_size
+        if tp > 1 and opt.collectives == "fused":
+            raise NotImplementedError("fused collectives do not cover tensor-parallel lanes; use --collectives library")
+        self.lane, self.tp_index = self.rank // tp, self.rank % tp
+        stage_groups = G.StageGroups.create_all(cfg.stages, self.rank, tp=tp)
         self.gloo_group = G.gloo_world_group() if (opt.gloo_p2p or self.device.type == "cuda") and G.is_dist() else None
         # --gloo_p2p on GPUs: keep an NCCL transport next to the Gloo one so that the ZeRO-2 schedule
         # can alternate between them by stage width; on CPU ranks there is only Gloo
@@ -78,17 +84,22 @@ class Trainer:
         self.transport = make_transport(self.device, use_gloo=opt.gloo_p2p and not both, gloo_group=self.gloo_group,
                                         streams=self.streams, split_parity=not is_regular(cfg))
         self.gloo_transport = GlooP2P(self.device, self.gloo_group) if both else None
+        if tp > 1:
+            self.transport = LaneTransport(self.transport, tp, self.tp_index)
+            if self.gloo_transport is not None:
+                self.gloo_transport = LaneTransport(self.gloo_transport, tp, self.tp_index)
         plans = create_static_comm_plans(cfg)
-        self.plan = plans.get(self.rank)     # None on a rank the plan leaves idle
+        self.plan = plans.get(self.lane)     # None on a rank the plan leaves idle
         offload_act = cfg.activation_offload if opt.activation_offload is None else opt.activation_offload
         mailbox = LocalMailbox()     # hand-offs between two stages of this rank never touch a transport
         self.stages = [
-            PipelineStage(cfg, st, rank=self.rank, device=self.device, ops=self.ops, engine_cfg=self.engine_cfg,
+            PipelineStage(cfg, st, rank=self.lane, process_rank=self.rank, device=self.device, ops=self.ops,
+                          engine_cfg=self.engine_cfg,
                           groups=stage_groups[st.stage_id], streams=self.streams, pattern=self.plan.stages[st.stage_id],
                           transport=self.transport, gloo_transport=self.gloo_transport,
                           activation_offload=bool(offload_act),
                           model_overrides=opt.model_overrides, local_mailbox=mailbox)
-            for st in cfg.stages_of_rank(self.rank)]
+            for st in cfg.stages_of_rank(self.lane)]
         self.spec = (self.stages[0].spec if self.stages else
                      registry.get_spec(cfg.model_name, vocab=cfg.vocab_size, **(opt.model_overrides or {})))
         recompute = cfg.activation_recompute if opt.activation_recompute is None else opt.activation_recompute
