@@ -159,3 +159,12 @@ def test_parallel_dims_layout_and_training():
                                                            autocast_dtype="float32", reduce_dtype="float32")
     res = run_workers(4, _worker, small, {"schedule": "layer_major"}, 2)
     _check_tp(res, small)
+
+
+@pytest.mark.parametrize("model", ["toygpt", "deepspeedmistral_toy"])
+def test_tp2_other_families(model):
+    """LayerNorm + biases + GELU + learned positions (GPT), and grouped-query attention with a sliding
+    window (Mistral): biases behind a reduce-scatter and the position table are lane-replicated."""
+    cfg = tiny_cfg(ONE_LANE, tensor_parallel_size=2, model_name=model)
+    res = run_workers(2, _worker, cfg, {"schedule": "layer_major"}, 2)
+    _check_tp(res, cfg)
