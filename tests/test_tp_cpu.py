@@ -168,3 +168,37 @@ def test_tp2_other_families(model):
     cfg = tiny_cfg(ONE_LANE, tensor_parallel_size=2, model_name=model)
     res = run_workers(2, _worker, cfg, {"schedule": "layer_major"}, 2)
     _check_tp(res, cfg)
+
+
+def _worker_ov(rank, world, cfg_dict, opts, overrides, steps):
+    return _worker(rank, world, cfg_dict, dict(opts, model_overrides=overrides), steps)
+
+
+def test_tp2_post_norm_block():
+    """BERT-style layer (post-norm, LayerNorm, biases, embedding norm, learned positions), cut to two
+    layers and a narrow width: residuals sit in front of the norms, so the residual gradient is added
+    behind the reduce-scatter of the projection gradients."""
+    from zorse_b200.models import registry
+    from zorse_b200.utils.oracle import OracleTrainer
+
+    ov = {"layers": 2, "hidden": 128, "heads": 4, "kv_heads": 4, "ffn": 256}
+    pipe = [{"gpu_ranks": [0], "num_microbatches_per_rank": [4], "layer_partition": [0, 2], "zero_config": [[0]]}]
+    cfg_dict = tiny_cfg(pipe, tensor_parallel_size=2, model_name="deepspeedbert_110m")
+    res = run_workers(2, _worker_ov, cfg_dict, {"schedule": "layer_major"}, ov, 2)
+    cfg = parse_pipeline_dict(cfg_dict)
+    orc = OracleTrainer(cfg, model_overrides=ov)
+    g = torch.Generator().manual_seed(7919)
+    M, B, S = cfg.num_microbatches, cfg.microbatch_size, cfg.sequence_length
+    batch = {"inputs": torch.randint(0, cfg.vocab_size, (M, B, S), generator=g),
+             "targets": torch.randint(0, cfg.vocab_size, (M, B, S), generator=g)}
+    want = [orc.step(batch) for _ in range(2)]
+    spec = registry.get_spec(cfg.model_name, vocab=cfg.vocab_size, **ov)
+    assert not spec.pre_norm
+    for r in res:
+        for a, b in zip(r["losses"], want):
+            assert abs(a - b) < 2e-4, (r["losses"], want)
+    for gid in (1, 2):
+        whole = torch.zeros_like(orc.flats[gid])
+        for r in res:
+            registry.make_block(spec, 2, r["tp_index"]).store_into_whole(r["params"][gid], whole)
+        assert (whole - orc.flats[gid].detach()).abs().max().item() < 5e-4

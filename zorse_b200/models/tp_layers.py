@@ -71,7 +71,7 @@ def put_slice(full: torch.Tensor, piece: torch.Tensor, dim: int, segments: tuple
 
 
 class TPTransformerBlock(TransformerBlock):
-    """Slice `tp_index` of a pre-norm transformer block split over `tp` processes."""
+    """Slice `tp_index` of a transformer block (pre- or post-norm) split over `tp` processes."""
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, ffn: int, *, tp: int, tp_index: int, **kw):
         if heads % tp or kv_heads % tp or ffn % tp:
@@ -79,8 +79,6 @@ class TPTransformerBlock(TransformerBlock):
         self.whole = TransformerBlock(hidden, heads, kv_heads, ffn, **kw)
         super().__init__(hidden, heads // tp, kv_heads // tp, ffn // tp, head_dim=self.whole.D,
                          **{k: v for k, v in kw.items() if k != "head_dim"})
-        if not self.pre_norm:
-            raise NotImplementedError("tensor parallelism covers pre-norm blocks")
         self.tp, self.tp_index = tp, tp_index
 
     # how each parameter of the unsplit block is cut: name -> (dim, segments along that dim)
@@ -132,60 +130,99 @@ class TPTransformerBlock(TransformerBlock):
         cuts = self._cuts()
         return [(o, math.prod(sh)) for name, (o, sh) in lay.items() if name not in cuts]
 
-    # ---- forward ------------------------------------------------------------------------
-    def forward(self, x, ctx, ops, saved=None):
-        p, sv, tp = self.p, saved, ctx["tp"]
-        B, S = ctx["B"], ctx["S"]
-        n1, st1 = _norm(ops, self.norm, x, p["norm1_w"], p.get("norm1_b"), self.eps)
-        qkv = ops.linear_fwd(tp.gather_rows(n1), p["qkv_w"], p.get("qkv_b"))
-        cs = self._rope(ops, S, x.device)
+    # ---- sub-blocks: rows in, rows out -----------------------------------------------------
+    # The gradient of a reduce-scatter is an all-gather and the other way round.
+    def _attn_rows_fwd(self, xin, resid, ctx, ops, sv):
+        p, tp, B, S = self.p, ctx["tp"], ctx["B"], ctx["S"]
+        qkv = ops.linear_fwd(tp.gather_rows(xin), p["qkv_w"], p.get("qkv_b"))
+        cs = self._rope(ops, S, xin.device)
         if cs is not None:
             ops.rope_(qkv, cs, S, self.Hq + self.Hkv, self.D)
         att, lse = ops.attn_fwd(qkv, B, S, self.Hq, self.Hkv, self.D, self.causal, self.window)
-        h1 = tp.reduce_scatter_rows(ops.linear_fwd(att, p["o_w"], None))
-        h1 += x
+        out = tp.reduce_scatter_rows(ops.linear_fwd(att, p["o_w"], None))
+        out += resid
         if "o_b" in p:
-            h1 += p["o_b"]
-        n2, st2 = _norm(ops, self.norm, h1, p["norm2_w"], p.get("norm2_b"), self.eps)
-        hpre = ops.linear_fwd(tp.gather_rows(n2), p["up_w"], p.get("up_b"))
+            out += p["o_b"]
+        if sv is not None:
+            sv.update(qkv=qkv, att=att, lse=lse)
+        return out
+
+    def _attn_rows_bwd(self, dout, xin, ctx, ops, sv):
+        """dout: gradient of the sub-block's output rows; returns the gradient reaching xin through the
+        projections (the residual branch is added by the caller)."""
+        p, g, tp, B, S = self.p, self.g, ctx["tp"], ctx["B"], ctx["S"]
+        if "o_b" in g:
+            g["o_b"].add_(dout.float().sum(0).to(g["o_b"].dtype))
+        df = tp.gather_rows(dout)
+        datt = ops.linear_dgrad(df, p["o_w"])
+        ops.linear_wgrad(df, sv["att"], g["o_w"], None)
+        dqkv = ops.attn_bwd(datt, sv["qkv"], sv["att"], sv["lse"], B, S, self.Hq, self.Hkv, self.D, self.causal,
+                            self.window)
+        cs = self._rope(ops, S, dout.device)
+        if cs is not None:
+            ops.rope_(dqkv, cs, S, self.Hq + self.Hkv, self.D, backward=True)
+        dxin = tp.reduce_scatter_rows(ops.linear_dgrad(dqkv, p["qkv_w"]))
+        ops.linear_wgrad(dqkv, tp.gather_rows(xin), g["qkv_w"], g.get("qkv_b"))
+        return dxin
+
+    def _mlp_rows_fwd(self, xin, resid, ctx, ops, sv):
+        p, tp = self.p, ctx["tp"]
+        hpre = ops.linear_fwd(tp.gather_rows(xin), p["up_w"], p.get("up_b"))
         a = ops.swiglu_fwd(hpre) if self.act == "swiglu" else ops.act_fwd(hpre, self.act)
         out = tp.reduce_scatter_rows(ops.linear_fwd(a, p["down_w"], None))
-        out += h1
+        out += resid
         if "down_b" in p:
             out += p["down_b"]
         if sv is not None:
-            sv.update(x=x, n1=n1, st1=st1, h1=h1, n2=n2, st2=st2, qkv=qkv, att=att, lse=lse, hpre=hpre, mlp_a=a)
+            sv.update(hpre=hpre, mlp_a=a)
         return out
 
-    # ---- backward -----------------------------------------------------------------------
-    def backward(self, dy, ctx, ops, saved):
-        p, g, sv, tp = self.p, self.g, saved, ctx["tp"]
-        B, S = ctx["B"], ctx["S"]
-        ln = self.norm == "ln"
-        # MLP: the gradient of a reduce-scatter is an all-gather and the other way round
+    def _mlp_rows_bwd(self, dout, xin, ctx, ops, sv):
+        p, g, tp = self.p, self.g, ctx["tp"]
         if "down_b" in g:
-            g["down_b"].add_(dy.float().sum(0).to(g["down_b"].dtype))
-        dyf = tp.gather_rows(dy)
-        da = ops.linear_dgrad(dyf, p["down_w"])
-        ops.linear_wgrad(dyf, sv["mlp_a"], g["down_w"], None)
+            g["down_b"].add_(dout.float().sum(0).to(g["down_b"].dtype))
+        df = tp.gather_rows(dout)
+        da = ops.linear_dgrad(df, p["down_w"])
+        ops.linear_wgrad(df, sv["mlp_a"], g["down_w"], None)
         dh = ops.swiglu_bwd(sv["hpre"], da) if self.act == "swiglu" else ops.act_bwd(sv["hpre"], da, self.act)
-        dn2 = tp.reduce_scatter_rows(ops.linear_dgrad(dh, p["up_w"]))
-        ops.linear_wgrad(dh, tp.gather_rows(sv["n2"]), g["up_w"], g.get("up_b"))
-        dh1 = ops.norm_bwd(dn2, sv["h1"], p["norm2_w"], sv["st2"], dy, g["norm2_w"], g.get("norm2_b"), ln)
-        # attention
-        if "o_b" in g:
-            g["o_b"].add_(dh1.float().sum(0).to(g["o_b"].dtype))
-        dh1f = tp.gather_rows(dh1)
-        datt = ops.linear_dgrad(dh1f, p["o_w"])
-        ops.linear_wgrad(dh1f, sv["att"], g["o_w"], None)
-        dqkv = ops.attn_bwd(datt, sv["qkv"], sv["att"], sv["lse"], B, S, self.Hq, self.Hkv, self.D, self.causal,
-                            self.window)
-        cs = self._rope(ops, S, dy.device)
-        if cs is not None:
-            ops.rope_(dqkv, cs, S, self.Hq + self.Hkv, self.D, backward=True)
-        dn1 = tp.reduce_scatter_rows(ops.linear_dgrad(dqkv, p["qkv_w"]))
-        ops.linear_wgrad(dqkv, tp.gather_rows(sv["n1"]), g["qkv_w"], g.get("qkv_b"))
-        return ops.norm_bwd(dn1, sv["x"], p["norm1_w"], sv["st1"], dh1, g["norm1_w"], g.get("norm1_b"), ln)
+        dxin = tp.reduce_scatter_rows(ops.linear_dgrad(dh, p["up_w"]))
+        ops.linear_wgrad(dh, tp.gather_rows(xin), g["up_w"], g.get("up_b"))
+        return dxin
+
+    # ---- block ------------------------------------------------------------------------------
+    def forward(self, x, ctx, ops, saved=None):
+        p, sv = self.p, saved
+        if self.pre_norm:
+            n1, st1 = _norm(ops, self.norm, x, p["norm1_w"], p.get("norm1_b"), self.eps)
+            h1 = self._attn_rows_fwd(n1, x, ctx, ops, sv)
+            n2, st2 = _norm(ops, self.norm, h1, p["norm2_w"], p.get("norm2_b"), self.eps)
+            out = self._mlp_rows_fwd(n2, h1, ctx, ops, sv)
+            if sv is not None:
+                sv.update(x=x, n1=n1, st1=st1, h1=h1, n2=n2, st2=st2)
+        else:
+            r1 = self._attn_rows_fwd(x, x, ctx, ops, sv)
+            h1, st1 = _norm(ops, self.norm, r1, p["norm1_w"], p.get("norm1_b"), self.eps)
+            r2 = self._mlp_rows_fwd(h1, h1, ctx, ops, sv)
+            out, st2 = _norm(ops, self.norm, r2, p["norm2_w"], p.get("norm2_b"), self.eps)
+            if sv is not None:
+                sv.update(x=x, r1=r1, st1=st1, h1=h1, r2=r2, st2=st2)
+        return out
+
+    def backward(self, dy, ctx, ops, saved):
+        p, g, sv = self.p, self.g, saved
+        ln = self.norm == "ln"
+        if self.pre_norm:
+            dn2 = self._mlp_rows_bwd(dy, sv["n2"], ctx, ops, sv)
+            dh1 = ops.norm_bwd(dn2, sv["h1"], p["norm2_w"], sv["st2"], dy, g["norm2_w"], g.get("norm2_b"), ln)
+            dn1 = self._attn_rows_bwd(dh1, sv["n1"], ctx, ops, sv)
+            return ops.norm_bwd(dn1, sv["x"], p["norm1_w"], sv["st1"], dh1, g["norm1_w"], g.get("norm1_b"), ln)
+        dr2 = ops.norm_bwd(dy, sv["r2"], p["norm2_w"], sv["st2"], None, g["norm2_w"], g.get("norm2_b"), ln)
+        dh1 = self._mlp_rows_bwd(dr2, sv["h1"], ctx, ops, sv)
+        dh1 += dr2
+        dr1 = ops.norm_bwd(dh1, sv["r1"], p["norm1_w"], sv["st1"], None, g["norm1_w"], g.get("norm1_b"), ln)
+        dx = self._attn_rows_bwd(dr1, sv["x"], ctx, ops, sv)
+        dx += dr1
+        return dx
 
 
 class _RowSplit:
