@@ -14,6 +14,7 @@
 #include "../common/host.h"
 #include "../common/ptx.cuh"
 #include "gemm_common.cuh"
+#include <type_traits>
 
 namespace zb {
 
@@ -100,11 +101,15 @@ struct Gemm2Extra {
   int a_3d, b_3d;  // MN-major operand fetched with one 3-D TMA box {64, BK, 2} instead of two 2-D boxes
 };
 
-template <bool A_MN, bool B_MN>
+// SCATTER: the epilogue sends every output row to the staging slot of the rank that owns it in a
+// row-wise reduce-scatter (plain stores over NVLink, tile by tile while the main loop goes on) and
+// the last CTA raises the arrival flags; the owners add the slots up (csrc/comm/tp_rs.cu).
+template <bool A_MN, bool B_MN, typename Params = GemmParams>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  const GemmParams p, const Gemm2Extra ex) {
+                  const Params p, const Gemm2Extra ex) {
   using Cfg = Gemm2Cfg;
+  constexpr bool SCATTER = std::is_same<Params, GemmScatterParams>::value;
   constexpr int BK = Cfg::BK, STAGES = Cfg::STAGES, BN = Cfg::BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -228,6 +233,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
+      __nv_bfloat16* crow = nullptr;   // SCATTER: this thread's destination row
+      if constexpr (SCATTER) if (row_ok) {
+        const int owner = row / p.sc_rows;
+        crow = static_cast<__nv_bfloat16*>(p.sc_dst[owner]) + size_t(row - owner * p.sc_rows) * p.ldc;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col0 = n0 + c * 32;
@@ -236,12 +246,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * BN + c * 32), r);
         tmem_wait_ld();
         if (!row_ok) continue;
-        epilogue_store_chunk(p, ecfg, row, col0, r);
+        if constexpr (SCATTER) epilogue_scatter_chunk(crow, col0, p.N, ecfg.vec_ok, r);
+        else epilogue_store_chunk(p, ecfg, row, col0, r);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(&tmem_empty[buf], 0);
     }
+    if constexpr (SCATTER) __threadfence_system();   // this thread's rows are visible to their owners before the flags
   }
 
   // ------------------------------ teardown ------------------------------
@@ -255,6 +267,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
   }
+  if constexpr (SCATTER) if (threadIdx.x == 0) {
+    // last CTA of the grid: every row has been stored and fenced; tell the owners (not after a timeout:
+    // the status word is then non-zero and the owners' bounded wait reports it)
+    if (atomicAdd(p.sc_counter, 1u) == gridDim.x - 1) {
+      __threadfence_system();
+      if (*reinterpret_cast<volatile int*>(p.status) == 0)
+        for (int q = 0; q < p.sc_R; ++q) st_release_sys(p.sc_flags[q] + p.sc_flag_index, p.sc_epoch);
+      *p.sc_counter = 0u;
+    }
+  }
 }
 
 // 3-D view of an MN-major operand stored [K rows, MN cols]: {64 within a block, K, MN/64 blocks}
@@ -265,8 +287,8 @@ static int make_tmap_mn3d(CUtensorMap* out, const void* base, uint64_t krows, ui
   return make_tmap_nd_bf16(out, base, 3, dims, strides, box);
 }
 
-template <bool A_MN, bool B_MN>
-static int launch_gemm2(const void* A, const void* B, const GemmParams& p, int lda, int ldb, int max_ctas,
+template <bool A_MN, bool B_MN, typename Params = GemmParams>
+static int launch_gemm2(const void* A, const void* B, const Params& p, int lda, int ldb, int max_ctas,
                         cudaStream_t stream) {
   using Cfg = Gemm2Cfg;
   CUtensorMap ta, tb;
@@ -280,7 +302,7 @@ static int launch_gemm2(const void* A, const void* B, const GemmParams& p, int l
   else if (p.N % 64 == 0) { rc = make_tmap_mn3d(&tb, B, p.K, p.N, ldb); ex.b_3d = 1; }
   else rc = make_tmap_2d_bf16(&tb, B, p.K, p.N, ldb, 64, 64);
   if (rc) return rc;
-  auto kern = gemm2_bf16_kernel<A_MN, B_MN>;
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN, Params>;
   static bool attr_set = false;
   if (!attr_set) {
     ZB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
@@ -318,4 +340,37 @@ extern "C" int zb_gemm2_bf16(const void* A, const void* B, void* C, int M, int N
   if (!a_mn_major && b_mn_major) return launch_gemm2<false, true>(A, B, p, lda, ldb, max_ctas, stream);
   if (a_mn_major && b_mn_major) return launch_gemm2<true, true>(A, B, p, lda, ldb, max_ctas, stream);
   return launch_gemm2<true, false>(A, B, p, lda, ldb, max_ctas, stream);
+}
+
+// C = A @ B^T (b_mn_major: A @ B) with the output rows scattered for a row-wise reduce-scatter over
+// R ranks: rows [q * M / R, (q + 1) * M / R) go to dst_ptrs[q] (this rank's bf16 staging slot in rank
+// q's memory, [M / R, N] with row stride ldc); when the grid is done `epoch` is stored to
+// flag_ptrs[q][flag_index] for every q.  A: [M, K] K-major.  counter: zeroed device int.
+extern "C" int zb_gemm2_rs_bf16(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int ldc,
+                                int b_mn_major, void* const* dst_ptrs, int* const* flag_ptrs, int R, int flag_index,
+                                int epoch, unsigned int* counter, int max_ctas, int* status, cudaStream_t stream) {
+  using namespace zb;
+  if (M <= 0 || N <= 0 || K <= 0) ZB_FAIL(-1, "gemm2_rs: empty problem %d x %d x %d", M, N, K);
+  if (R < 1 || R > 8 || M % R != 0) ZB_FAIL(-1, "gemm2_rs: %d rows do not split over %d ranks (1..8)", M, R);
+  GemmScatterParams p;
+  p.C = nullptr;
+  p.bias = nullptr; p.addend = nullptr;
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc; p.ld_addend = 0;
+  p.flags = 0;
+  p.status = status;
+  p.gate_flags = nullptr;
+  p.gate_epoch = 0;
+  p.gate_base = 0; p.gate_row_bytes = 0; p.gate_shard_bytes = 1;
+  p.gate_chunk_bytes = 1; p.gate_cps = 1; p.gate_self = -1;
+  for (int q = 0; q < 8; ++q) { p.sc_dst[q] = nullptr; p.sc_flags[q] = nullptr; }
+  for (int q = 0; q < R; ++q) {
+    if (reinterpret_cast<uintptr_t>(dst_ptrs[q]) & 15) ZB_FAIL(-1, "gemm2_rs: destination %d not 16-byte aligned", q);
+    p.sc_dst[q] = dst_ptrs[q];
+    p.sc_flags[q] = flag_ptrs[q];
+  }
+  p.C = dst_ptrs[0];   // alignment of the vector path is judged on a destination
+  p.sc_rows = M / R; p.sc_R = R; p.sc_flag_index = flag_index; p.sc_epoch = epoch; p.sc_counter = counter;
+  if (b_mn_major) return launch_gemm2<false, true, GemmScatterParams>(A, B, p, lda, ldb, max_ctas, stream);
+  return launch_gemm2<false, false, GemmScatterParams>(A, B, p, lda, ldb, max_ctas, stream);
 }

@@ -34,6 +34,19 @@ struct GemmParams {
 };
 
 
+// Row scatter of the output (GEMM fused with the send half of a reduce-scatter over rows; used by
+// the kernels instantiated with this parameter type): output row m goes to row m % sc_rows of the
+// bf16 buffer sc_dst[m / sc_rows] (ld = ldc), which may be a peer GPU's memory; when the whole grid
+// is done, sc_epoch is stored (release, system scope) to sc_flags[q][sc_flag_index] of every
+// q < sc_R.  sc_counter: zeroed device int (last-CTA detection).
+struct GemmScatterParams : GemmParams {
+  void* sc_dst[8];
+  int* sc_flags[8];
+  int sc_rows, sc_R, sc_flag_index, sc_epoch;
+  unsigned int* sc_counter;
+};
+
+
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   float u = k0 * (x + k1 * x * x * x);
@@ -132,5 +145,28 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const 
           }
         }
       }
+
+// Scatter epilogue: 32 accumulator columns [col0, col0+32) as bf16 to `crow` (the destination row,
+// possibly in a peer GPU's memory); plain 16-byte stores when aligned.
+__device__ __forceinline__ void epilogue_scatter_chunk(__nv_bfloat16* crow, int col0, int N, bool vec_ok,
+                                                       const uint32_t (&r)[32]) {
+  if (vec_ok && col0 + 32 <= N) {
+    uint4* cp = reinterpret_cast<uint4*>(crow + col0);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 o;
+      o.x = pack_bf16x2(__uint_as_float(r[j * 8 + 0]), __uint_as_float(r[j * 8 + 1]));
+      o.y = pack_bf16x2(__uint_as_float(r[j * 8 + 2]), __uint_as_float(r[j * 8 + 3]));
+      o.z = pack_bf16x2(__uint_as_float(r[j * 8 + 4]), __uint_as_float(r[j * 8 + 5]));
+      o.w = pack_bf16x2(__uint_as_float(r[j * 8 + 6]), __uint_as_float(r[j * 8 + 7]));
+      cp[j] = o;
+    }
+  } else {
+    for (int i = 0; i < 32; ++i) {
+      if (col0 + i >= N) break;
+      crow[col0 + i] = __float2bfloat16(__uint_as_float(r[i]));
+    }
+  }
+}
 
 }  // namespace zb

@@ -66,6 +66,13 @@ def test_tensor_parallel_two_gpus():
     assert "WORKER_OK" in out
 
 
+@pytest.mark.skipif(_ngpu() < 2 or not CANDIDATES, reason="needs 2 GPUs and ZORSE_TEST_CANDIDATES=1")
+def test_tensor_parallel_scatter_gemm_two_gpus():
+    """Same job with the reduce-scatter sent from inside the row-split GEMMs (scatter epilogue + rs_finish)."""
+    out = _run(2, "tp2_library", timeout=300, ZORSE_TP_FUSED="1")
+    assert "WORKER_OK" in out
+
+
 @pytest.mark.skipif(_ngpu() < 4 or not CANDIDATES, reason="needs 4 GPUs and ZORSE_TEST_CANDIDATES=1")
 def test_tensor_parallel_four_gpus():
     out = _run(4, "tp2_library", timeout=300)

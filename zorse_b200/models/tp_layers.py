@@ -46,6 +46,19 @@ class TPComm:
         dist.reduce_scatter_tensor(out, x.contiguous(), group=self.pg)
         return out
 
+    def linear_rs(self, ops, x: torch.Tensor, w: torch.Tensor, w_kmajor: bool, resid=None, bias=None) -> torch.Tensor:
+        """Rows of sum over the lane of `x @ w^T` (w_kmajor, a forward projection with w [out, in]) or
+        `x @ w` (an input gradient with w [in, out]), plus residual rows and bias: a row-split GEMM and
+        the reduce-scatter behind it.  Here: library GEMM call + library collective + ATen adds;
+        `parallel/tp_fused.py` replaces the three by two kernels."""
+        part = ops.linear_fwd(x, w, None) if w_kmajor else ops.linear_dgrad(x, w)
+        out = self.reduce_scatter_rows(part)
+        if resid is not None:
+            out += resid
+        if bias is not None:
+            out += bias
+        return out
+
     def rows(self, n: int) -> tuple[int, int]:
         """This process's [lo, hi) of n rows."""
         if n % self.size:
@@ -139,10 +152,7 @@ class TPTransformerBlock(TransformerBlock):
         if cs is not None:
             ops.rope_(qkv, cs, S, self.Hq + self.Hkv, self.D)
         att, lse = ops.attn_fwd(qkv, B, S, self.Hq, self.Hkv, self.D, self.causal, self.window)
-        out = tp.reduce_scatter_rows(ops.linear_fwd(att, p["o_w"], None))
-        out += resid
-        if "o_b" in p:
-            out += p["o_b"]
+        out = tp.linear_rs(ops, att, p["o_w"], True, resid, p.get("o_b"))
         if sv is not None:
             sv.update(qkv=qkv, att=att, lse=lse)
         return out
@@ -161,7 +171,7 @@ class TPTransformerBlock(TransformerBlock):
         cs = self._rope(ops, S, dout.device)
         if cs is not None:
             ops.rope_(dqkv, cs, S, self.Hq + self.Hkv, self.D, backward=True)
-        dxin = tp.reduce_scatter_rows(ops.linear_dgrad(dqkv, p["qkv_w"]))
+        dxin = tp.linear_rs(ops, dqkv, p["qkv_w"], False)
         ops.linear_wgrad(dqkv, tp.gather_rows(xin), g["qkv_w"], g.get("qkv_b"))
         return dxin
 
@@ -169,10 +179,7 @@ class TPTransformerBlock(TransformerBlock):
         p, tp = self.p, ctx["tp"]
         hpre = ops.linear_fwd(tp.gather_rows(xin), p["up_w"], p.get("up_b"))
         a = ops.swiglu_fwd(hpre) if self.act == "swiglu" else ops.act_fwd(hpre, self.act)
-        out = tp.reduce_scatter_rows(ops.linear_fwd(a, p["down_w"], None))
-        out += resid
-        if "down_b" in p:
-            out += p["down_b"]
+        out = tp.linear_rs(ops, a, p["down_w"], True, resid, p.get("down_b"))
         if sv is not None:
             sv.update(hpre=hpre, mlp_a=a)
         return out
@@ -185,7 +192,7 @@ class TPTransformerBlock(TransformerBlock):
         da = ops.linear_dgrad(df, p["down_w"])
         ops.linear_wgrad(df, sv["mlp_a"], g["down_w"], None)
         dh = ops.swiglu_bwd(sv["hpre"], da) if self.act == "swiglu" else ops.act_bwd(sv["hpre"], da, self.act)
-        dxin = tp.reduce_scatter_rows(ops.linear_dgrad(dh, p["up_w"]))
+        dxin = tp.linear_rs(ops, dh, p["up_w"], False)
         ops.linear_wgrad(dh, tp.gather_rows(xin), g["up_w"], g.get("up_b"))
         return dxin
 

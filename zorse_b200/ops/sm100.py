@@ -392,6 +392,34 @@ def ag_gemm(a: torch.Tensor, full: torch.Tensor, w_offset: int, w_shape, out: to
     return out
 
 
+def gemm_rs(a: torch.Tensor, b: torch.Tensor, *, b_mn: bool, dst_ptrs, flag_ptrs, flag_index: int, epoch: int,
+            counter: torch.Tensor, ldc: int, max_ctas: int = 0) -> None:
+    """Partial product a @ b^T (b_mn: a @ b) whose rows are scattered for a row-wise reduce-scatter over
+    R = len(dst_ptrs) processes: rows of chunk q are stored (bf16, row stride ldc) at dst_ptrs[q], a device
+    address that may be in a peer's memory; afterwards `epoch` is stored to flag_ptrs[q][flag_index]."""
+    _bf16(a, "a"); _bf16(b, "b")
+    M, K = a.shape
+    N = b.shape[1] if b_mn else b.shape[0]
+    assert (b.shape[0] if b_mn else b.shape[1]) == K and a.stride(-1) == 1 and b.stride(-1) == 1
+    R = len(dst_ptrs)
+    rc = lib().zb_gemm2_rs_bf16(_p(a), _p(b), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)),
+                                c_int(ldc), c_int(int(b_mn)), _ptr_array(dst_ptrs), _ptr_array(flag_ptrs), c_int(R),
+                                c_int(flag_index), c_int(epoch), _p(counter), c_int(max_ctas),
+                                _p(status_word(a.device)), _stream())
+    _check(rc, "gemm_rs")
+
+
+def rs_finish(slots: torch.Tensor, flags: torch.Tensor, R: int, rows: int, H: int, epoch: int, out: torch.Tensor,
+              resid: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, wait_seconds: float = 2.0):
+    """out[rows, H] = sum over the R staging slots ([R, rows, H] bf16, filled by the peers' gemm_rs) (+ resid)
+    (+ bias), after every sender's flag has reached `epoch` (bounded wait)."""
+    rc = lib().zb_rs_finish(_p(slots), _p(flags), c_int(R), c_int(rows), c_int(H), c_int(H), c_int(epoch), _p(resid),
+                            c_int(0 if resid is None else resid.stride(0)), _p(bias), _p(out), c_int(out.stride(0)),
+                            ctypes.c_double(wait_seconds), _p(status_word(out.device)), _stream())
+    _check(rc, "rs_finish")
+    return out
+
+
 def rs_adam(grad_ptrs, flag_ptrs, R: int, r: int, shard_elems: int, master, m, v, p16, *, lr, beta1, beta2, eps,
             weight_decay, step, grad_scale, grad_f32: bool, epoch: int, counter: torch.Tensor, max_blocks: int = 0,
             wait_seconds: float = 2.0):

@@ -7,6 +7,7 @@ stages (interleaving), as in the reference (zorse_utils/pipeline.py:36-318).
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -97,6 +98,8 @@ class PipelineStage:
 
             tp_index = groups.tp.index_of(process_rank)
             self.tp = TPComm(groups.tp.pg, tp_size, tp_index)
+            self._tp_fused = (os.environ.get("ZORSE_TP_FUSED") == "1" and device.type == "cuda"
+                              and getattr(ops, "name", "") == "sm100")
         self.stage_id = st.stage_id
         self.num_stages = len(cfg.stages)
         self.is_first = st.layer_partition[0] == 0
@@ -128,6 +131,11 @@ class PipelineStage:
             self.tokens = self.B * self.S
         if self.tokens % tp_size:
             raise ValueError(f"{self.tokens} tokens per microbatch do not split over {tp_size} tensor-parallel processes")
+        if self.tp is not None and self._tp_fused:
+            from .tp_fused import FusedTPComm
+
+            self.tp = FusedTPComm(groups.tp.pg, tp_size, tp_index, device=device, rows=self.tokens // tp_size,
+                                  hidden=self.hidden, kernels=ops.k)
         self.act_dtype = engine_cfg.compute_dtype
         self.stash = ActivationStash(device, activation_offload, streams.copy)
         self.saved: dict = {}
