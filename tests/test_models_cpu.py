@@ -1,7 +1,6 @@
 """Every model family: the layers' explicit backward passes (through the PyTorch ops backend)
 must reproduce autograd of the same forward, for the whole model, after an optimizer step."""
 import pytest
-import torch
 
 from zorse_b200.config.training_config import parse_pipeline_dict
 from zorse_b200.trainer import Trainer, TrainerOptions

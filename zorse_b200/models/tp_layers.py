@@ -22,12 +22,11 @@ unsplit layer's generator sequence and keeps this process's slice.
 from __future__ import annotations
 
 import math
-from typing import Optional
 
 import torch
 import torch.distributed as dist
 
-from .layers import EmbeddingLayer, HeadLayer, Layer, ParamSpec, TransformerBlock, _norm
+from .layers import EmbeddingLayer, HeadLayer, Layer, TransformerBlock, _norm
 
 
 class TPComm:
