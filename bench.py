@@ -57,11 +57,15 @@ def interleave_plan(stages, layers: int, v: int):
     return out
 
 
-def build_config(n, model, gbs, mbs, seq, vocab, reduce_dtype, schedule, layers_override=None, interleave=1):
+def build_config(n, model, gbs, mbs, seq, vocab, reduce_dtype, schedule, layers_override=None, interleave=1, tp=1):
     from zorse_b200.models import registry
 
     spec = registry.get_spec(model, layers=layers_override)
-    stages, par = parallel_plan(n, spec.layers)
+    if n % tp:
+        raise SystemExit(f"--tp {tp} does not divide --gpus {n}")
+    stages, par = parallel_plan(n // tp, spec.layers)     # with tp > 1 the plan numbers lanes of tp processes
+    if tp > 1:
+        par += f"-tp{tp}"
     if interleave > 1 and len(stages) > 1:
         stages = interleave_plan(stages, spec.layers, interleave)
         par += f"-v{interleave}"
@@ -71,9 +75,12 @@ def build_config(n, model, gbs, mbs, seq, vocab, reduce_dtype, schedule, layers_
         base, rem = divmod(M, len(ranks))
         pipe.append({"gpu_ranks": ranks, "num_microbatches_per_rank": [base + (1 if i < rem else 0) for i in range(len(ranks))],
                      "layer_partition": [a, b], "zero_config": [ranks]})
-    return {"model_name": model, "global_batch_size": gbs, "microbatch_size": mbs, "sequence_length": seq,
-            "vocab_size": vocab, "fused_optimizer": True, "autocast_dtype": "bfloat16", "reduce_dtype": reduce_dtype,
-            "pipeline_config": pipe, "schedule": schedule}, par
+    cfg = {"model_name": model, "global_batch_size": gbs, "microbatch_size": mbs, "sequence_length": seq,
+           "vocab_size": vocab, "fused_optimizer": True, "autocast_dtype": "bfloat16", "reduce_dtype": reduce_dtype,
+           "pipeline_config": pipe, "schedule": schedule}
+    if tp > 1:
+        cfg["tensor_parallel_size"] = tp
+    return cfg, par
 
 
 class ClockSampler(threading.Thread):
@@ -136,6 +143,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the JSON line says so)")
     ap.add_argument("--interleave", type=int, default=1,
                     help="model chunks per rank group (>1 selects the interleaved 1F1B schedule on 4 and 8 GPUs)")
+    ap.add_argument("--tp", type=int, default=1,
+                    help="tensor-parallel processes per lane (not the baseline configuration; the JSON line says so)")
     ap.add_argument("--skip_e2e", action="store_true")
     ap.add_argument("--stall_timeout", type=float, default=420.0,
                     help="abort (non-zero exit) if no training step completes on the host for this many seconds")
@@ -158,7 +167,7 @@ def main():
     if schedule == "auto":
         schedule = "1f1b_interleaved" if (args.interleave > 1 and args.gpus >= 4) else "1f1b"
     cfg_dict, par = build_config(args.gpus, args.model, args.global_batch, args.microbatch, args.seq_len, args.vocab,
-                                 args.reduce_dtype, schedule, args.layers, args.interleave)
+                                 args.reduce_dtype, schedule, args.layers, args.interleave, args.tp)
     cfg = parse_pipeline_dict(cfg_dict)
     recompute = None if args.recompute == "auto" else (args.recompute == "on")
     tr = Trainer(cfg, TrainerOptions(schedule=schedule, ops="sm100", optimizer_in_backward=args.optimizer_in_backward,
