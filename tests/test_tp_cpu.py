@@ -202,3 +202,78 @@ def test_tp2_post_norm_block():
         for r in res:
             registry.make_block(spec, 2, r["tp_index"]).store_into_whole(r["params"][gid], whole)
         assert (whole - orc.flats[gid].detach()).abs().max().item() < 5e-4
+
+
+def test_scatter_gemm_bookkeeping_with_fake_kernels():
+    """The slot offsets, flag indices, buffer parity and epochs `FusedTPComm` hands to its two kernels,
+    checked by stand-ins that interpret device addresses in a fake address space: three processes, five
+    operations with changing inputs, every result must equal the lane-wide sum of that operation."""
+    from zorse_b200.parallel.tp_fused import FusedTPComm
+
+    R, rows, H, K = 3, 256, 256, 64
+    T = R * rows
+    space = {}        # base address -> flat byte view
+
+    def view_at(addr, nbytes):
+        for base, buf in space.items():
+            if base <= addr and addr + nbytes <= base + buf.numel():
+                return buf[addr - base: addr - base + nbytes]
+        raise AssertionError(f"address {addr} (+{nbytes}) outside every buffer")
+
+    class Fake:
+        def gemm_rs(self, a, b, *, b_mn, dst_ptrs, flag_ptrs, flag_index, epoch, counter, ldc, max_ctas=0):
+            part = (a.float() @ (b.float() if b_mn else b.float().t())).to(torch.bfloat16)
+            assert ldc == part.shape[1] and part.shape[0] % len(dst_ptrs) == 0
+            n = part.shape[0] // len(dst_ptrs)
+            for q, dst in enumerate(dst_ptrs):
+                view_at(dst, n * ldc * 2).view(torch.bfloat16).copy_(part[q * n:(q + 1) * n].reshape(-1))
+                view_at(flag_ptrs[q] + 4 * flag_index, 4).view(torch.int32).fill_(epoch)
+
+        def rs_finish(self, slots, flags, R_, rows_, H_, epoch, out, resid=None, bias=None, wait_seconds=2.0):
+            assert flags.numel() == R_ and int(flags.min()) >= epoch, (flags, epoch)   # a real kernel would wait
+            acc = slots.view(R_, rows_, H_).float().sum(0)
+            if resid is not None:
+                acc = acc + resid.float()
+            if bias is not None:
+                acc = acc + bias.float()
+            out.copy_(acc.to(out.dtype))
+            return out
+
+    def buffers_for(rank):
+        def make(pg, size, device, stage_elems):
+            return shared[rank]
+        return make
+
+    shared = []
+    bases = []
+    for r in range(R):
+        stage = torch.zeros(2 * R * rows * H, dtype=torch.bfloat16)
+        flags = torch.zeros(64, dtype=torch.int32)
+        sb, fb = 1_000_000 * (r + 1), 1_000_000 * (r + 1) + 900_000
+        space[sb] = stage.view(torch.uint8)
+        space[fb] = flags.view(torch.uint8)
+        bases.append((stage, flags, sb, fb))
+    for r in range(R):
+        shared.append((bases[r][0], bases[r][1], [b[2] for b in bases], [b[3] for b in bases]))
+    comms = [FusedTPComm(None, R, r, device=torch.device("cpu"), rows=rows, hidden=H, kernels=Fake(),
+                         buffers=buffers_for(r)) for r in range(R)]
+    g = torch.Generator().manual_seed(0)
+    for op in range(5):
+        kmajor = op % 2 == 0
+        xs = [torch.randn(T, K, generator=g).to(torch.bfloat16) for _ in range(R)]
+        ws = [(torch.randn(H, K, generator=g) if kmajor else torch.randn(K, H, generator=g)).to(torch.bfloat16) for _ in range(R)]
+        resid = [torch.randn(rows, H, generator=g).to(torch.bfloat16) for _ in range(R)]
+        bias = torch.randn(H, generator=g).to(torch.bfloat16)
+        parts = [(x.float() @ (w.float().t() if kmajor else w.float())).to(torch.bfloat16).float() for x, w in zip(xs, ws)]
+        total = sum(parts)
+        # every process sends, then every process finishes (the order real streams allow as well)
+        ops_ = [comms[r].send(xs[r], ws[r], kmajor) for r in range(R)]
+        outs = [comms[r].finish(ops_[r], resid[r] if op % 3 else None, bias if op % 2 else None) for r in range(R)]
+        for r in range(R):
+            want = total[r * rows:(r + 1) * rows]
+            if op % 3:
+                want = want + resid[r].float()
+            if op % 2:
+                want = want + bias.float()
+            assert (outs[r].float() - want).abs().max().item() < 0.51, (op, r)
+    assert all(c.n_ops == 5 for c in comms)

@@ -26,33 +26,46 @@ import torch.distributed as dist
 from ..models.tp_layers import TPComm
 
 
-class FusedTPComm(TPComm):
-    def __init__(self, pg, size: int, index: int, *, device: torch.device, rows: int, hidden: int, kernels):
-        super().__init__(pg, size, index)
-        import torch.distributed._symmetric_memory as symm
+def symmetric_buffers(pg, size: int, device: torch.device, stage_elems: int):
+    """Staging buffer and flag words in symmetric memory: (stage, flags, every process's stage address,
+    every process's flag address)."""
+    import torch.distributed._symmetric_memory as symm
 
+    stage = symm.empty(stage_elems, dtype=torch.bfloat16, device=device)
+    flags = symm.empty(64, dtype=torch.int32, device=device)
+    stage.zero_()
+    flags.zero_()
+    torch.cuda.synchronize()
+    h_stage, h_flags = symm.rendezvous(stage, pg), symm.rendezvous(flags, pg)
+    dist.barrier(group=pg)
+    stage._zb_handle, flags._zb_handle = h_stage, h_flags      # keep the mappings alive with the tensors
+    return (stage, flags, [int(h_stage.buffer_ptrs[q]) for q in range(size)],
+            [int(h_flags.buffer_ptrs[q]) for q in range(size)])
+
+
+class FusedTPComm(TPComm):
+    def __init__(self, pg, size: int, index: int, *, device: torch.device, rows: int, hidden: int, kernels,
+                 buffers=symmetric_buffers):
+        super().__init__(pg, size, index)
         if size > 8:
             raise ValueError("the scatter GEMM addresses at most 8 processes")
+        if 2 * size > 64:
+            raise ValueError("flag block too small")
         self.k, self.device, self.n_rows, self.hidden = kernels, device, rows, hidden
         self.slot = rows * hidden                     # elements of one sender's slot
-        self.stage = symm.empty(2 * size * self.slot, dtype=torch.bfloat16, device=device)
-        self.flags = symm.empty(64, dtype=torch.int32, device=device)
-        self.stage.zero_()
-        self.flags.zero_()
-        torch.cuda.synchronize()
-        h_stage, h_flags = symm.rendezvous(self.stage, pg), symm.rendezvous(self.flags, pg)
-        self._handles = (h_stage, h_flags)
-        self.stage_ptrs = [int(h_stage.buffer_ptrs[q]) for q in range(size)]
-        self.flag_ptrs = [int(h_flags.buffer_ptrs[q]) for q in range(size)]
+        self.stage, self.flags, self.stage_ptrs, self.flag_ptrs = buffers(pg, size, device, 2 * size * self.slot)
         self.counter = torch.zeros(1, dtype=torch.int32, device=device)
         self.n_ops = 0
-        dist.barrier(group=pg)
 
     def linear_rs(self, ops, x, w, w_kmajor: bool, resid=None, bias=None):
         T = x.shape[0]
         N = w.shape[0] if w_kmajor else w.shape[1]
         if T != self.n_rows * self.size or N != self.hidden or T < 256 or N < 256:
             return super().linear_rs(ops, x, w, w_kmajor, resid, bias)      # the same choice on every process
+        return self.finish(self.send(x, w, w_kmajor), resid, bias)
+
+    def send(self, x, w, w_kmajor: bool) -> tuple[int, int]:
+        """Scatter GEMM of this process's partial product; returns (buffer parity, epoch) of the operation."""
         i = self.n_ops
         self.n_ops += 1
         par, epoch, R, r = i & 1, i + 1, self.size, self.index
@@ -60,6 +73,12 @@ class FusedTPComm(TPComm):
         self.k.gemm_rs(x, w, b_mn=not w_kmajor, dst_ptrs=[p + mine for p in self.stage_ptrs],
                        flag_ptrs=self.flag_ptrs, flag_index=par * R + r, epoch=epoch, counter=self.counter,
                        ldc=self.hidden)
+        return par, epoch
+
+    def finish(self, op: tuple[int, int], resid=None, bias=None) -> torch.Tensor:
+        """Sum of the lane's slots for this process's rows (+ residual, + bias) once every sender's flag is up."""
+        par, epoch = op
+        R = self.size
         out = torch.empty(self.n_rows, self.hidden, dtype=torch.bfloat16, device=self.device)
         slots = self.stage[par * R * self.slot:(par + 1) * R * self.slot]
         return self.k.rs_finish(slots, self.flags[par * R:(par + 1) * R], R, self.n_rows, self.hidden, epoch, out,
