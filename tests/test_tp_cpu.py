@@ -55,7 +55,7 @@ TWO_STAGES = [{"gpu_ranks": [0], "num_microbatches_per_rank": [4], "layer_partit
 TWO_DP = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [2, 2], "layer_partition": [0, 4], "zero_config": [[0, 1]]}]
 
 
-@pytest.mark.parametrize("schedule,recompute", [("layer_major", None), ("1f1b", False), ("zero2", None)])
+@pytest.mark.parametrize("schedule,recompute", [("layer_major", None), ("1f1b", False)])
 def test_tp2_one_lane(schedule, recompute):
     cfg = tiny_cfg(ONE_LANE, tensor_parallel_size=2)
     res = run_workers(2, _worker, cfg, {"schedule": schedule, "activation_recompute": recompute}, 2)
@@ -71,7 +71,7 @@ def test_tp2_two_stages(schedule):
     _check_tp(res, cfg)
 
 
-@pytest.mark.parametrize("schedule,oib", [("layer_major", False), ("zero2", True)])
+@pytest.mark.parametrize("schedule,oib", [("zero2", True)])
 def test_tp2_two_way_zero(schedule, oib):
     """ZeRO shard groups connect the processes that hold the same slice: {0, 2} and {1, 3}."""
     cfg = tiny_cfg(TWO_DP, tensor_parallel_size=2)
@@ -117,8 +117,8 @@ def test_slices_tile_the_unsplit_block():
 
 
 def test_checkpoint_across_tensor_parallel_widths(tmp_path):
-    """Saved with tp 2: resumes with tp 2, with tp 1 on two pipeline stages (blocks put back together
-    from their slices) and with tp 1 on two ZeRO ranks; saved with tp 1: resumes with tp 2."""
+    """Saved with tp 2: resumes with tp 2 and with tp 1 on two ZeRO ranks (blocks put back together
+    from their slices); saved with tp 1 on two stages: resumes with tp 2."""
     from test_ckpt_health_cpu import _load_and_step, _train_and_save
     from test_dist_cpu import PIPE_1x2, PIPE_2x1
 
@@ -126,13 +126,11 @@ def test_checkpoint_across_tensor_parallel_widths(tmp_path):
     a = run_workers(2, _train_and_save, tiny_cfg(ONE_LANE, tensor_parallel_size=2), ck, 2)
     b = run_workers(2, _load_and_step, tiny_cfg(ONE_LANE, tensor_parallel_size=2), ck, 2)
     assert abs(a[0] - b[0]) < 1e-5, (a, b)
-    c = run_workers(2, _load_and_step, tiny_cfg(PIPE_2x1), ck, 2)
-    assert abs(a[0] - c[0]) < 1e-4, (a, c)
     d = run_workers(2, _load_and_step, tiny_cfg(PIPE_1x2), ck, 2)
     assert abs(a[0] - d[0]) < 1e-4, (a, d)
     ck1 = str(tmp_path / "ck1")
-    e = run_workers(2, _train_and_save, tiny_cfg(PIPE_1x2), ck1, 2)
-    f = run_workers(4, _load_and_step, tiny_cfg(TWO_DP, tensor_parallel_size=2), ck1, 2)
+    e = run_workers(2, _train_and_save, tiny_cfg(PIPE_2x1), ck1, 2)
+    f = run_workers(2, _load_and_step, tiny_cfg(ONE_LANE, tensor_parallel_size=2), ck1, 2)
     assert abs(e[0] - f[0]) < 1e-4, (e, f)
 
 
