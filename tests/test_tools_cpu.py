@@ -206,3 +206,17 @@ def test_perf_check_flags_regressions(tmp_path):
     f.write_text(json.dumps({"rows": rows}))
     assert perf_check.main([str(f)]) == 1
     assert perf_check.main([str(f), "--tolerance", "0.5"]) == 0
+
+
+def test_mesh_cli_writes_a_valid_config(capsys):
+    import json
+
+    from zorse_b200.config.training_config import parse_pipeline_dict
+    from zorse_b200.parallel import mesh
+
+    assert mesh.main(["--pp", "2", "--dp_shard", "2", "--tp", "2", "--model_name", "tiny_llama",
+                      "--global_batch_size", "8", "--microbatch_size", "2", "--sequence_length", "32",
+                      "--schedule", "1f1b"]) == 0
+    cfg = parse_pipeline_dict(json.loads(capsys.readouterr().out))
+    assert cfg.world_size == 8 and cfg.tensor_parallel_size == 2 and cfg.schedule == "1f1b"
+    assert [s.layer_partition for s in cfg.stages] == [(0, 2), (2, 4)]

@@ -73,3 +73,39 @@ class ParallelDims:
             d["tensor_parallel_size"] = self.tp
         d.update(extra)
         return d
+
+
+def main(argv=None) -> int:
+    """`python -m zorse_b200.parallel.mesh --pp 4 --dp_shard 2 --model_name llama2_7b ...` prints the
+    training config of a regular layout (redirect it to a file for `zorse.py --config_file`)."""
+    import argparse
+    import json
+
+    from ..models import registry
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--dp_replicate", type=int, default=1)
+    ap.add_argument("--dp_shard", type=int, default=1)
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--pp", type=int, default=1)
+    ap.add_argument("--model_name", required=True)
+    ap.add_argument("--global_batch_size", type=int, required=True)
+    ap.add_argument("--microbatch_size", type=int, default=1)
+    ap.add_argument("--sequence_length", type=int, required=True)
+    ap.add_argument("--vocab_size", type=int, default=None)
+    ap.add_argument("--zero_level", type=int, default=3, choices=[2, 3])
+    ap.add_argument("--schedule", default=None)
+    a = ap.parse_args(argv)
+    dims = ParallelDims(a.dp_replicate, a.dp_shard, a.tp, a.pp)
+    spec = registry.get_spec(a.model_name, vocab=a.vocab_size)
+    extra = {"vocab_size": spec.vocab}
+    if a.schedule:
+        extra["schedule"] = a.schedule
+    d = dims.training_config(a.model_name, spec.layers, a.global_batch_size, a.microbatch_size, a.sequence_length,
+                             zero_level=a.zero_level, **extra)
+    print(json.dumps(d, indent=1))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
