@@ -15,6 +15,9 @@ SCHEDULES = {
     "two_stage_sync": TwoStageSyncSchedule,
     "zero2": Zero2Schedule, "zero2_pipeline": Zero2Schedule,
     "flashflex": FlashflexSchedule, "flashflex_pipeline": FlashflexSchedule,
+    # all forwards, then all backwards, microbatch-major with activations kept on the GPU is GPipe's order
+    # (the reference names it only in its unused torch.distributed.pipelining wrapper, models/pipeline_model.py:51-78)
+    "gpipe": FlashflexSchedule,
     "1f1b": OneFOneBSchedule, "one_f_one_b": OneFOneBSchedule,
     "1f1b_interleaved": InterleavedOneFOneBSchedule, "interleaved_1f1b": InterleavedOneFOneBSchedule,
 }
