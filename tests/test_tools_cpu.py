@@ -220,3 +220,25 @@ def test_mesh_cli_writes_a_valid_config(capsys):
     cfg = parse_pipeline_dict(json.loads(capsys.readouterr().out))
     assert cfg.world_size == 8 and cfg.tensor_parallel_size == 2 and cfg.schedule == "1f1b"
     assert [s.layer_partition for s in cfg.stages] == [(0, 2), (2, 4)]
+
+
+def test_candidate_report_parent_side(monkeypatch, capsys):
+    """Case list, child-failure handling and the table of the candidate report (no GPU: children are faked)."""
+    from zorse_b200.profiler import candidates as C
+
+    assert len(C.CASES) == len(set(C.CASES)) == 24
+    fake = {"flash_bwd2:7b": {"case": "flash_bwd2:7b", "agrees": True, "max_diff": 0.01, "tolerance": 0.06, "status_word": 0,
+                              "ms_default": 0.9, "ms_candidate": 0.45},
+            "norm_bwd2_rms:7b": {"case": "norm_bwd2_rms:7b", "agrees": False, "max_diff": 0.5, "tolerance": 0.03,
+                                 "status_word": 3}}
+    monkeypatch.setattr(C, "run_child", lambda case, timeout: fake.get(case, {"case": case, "error": "exit code 1: boom"}))
+    rc = C.main(["--only", "flash_bwd2:7b,norm_bwd2_rms:7b,norm_fwd2_ln:gqa64"])
+    out = capsys.readouterr().out
+    assert rc == 1
+    assert "| flash_bwd2:7b | yes | 0.01 (0.06) | 0 | 0.900 | 0.450 | 2.00x |" in out
+    assert "| norm_bwd2_rms:7b | NO |" in out and "exit code 1: boom" in out
+    # a child that prints nothing useful is reported, not raised
+    import subprocess as sp
+    monkeypatch.undo()
+    monkeypatch.setattr(sp, "run", lambda *a, **k: sp.CompletedProcess(a, 3, stdout="", stderr="Traceback\nRuntimeError: x"))
+    assert C.run_child("flash_bwd2:7b", 1.0)["error"].startswith("exit code 3: RuntimeError")

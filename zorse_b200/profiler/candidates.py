@@ -1,0 +1,176 @@
+"""One report on every kernel version that is built but not the default: does it agree with the
+default kernel, and is it faster?
+
+    python -m zorse_b200.profiler.candidates [--out report.json] [--only flash_fwd4,norm_bwd2] [--timeout 120]
+
+Every case runs in its own child process (a kernel that faults or trips a bounded wait cannot take
+the other cases with it), computes the same op with the default version and with the candidate on
+identical inputs, and reports the largest difference, the kernel status word and CUDA-event
+timings (3 warm-up + 10 timed runs, a 256 MB write between runs so that no operand is served from
+L2, median).  The parent prints one table and writes the JSON.  Defaults were checked against the
+fp32 oracle by the GPU tests, so agreement with them within the bf16 tolerance is the criterion.
+
+Cases: flash_fwd4 (flags 0, 1, 2), flash_bwd2, norm_fwd2, norm_bwd2, each on a Llama-2-7B-like
+shape, a grouped-query d = 64 shape and a ragged / sliding-window shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+
+ATTN_SHAPES = {   # name: (B, S, Hq, Hkv, D, window)
+    "7b": (1, 4096, 32, 32, 128, 0),
+    "gqa64": (2, 2048, 32, 8, 64, 0),
+    "ragged_window": (1, 1000, 8, 2, 128, 384),
+}
+NORM_SHAPES = {"7b": (4096, 4096), "gqa64": (4096, 2048), "ragged_window": (1000, 5120)}
+
+CASES = [f"{k}:{s}" for k in ("flash_fwd4_f0", "flash_fwd4_f1", "flash_fwd4_f2", "flash_bwd2") for s in ATTN_SHAPES] + \
+        [f"{k}:{s}" for k in ("norm_fwd2_rms", "norm_fwd2_ln", "norm_bwd2_rms", "norm_bwd2_ln") for s in NORM_SHAPES]
+
+
+def _time(fn, flush, warm=3, reps=10):
+    import torch
+
+    for _ in range(warm):
+        fn()
+    ts = []
+    for _ in range(reps):
+        flush.add_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return statistics.median(ts)
+
+
+def _diff(a, b):
+    return float((a.float() - b.float()).abs().max().item())
+
+
+def run_case(case: str) -> dict:
+    """Child process: one candidate against the default on one shape."""
+    import torch
+
+    from zorse_b200.ops import sm100 as k
+
+    kind, shape = case.split(":")
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(1)
+    rnd = lambda *s: (torch.randn(*s, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device=dev)
+    res: dict = {"case": case}
+    if kind.startswith("flash"):
+        B, S, Hq, Hkv, D, win = ATTN_SHAPES[shape]
+        qkv, do = rnd(B * S, (Hq + 2 * Hkv) * D), rnd(B * S, Hq * D)
+        out1, lse1 = k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win, version=1)
+        if kind.startswith("flash_fwd4"):
+            fl = int(kind[-1])
+            cand = lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win, version=4, flags=fl)
+            base = lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win, version=1)
+            out4, lse4 = cand()
+            torch.cuda.synchronize()
+            res["max_diff"] = max(_diff(out4, out1), _diff(lse4, lse1))
+            res["tolerance"] = 3e-2 if fl < 2 else 4e-2
+        else:
+            cand = lambda: k.flash_bwd(do, qkv, out1, lse1, B, S, Hq, Hkv, D, True, win, version=2)
+            base = lambda: k.flash_bwd(do, qkv, out1, lse1, B, S, Hq, Hkv, D, True, win, version=1)
+            d1, d2 = base(), cand()
+            torch.cuda.synchronize()
+            res["max_diff"] = _diff(d1, d2)
+            res["tolerance"] = 6e-2
+    else:
+        T, H = NORM_SHAPES[shape]
+        ln = kind.endswith("_ln")
+        x, w = rnd(T, H), (1.0 + 0.1 * torch.randn(H, device=dev, generator=g)).to(torch.bfloat16)
+        b = (0.1 * torch.randn(H, device=dev, generator=g)).to(torch.bfloat16) if ln else None
+        y1, st1 = k.norm_fwd(x, w, b, 1e-5, ln, version=1)
+        if kind.startswith("norm_fwd2"):
+            cand = lambda: k.norm_fwd(x, w, b, 1e-5, ln, version=2)
+            base = lambda: k.norm_fwd(x, w, b, 1e-5, ln, version=1)
+            y2, st2 = cand()
+            torch.cuda.synchronize()
+            res["max_diff"] = max(_diff(y1, y2), _diff(st1, st2))
+            res["tolerance"] = 2e-2
+        else:
+            dy, dres = rnd(T, H), rnd(T, H)
+
+            def run(version):
+                dw = torch.zeros(H, dtype=torch.float32, device=dev)
+                db = torch.zeros(H, dtype=torch.float32, device=dev) if ln else None
+                dx = k.norm_bwd(dy, x, w, st1, dres, dw, db, ln, version=version)
+                return dx, dw, db
+
+            cand, base = (lambda: run(2)), (lambda: run(1))
+            (dx1, dw1, db1), (dx2, dw2, db2) = base(), cand()
+            torch.cuda.synchronize()
+            rel = lambda a, c: _diff(a, c) / max(1.0, float(a.float().abs().max().item()))
+            res["max_diff"] = max(_diff(dx1, dx2), rel(dw1, dw2), rel(db1, db2) if ln else 0.0)
+            res["tolerance"] = 3e-2
+    st = int(k.status_word().item())
+    res["status_word"] = st
+    res["agrees"] = bool(st == 0 and res["max_diff"] <= res["tolerance"])
+    if st == 0:
+        res["ms_default"], res["ms_candidate"] = _time(base, flush), _time(cand, flush)
+        res["status_word"] = int(k.status_word().item())
+    return res
+
+
+def format_table(results: list[dict]) -> str:
+    rows = ["| case | agrees | max diff (tol) | status | default ms | candidate ms | speed-up |", "|---|---|---|---|---|---|---|"]
+    for r in results:
+        if "error" in r:
+            rows.append(f"| {r['case']} | - | - | - | - | - | {r['error']} |")
+            continue
+        d, c = r.get("ms_default"), r.get("ms_candidate")
+        sp = f"{d / c:.2f}x" if d and c else "-"
+        ms = lambda v: f"{v:.3f}" if v is not None else "-"
+        rows.append(f"| {r['case']} | {'yes' if r['agrees'] else 'NO'} | {r['max_diff']:.3g} ({r['tolerance']:g}) | "
+                    f"{r['status_word']} | {ms(d)} | {ms(c)} | {sp} |")
+    return "\n".join(rows)
+
+
+def run_child(case: str, timeout: float) -> dict:
+    """Runs one case in a child interpreter and parses the JSON line it prints."""
+    cmd = [sys.executable, "-m", "zorse_b200.profiler.candidates", "--child", case]
+    try:
+        p = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+    except subprocess.TimeoutExpired:
+        return {"case": case, "error": f"no answer within {timeout:.0f} s"}
+    for line in reversed(p.stdout.strip().splitlines()):
+        if line.startswith("{"):
+            return json.loads(line)
+    tail = (p.stderr.strip().splitlines() or ["no output"])[-1]
+    return {"case": case, "error": f"exit code {p.returncode}: {tail[:200]}"}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--out", default=None)
+    ap.add_argument("--only", default=None, help="comma-separated substrings of case names")
+    ap.add_argument("--timeout", type=float, default=120.0, help="seconds per case")
+    ap.add_argument("--child", default=None, help=argparse.SUPPRESS)
+    a = ap.parse_args(argv)
+    if a.child:
+        print(json.dumps(run_case(a.child)), flush=True)
+        return 0
+    want = [c for c in CASES if a.only is None or any(s in c for s in a.only.split(","))]
+    results = []
+    for c in want:
+        r = run_child(c, a.timeout)
+        results.append(r)
+        print(json.dumps(r), flush=True)
+    print(format_table(results))
+    if a.out:
+        with open(a.out, "w") as f:
+            json.dump(results, f, indent=1)
+    return 0 if all(r.get("agrees") for r in results) else 1
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
