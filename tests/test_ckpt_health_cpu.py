@@ -100,6 +100,25 @@ def test_watchdog_fires_on_a_stuck_step():
     w.stop()
 
 
+def test_watchdog_allows_a_slow_first_step():
+    """Until the first beat the longer start-up limit applies; afterwards the normal one."""
+    fired = []
+    w = Watchdog(0.2, on_timeout=lambda step, idle: fired.append((step, idle)), poll_s=0.05, startup_s=1.0)
+    w.start()
+    time.sleep(0.5)
+    assert not fired            # 0.5 s without any beat: inside the start-up limit
+    w.beat(0)
+    time.sleep(0.5)
+    assert fired and fired[0][0] == 0
+    w.stop()
+    fired2 = []
+    w2 = Watchdog(0.2, on_timeout=lambda step, idle: fired2.append(step), poll_s=0.05, startup_s=0.4)
+    w2.start()
+    time.sleep(0.8)
+    assert fired2 == [-1]       # a first step that never ends is still caught
+    w2.stop()
+
+
 def _rank_that_dies(rank, world):
     """A rank that raises before joining a collective: the others see a bounded failure."""
     import datetime

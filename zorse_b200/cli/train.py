@@ -65,14 +65,16 @@ def main(argv=None) -> int:
             # name the ranks whose heartbeat is older than ours before giving up
             msg = f"[watchdog] rank {tr.rank}: no progress for {idle:.1f}s after step {step}"
             if heartbeat is not None:
-                behind = [r for r in heartbeat.stale_ranks(args.heartbeat_timeout, min_step=step) if r != tr.rank]
+                # half the limit: a peer that beat a moment after this rank's last beat is just as stuck
+                behind = [r for r in heartbeat.stale_ranks(args.heartbeat_timeout / 2, min_step=step) if r != tr.rank]
                 msg += f"; ranks behind or silent: {behind}"
             sys.stderr.write(msg + "; dumping stacks and aborting\n")
             faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
             sys.stderr.flush()
             os._exit(3)
 
-        watchdog = Watchdog(args.heartbeat_timeout, rank=tr.rank, on_timeout=stuck)
+        watchdog = Watchdog(args.heartbeat_timeout, rank=tr.rank, on_timeout=stuck,
+                            startup_s=args.heartbeat_startup or 10 * args.heartbeat_timeout)
         watchdog.start()
     batch = tr.synthetic_batch()
     inputs, targets, _ = tr.to_device(batch)

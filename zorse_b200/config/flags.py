@@ -73,6 +73,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--checkpoint_every", type=int, default=0)
     p.add_argument("--resume", type=str, default=None)
     p.add_argument("--heartbeat_timeout", type=float, default=0.0, help="seconds; 0 disables the watchdog")
+    p.add_argument("--heartbeat_startup", type=float, default=0.0,
+                   help="seconds the first step may take (default: ten times --heartbeat_timeout)")
     p.add_argument("--inject_fault", type=str, default=None,
                    help="testing: rank:step:kind (stall | raise | exit), a host-side failure of one rank between steps")
     p.add_argument("--shift_labels", action="store_true",

@@ -67,9 +67,12 @@ class DictStore:
 
 class Watchdog(threading.Thread):
     def __init__(self, timeout_s: float, rank: int = 0, on_timeout: Optional[Callable[[int, float], None]] = None,
-                 poll_s: float = 0.5):
+                 poll_s: float = 0.5, startup_s: Optional[float] = None):
+        """`startup_s`: limit that applies until the first beat (the first step pays for lazy communicator
+        set-up, library loading and allocator warm-up, several times a normal step); default: timeout_s."""
         super().__init__(daemon=True)
         self.timeout_s, self.rank, self.poll_s = timeout_s, rank, poll_s
+        self.startup_s = max(timeout_s, startup_s) if startup_s is not None else timeout_s
         self.on_timeout = on_timeout or self._abort
         self._last = time.monotonic()
         self._step = -1
@@ -86,7 +89,7 @@ class Watchdog(threading.Thread):
     def run(self) -> None:
         while not self._stop.wait(self.poll_s):
             idle = time.monotonic() - self._last
-            if idle > self.timeout_s:
+            if idle > (self.startup_s if self._step < 0 else self.timeout_s):
                 self.fired = True
                 self.on_timeout(self._step, idle)
                 return
