@@ -88,14 +88,14 @@ def test_heartbeat_names_the_silent_rank():
 
 def test_watchdog_fires_on_a_stuck_step():
     fired = []
-    w = Watchdog(0.3, on_timeout=lambda step, idle: fired.append((step, idle)), poll_s=0.05)
+    w = Watchdog(1.0, on_timeout=lambda step, idle: fired.append((step, idle)), poll_s=0.05)
     w.start()
     w.beat(7)
-    time.sleep(0.15)
+    time.sleep(0.2)
     w.beat(8)
-    time.sleep(0.15)
+    time.sleep(0.2)
     assert not fired
-    time.sleep(0.5)
+    time.sleep(1.3)
     assert fired and fired[0][0] == 8
     w.stop()
 
