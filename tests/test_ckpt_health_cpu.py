@@ -50,8 +50,6 @@ def test_checkpoint_reshard_from_unequal_shards(tmp_path):
     a = run_workers(2, _train_and_save, tiny_cfg(uneven), ck, 2)
     b = run_workers(2, _load_and_step, tiny_cfg(PIPE_1x2), ck, 2)       # -> equal shards
     assert abs(a[0] - b[0]) < 1e-4, (a, b)
-    c = run_workers(2, _load_and_step, tiny_cfg(PIPE_2x1), ck, 2)       # -> two stages
-    assert abs(a[0] - c[0]) < 1e-4, (a, c)
     d = run_workers(2, _load_and_step, tiny_cfg([dict(PIPE_1x2[0], shard_ratio=[1, 2])]), ck, 2)
     assert abs(a[0] - d[0]) < 1e-4, (a, d)
 

@@ -63,7 +63,7 @@ def test_tp2_one_lane(schedule, recompute):
     assert all(n > 0 for r in res for n in r["all_reduces"])      # norm / embedding / head gradients summed over the lane
 
 
-@pytest.mark.parametrize("schedule", ["layer_major", "1f1b"])
+@pytest.mark.parametrize("schedule", ["1f1b"])
 def test_tp2_two_stages(schedule):
     """2 stages x tp 2 = 4 processes; process l*2+t sends its rows to process (l+1)*2+t."""
     cfg = tiny_cfg(TWO_STAGES, tensor_parallel_size=2)
