@@ -315,3 +315,24 @@ def test_latency_probe_and_attention_traces_run(k):
     for kern in ("fwd4", "bwd2"):
         attn_trace.main(["--kernel", kern, "--S", "1024", "--heads", "2", "--kv_heads", "2", "--ctas", "2"])
         k.check_status()
+
+
+@pytest.mark.skipif(not CANDIDATES, reason="ZORSE_TEST_CANDIDATES=1: first run on hardware pending")
+def test_a_wait_that_runs_out_reports_and_leaves_the_context_usable(k):
+    """Failure detection on the device: a wait on a flag that nothing sets gives up after its (short)
+    limit, the kernel returns, the host reads which wait it was, and the next launches work.  Nothing
+    here faults, traps or spins without bound."""
+    from zorse_b200.ops.sm100 import KernelError
+
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    k.check_status()
+    k.wait_flags(flags, 2, 0, 1, wait_seconds=0.05)        # flags[0..1] never reach epoch 1
+    torch.cuda.synchronize()
+    with pytest.raises(KernelError, match="status"):
+        k.check_status()
+    k.check_status()                                        # the word was cleared by the report
+    flags[:2] = 1
+    k.wait_flags(flags, 2, 0, 1, wait_seconds=0.05)        # satisfied at once
+    k.check_status()
+    x = torch.arange(8, device="cuda", dtype=torch.float32)
+    assert float(x.sum().item()) == 28.0
