@@ -207,3 +207,49 @@ def test_read_range_against_synthetic_shard_files(tmp_path):
                 got = read_range(str(d), meta, offsets, u, which, a, b)
                 want = torch.from_numpy((u["gid"] * 1e6 + which * 1e5 + np.arange(a, b)).astype("float32"))
                 assert torch.equal(got, want), (trial, u, which, a, b)
+
+
+def _resume_cli_like(rank, world, cfg_dict, ck):
+    from zorse_b200.ckpt.reader import load_checkpoint
+    from zorse_b200.trainer import Trainer, TrainerOptions
+
+    tr = Trainer(parse_pipeline_dict(cfg_dict), TrainerOptions(backend="gloo", schedule="layer_major", seed=0))
+    load_checkpoint(tr, ck)
+    return tr.global_loss(tr.train_step_from_host(tr.synthetic_batch()))
+
+
+def test_recover_replans_for_the_gpus_that_are_left(tmp_path):
+    """A two-rank job saves, one GPU is lost: the recovery tool picks the newest complete checkpoint,
+    drops the GPU from the cluster description, plans for the remaining one, and the job resumes
+    there with the loss the old job would have had."""
+    import json
+
+    from zorse_b200.cli import recover
+
+    ck = str(tmp_path / "ck")
+    a = run_workers(2, _train_and_save, tiny_cfg(PIPE_1x2), ck, 2)
+    os.makedirs(os.path.join(ck, "step_9"))                      # newer but incomplete: no meta.json
+    assert recover.latest_checkpoint(ck) == os.path.join(ck, "step_2")
+    assert recover.latest_checkpoint(str(tmp_path / "nothing")) is None
+    gl = [{"index": i, "name": "NVIDIA B200", "memory_total_mib": 183359, "id": f"gpu_{i}", "machine": "m0",
+           "global_rank": i} for i in range(2)]
+    cluster = {"machines": [{"machine": "m0", "num_gpus": 2, "machine_index": 0, "gpus": gl}], "gpu_list": gl,
+               "total_gpus": 2, "bandwidth": {"internode_bandwidth": {}, "intranode_bandwidth": {"0": 770.0},
+                                              "internode_latency": {}, "intranode_latency": {"0": 2e-5}}}
+    small = recover.shrink_cluster(cluster, [0])
+    assert small["total_gpus"] == 1 and small["gpu_list"][0]["global_rank"] == 0 and small["gpu_list"][0]["index"] == 1
+    assert small["machines"][0]["num_gpus"] == 1 and cluster["total_gpus"] == 2       # the input is not modified
+    with pytest.raises(ValueError):
+        recover.shrink_cluster(cluster, [0, 1])
+    with pytest.raises(ValueError):
+        recover.shrink_cluster(cluster, [7])
+    cfile, out = tmp_path / "cluster.json", tmp_path / "new.json"
+    cfile.write_text(json.dumps(cluster))
+    assert recover.main(["--checkpoint_dir", ck, "--cluster_info_file", str(cfile), "--exclude_ranks", "1",
+                         "--output", str(out)]) == 0
+    new = json.loads(out.read_text())
+    cfg = parse_pipeline_dict(new)
+    assert cfg.world_size == 1 and cfg.model_name == "tiny_llama" and cfg.global_batch_size == 8
+    assert cfg.vocab_size == 512 and cfg.autocast_dtype == "float32"
+    b = run_workers(1, _resume_cli_like, new, os.path.join(ck, "step_2"))
+    assert abs(a[0] - b[0]) < 1e-4, (a, b)
