@@ -242,3 +242,24 @@ def test_candidate_report_parent_side(monkeypatch, capsys):
     monkeypatch.undo()
     monkeypatch.setattr(sp, "run", lambda *a, **k: sp.CompletedProcess(a, 3, stdout="", stderr="Traceback\nRuntimeError: x"))
     assert C.run_child("flash_bwd2:7b", 1.0)["error"].startswith("exit code 3: RuntimeError")
+
+
+def test_step_model_adds_up_the_recorded_kernel_times():
+    import json
+    import os
+
+    from zorse_b200.profiler import step_model as SM
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    t = json.load(open(os.path.join(root, "data", "kernel_baseline_b200.json")))["kernels"]
+    m = SM.step_model(t, layers=32, microbatches=64)
+    want = 32 * 64 * t["flash fwd | 7b S4096 Hq32 Hkv32 D128 win0"]["ours_ms"]
+    assert abs(m["attention fwd"]["ours_ms"] - want) < 1e-6
+    assert abs(m["optimizer"]["ours_ms"] - 64 * t["adam (bf16 grad) | n101191680"]["ours_ms"]) < 1e-6
+    total = sum(g["ours_ms"] for g in m.values())
+    assert 9000 < total < 12452            # below the measured step, and most of it
+    one = SM.step_model(t, layers=1, microbatches=1)
+    assert abs(sum(g["ours_ms"] for g in one.values()) * 1.0 - (total - m["head"]["ours_ms"] - m["optimizer"]["ours_ms"]) / 2048
+               - one["head"]["ours_ms"] - one["optimizer"]["ours_ms"]) < 1e-6
+    table = SM.format_table(m, 12452.0)
+    assert "not explained by isolated timings" in table and "| attention bwd |" in table
