@@ -123,6 +123,9 @@ class PipelineConfig:
     interleave_stage_sync: bool = False
     gloo_batch_recv: bool = True
     alternate_nccl_gloo: bool = True
+    # accepted for compatibility: the reference builds non-leader ranks' models on the meta device when set
+    # (zorse_utils/pipeline.py:205-226); here every unit is always initialised on its own, on the device,
+    # and only the rank's shard is kept, so no rank ever holds more than one whole layer in fp32
     large_model_init: bool = False
     # extensions
     schedule: Optional[str] = None
