@@ -254,6 +254,11 @@ class PipelineStage:
             sv: dict = {}
             with phase("recompute." + layer.kind):
                 layer.forward(x, c, self.ops, sv)
+            if self.cfg.sync_after_recompute and self.device.type == "cuda":
+                # `"skip_compute_sync": false` in the config: the host waits for the recomputed forward, which
+                # lets the caching allocator reuse freed blocks sooner (fewer allocation retries when memory is
+                # tight; reference zorse_utils/pipeline_schedule_v2.py:187-194)
+                torch.cuda.current_stream().synchronize()
         else:
             sv = self.saved.pop((li, mbl))
         with phase("bwd." + layer.kind):
