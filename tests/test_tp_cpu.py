@@ -275,3 +275,128 @@ def test_scatter_gemm_bookkeeping_with_fake_kernels():
                 want = want + bias.float()
             assert (outs[r].float() - want).abs().max().item() < 0.51, (op, r)
     assert all(c.n_ops == 5 for c in comms)
+
+
+def test_fused_lane_gather_and_scatter_protocol_with_threads():
+    """The whole fused-lane protocol (scatter GEMM -> sum + norm + push -> gathered buffers, buffer parity,
+    flag indices, epochs) with stand-in kernels over a fake address space, one thread per process so that a
+    fast process really can run ahead: every gathered tensor must hold the rows of the operation it belongs
+    to.  The stand-ins wait on flags by polling, as the kernels do."""
+    import threading
+    import time
+
+    from zorse_b200.ops.api import get_ops
+    from zorse_b200.parallel.tp_fused import FusedTPComm
+
+    R, rows, H, K = 3, 256, 256, 32
+    T = R * rows
+    space = {}
+
+    def view_at(addr, nbytes):
+        for base, buf in space.items():
+            if base <= addr and addr + nbytes <= base + buf.numel():
+                return buf[addr - base: addr - base + nbytes]
+        raise AssertionError(f"address {addr} (+{nbytes}) outside every buffer")
+
+    def poll(flags, want):
+        t0 = time.time()
+        while int(flags.min()) < want:
+            assert time.time() - t0 < 20, "flag never arrived"
+            time.sleep(0.0005)
+
+    def rms(x, w, eps=1e-5):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(torch.bfloat16)
+
+    class Fake:
+        def gemm_rs(self, a, b, *, b_mn, dst_ptrs, flag_ptrs, flag_index, epoch, counter, ldc, max_ctas=0):
+            part = (a.float() @ (b.float() if b_mn else b.float().t())).to(torch.bfloat16)
+            n = part.shape[0] // len(dst_ptrs)
+            for q, dst in enumerate(dst_ptrs):
+                view_at(dst, n * ldc * 2).view(torch.bfloat16).copy_(part[q * n:(q + 1) * n].reshape(-1))
+            for q in range(len(dst_ptrs)):
+                view_at(flag_ptrs[q] + 4 * flag_index, 4).view(torch.int32).fill_(epoch)
+
+        def rs_finish(self, *a, **k):
+            raise AssertionError("not used in this test")
+
+        def wait_flags(self, flags, R_, which, epoch, wait_seconds=2.0):
+            poll(flags[which * R_:(which + 1) * R_], epoch)
+
+        def _push(self, y, dst_ptrs, flag_ptrs, flag_index, epoch):
+            for dst in dst_ptrs:
+                view_at(dst, y.numel() * 2).view(torch.bfloat16).copy_(y.reshape(-1))
+            for q in range(len(dst_ptrs)):
+                view_at(flag_ptrs[q] + 4 * flag_index, 4).view(torch.int32).fill_(epoch)
+
+        def tp_push(self, src, dst_ptrs, flag_ptrs, flag_index, epoch, counter):
+            self._push(src, dst_ptrs, flag_ptrs, flag_index, epoch)
+
+        def tp_norm_push(self, *, w, b, eps, layernorm, y_local, dst_ptrs, flag_ptrs, flag_index, epoch, stats, counter,
+                         x=None, slots=None, in_flags=None, in_epoch=0, resid=None, bias=None, h_out=None, wait_seconds=2.0):
+            assert not layernorm
+            if slots is not None:
+                poll(in_flags, in_epoch)
+                acc = slots.view(-1, *y_local.shape).float().sum(0)
+                if resid is not None:
+                    acc = acc + resid.float()
+                h_out.copy_(acc.to(torch.bfloat16))
+                x = h_out
+            y_local.copy_(rms(x, w, eps))
+            self._push(y_local, dst_ptrs, flag_ptrs, flag_index, epoch)
+
+    bases = []
+    for r in range(R):
+        stage = torch.zeros(4 * R * rows * H, dtype=torch.bfloat16)
+        flags = torch.zeros(64, dtype=torch.int32)
+        sb, fb = 100_000_000 * (r + 1), 100_000_000 * (r + 1) + 90_000_000
+        space[sb], space[fb] = stage.view(torch.uint8), flags.view(torch.uint8)
+        bases.append((stage, flags, sb, fb))
+    shared = [(bases[r][0], bases[r][1], [b[2] for b in bases], [b[3] for b in bases]) for r in range(R)]
+    comms = [FusedTPComm(None, R, r, device=torch.device("cpu"), rows=rows, hidden=H, kernels=Fake(),
+                         buffers=(lambda rr: (lambda pg, size, device, n: shared[rr]))(r)) for r in range(R)]
+    g = torch.Generator().manual_seed(3)
+    rounds = 4
+    w1 = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    data = [[{"x": torch.randn(rows, H, generator=g).to(torch.bfloat16), "a": torch.randn(T, K, generator=g).to(torch.bfloat16),
+              "w": torch.randn(H, K, generator=g).to(torch.bfloat16), "res": torch.randn(rows, H, generator=g).to(torch.bfloat16),
+              "y": torch.randn(rows, H, generator=g).to(torch.bfloat16)} for _ in range(R)] for _ in range(rounds)]
+    got = [[None] * R for _ in range(rounds)]
+    errors = []
+    ops = get_ops("ref")
+
+    def program(r):
+        try:
+            c = comms[r]
+            for k in range(rounds):
+                d = data[k][r]
+                if r == k % R:
+                    time.sleep(0.02)                     # somebody is always late
+                n, st, n_all = c.norm_gather(ops, d["x"], w1, None, 1e-5, "rms")
+                n_all = n_all.clone()
+                h, n2, st2, n2_all = c.linear_rs_norm_gather(ops, d["a"], d["w"], True, d["res"], None, w1, None, 1e-5, "rms")
+                n2_all = n2_all.clone()
+                y_all = c.gather_rows(d["y"]).clone()
+                got[k][r] = (n_all, h.clone(), n2_all, y_all)
+        except Exception as e:      # noqa: BLE001 - reported through the list
+            errors.append((r, repr(e)))
+
+    ths = [threading.Thread(target=program, args=(r,)) for r in range(R)]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join(120)
+    assert not errors, errors
+    for k in range(rounds):
+        want_n = torch.cat([rms(data[k][q]["x"], w1) for q in range(R)])
+        parts = [(data[k][q]["a"].float() @ data[k][q]["w"].float().t()).to(torch.bfloat16).float() for q in range(R)]
+        total = sum(parts)
+        hs = [(total[q * rows:(q + 1) * rows] + data[k][q]["res"].float()).to(torch.bfloat16) for q in range(R)]
+        want_n2 = torch.cat([rms(h, w1) for h in hs])
+        want_y = torch.cat([data[k][q]["y"] for q in range(R)])
+        for r in range(R):
+            n_all, h, n2_all, y_all = got[k][r]
+            assert torch.equal(n_all, want_n), (k, r, "norm gather")
+            assert torch.equal(h, hs[r]), (k, r, "reduce-scatter sum")
+            assert torch.equal(n2_all, want_n2), (k, r, "sum + norm gather")
+            assert torch.equal(y_all, want_y), (k, r, "plain gather")

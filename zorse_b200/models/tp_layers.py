@@ -58,6 +58,18 @@ class TPComm:
             out += bias
         return out
 
+    def norm_gather(self, ops, x, w, b, eps: float, kind: str):
+        """Norm of this process's rows and the lane's gathered result: (rows, stats, all rows).  The gathered
+        tensor is only valid until the next gather (the fused lane hands out a staging buffer)."""
+        n, st = _norm(ops, kind, x, w, b, eps)
+        return n, st, self.gather_rows(n)
+
+    def linear_rs_norm_gather(self, ops, x, wmat, w_kmajor: bool, resid, bias, w, b, eps: float, kind: str):
+        """linear_rs followed by norm_gather of its result: (sum rows, normalised rows, stats, all normalised rows)."""
+        h = self.linear_rs(ops, x, wmat, w_kmajor, resid, bias)
+        n, st, nf = self.norm_gather(ops, h, w, b, eps, kind)
+        return h, n, st, nf
+
     def rows(self, n: int) -> tuple[int, int]:
         """This process's [lo, hi) of n rows."""
         if n % self.size:
@@ -144,17 +156,25 @@ class TPTransformerBlock(TransformerBlock):
 
     # ---- sub-blocks: rows in, rows out -----------------------------------------------------
     # The gradient of a reduce-scatter is an all-gather and the other way round.
-    def _attn_rows_fwd(self, xin, resid, ctx, ops, sv):
-        p, tp, B, S = self.p, ctx["tp"], ctx["B"], ctx["S"]
-        qkv = ops.linear_fwd(tp.gather_rows(xin), p["qkv_w"], p.get("qkv_b"))
-        cs = self._rope(ops, S, xin.device)
+    def _attn_core_fwd(self, xin_all, ctx, ops, sv):
+        """Gathered rows in, this process's heads' attention output (all rows) out."""
+        p, B, S = self.p, ctx["B"], ctx["S"]
+        qkv = ops.linear_fwd(xin_all, p["qkv_w"], p.get("qkv_b"))
+        cs = self._rope(ops, S, xin_all.device)
         if cs is not None:
             ops.rope_(qkv, cs, S, self.Hq + self.Hkv, self.D)
         att, lse = ops.attn_fwd(qkv, B, S, self.Hq, self.Hkv, self.D, self.causal, self.window)
-        out = tp.linear_rs(ops, att, p["o_w"], True, resid, p.get("o_b"))
         if sv is not None:
             sv.update(qkv=qkv, att=att, lse=lse)
-        return out
+        return att
+
+    def _mlp_core_fwd(self, xin_all, ops, sv):
+        p = self.p
+        hpre = ops.linear_fwd(xin_all, p["up_w"], p.get("up_b"))
+        a = ops.swiglu_fwd(hpre) if self.act == "swiglu" else ops.act_fwd(hpre, self.act)
+        if sv is not None:
+            sv.update(hpre=hpre, mlp_a=a)
+        return a
 
     def _attn_rows_bwd(self, dout, xin, ctx, ops, sv):
         """dout: gradient of the sub-block's output rows; returns the gradient reaching xin through the
@@ -174,15 +194,6 @@ class TPTransformerBlock(TransformerBlock):
         ops.linear_wgrad(dqkv, tp.gather_rows(xin), g["qkv_w"], g.get("qkv_b"))
         return dxin
 
-    def _mlp_rows_fwd(self, xin, resid, ctx, ops, sv):
-        p, tp = self.p, ctx["tp"]
-        hpre = ops.linear_fwd(tp.gather_rows(xin), p["up_w"], p.get("up_b"))
-        a = ops.swiglu_fwd(hpre) if self.act == "swiglu" else ops.act_fwd(hpre, self.act)
-        out = tp.linear_rs(ops, a, p["down_w"], True, resid, p.get("down_b"))
-        if sv is not None:
-            sv.update(hpre=hpre, mlp_a=a)
-        return out
-
     def _mlp_rows_bwd(self, dout, xin, ctx, ops, sv):
         p, g, tp = self.p, self.g, ctx["tp"]
         if "down_b" in g:
@@ -197,19 +208,23 @@ class TPTransformerBlock(TransformerBlock):
 
     # ---- block ------------------------------------------------------------------------------
     def forward(self, x, ctx, ops, saved=None):
-        p, sv = self.p, saved
+        p, sv, tp, kind, eps = self.p, saved, ctx["tp"], self.norm, self.eps
         if self.pre_norm:
-            n1, st1 = _norm(ops, self.norm, x, p["norm1_w"], p.get("norm1_b"), self.eps)
-            h1 = self._attn_rows_fwd(n1, x, ctx, ops, sv)
-            n2, st2 = _norm(ops, self.norm, h1, p["norm2_w"], p.get("norm2_b"), self.eps)
-            out = self._mlp_rows_fwd(n2, h1, ctx, ops, sv)
+            n1, st1, n1_all = tp.norm_gather(ops, x, p["norm1_w"], p.get("norm1_b"), eps, kind)
+            att = self._attn_core_fwd(n1_all, ctx, ops, sv)
+            h1, n2, st2, n2_all = tp.linear_rs_norm_gather(ops, att, p["o_w"], True, x, p.get("o_b"),
+                                                           p["norm2_w"], p.get("norm2_b"), eps, kind)
+            a = self._mlp_core_fwd(n2_all, ops, sv)
+            out = tp.linear_rs(ops, a, p["down_w"], True, h1, p.get("down_b"))
             if sv is not None:
                 sv.update(x=x, n1=n1, st1=st1, h1=h1, n2=n2, st2=st2)
         else:
-            r1 = self._attn_rows_fwd(x, x, ctx, ops, sv)
-            h1, st1 = _norm(ops, self.norm, r1, p["norm1_w"], p.get("norm1_b"), self.eps)
-            r2 = self._mlp_rows_fwd(h1, h1, ctx, ops, sv)
-            out, st2 = _norm(ops, self.norm, r2, p["norm2_w"], p.get("norm2_b"), self.eps)
+            att = self._attn_core_fwd(tp.gather_rows(x), ctx, ops, sv)
+            r1, h1, st1, h1_all = tp.linear_rs_norm_gather(ops, att, p["o_w"], True, x, p.get("o_b"),
+                                                           p["norm1_w"], p.get("norm1_b"), eps, kind)
+            a = self._mlp_core_fwd(h1_all, ops, sv)
+            r2 = tp.linear_rs(ops, a, p["down_w"], True, h1, p.get("down_b"))
+            out, st2 = _norm(ops, kind, r2, p["norm2_w"], p.get("norm2_b"), eps)
             if sv is not None:
                 sv.update(x=x, r1=r1, st1=st1, h1=h1, r2=r2, st2=st2)
         return out

@@ -420,6 +420,33 @@ def rs_finish(slots: torch.Tensor, flags: torch.Tensor, R: int, rows: int, H: in
     return out
 
 
+def tp_norm_push(*, w, b, eps: float, layernorm: bool, y_local, dst_ptrs, flag_ptrs, flag_index: int, epoch: int,
+                 stats, counter, x=None, slots=None, in_flags=None, in_epoch: int = 0, resid=None, bias=None, h_out=None,
+                 wait_seconds: float = 2.0) -> None:
+    """Row-wise norm whose output also goes to every lane member's gathered buffer (dst_ptrs: device addresses
+    of this process's row block there).  Input rows: `x`, or the sum of the reduce-scatter `slots`
+    ([R, rows, H], ready when in_flags reach in_epoch) + resid + bias, which is written to h_out."""
+    rows, H = y_local.shape
+    R_in = 0 if slots is None else slots.numel() // (rows * H)
+    rc = lib().zb_tp_norm_push(_p(x), _p(slots), _p(in_flags), c_int(R_in), c_int(in_epoch), _p(resid),
+                               c_int(0 if resid is None else resid.stride(0)), _p(bias), _p(h_out), _p(w), _p(b),
+                               c_float(eps), c_int(int(layernorm)), _p(y_local), _ptr_array(dst_ptrs),
+                               _ptr_array(flag_ptrs), c_int(len(dst_ptrs)), c_int(flag_index), c_int(epoch), _p(stats),
+                               c_int(rows), c_int(H), _p(counter), ctypes.c_double(wait_seconds),
+                               _p(status_word(y_local.device)), _stream())
+    _check(rc, "tp_norm_push")
+
+
+def tp_push(src: torch.Tensor, dst_ptrs, flag_ptrs, flag_index: int, epoch: int, counter) -> None:
+    """Copies the contiguous tensor `src` to every device address in dst_ptrs, then stores `epoch` to
+    flag_ptrs[q][flag_index] (all-gather by stores, for rows that need no arithmetic)."""
+    assert src.is_contiguous()
+    rc = lib().zb_tp_push(_p(src), _ptr_array(dst_ptrs), _ptr_array(flag_ptrs), c_int(len(dst_ptrs)), c_int(flag_index),
+                          c_int(epoch), c_long(src.numel() * src.element_size()), _p(counter),
+                          _p(status_word(src.device)), _stream())
+    _check(rc, "tp_push")
+
+
 def rs_adam(grad_ptrs, flag_ptrs, R: int, r: int, shard_elems: int, master, m, v, p16, *, lr, beta1, beta2, eps,
             weight_decay, step, grad_scale, grad_f32: bool, epoch: int, counter: torch.Tensor, max_blocks: int = 0,
             wait_seconds: float = 2.0):
