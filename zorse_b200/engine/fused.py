@@ -31,9 +31,10 @@ from ..utils import canary
 from ..utils.ranges import phase
 from .zero import ZeroUnit
 
-# small chunks: every CTA copies one chunk at a time at 1/148 of the link rate, so a chunk is the
-# granularity at which weight rows become visible to the GEMM tiles waiting for them
-CHUNK_BYTES = 1 << 15
+# Granularity at which gathered weight rows become visible to the GEMM tiles waiting for them: every CTA copies one
+# chunk at a time.  256 KiB is the size the multi-GPU tests and measurements ran with; smaller chunks (a multiple of
+# 2 KiB, e.g. ZORSE_AG_CHUNK_BYTES=32768) let the first tiles start earlier at the price of more flag traffic.
+CHUNK_BYTES = int(os.environ.get("ZORSE_AG_CHUNK_BYTES", str(1 << 18)))
 # candidates of the reduce-scatter + Adam kernel that use NVSwitch multicast (csrc/comm/rs_adam.cu):
 # 2 = gradient slice summed inside the switch; 3 = as 2, and the refreshed bf16 shard is stored through
 # the multicast address of the unsharded buffers, so that no all-gather follows an update at all
