@@ -263,3 +263,18 @@ def test_step_model_adds_up_the_recorded_kernel_times():
                - one["head"]["ours_ms"] - one["optimizer"]["ours_ms"]) < 1e-6
     table = SM.format_table(m, 12452.0)
     assert "not explained by isolated timings" in table and "| attention bwd |" in table
+
+
+def test_package_exports_load_lazily():
+    import importlib
+    import sys
+
+    import zorse_b200
+
+    assert zorse_b200.__version__
+    assert zorse_b200.ParallelDims(tp=2, pp=2).world_size == 4
+    assert zorse_b200.parse_pipeline_dict is importlib.import_module("zorse_b200.config.training_config").parse_pipeline_dict
+    assert "zorse_b200.trainer" in sys.modules or zorse_b200.Trainer.__name__ == "Trainer"
+    import pytest
+    with pytest.raises(AttributeError):
+        zorse_b200.no_such_name
