@@ -255,3 +255,34 @@ def test_shard_bounds_properties(R, blocks_per_rank, ratios):
     assert b[0] == 0 and b[-1] == n and len(b) == R + 1
     assert all(x % ALIGN == 0 for x in b) and all(y > x for x, y in zip(b, b[1:]))
     assert shard_bounds(n, R, [1.0] * R) == shard_bounds(n, R)
+
+
+def test_planner_with_tensor_parallel_lanes():
+    """tp = 2 on eight GPUs: the plan numbers four lanes, the config carries tensor_parallel_size and names
+    eight processes; lanes cost compute / 2 plus their collectives; mixed GPU models inside a lane are refused."""
+    from zorse_b200.planner.plan import export_config, plan
+    from zorse_b200.planner.tensor_parallel import coarsen, lane_collective_ms
+
+    gl = [{"index": i, "name": "NVIDIA B200", "memory_total_mib": 183359, "id": f"gpu_{i}", "machine": "m0",
+           "global_rank": i} for i in range(8)]
+    data = {"machines": [{"machine": "m0", "num_gpus": 8, "machine_index": 0, "gpus": gl}], "gpu_list": gl,
+            "total_gpus": 8, "bandwidth": {"internode_bandwidth": {}, "intranode_bandwidth": {"0": 770.0},
+                                           "internode_latency": {}, "intranode_latency": {"0": 2e-5}}}
+    lanes, members = coarsen(data, 2)
+    assert lanes["total_gpus"] == 4 and members[1] == [2, 3] and lanes["gpu_list"][0]["memory_total_mib"] == 2 * 183359
+    assert data["total_gpus"] == 8                                     # the input is left alone
+    f, b = lane_collective_ms(data, [0, 1], 4096, 4096, 2)
+    assert f > 0 and abs(b / f - 1.5) < 0.2                            # 6 against 4 collectives of the same size
+    one, _ = plan(data, "llama2_7b", global_batch_size=64, sequence_length=4096, ks=[4])
+    two, _ = plan(data, "llama2_7b", global_batch_size=64, sequence_length=4096, ks=[4], tensor_parallel_size=2)
+    assert two is not None and len(two.stages) == 4 and all(len(s.gpu_ranks) == 1 for s in two.stages)
+    d = export_config(two, "llama2_7b", 64, 4096, 32000, "bfloat16", "float32", total_ranks=4, tensor_parallel_size=2)
+    cfg = tc.parse_pipeline_dict(d)
+    assert cfg.tensor_parallel_size == 2 and cfg.world_size == 8 and cfg.num_lanes == 4
+    assert one is not None and two.latency_ms != one.latency_ms
+    mixed = [dict(g) for g in gl]
+    mixed[1]["name"] = "NVIDIA H100"
+    with pytest.raises(ValueError):
+        coarsen(dict(data, gpu_list=mixed), 2)
+    with pytest.raises(ValueError):
+        coarsen(data, 3)

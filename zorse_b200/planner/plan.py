@@ -74,10 +74,15 @@ def plan_partition(data: dict, pmap: dict, model_name: str, *, global_batch_size
                    autocast_dtype: str, vocab_size: int, dtype_multiplier: float, optimizer_multiplier: float,
                    reserved_memory_gb: float, recompute: bool = True, measured_agrs: Optional[dict] = None,
                    table: Optional[dict] = None, optimizer_gbs: float = 6000.0,
-                   microbatch_size: Optional[int] = None, compute_overhead: float = 1.075) -> Optional[PlanResult]:
+                   microbatch_size: Optional[int] = None, compute_overhead: float = 1.075,
+                   tensor_parallel_size: int = 1, lane_members: Optional[dict] = None,
+                   full_data: Optional[dict] = None) -> Optional[PlanResult]:
+    """With tensor_parallel_size t > 1, `data` describes lanes (planner/tensor_parallel.coarsen), `lane_members` maps
+    a lane to the GPUs of `full_data` it is made of, parameters per layer and block latencies are per lane."""
     stats = registry.get_model_stats(model_name, vocab=vocab_size)
-    model = ModelConfig(model_name, stats["num_layers"], stats["hidden_size"], stats["parameters_per_layer"],
-                        stats["total_parameters"], sequence_length, global_batch_size, vocab_size)
+    tp = max(int(tensor_parallel_size), 1)
+    model = ModelConfig(model_name, stats["num_layers"], stats["hidden_size"], stats["parameters_per_layer"] // tp,
+                        stats["total_parameters"] // tp, sequence_length, global_batch_size, vocab_size)
     groups = groups_from_partition(data, pmap)
     size = comm_model.tensor_size_bytes(model.parameters_per_layer, autocast_dtype)
     for g in groups:
@@ -102,6 +107,12 @@ def plan_partition(data: dict, pmap: dict, model_name: str, *, global_batch_size
         # the layer profile times one block in a tight loop; a whole step also pays for launch gaps,
         # allocator traffic and the small kernels between blocks (7.5 % on the B200 runs used to calibrate)
         lat_tbl = {g: type(v)(v.forward * compute_overhead, v.backward * compute_overhead) for g, v in lat_tbl.items()}
+        if tp > 1:
+            from .tensor_parallel import lane_collective_ms, lane_latencies
+
+            cf, cb = lane_collective_ms(full_data, next(iter(lane_members.values())), mbs * sequence_length,
+                                        model.hidden_size, comm_model.DTYPE_BYTES[autocast_dtype])
+            lat_tbl = lane_latencies(lat_tbl, tp, cf, cb)
         # optimizer: 28 bytes per parameter of HBM traffic on each rank's shard
         opt_ms = model.parameters_per_layer / max(min(len(g.gpus) for g in groups), 1) * 28 / (optimizer_gbs * 1e9) * 1e3
         slowest = max(gpus, key=lambda g: lat_tbl[g].total)
@@ -132,7 +143,14 @@ def plan(data: dict, model_name: str, *, global_batch_size: int, sequence_length
          dtype_multiplier: float = 2.0, optimizer_multiplier: float = 12.0, reserved_memory_gb: float = 2.0,
          recompute: bool = True, measured_agrs: Optional[dict] = None, table: Optional[dict] = None,
          ks: Optional[list[int]] = None, microbatch_size: Optional[int] = None,
-         compute_overhead: float = 1.075) -> tuple[Optional[PlanResult], list[dict]]:
+         compute_overhead: float = 1.075, tensor_parallel_size: int = 1) -> tuple[Optional[PlanResult], list[dict]]:
+    """tensor_parallel_size t > 1 plans for lanes of t GPUs; the ranks of the result are lane numbers, which is
+    what the trainer's config means when it carries `tensor_parallel_size` (export_config writes it)."""
+    full_data, lane_members = data, None
+    if tensor_parallel_size > 1:
+        from .tensor_parallel import coarsen
+
+        data, lane_members = coarsen(data, tensor_parallel_size)
     G = build_gpu_graph(data)
     best, tried = None, []
     for k in (ks or candidate_ks(data)):
@@ -141,7 +159,8 @@ def plan(data: dict, model_name: str, *, global_batch_size: int, sequence_length
                              sequence_length=sequence_length, autocast_dtype=autocast_dtype, vocab_size=vocab_size,
                              dtype_multiplier=dtype_multiplier, optimizer_multiplier=optimizer_multiplier,
                              reserved_memory_gb=reserved_memory_gb, recompute=recompute, measured_agrs=measured_agrs,
-                             table=table, microbatch_size=microbatch_size, compute_overhead=compute_overhead)
+                             table=table, microbatch_size=microbatch_size, compute_overhead=compute_overhead,
+                             tensor_parallel_size=tensor_parallel_size, lane_members=lane_members, full_data=full_data)
         tried.append({"k": k, "latency_ms": None if res is None else res.latency_ms,
                       "microbatch_size": None if res is None else res.microbatch_size,
                       "interleave_degree": None if res is None else res.interleave_degree})
@@ -152,7 +171,7 @@ def plan(data: dict, model_name: str, *, global_batch_size: int, sequence_length
 
 def export_config(res: PlanResult, model_name: str, global_batch_size: int, sequence_length: int, vocab_size: int,
                   autocast_dtype: str, reduce_dtype: str, path: Optional[str] = None,
-                  total_ranks: Optional[int] = None) -> dict:
+                  total_ranks: Optional[int] = None, tensor_parallel_size: int = 1) -> dict:
     """The training_config.json the trainer reads (reference zorse_planner.py:616-647).  A group of
     GPUs that is too slow to be given a single layer owns no stage; with `total_ranks` such ranks are
     listed under `unused_ranks` so that a job launched on every GPU of the cluster file still starts
@@ -167,6 +186,8 @@ def export_config(res: PlanResult, model_name: str, global_batch_size: int, sequ
                              "layer_partition": list(s.layer_partition), "zero_config": [list(s.gpu_ranks)]}
                             for s in res.stages],
     }
+    if tensor_parallel_size > 1:
+        d["tensor_parallel_size"] = tensor_parallel_size      # rank numbers above are lanes; total_ranks counts lanes
     if total_ranks is not None:
         used = {r for s in res.stages for r in s.gpu_ranks}
         idle = [r for r in range(total_ranks) if r not in used]

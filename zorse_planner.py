@@ -34,6 +34,9 @@ def main(argv=None) -> int:
     ap.add_argument("--no_recompute", action="store_true")
     ap.add_argument("--num_stages", type=int, default=None, help="only try this number of GPU groups")
     ap.add_argument("--microbatch_size", type=int, default=None, help="plan for this microbatch size only (no sweep)")
+    ap.add_argument("--tensor_parallel_size", type=int, default=1,
+                    help="plan for lanes of this many GPUs that split every block (tensor parallelism); "
+                         "the lane model is not calibrated against measurements yet")
     ap.add_argument("--compute_overhead", type=float, default=1.075,
                     help="whole-step time over the sum of profiled layer times (launch gaps, small kernels)")
     ap.add_argument("--draw", default=None, help="write a PNG of the partitioned GPU graph (needs matplotlib)")
@@ -52,14 +55,17 @@ def main(argv=None) -> int:
                       partition_algorithm=a.partition_algorithm, dtype_multiplier=a.dtype_multiplier,
                       optimizer_multiplier=a.optimizer_multiplier, reserved_memory_gb=a.reserved_memory_gb,
                       recompute=not a.no_recompute, measured_agrs=measured,
-                      ks=[a.num_stages] if a.num_stages else None, microbatch_size=a.microbatch_size, compute_overhead=a.compute_overhead)
+                      ks=[a.num_stages] if a.num_stages else None, microbatch_size=a.microbatch_size, compute_overhead=a.compute_overhead,
+                      tensor_parallel_size=a.tensor_parallel_size)
     for t in tried:
         print(f"k={t['k']}: predicted {t['latency_ms']} ms (microbatch {t['microbatch_size']}, interleave {t['interleave_degree']})")
     if res is None:
         print("no plan fits in memory", file=sys.stderr)
         return 1
     cfg = export_config(res, a.model_name, a.global_batch_size, a.sequence_length, a.vocab_size, a.autocast_dtype,
-                        a.reduce_dtype, a.output_file, total_ranks=int(data.get("total_gpus", 0)) or None)
+                        a.reduce_dtype, a.output_file,
+                        total_ranks=(int(data.get("total_gpus", 0)) // a.tensor_parallel_size) or None,
+                        tensor_parallel_size=a.tensor_parallel_size)
     if cfg.get("unused_ranks"):
         print(f"ranks {cfg['unused_ranks']} own no stage (too slow to be given a layer); they idle during training")
     print(f"best: {len(res.stages)} stages, microbatch {res.microbatch_size}, interleave {res.interleave_degree}, "
