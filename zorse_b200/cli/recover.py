@@ -75,13 +75,23 @@ def replan(meta: dict, cluster: dict, **plan_kw) -> dict:
     from ..planner.plan import export_config, plan
 
     tc = meta["training_config"]
+    # keep the old job's tensor-parallel width while the remaining GPUs still form whole lanes; otherwise plan
+    # without it (the checkpoint reader re-cuts the blocks for any width)
+    tp = int(tc.get("tensor_parallel_size", 1))
+    if tp > 1:
+        per_machine = {}
+        for g in cluster["gpu_list"]:
+            per_machine[g.get("machine")] = per_machine.get(g.get("machine"), 0) + 1
+        if any(n % tp for n in per_machine.values()):
+            tp = 1
     best, _ = plan(cluster, tc["model_name"], global_batch_size=int(tc["global_batch_size"]),
-                   sequence_length=int(tc["sequence_length"]), **plan_kw)
+                   sequence_length=int(tc["sequence_length"]), tensor_parallel_size=tp, **plan_kw)
     if best is None:
         raise RuntimeError("the planner found no plan that fits the remaining GPUs")
     d = export_config(best, tc["model_name"], int(tc["global_batch_size"]), int(tc["sequence_length"]),
                       int(tc.get("vocab_size", 32000)), tc.get("autocast_dtype", "bfloat16"),
-                      tc.get("reduce_dtype", "float32"), total_ranks=cluster["total_gpus"])
+                      tc.get("reduce_dtype", "float32"), total_ranks=cluster["total_gpus"] // tp,
+                      tensor_parallel_size=tp)
     for k in ("schedule", "grad_norm_compat", "activation_recompute", "activation_offload"):
         if k in tc and k not in d:
             d[k] = tc[k]      # choices of the old job that do not depend on the layout
@@ -111,6 +121,9 @@ def main(argv=None) -> int:
     with open(a.output, "w") as f:
         json.dump(cfg, f, indent=1)
     n = cluster["total_gpus"]
+    from ..config.training_config import parse_pipeline_dict
+
+    n = min(n, parse_pipeline_dict(cfg).world_size)
     print(f"checkpoint {ck} (step {meta['step']}), {n} GPUs left, plan written to {a.output}")
     print(f"python -m torch.distributed.run --nproc-per-node {n} zorse.py --config_file {a.output} --resume {ck}")
     return 0
