@@ -136,11 +136,13 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
       tma_prefetch_desc(&tmap_do);
-      mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
+      if (n_iters > 0) {   // nobody waits for K / V otherwise, and a copy must not outlive the CTA
+        mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
 #pragma unroll
-      for (int b = 0; b < DB; ++b) {
-        tma_load_4d(sK + b * BLK, &tmap_k, kv_full, b * 64, kv_head, kv0, batch);
-        tma_load_4d(sV + b * BLK, &tmap_v, kv_full, b * 64, kv_head, kv0, batch);
+        for (int b = 0; b < DB; ++b) {
+          tma_load_4d(sK + b * BLK, &tmap_k, kv_full, b * 64, kv_head, kv0, batch);
+          tma_load_4d(sV + b * BLK, &tmap_v, kv_full, b * 64, kv_head, kv0, batch);
+        }
       }
       for (int it = 0; it < n_iters; ++it) {
         const int st = it % QS;
