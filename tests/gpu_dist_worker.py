@@ -144,12 +144,64 @@ def fused_kernels(variant: int = 0):
     dist.barrier()
 
 
+def tp_kernels():
+    """The fused tensor-parallel lane kernels (scatter GEMM + rs_finish, tp_norm_push, tp_push) against the
+    library lane (torch GEMM results reduced / gathered with NCCL) on identical inputs, several operations in
+    a row so that both staging buffers and both gathered buffers are reused."""
+    from zorse_b200.models.tp_layers import TPComm
+    from zorse_b200.ops import sm100 as k
+    from zorse_b200.ops.api import get_ops
+    from zorse_b200.parallel.tp_fused import FusedTPComm
+
+    rank, R = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", rank)
+    ops = get_ops("sm100")
+    rows, H, K = 256, 512, 384
+    T = rows * R
+    fused = FusedTPComm(dist.group.WORLD, R, rank, device=dev, rows=rows, hidden=H, kernels=k)
+    lib = TPComm(dist.group.WORLD, R, rank)
+    g = torch.Generator(device=dev).manual_seed(50 + rank)
+    rnd = lambda *s: (torch.randn(*s, device=dev, generator=g) * 0.3).to(torch.bfloat16)
+    w_n = (1 + 0.1 * torch.randn(H, device=dev, generator=torch.Generator(device=dev).manual_seed(5))).to(torch.bfloat16)
+    b_n = (0.1 * torch.randn(H, device=dev, generator=torch.Generator(device=dev).manual_seed(6))).to(torch.bfloat16)
+    bias = (0.1 * torch.randn(H, device=dev, generator=torch.Generator(device=dev).manual_seed(7))).to(torch.bfloat16)
+
+    def close(a, b, what, tol=6e-2):
+        err = (a.float() - b.float()).abs().max().item()
+        assert err < tol, f"{what}: max difference {err}"
+
+    for it in range(3):
+        x, wk, wn_, resid, rows_x = rnd(T, K), rnd(H, K), rnd(K, H), rnd(rows, H), rnd(rows, H)
+        close(fused.linear_rs(ops, x, wk, True, resid, bias), lib.linear_rs(ops, x, wk, True, resid.clone(), bias),
+              f"linear_rs forward form, pass {it}")
+        close(fused.linear_rs(ops, x, wn_, False), lib.linear_rs(ops, x, wn_, False), f"linear_rs gradient form, pass {it}")
+        for kind, b in (("rms", None), ("ln", b_n)):
+            n1, s1, a1 = fused.norm_gather(ops, rows_x, w_n, b, 1e-5, kind)
+            a1 = a1.clone()
+            n2, s2, a2 = lib.norm_gather(ops, rows_x, w_n, b, 1e-5, kind)
+            close(n1, n2, f"norm_gather rows ({kind})", 3e-2)
+            close(s1, s2, f"norm_gather statistics ({kind})", 1e-2)
+            close(a1, a2, f"norm_gather gathered ({kind})", 3e-2)
+        h1, m1, t1, f1 = fused.linear_rs_norm_gather(ops, x, wk, True, resid, bias, w_n, None, 1e-5, "rms")
+        f1 = f1.clone()
+        h2, m2, t2, f2 = lib.linear_rs_norm_gather(ops, x, wk, True, resid.clone(), bias, w_n, None, 1e-5, "rms")
+        close(h1, h2, "sum rows")
+        close(m1, m2, "normalised rows", 8e-2)
+        close(f1, f2, "gathered normalised rows", 8e-2)
+        close(fused.gather_rows(rows_x).clone(), lib.gather_rows(rows_x), "gather_rows", 1e-6)
+    torch.cuda.synchronize()
+    k.check_status()
+    assert fused.n_ops == 9 and fused.n_gathers == 12
+
+
 def main():
     case = sys.argv[1]
     from zorse_b200.parallel.groups import dist_init
 
     dist_init()
-    if case.startswith("fused_kernels"):
+    if case == "tp_kernels":
+        tp_kernels()
+    elif case.startswith("fused_kernels"):
         fused_kernels(int(case[-1]) if case[-2:] in ("v1", "v2", "v3") else 0)
     else:
         losses, masters, tr = train_case(case)

@@ -67,6 +67,13 @@ def test_tensor_parallel_two_gpus():
 
 
 @pytest.mark.skipif(_ngpu() < 2 or not CANDIDATES, reason="needs 2 GPUs and ZORSE_TEST_CANDIDATES=1")
+def test_tensor_parallel_lane_kernels_two_gpus():
+    """The lane kernels alone (no trainer): scatter GEMM + sum, sum + norm + push, plain push, against NCCL."""
+    out = _run(2, "tp_kernels", timeout=300)
+    assert "WORKER_OK" in out
+
+
+@pytest.mark.skipif(_ngpu() < 2 or not CANDIDATES, reason="needs 2 GPUs and ZORSE_TEST_CANDIDATES=1")
 def test_tensor_parallel_scatter_gemm_two_gpus():
     """Same job with the reduce-scatter sent from inside the row-split GEMMs (scatter epilogue + rs_finish)."""
     out = _run(2, "tp2_library", timeout=300, ZORSE_TP_FUSED="1")
