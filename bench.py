@@ -145,6 +145,8 @@ def main():
                     help="model chunks per rank group (>1 selects the interleaved 1F1B schedule on 4 and 8 GPUs)")
     ap.add_argument("--tp", type=int, default=1,
                     help="tensor-parallel processes per lane (not the baseline configuration; the JSON line says so)")
+    ap.add_argument("--defer_wgrad", action="store_true",
+                    help="1F1B: input gradients are sent upstream before the weight-gradient GEMMs (same arithmetic)")
     ap.add_argument("--skip_e2e", action="store_true")
     ap.add_argument("--stall_timeout", type=float, default=420.0,
                     help="abort (non-zero exit) if no training step completes on the host for this many seconds")
@@ -172,6 +174,7 @@ def main():
     recompute = None if args.recompute == "auto" else (args.recompute == "on")
     tr = Trainer(cfg, TrainerOptions(schedule=schedule, ops="sm100", optimizer_in_backward=args.optimizer_in_backward,
                                      collectives=args.collectives, activation_recompute=recompute,
+                                     defer_wgrad=args.defer_wgrad,
                                      model_overrides={} if args.layers is None else {"layers": args.layers}))
     from zorse_b200.ops import sm100
     from zorse_b200.utils.health import Watchdog
@@ -279,7 +282,7 @@ def main():
                        "global_batch": args.global_batch, "seq_len": args.seq_len, "microbatch": args.microbatch,
                        "parallelism": par, "schedule": schedule, "activation_recompute": tr.schedule.recompute,
                        "optimizer": "Adam fp32 master+moments, step inside the timed region",
-                       "reduce_dtype": args.reduce_dtype, "collectives": args.collectives,
+                       "reduce_dtype": args.reduce_dtype, "collectives": args.collectives, "defer_wgrad": args.defer_wgrad,
                        "l2": "per-step working set (>100 GB of parameters, optimizer state and activations) far exceeds the 126 MB L2; no flush needed"},
             "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches, "loss": loss_val,
             "exposed_comm_ms_per_step": exposed_ms,

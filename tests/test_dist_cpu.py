@@ -234,3 +234,37 @@ def test_consecutive_stages_on_the_same_ranks(schedule):
     cfg = tiny_cfg(pipe, gbs=8, mbs=2)
     res = run_workers(2, _worker, cfg, {"schedule": schedule, "optimizer_in_backward": True}, 2)
     _check(res, cfg)
+
+
+@pytest.mark.parametrize("schedule,pipe_name", [("1f1b", "PIPE_2x1"), ("1f1b_interleaved", "INTERLEAVED")])
+def test_deferred_weight_gradients_give_the_same_training(schedule, pipe_name):
+    """Sending a microbatch's input gradient upstream before its weight-gradient GEMMs run reorders work
+    only: losses and parameters still match the oracle, and the hold-back really happened."""
+    if pipe_name == "PIPE_2x1":
+        pipe = PIPE_2x1
+    else:
+        pipe = [{"gpu_ranks": [k % 2], "num_microbatches_per_rank": [4], "layer_partition": [k, k + 1],
+                 "zero_config": [[k % 2]]} for k in range(4)]
+    cfg = tiny_cfg(pipe)
+    res = run_workers(2, _worker_defer, cfg, {"schedule": schedule, "defer_wgrad": True}, 2)
+    _check([r["result"] for r in res], cfg)
+    assert any(r["deferred"] > 0 for r in res), [r["deferred"] for r in res]
+    if pipe_name == "PIPE_2x1":
+        assert res[0]["deferred"] == 0        # the first stage sends nothing upstream: nothing to gain there
+
+
+def _worker_defer(rank, world, cfg_dict, opts, steps):
+    from zorse_b200.parallel.stage import DeferredWgrad
+
+    count = {"n": 0}
+    orig = DeferredWgrad.flush
+
+    def counting_flush(self):
+        count["n"] += len(self._queue)
+        return orig(self)
+
+    DeferredWgrad.flush = counting_flush
+    try:
+        return {"result": _worker(rank, world, cfg_dict, opts, steps), "deferred": count["n"]}
+    finally:
+        DeferredWgrad.flush = orig

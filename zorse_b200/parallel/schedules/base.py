@@ -20,9 +20,12 @@ class ScheduleBase:
     name = "base"
     recompute_default = True
 
-    def __init__(self, stages: list[PipelineStage], cfg, *, recompute: Optional[bool] = None, pipeline_log=None):
+    def __init__(self, stages: list[PipelineStage], cfg, *, recompute: Optional[bool] = None, pipeline_log=None,
+                 defer_wgrad: bool = False):
         self.stages = sorted(stages, key=lambda s: s.stage_id)
         self.cfg = cfg
+        # 1F1B schedules: send a microbatch's input gradient upstream before computing its weight gradients
+        self.defer_wgrad = defer_wgrad
         self.recompute = self.recompute_default if recompute is None else recompute
         self.log = pipeline_log
         self.device = stages[0].device if stages else torch.device("cpu")

@@ -68,6 +68,8 @@ class InterleavedOneFOneBSchedule(ScheduleBase):
             units = st.engine.units
             dy = None if st.is_last else st.recv_bwd(mbl).wait()
             last, asynchronous = mbl == M - 1, st.device.type == "cuda"   # see one_f_one_b.py
+            defer = self.defer_wgrad and not last and not st.is_first and st.can_defer_wgrad()
+            st.wgrad.active = defer
             for li in reversed(range(len(st.layers))):
                 units[li].acquire()
                 units[li].grad_views()
@@ -76,6 +78,9 @@ class InterleavedOneFOneBSchedule(ScheduleBase):
                     units[li].reduce_grads()
             if not st.is_first:
                 st.send_bwd(mbl, dy)
+            if defer:
+                st.wgrad.active = False
+                st.wgrad.flush()
             if last and not asynchronous:
                 for li in reversed(range(len(st.layers))):
                     units[li].reduce_grads()

@@ -59,6 +59,9 @@ class OneFOneBSchedule(ScheduleBase):
             # would otherwise sit in the collective while upstream stages still need that gradient to
             # produce the forwards its peers are waiting for.
             last, asynchronous = mbl == M - 1, st.device.type == "cuda"
+            # weight gradients after the send (not for the last microbatch, whose layers are reduced as they finish)
+            defer = self.defer_wgrad and not last and not st.is_first and st.can_defer_wgrad()
+            st.wgrad.active = defer
             for li in reversed(range(L)):
                 units[li].acquire()
                 units[li].grad_views()
@@ -67,6 +70,9 @@ class OneFOneBSchedule(ScheduleBase):
                     units[li].reduce_grads()
             if not st.is_first:
                 st.send_bwd(mbl, dy)
+            if defer:
+                st.wgrad.active = False
+                st.wgrad.flush()
             if last and not asynchronous:
                 for li in reversed(range(L)):
                     units[li].reduce_grads()

@@ -82,6 +82,36 @@ class ActivationStash:
         self.store.clear()
 
 
+class DeferredWgrad:
+    """Ops front that can hold back the weight-gradient GEMMs of a backward pass.
+
+    The gradient a stage sends upstream depends only on the input-gradient GEMMs; the weight-gradient GEMMs
+    (a third of a step's arithmetic) feed nothing but the gradient bucket.  While `active`, `linear_wgrad`
+    calls are queued with their arguments (the views into the bucket they accumulate into stay valid), and
+    `flush()` runs them in order, so a schedule can send the input gradient first and do the weight gradients
+    while the upstream stage is already working: the chain between stages gets shorter by the weight-gradient
+    time per stage.  Results are bit-identical: every bucket entry receives the same additions in the same order."""
+
+    def __init__(self, ops):
+        self._ops = ops
+        self._queue: list = []
+        self.active = False
+
+    def __getattr__(self, name):
+        return getattr(self._ops, name)
+
+    def linear_wgrad(self, *a, **k):
+        if self.active:
+            self._queue.append((a, k))
+        else:
+            self._ops.linear_wgrad(*a, **k)
+
+    def flush(self) -> None:
+        q, self._queue = self._queue, []
+        for a, k in q:
+            self._ops.linear_wgrad(*a, **k)
+
+
 class PipelineStage:
     def __init__(self, cfg: PipelineConfig, st: StageConfig, *, rank: int, device: torch.device, ops,
                  engine_cfg: EngineConfig, groups: StageGroups, streams: Streams, pattern: StageCommPattern,
@@ -137,6 +167,7 @@ class PipelineStage:
             self.tp = FusedTPComm(groups.tp.pg, tp_size, tp_index, device=device, rows=self.tokens // tp_size,
                                   hidden=self.hidden, kernels=ops.k)
         self.act_dtype = engine_cfg.compute_dtype
+        self.wgrad = DeferredWgrad(ops)      # what backward_layer hands to the layers as their ops
         self.stash = ActivationStash(device, activation_offload, streams.copy)
         self.saved: dict = {}
         self.loss_sum: Optional[torch.Tensor] = None
@@ -223,6 +254,11 @@ class PipelineStage:
         with phase("p2p.send_grad"):
             return self.boundary_transport(False).send(dx, dst, tag, self._kind("grad", False))
 
+    def can_defer_wgrad(self) -> bool:
+        """Deferred weight gradients keep their operands alive until the flush; the fused tensor-parallel lane
+        hands out gathered operands in staging buffers that the next gather overwrites."""
+        return type(self.tp).__name__ != "FusedTPComm"
+
     def add_loss(self, rows: torch.Tensor) -> None:
         v = rows.float().sum() * self.loss_scale
         self.loss_sum = v if self.loss_sum is None else self.loss_sum + v
@@ -262,4 +298,4 @@ class PipelineStage:
         else:
             sv = self.saved.pop((li, mbl))
         with phase("bwd." + layer.kind):
-            return layer.backward(dy, c, self.ops, sv)
+            return layer.backward(dy, c, self.wgrad if self.wgrad.active else self.ops, sv)

@@ -45,6 +45,7 @@ class TrainerOptions:
     backend: Optional[str] = None          # torch.distributed backend override ("gloo" forces CPU)
     model_overrides: dict = field(default_factory=dict)
     pipeline_log: object = None
+    defer_wgrad: bool = False              # 1F1B: input gradients are sent upstream before the weight-gradient GEMMs run
     shift_labels: bool = False             # synthetic targets = next token of the inputs (last position ignored)
 
 
@@ -104,7 +105,8 @@ class Trainer:
                      registry.get_spec(cfg.model_name, vocab=cfg.vocab_size, **(opt.model_overrides or {})))
         recompute = cfg.activation_recompute if opt.activation_recompute is None else opt.activation_recompute
         name = cfg.schedule or opt.schedule
-        self.schedule = build_schedule(name, self.stages, cfg, recompute=recompute, pipeline_log=opt.pipeline_log)
+        self.schedule = build_schedule(name, self.stages, cfg, recompute=recompute, pipeline_log=opt.pipeline_log,
+                                       defer_wgrad=opt.defer_wgrad)
         self.step_idx = 0
 
     # ------------------------------------------------------------------ data
