@@ -159,3 +159,34 @@ def test_canary_detects_writes_outside_a_guarded_buffer():
     with pytest.raises(canary.CanaryError, match="unit 3 gradients"):
         canary.check_all()
     canary.reset()
+
+
+def test_deferred_wgrad_front_queues_in_order_and_passes_everything_else_through():
+    from zorse_b200.parallel.stage import DeferredWgrad
+
+    calls = []
+
+    class Ops:
+        name = "fake"
+
+        def linear_wgrad(self, *a, **k):
+            calls.append(("wgrad", a, k))
+
+        def linear_dgrad(self, *a):
+            calls.append(("dgrad", a))
+            return "dx"
+
+    d = DeferredWgrad(Ops())
+    assert d.name == "fake" and d.linear_dgrad(1) == "dx"
+    d.linear_wgrad(1, 2, accumulate=True)                 # not active: runs at once
+    assert calls == [("dgrad", (1,)), ("wgrad", (1, 2), {"accumulate": True})]
+    d.active = True
+    d.linear_wgrad("a")
+    d.linear_dgrad(2)
+    d.linear_wgrad("b")
+    assert [c[0] for c in calls] == ["dgrad", "wgrad", "dgrad"]     # the two weight gradients are held back
+    d.active = False
+    d.flush()
+    assert [c[1][0] for c in calls[3:]] == ["a", "b"]               # in the order they were asked for
+    d.flush()
+    assert len(calls) == 5
