@@ -145,7 +145,8 @@ def run_child(case: str, timeout: float) -> dict:
     for line in reversed(p.stdout.strip().splitlines()):
         if line.startswith("{"):
             return json.loads(line)
-    tail = (p.stderr.strip().splitlines() or ["no output"])[-1]
+    lines = p.stderr.strip().splitlines() or ["no output"]
+    tail = next((ln for ln in reversed(lines) if "Error" in ln or "error:" in ln), lines[-1])
     return {"case": case, "error": f"exit code {p.returncode}: {tail[:200]}"}
 
 
