@@ -147,6 +147,8 @@ def main():
                     help="tensor-parallel processes per lane (not the baseline configuration; the JSON line says so)")
     ap.add_argument("--defer_wgrad", action="store_true",
                     help="1F1B: input gradients are sent upstream before the weight-gradient GEMMs (same arithmetic)")
+    ap.add_argument("--no_preflight", action="store_true",
+                    help="skip the host-side replay of the schedule's p2p program before the first multi-stage step")
     ap.add_argument("--skip_e2e", action="store_true")
     ap.add_argument("--stall_timeout", type=float, default=420.0,
                     help="abort (non-zero exit) if no training step completes on the host for this many seconds")
@@ -171,6 +173,20 @@ def main():
     cfg_dict, par = build_config(args.gpus, args.model, args.global_batch, args.microbatch, args.seq_len, args.vocab,
                                  args.reduce_dtype, schedule, args.layers, args.interleave, args.tp)
     cfg = parse_pipeline_dict(cfg_dict)
+    if world > 1 and len(cfg.stages) > 1 and not args.no_preflight:
+        # a p2p program that cannot complete would leave the GPUs spinning in NCCL kernels: replay it on the host first
+        stuck = None
+        try:
+            from zorse_b200.parallel.p2p_sim import preflight
+
+            stuck = preflight(cfg, schedule, defer_wgrad=args.defer_wgrad)
+        except Exception as e:      # noqa: BLE001 - the replay is a safety net, not a precondition
+            sys.stderr.write(f"[bench] p2p replay skipped: {e!r}\n")
+        if stuck is not None:
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"metric": "tokens/s", "impl": "ours", "n_gpus": args.gpus,
+                                  "error": f"schedule {schedule} would deadlock on this plan: {stuck}"}), flush=True)
+            return 5
     recompute = None if args.recompute == "auto" else (args.recompute == "on")
     tr = Trainer(cfg, TrainerOptions(schedule=schedule, ops="sm100", optimizer_in_backward=args.optimizer_in_backward,
                                      collectives=args.collectives, activation_recompute=recompute,

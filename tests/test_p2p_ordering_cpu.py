@@ -211,3 +211,29 @@ def test_planned_1f1b_order_properties_on_random_plans():
                         inflight -= 1
                     peak = max(peak, inflight)
                 assert peak <= P - s + M
+
+
+def test_preflight_replays_the_real_plans_and_reports_a_stuck_program(monkeypatch):
+    """The replay a multi-stage job runs before its first step: the benchmark's 8-process plan (4 stages x 2,
+    64 microbatches, all 32 layers) completes for 1F1B with and without deferred weight gradients; a program
+    with a cycle is reported with the ranks involved."""
+    from zorse_b200.parallel import p2p_sim
+    from zorse_b200.parallel.p2p_sim import Event, preflight
+
+    pipe = [{"gpu_ranks": [2 * i, 2 * i + 1], "num_microbatches_per_rank": [32, 32], "layer_partition": [8 * i, 8 * i + 8],
+             "zero_config": [[2 * i, 2 * i + 1]]} for i in range(4)]
+    cfg = parse_pipeline_dict({"model_name": "llama2_7b", "global_batch_size": 64, "microbatch_size": 1,
+                               "sequence_length": 4096, "vocab_size": 32000, "pipeline_config": pipe})
+    assert preflight(cfg, "1f1b") is None
+    assert preflight(cfg, "1f1b", defer_wgrad=True) is None
+    one = parse_pipeline_dict({"model_name": "llama2_7b", "global_batch_size": 64, "microbatch_size": 1,
+                               "sequence_length": 4096, "vocab_size": 32000,
+                               "pipeline_config": [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [32, 32],
+                                                    "layer_partition": [0, 32], "zero_config": [[0, 1]]}]})
+    assert preflight(one, "1f1b") is None                      # a single stage has no p2p program
+    # two ranks that both wait for the other's message before sending their own
+    cyc = {0: [Event("post_recv", 1, "act", 0), Event("wait_recv", 1, "act", 0), Event("send", 1, "grad", 1)],
+           1: [Event("post_recv", 0, "grad", 1), Event("wait_recv", 0, "grad", 1), Event("send", 0, "act", 0)]}
+    monkeypatch.setattr(p2p_sim, "record_programs", lambda *a, **k: cyc)
+    stuck = preflight(cfg, "1f1b")
+    assert stuck is not None and "0" in stuck and "1" in stuck

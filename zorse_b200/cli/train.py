@@ -43,6 +43,20 @@ def main(argv=None) -> int:
         from ..utils import stream_check
 
         checker = stream_check.install()
+    if (len(cfg.stages) > 1 and torch.cuda.is_available() and args.backend != "gloo" and not opt.gloo_p2p
+            and not args.no_preflight):
+        # NCCL p2p between stages: replay the schedule's p2p program on the host first; a program that cannot
+        # complete would leave the GPUs spinning in NCCL kernels until a timeout
+        from ..parallel.p2p_sim import preflight
+
+        name = cfg.schedule or opt.schedule
+        stuck = None
+        try:
+            stuck = preflight(cfg, name, defer_wgrad=opt.defer_wgrad)
+        except Exception as e:      # noqa: BLE001 - the replay is a safety net, not a precondition
+            log.warning(f"p2p replay skipped: {e!r}")
+        if stuck is not None:
+            raise SystemExit(f"schedule {name} would deadlock on this plan: {stuck} (try --gloo_p2p, --sync_comm or another schedule)")
     tr = Trainer(cfg, opt)
     log.info(f"rank {tr.rank}/{tr.world} on {tr.device}; schedule {tr.schedule.name}; ops {tr.ops.name}; "
              f"stages {[s.stage_id for s in tr.stages]}", leader_only=False)

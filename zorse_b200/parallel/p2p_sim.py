@@ -180,3 +180,23 @@ def record_programs(cfg, schedule_name: str, model_overrides: Optional[dict] = N
         sched.step(0, inputs, inputs)
         out[r] = tp.events
     return out
+
+
+def preflight(cfg, schedule_name: str, **schedule_kw) -> Optional[str]:
+    """Replays the p2p program that `schedule_name` issues for `cfg` (same stages, ranks, microbatch counts and
+    schedule code, on a few-parameter stand-in model on the CPU) under the rules above.  Returns None when every
+    transfer completes, else a description of the wait cycle: a job whose program cannot complete must not be
+    started on GPUs, where it would sit in NCCL kernels until somebody's timeout.  Takes seconds."""
+    import dataclasses
+
+    from ..models import registry
+
+    if len(cfg.stages) < 2:
+        return None
+    if registry.get_spec(cfg.model_name).family == "vit":
+        return None        # image inputs: the stand-in below feeds token ids
+    small = dataclasses.replace(cfg, sequence_length=8, vocab_size=64, tensor_parallel_size=1)
+    tiny = {"hidden": 16, "heads": 2, "kv_heads": 2, "ffn": 32, "max_positions": 0} \
+        if registry.get_spec(cfg.model_name).max_positions == 0 else {"hidden": 16, "heads": 2, "kv_heads": 2, "ffn": 32}
+    progs = record_programs(small, schedule_name, model_overrides=tiny, **schedule_kw)
+    return simulate(progs)
