@@ -198,5 +198,10 @@ def preflight(cfg, schedule_name: str, **schedule_kw) -> Optional[str]:
     small = dataclasses.replace(cfg, sequence_length=8, vocab_size=64, tensor_parallel_size=1)
     tiny = {"hidden": 16, "heads": 2, "kv_heads": 2, "ffn": 32, "max_positions": 0} \
         if registry.get_spec(cfg.model_name).max_positions == 0 else {"hidden": 16, "heads": 2, "kv_heads": 2, "ffn": 32}
-    progs = record_programs(small, schedule_name, model_overrides=tiny, **schedule_kw)
+    threads = torch.get_num_threads()
+    torch.set_num_threads(1)          # tiny tensors, and every rank of a node runs this at the same time
+    try:
+        progs = record_programs(small, schedule_name, model_overrides=tiny, **schedule_kw)
+    finally:
+        torch.set_num_threads(threads)
     return simulate(progs)
