@@ -400,3 +400,30 @@ def test_fused_lane_gather_and_scatter_protocol_with_threads():
             assert torch.equal(h, hs[r]), (k, r, "reduce-scatter sum")
             assert torch.equal(n2_all, want_n2), (k, r, "sum + norm gather")
             assert torch.equal(y_all, want_y), (k, r, "plain gather")
+
+
+def test_take_and_put_slice_are_inverse_for_random_cuts():
+    """Property: for random segment layouts, widths and cut dimensions the slices of all processes tile the
+    tensor exactly once and put_slice restores it."""
+    from hypothesis import given, settings, strategies as st
+
+    from zorse_b200.models.tp_layers import put_slice, take_slice
+
+    @settings(max_examples=60, deadline=None)
+    @given(tp=st.sampled_from([1, 2, 3, 4]), segs=st.lists(st.integers(1, 5), min_size=1, max_size=3),
+           other=st.integers(1, 4), dim=st.sampled_from([0, 1]))
+    def check(tp, segs, other, dim):
+        segments = tuple(s * tp for s in segs)
+        shape = (sum(segments), other) if dim == 0 else (other, sum(segments))
+        full = torch.arange(shape[0] * shape[1], dtype=torch.float32).view(shape)
+        back = torch.full(shape, -1.0)
+        seen = []
+        for t in range(tp):
+            piece = take_slice(full, dim, segments, tp, t)
+            assert piece.shape[dim] == sum(segments) // tp and piece.shape[1 - dim] == other
+            seen.append(piece.reshape(-1))
+            put_slice(back, piece, dim, segments, tp, t)
+        assert torch.equal(back, full)
+        assert sorted(torch.cat(seen).tolist()) == full.reshape(-1).tolist()
+
+    check()
