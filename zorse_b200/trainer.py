@@ -75,7 +75,10 @@ class Trainer:
         # (stages, microbatches, p2p peers) uses the lane number, the groups use process ranks
         tp = cfg.tensor_parallel_size
         if tp > 1 and opt.collectives == "fused":
-            raise NotImplementedError("fused collectives do not cover tensor-parallel lanes; use --collectives library")
+            import warnings
+
+            warnings.warn("fused ZeRO collectives do not cover tensor-parallel lanes: their units use the library "
+                          "collectives (the lane's own fused kernels are selected with ZORSE_TP_FUSED=1)")
         self.lane, self.tp_index = self.rank // tp, self.rank % tp
         stage_groups = G.StageGroups.create_all(cfg.stages, self.rank, tp=tp)
         self.gloo_group = G.gloo_world_group() if (opt.gloo_p2p or self.device.type == "cuda") and G.is_dist() else None
