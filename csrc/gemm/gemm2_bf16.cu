@@ -110,6 +110,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                   const Params p, const Gemm2Extra ex) {
   using Cfg = Gemm2Cfg;
   constexpr bool SCATTER = std::is_same<Params, GemmScatterParams>::value;
+  constexpr bool ACCPF = std::is_same<Params, GemmAccPrefetchParams>::value;
   constexpr int BK = Cfg::BK, STAGES = Cfg::STAGES, BN = Cfg::BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -229,6 +230,45 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const int n0 = (tile / tiles_m) * BN;
       const int buf = local & 1;
       const uint32_t use = uint32_t(local >> 1);
+      if constexpr (ACCPF) {
+        // bf16 C += result without bias / addend / activation (checked on the host): request this thread's whole
+        // old C row of the tile now; the loads complete while the tile's main loop is still running
+        const int row = m0 + q * 32 + lane;
+        const bool row_ok = row < p.M;
+        const bool fast = row_ok && ecfg.vec_ok && n0 + BN <= p.N;
+        uint4 oldc[BN / 8];
+        __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(p.C) + size_t(row_ok ? row : 0) * p.ldc + n0;
+        if (fast) {
+#pragma unroll
+          for (int j = 0; j < BN / 8; ++j) oldc[j] = reinterpret_cast<const uint4*>(crow)[j];
+        }
+        if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[buf], use & 1, wctx, ST_TIMEOUT_TMEM_FULL))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 < p.N) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * BN + c * 32), r);
+            tmem_wait_ld();
+            if (fast) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 a = oldc[c * 4 + j];
+                const float2 f0 = unpack_bf16x2(a.x), f1 = unpack_bf16x2(a.y), f2 = unpack_bf16x2(a.z), f3 = unpack_bf16x2(a.w);
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r[j * 8 + 0]) + f0.x, __uint_as_float(r[j * 8 + 1]) + f0.y);
+                o.y = pack_bf16x2(__uint_as_float(r[j * 8 + 2]) + f1.x, __uint_as_float(r[j * 8 + 3]) + f1.y);
+                o.z = pack_bf16x2(__uint_as_float(r[j * 8 + 4]) + f2.x, __uint_as_float(r[j * 8 + 5]) + f2.y);
+                o.w = pack_bf16x2(__uint_as_float(r[j * 8 + 6]) + f3.x, __uint_as_float(r[j * 8 + 7]) + f3.y);
+                reinterpret_cast<uint4*>(crow)[c * 4 + j] = o;
+              }
+            } else if (row_ok) {
+              epilogue_store_chunk(p, ecfg, row, col0, r);
+            }
+          }
+        }
+      } else {
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[buf], use & 1, wctx, ST_TIMEOUT_TMEM_FULL))) break;
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
@@ -248,6 +288,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (!row_ok) continue;
         if constexpr (SCATTER) epilogue_scatter_chunk(crow, col0, p.N, ecfg.vec_ok, r);
         else epilogue_store_chunk(p, ecfg, row, col0, r);
+      }
       }
       tc_fence_before();
       __syncwarp();
@@ -373,4 +414,32 @@ extern "C" int zb_gemm2_rs_bf16(const void* A, const void* B, int M, int N, int 
   p.sc_rows = M / R; p.sc_R = R; p.sc_flag_index = flag_index; p.sc_epoch = epoch; p.sc_counter = counter;
   if (b_mn_major) return launch_gemm2<false, true, GemmScatterParams>(A, B, p, lda, ldb, max_ctas, stream);
   return launch_gemm2<false, false, GemmScatterParams>(A, B, p, lda, ldb, max_ctas, stream);
+}
+
+// C (bf16) += A @ B^T with the old C tile requested before the tile's accumulators are ready (candidate for the
+// weight-gradient GEMMs).  Same operand conventions as zb_gemm2_bf16; only bf16 accumulation without bias,
+// addend or activation takes the prefetching kernel, anything else is forwarded to zb_gemm2_bf16.
+extern "C" int zb_gemm2_accpf_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                                   int ldc, int a_mn_major, int b_mn_major, const void* bias, const void* addend,
+                                   int ld_addend, int flags, int max_ctas, int* status, cudaStream_t stream) {
+  using namespace zb;
+  if (flags != GEMM_ACCUMULATE || bias != nullptr || addend != nullptr)
+    return zb_gemm2_bf16(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, bias, addend, ld_addend, flags,
+                         max_ctas, status, stream);
+  if (M <= 0 || N <= 0 || K <= 0) ZB_FAIL(-1, "gemm2: empty problem %d x %d x %d", M, N, K);
+  GemmAccPrefetchParams p;
+  p.C = C;
+  p.bias = nullptr; p.addend = nullptr;
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc; p.ld_addend = 0;
+  p.flags = flags;
+  p.status = status;
+  p.gate_flags = nullptr;
+  p.gate_epoch = 0;
+  p.gate_base = 0; p.gate_row_bytes = 0; p.gate_shard_bytes = 1;
+  p.gate_chunk_bytes = 1; p.gate_cps = 1; p.gate_self = -1;
+  if (!a_mn_major && !b_mn_major) return launch_gemm2<false, false, GemmAccPrefetchParams>(A, B, p, lda, ldb, max_ctas, stream);
+  if (!a_mn_major && b_mn_major) return launch_gemm2<false, true, GemmAccPrefetchParams>(A, B, p, lda, ldb, max_ctas, stream);
+  if (a_mn_major && b_mn_major) return launch_gemm2<true, true, GemmAccPrefetchParams>(A, B, p, lda, ldb, max_ctas, stream);
+  return launch_gemm2<true, false, GemmAccPrefetchParams>(A, B, p, lda, ldb, max_ctas, stream);
 }

@@ -47,6 +47,11 @@ struct GemmScatterParams : GemmParams {
 };
 
 
+// Selects the kernels whose accumulate epilogue (C += result, bf16) reads the old C tile before the tile's
+// accumulators are ready, so that the read latency hides behind the main loop (weight gradients).
+struct GemmAccPrefetchParams : GemmParams {};
+
+
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   float u = k0 * (x + k1 * x * x * x);

@@ -336,3 +336,21 @@ def test_a_wait_that_runs_out_reports_and_leaves_the_context_usable(k):
     k.check_status()
     x = torch.arange(8, device="cuda", dtype=torch.float32)
     assert float(x.sum().item()) == 28.0
+
+
+@pytest.mark.skipif(not CANDIDATES, reason="ZORSE_TEST_CANDIDATES=1: first run on hardware pending")
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn", [(512, 768, 1024, True, True), (300, 520, 256, True, True),
+                                              (512, 512, 512, False, False), (256, 1000, 384, False, True)])
+def test_accumulate_prefetch_gemm_matches_the_default(k, M, N, K, a_mn, b_mn):
+    """The accumulating GEMM that reads the old C tile ahead of the accumulators must give the default kernel's
+    result bit for bit (same arithmetic, same order), ragged edges included, twice in a row."""
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda", generator=g).to(torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda", generator=g).to(torch.bfloat16)
+    c0 = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    want, got = c0.clone(), c0.clone()
+    for _ in range(2):
+        k.gemm(a, b, want, a_mn=a_mn, b_mn=b_mn, accumulate=True, kernel="2cta")
+        k.gemm(a, b, got, a_mn=a_mn, b_mn=b_mn, accumulate=True, kernel="2cta_accpf")
+    k.check_status()
+    assert torch.equal(got, want)

@@ -28,6 +28,8 @@ GEMM_GELU = 4
 GEMM_RELU = 8
 
 GEMM_KERNEL = os.environ.get("ZORSE_GEMM", "2cta")
+# candidate: accumulating GEMMs (weight gradients) request the old C tile before the tile's accumulators are ready
+GEMM_ACC_PREFETCH = os.environ.get("ZORSE_GEMM_ACC_PREFETCH", "0") == "1"
 
 ACT_GELU_TANH = 0
 ACT_RELU = 1
@@ -113,7 +115,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = Fa
 
     a: [M,K] (K-major) or [K,M] when a_mn; b: [N,K] (K-major) or [K,N] when b_mn.
     out: bf16 or fp32 [M,N]. kernel: "1cta" (128x{128,256} tile per CTA), "2cta" (256x256 tile per
-    CTA pair, tcgen05 cta_group::2) or None = GEMM_KERNEL default ("2cta" for M, N >= 256).
+    CTA pair, tcgen05 cta_group::2), "2cta_accpf" (candidate: as "2cta", bf16 `accumulate` reads the old C
+    tile ahead of the accumulators) or None = GEMM_KERNEL default ("2cta" for M, N >= 256).
     """
     _bf16(a, "a"); _bf16(b, "b")
     M, N = out.shape
@@ -133,8 +136,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = Fa
     elif act == "relu":
         flags |= GEMM_RELU
     kern = kernel or GEMM_KERNEL
-    if kern == "2cta" and bn == 0 and M >= 256 and N >= 256:
-        rc = lib().zb_gemm2_bf16(_p(a), _p(b), _p(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
+    if kern in ("2cta", "2cta_accpf") and bn == 0 and M >= 256 and N >= 256:
+        accpf = kern == "2cta_accpf" or (GEMM_ACC_PREFETCH and accumulate)
+        fn = lib().zb_gemm2_accpf_bf16 if accpf else lib().zb_gemm2_bf16
+        rc = fn(_p(a), _p(b), _p(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
                                  c_int(b.stride(0)), c_int(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)),
                                  _p(bias), _p(addend), c_int(0 if addend is None else addend.stride(0)),
                                  c_int(flags), c_int(max_ctas), _p(status_word(a.device)), _stream())

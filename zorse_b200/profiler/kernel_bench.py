@@ -78,6 +78,11 @@ def bench_gemm(k, peaks, rows):
                 rows.append({"op": f"gemm {kind} {kern}", "shape": f"{name} M{M} N{N} K{K}", "ours_ms": t_o, "lib_ms": t_l,
                              "ours_tflops": fl / t_o / 1e9, "lib_tflops": fl / t_l / 1e9,
                              "frac_of_peak": fl / t_o / 1e9 / peaks["bf16_tflops"]})
+        if os.environ.get("ZORSE_BENCH_CANDIDATES") == "1":     # kernels not yet validated on hardware
+            t_o = time_fn(lambda: k.gemm(dy, a, gw, a_mn=True, b_mn=True, accumulate=True, kernel="2cta_accpf"))
+            rows.append({"op": "gemm wgrad+= 2cta_accpf", "shape": f"{name} M{M} N{N} K{K}", "ours_ms": t_o, "lib_ms": None,
+                         "ours_tflops": fl / t_o / 1e9, "lib_tflops": None,
+                         "frac_of_peak": fl / t_o / 1e9 / peaks["bf16_tflops"]})
         k.check_status()
         del a, w, dy, out, dx, gw
 
