@@ -226,7 +226,7 @@ def test_candidate_report_parent_side(monkeypatch, capsys):
     """Case list, child-failure handling and the table of the candidate report (no GPU: children are faked)."""
     from zorse_b200.profiler import candidates as C
 
-    assert len(C.CASES) == len(set(C.CASES)) == 24
+    assert len(C.CASES) == len(set(C.CASES)) == 27
     fake = {"flash_bwd2:7b": {"case": "flash_bwd2:7b", "agrees": True, "max_diff": 0.01, "tolerance": 0.06, "status_word": 0,
                               "ms_default": 0.9, "ms_candidate": 0.45},
             "norm_bwd2_rms:7b": {"case": "norm_bwd2_rms:7b", "agrees": False, "max_diff": 0.5, "tolerance": 0.03,

@@ -11,7 +11,8 @@ L2, median).  The parent prints one table and writes the JSON.  Defaults were ch
 fp32 oracle by the GPU tests, so agreement with them within the bf16 tolerance is the criterion.
 
 Cases: flash_fwd4 (flags 0, 1, 2), flash_bwd2, norm_fwd2, norm_bwd2, each on a Llama-2-7B-like
-shape, a grouped-query d = 64 shape and a ragged / sliding-window shape.
+shape, a grouped-query d = 64 shape and a ragged / sliding-window shape; the accumulate-prefetch GEMM on two
+weight-gradient shapes of the 7B model and a ragged one.
 """
 from __future__ import annotations
 
@@ -27,9 +28,11 @@ ATTN_SHAPES = {   # name: (B, S, Hq, Hkv, D, window)
     "ragged_window": (1, 1000, 8, 2, 128, 384),
 }
 NORM_SHAPES = {"7b": (4096, 4096), "gqa64": (4096, 2048), "ragged_window": (1000, 5120)}
+WGRAD_SHAPES = {"7b_qkv": (4096, 12288, 4096), "7b_gate_up": (4096, 22016, 4096), "ragged": (1000, 1320, 520)}   # tokens, N, K
 
 CASES = [f"{k}:{s}" for k in ("flash_fwd4_f0", "flash_fwd4_f1", "flash_fwd4_f2", "flash_bwd2") for s in ATTN_SHAPES] + \
-        [f"{k}:{s}" for k in ("norm_fwd2_rms", "norm_fwd2_ln", "norm_bwd2_rms", "norm_bwd2_ln") for s in NORM_SHAPES]
+        [f"{k}:{s}" for k in ("norm_fwd2_rms", "norm_fwd2_ln", "norm_bwd2_rms", "norm_bwd2_ln") for s in NORM_SHAPES] + \
+        [f"gemm_accpf:{s}" for s in WGRAD_SHAPES]
 
 
 def _time(fn, flush, warm=3, reps=10):
@@ -65,7 +68,18 @@ def run_case(case: str) -> dict:
     rnd = lambda *s: (torch.randn(*s, device=dev, generator=g) * 0.5).to(torch.bfloat16)
     flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device=dev)
     res: dict = {"case": case}
-    if kind.startswith("flash"):
+    if kind == "gemm_accpf":
+        T, N, K = WGRAD_SHAPES[shape]
+        dy, a = rnd(T, N), rnd(T, K)
+        c0 = rnd(N, K)
+        g1, g2 = c0.clone(), c0.clone()
+        base = lambda: k.gemm(dy, a, g1, a_mn=True, b_mn=True, accumulate=True, kernel="2cta")
+        cand = lambda: k.gemm(dy, a, g2, a_mn=True, b_mn=True, accumulate=True, kernel="2cta_accpf")
+        base(), cand()
+        torch.cuda.synchronize()
+        res["max_diff"] = _diff(g1, g2)
+        res["tolerance"] = 0.0          # same arithmetic in the same order
+    elif kind.startswith("flash"):
         B, S, Hq, Hkv, D, win = ATTN_SHAPES[shape]
         qkv, do = rnd(B * S, (Hq + 2 * Hkv) * D), rnd(B * S, Hq * D)
         out1, lse1 = k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win, version=1)
