@@ -1,0 +1,158 @@
+"""Every Python wrapper of the kernel library, called on CPU tensors against a stand-in library that only
+records which entry point was reached: catches mistakes in argument marshalling, names and version
+selection of code that otherwise only runs on a GPU.  (What the kernels compute is tested on the GPU.)"""
+import pytest
+import torch
+
+from zorse_b200.ops import sm100 as k
+
+
+class FakeLib:
+    def __init__(self):
+        self.calls = []
+
+    def __getattr__(self, name):
+        def f(*args):
+            self.calls.append((name, len(args)))
+            if name.endswith("partial_rows"):
+                return 8
+            if name.endswith("stats_floats"):
+                return 2 * 128 * 4
+            if name.endswith("trace_warps"):
+                return 10
+            if name.endswith("trace_events"):
+                return 16
+            return 0
+        return f
+
+
+def c_prototypes():
+    """{entry point: number of parameters} read from the CUDA sources."""
+    import pathlib
+    import re
+
+    root = pathlib.Path(__file__).resolve().parent.parent / "csrc"
+    out = {}
+    for f in root.rglob("*.cu"):
+        text = f.read_text()
+        for m in re.finditer(r"\b(?:int|void)\s+(zb_\w+)\s*\(([^)]*)\)\s*\{", text):
+            params = m.group(2).strip()
+            out[m.group(1)] = 0 if params in ("", "void") else params.count(",") + 1
+    return out
+
+
+@pytest.fixture
+def lib(monkeypatch):
+    fake = FakeLib()
+    monkeypatch.setattr(k, "_lib", fake)
+    monkeypatch.setattr(k, "_bf16", lambda t, name: None)
+    monkeypatch.setattr(k, "status_word", lambda device=None: torch.zeros(1, dtype=torch.int32))
+    monkeypatch.setattr(k, "_stream", lambda: None)
+    monkeypatch.setattr(k, "_attn_scratch", {})
+    monkeypatch.setattr(k, "_attn_scratch2", {})
+    yield fake
+    protos = c_prototypes()
+    for name, nargs in fake.calls:
+        assert name in protos, f"{name} is not defined in csrc/"
+        assert nargs == protos[name], f"{name}: called with {nargs} arguments, the C function takes {protos[name]}"
+
+
+def bf(*shape):
+    return torch.zeros(*shape, dtype=torch.bfloat16)
+
+
+def names(lib):
+    return [c[0] for c in lib.calls]
+
+
+def test_gemm_dispatch(lib, monkeypatch):
+    a, w, out = bf(512, 256), bf(384, 256), bf(512, 384)
+    k.gemm(a, w, out)
+    k.gemm(a, w, out, accumulate=True, kernel="2cta_accpf")
+    k.gemm(a[:100], w, out[:100])                        # below the 2-CTA tile: single-CTA kernel
+    k.gemm(a, w, out, kernel="1cta", act="gelu", bias=bf(384), addend=bf(512, 384))
+    monkeypatch.setattr(k, "GEMM_ACC_PREFETCH", True)
+    k.gemm(a, w, out, accumulate=True)
+    k.gemm(a, w, out)
+    assert names(lib) == ["zb_gemm2_bf16", "zb_gemm2_accpf_bf16", "zb_gemm_bf16", "zb_gemm_bf16",
+                          "zb_gemm2_accpf_bf16", "zb_gemm2_bf16"]
+    with pytest.raises(TypeError):
+        k.gemm(a, w, torch.zeros(512, 384, dtype=torch.float16))
+
+
+def test_norm_and_attention_versions(lib):
+    x, w, b = bf(64, 256), bf(256), bf(256)
+    y, st = k.norm_fwd(x, w, None, 1e-5, False)
+    k.norm_fwd(x, w, b, 1e-5, True, version=2)
+    dw, db = torch.zeros(256), torch.zeros(256)
+    k.norm_bwd(x, x, w, st, None, dw, None, False)
+    k.norm_bwd(x, x, w, st, x, dw, db, True, version=2)
+    B, S, Hq, Hkv, D = 1, 128, 4, 2, 64
+    qkv, do = bf(B * S, (Hq + 2 * Hkv) * D), bf(B * S, Hq * D)
+    out, lse = k.flash_fwd(qkv, B, S, Hq, Hkv, D)
+    k.flash_fwd(qkv, B, S, Hq, Hkv, D, version=2)
+    k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, 32, version=4, flags=2,
+                trace=k.flash_fwd4_trace_buffer("cpu", 2), trace_ctas=2)
+    k.flash_bwd(do, qkv, out, lse, B, S, Hq, Hkv, D)
+    k.flash_bwd(do, qkv, out, lse, B, S, Hq, Hkv, D, version=2, trace=k.flash_bwd2_trace_buffer("cpu", 1), trace_ctas=1)
+    got = [n for n in names(lib) if not n.endswith(("partial_rows", "stats_floats", "trace_warps", "trace_events"))]
+    assert got == ["zb_norm_fwd", "zb_norm_fwd2", "zb_norm_bwd", "zb_norm_bwd2", "zb_flash_fwd", "zb_flash_fwd2",
+                   "zb_flash_fwd4", "zb_flash_bwd", "zb_flash_bwd2"]
+    assert out.shape == (B * S, Hq * D) and lse.shape == (B, Hq, S) and y.shape == x.shape and st.shape == (64, 2)
+
+
+def test_elementwise_loss_optimizer(lib):
+    gu = bf(32, 512)
+    k.swiglu_fwd(gu)
+    k.swiglu_bwd(gu, bf(32, 256))
+    k.act_fwd(gu, k.ACT_GELU_TANH)
+    k.act_bwd(gu, gu, k.ACT_RELU)
+    k.rope_(bf(32, 6 * 64), torch.zeros(32, 64), 32, 4, 64)
+    ids = torch.zeros(32, dtype=torch.long)
+    k.embedding_fwd(ids, bf(100, 64), bf(40, 64), 32, 2)
+    k.embedding_bwd(ids, bf(32, 64), torch.zeros(100, 64), torch.zeros(40, 64), 32, 2)
+    k.cross_entropy(bf(32, 100), ids, 1.0, dlogits=bf(32, 100))
+    n = 1024
+    k.adam_step(torch.zeros(n), torch.zeros(n), torch.zeros(n), bf(n), bf(n), lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8,
+                weight_decay=0.0, step=1)
+    k.colsum_accumulate(bf(32, 64), torch.zeros(64))
+    assert len(lib.calls) >= 10 and all(isinstance(c[1], int) for c in lib.calls)
+
+
+def test_fused_collective_wrappers(lib):
+    R, rows, H = 2, 256, 256
+    ptrs = [1 << 20, 2 << 20]
+    counter = torch.zeros(1, dtype=torch.int32)
+    flags = torch.zeros(64, dtype=torch.int32)
+    hyper = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1, grad_scale=1.0, grad_f32=False,
+                 epoch=1, counter=counter)
+    sh = torch.zeros(1024)
+    k.rs_adam(ptrs, ptrs, R, 0, 1024, sh, sh, sh, bf(1024), **hyper)
+    k.rs_adam_nvls(1 << 30, ptrs, R, 0, 1024, sh, sh, sh, bf(1024), p16_mc=(1 << 31), **hyper)
+    k.set_rs_adam_variant(1)
+    k.wait_flags(flags, R, 2, 1)
+    k.peer_pull(ptrs[1], bf(1024), 2048)
+    k.ag_gemm(bf(64, 128), bf(8192 * 4), 64, (256, 128), bf(64, 256), shard_ptrs=ptrs, R=R, r=0, shard_elems=16384,
+              chunk_bytes=4096, chunk_flags=torch.zeros(16, dtype=torch.int32), epoch=1, version_flags=flags, need_version=0)
+    k.gemm_rs(bf(R * rows, 128), bf(H, 128), b_mn=False, dst_ptrs=ptrs, flag_ptrs=ptrs, flag_index=1, epoch=3,
+              counter=counter, ldc=H)
+    k.gemm_rs(bf(R * rows, 128), bf(128, H), b_mn=True, dst_ptrs=ptrs, flag_ptrs=ptrs, flag_index=1, epoch=3,
+              counter=counter, ldc=H)
+    out = k.rs_finish(bf(R * rows * H), flags[:R], R, rows, H, 3, bf(rows, H), resid=bf(rows, H), bias=bf(H))
+    assert out.shape == (rows, H)
+    st = torch.zeros(rows, 2)
+    k.tp_norm_push(x=bf(rows, H), w=bf(H), b=None, eps=1e-5, layernorm=False, y_local=bf(rows, H), dst_ptrs=ptrs,
+                   flag_ptrs=ptrs, flag_index=17, epoch=1, stats=st, counter=counter)
+    k.tp_norm_push(slots=bf(R * rows * H), in_flags=flags[:R], in_epoch=3, resid=bf(rows, H), bias=bf(H), h_out=bf(rows, H),
+                   w=bf(H), b=bf(H), eps=1e-5, layernorm=True, y_local=bf(rows, H), dst_ptrs=ptrs, flag_ptrs=ptrs,
+                   flag_index=17, epoch=2, stats=st, counter=counter)
+    k.tp_push(bf(rows, H), ptrs, ptrs, 16, 1, counter)
+    assert names(lib) == ["zb_rs_adam", "zb_rs_adam_nvls", "zb_set_rs_adam_variant", "zb_wait_flags", "zb_peer_pull",
+                          "zb_ag_gemm_bf16", "zb_gemm2_rs_bf16", "zb_gemm2_rs_bf16", "zb_rs_finish", "zb_tp_norm_push",
+                          "zb_tp_norm_push", "zb_tp_push"]
+    # argument counts match the C signatures (a miscount would shift every later argument)
+    want = {"zb_rs_adam": 23, "zb_rs_adam_nvls": 24, "zb_wait_flags": 7, "zb_peer_pull": 5, "zb_gemm2_rs_bf16": 18,
+            "zb_rs_finish": 15, "zb_tp_norm_push": 26, "zb_tp_push": 10}
+    for name, nargs in lib.calls:
+        if name in want:
+            assert nargs == want[name], (name, nargs)
