@@ -156,3 +156,32 @@ def test_fused_collective_wrappers(lib):
     for name, nargs in lib.calls:
         if name in want:
             assert nargs == want[name], (name, nargs)
+
+
+@pytest.mark.parametrize("model,overrides", [("tiny_llama", {}), ("toygpt", {}), ("deepspeedmistral_toy", {}),
+                                              ("deepspeedbert_110m", {"layers": 2, "hidden": 128, "heads": 4, "kv_heads": 4, "ffn": 256}),
+                                              ("opt_1b", {"layers": 2, "hidden": 128, "heads": 4, "kv_heads": 4, "ffn": 256}),
+                                              ("deepspeedvit_default", {"layers": 2, "hidden": 128, "heads": 4, "kv_heads": 4,
+                                                                        "ffn": 256, "image": 64, "patch": 16})])
+def test_a_whole_step_through_the_gpu_op_layer(lib, model, overrides):
+    """One training step per schedule family with the sm100 op layer on top of the stand-in library: every
+    call the GPU path would make is made (outputs are meaningless), so a wrong argument, shape or name in the
+    layers, the op layer or the wrappers shows up without a GPU; the fixture checks the argument counts."""
+    from zorse_b200.config.training_config import parse_pipeline_dict
+    from zorse_b200.trainer import Trainer, TrainerOptions
+
+    L = overrides.get("layers", 4)
+    cfg = parse_pipeline_dict({"model_name": model, "global_batch_size": 4, "microbatch_size": 2, "sequence_length": 128,
+                               "vocab_size": 512, "autocast_dtype": "bfloat16", "reduce_dtype": "bfloat16",
+                               "pipeline_config": [{"gpu_ranks": [0], "num_microbatches_per_rank": [2],
+                                                    "layer_partition": [0, L], "zero_config": [[0]]}]})
+    for schedule, recompute, oib in (("1f1b", False, False), ("zero2", True, True), ("layer_major", None, False)):
+        before = len(lib.calls)
+        tr = Trainer(cfg, TrainerOptions(schedule=schedule, ops="sm100", activation_recompute=recompute,
+                                         optimizer_in_backward=oib, model_overrides=overrides))
+        tr.train_step_from_host(tr.synthetic_batch())
+        made = {n for n, _ in lib.calls[before:]}
+        need = {"zb_flash_fwd", "zb_flash_bwd", "zb_norm_fwd", "zb_norm_bwd", "zb_cross_entropy", "zb_adam"}
+        if "vit" not in model:
+            need |= {"zb_embedding_fwd", "zb_embedding_bwd"}
+        assert need <= made and ({"zb_gemm2_bf16", "zb_gemm_bf16"} & made), sorted(made)
