@@ -185,3 +185,20 @@ def test_a_whole_step_through_the_gpu_op_layer(lib, model, overrides):
         if "vit" not in model:
             need |= {"zb_embedding_fwd", "zb_embedding_bwd"}
         assert need <= made and ({"zb_gemm2_bf16", "zb_gemm_bf16"} & made), sorted(made)
+
+
+def test_candidate_report_cases_run_end_to_end_on_the_stand_in_library(lib, monkeypatch):
+    """Every case of the candidate report, executed on CPU tensors against the stand-in library (small shapes):
+    the tool's own code must not be what fails on the first GPU run."""
+    from zorse_b200.profiler import candidates as C
+
+    monkeypatch.setattr(C, "ATTN_SHAPES", {"7b": (1, 256, 4, 4, 128, 0), "gqa64": (2, 128, 4, 2, 64, 0),
+                                           "ragged_window": (1, 200, 4, 2, 128, 64)})
+    monkeypatch.setattr(C, "NORM_SHAPES", {"7b": (64, 256), "gqa64": (64, 128), "ragged_window": (50, 320)})
+    monkeypatch.setattr(C, "WGRAD_SHAPES", {"7b_qkv": (256, 512, 256), "7b_gate_up": (256, 768, 256), "ragged": (100, 300, 264)})
+    for case in C.CASES:
+        r = C.run_case(case, dev="cpu", flush_floats=16)
+        assert r["case"] == case and "max_diff" in r and "tolerance" in r and "agrees" in r, r
+        assert "ms_default" in r and "ms_candidate" in r, r          # status word stayed 0 on the stand-in
+    table = C.format_table([C.run_case(c, dev="cpu", flush_floats=16) for c in C.CASES[:2]])
+    assert table.count("\n") == 3

@@ -36,19 +36,27 @@ CASES = [f"{k}:{s}" for k in ("flash_fwd4_f0", "flash_fwd4_f1", "flash_fwd4_f2",
 
 
 def _time(fn, flush, warm=3, reps=10):
+    import time
+
     import torch
 
+    cuda = flush.is_cuda
     for _ in range(warm):
         fn()
     ts = []
     for _ in range(reps):
         flush.add_(1)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fn()
-        b.record()
-        torch.cuda.synchronize()
-        ts.append(a.elapsed_time(b))
+        if cuda:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        else:                       # only reached by the tool's own dry-run test
+            t0 = time.perf_counter()
+            fn()
+            ts.append((time.perf_counter() - t0) * 1e3)
     return statistics.median(ts)
 
 
@@ -56,17 +64,17 @@ def _diff(a, b):
     return float((a.float() - b.float()).abs().max().item())
 
 
-def run_case(case: str) -> dict:
+def run_case(case: str, dev: str = "cuda", flush_floats: int = 64 * 1024 * 1024) -> dict:
     """Child process: one candidate against the default on one shape."""
     import torch
 
     from zorse_b200.ops import sm100 as k
 
     kind, shape = case.split(":")
-    dev = "cuda"
+    sync = torch.cuda.synchronize if dev == "cuda" else (lambda: None)
     g = torch.Generator(device=dev).manual_seed(1)
     rnd = lambda *s: (torch.randn(*s, device=dev, generator=g) * 0.5).to(torch.bfloat16)
-    flush = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device=dev)
+    flush = torch.zeros(flush_floats, dtype=torch.float32, device=dev)
     res: dict = {"case": case}
     if kind == "gemm_accpf":
         T, N, K = WGRAD_SHAPES[shape]
@@ -76,7 +84,7 @@ def run_case(case: str) -> dict:
         base = lambda: k.gemm(dy, a, g1, a_mn=True, b_mn=True, accumulate=True, kernel="2cta")
         cand = lambda: k.gemm(dy, a, g2, a_mn=True, b_mn=True, accumulate=True, kernel="2cta_accpf")
         base(), cand()
-        torch.cuda.synchronize()
+        sync()
         res["max_diff"] = _diff(g1, g2)
         res["tolerance"] = 0.0          # same arithmetic in the same order
     elif kind.startswith("flash"):
@@ -88,14 +96,14 @@ def run_case(case: str) -> dict:
             cand = lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win, version=4, flags=fl)
             base = lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win, version=1)
             out4, lse4 = cand()
-            torch.cuda.synchronize()
+            sync()
             res["max_diff"] = max(_diff(out4, out1), _diff(lse4, lse1))
             res["tolerance"] = 3e-2 if fl < 2 else 4e-2
         else:
             cand = lambda: k.flash_bwd(do, qkv, out1, lse1, B, S, Hq, Hkv, D, True, win, version=2)
             base = lambda: k.flash_bwd(do, qkv, out1, lse1, B, S, Hq, Hkv, D, True, win, version=1)
             d1, d2 = base(), cand()
-            torch.cuda.synchronize()
+            sync()
             res["max_diff"] = _diff(d1, d2)
             res["tolerance"] = 6e-2
     else:
@@ -108,7 +116,7 @@ def run_case(case: str) -> dict:
             cand = lambda: k.norm_fwd(x, w, b, 1e-5, ln, version=2)
             base = lambda: k.norm_fwd(x, w, b, 1e-5, ln, version=1)
             y2, st2 = cand()
-            torch.cuda.synchronize()
+            sync()
             res["max_diff"] = max(_diff(y1, y2), _diff(st1, st2))
             res["tolerance"] = 2e-2
         else:
@@ -122,7 +130,7 @@ def run_case(case: str) -> dict:
 
             cand, base = (lambda: run(2)), (lambda: run(1))
             (dx1, dw1, db1), (dx2, dw2, db2) = base(), cand()
-            torch.cuda.synchronize()
+            sync()
             rel = lambda a, c: _diff(a, c) / max(1.0, float(a.float().abs().max().item()))
             res["max_diff"] = max(_diff(dx1, dx2), rel(dw1, dw2), rel(db1, db2) if ln else 0.0)
             res["tolerance"] = 3e-2
