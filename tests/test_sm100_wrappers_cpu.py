@@ -202,3 +202,16 @@ def test_candidate_report_cases_run_end_to_end_on_the_stand_in_library(lib, monk
         assert "ms_default" in r and "ms_candidate" in r, r          # status word stayed 0 on the stand-in
     table = C.format_table([C.run_case(c, dev="cpu", flush_floats=16) for c in C.CASES[:2]])
     assert table.count("\n") == 3
+
+
+@pytest.mark.parametrize("kernel", ["fwd4", "bwd2"])
+def test_attention_trace_tool_runs_and_copes_with_an_empty_trace(lib, monkeypatch, capsys, tmp_path, kernel):
+    """The trace tool end to end on the stand-in library: nothing is recorded (all-zero buffer), which is
+    also what a kernel that returned early would leave; the tool must report that instead of failing."""
+    from zorse_b200.profiler import attn_trace
+
+    monkeypatch.setattr(k, "check_status", lambda device=None: None)
+    out = tmp_path / "trace.json"
+    attn_trace.main(["--kernel", kernel, "--S", "256", "--heads", "2", "--kv_heads", "2", "--D", "64", "--ctas", "2",
+                     "--device", "cpu", "--out", str(out)])
+    assert out.exists() and capsys.readouterr().out.strip()

@@ -65,6 +65,9 @@ def summarize(trace, cta: int, codes=None) -> dict:
 
 
 def format_summary(summary: dict) -> str:
+    if not summary:
+        return ("no events recorded for this CTA: the kernel returned before its first trace point "
+                "(check the status word), or the CTA index is beyond the traced ones")
     lines = []
     t0 = min(v["first"] for v in summary.values()) if summary else 0
     for w, v in sorted(summary.items()):
@@ -87,12 +90,13 @@ def main(argv=None):
     ap.add_argument("--cta", type=int, default=0, help="which traced CTA to print (0 = heaviest query pair of head 0)")
     ap.add_argument("--flags", type=int, default=0)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--device", default="cuda", help=argparse.SUPPRESS)     # "cpu" only for the tool's own dry-run test
     a = ap.parse_args(argv)
     import torch
 
     from zorse_b200.ops import sm100 as k
 
-    dev = "cuda"
+    dev = a.device
     g = torch.Generator(device=dev).manual_seed(0)
     qkv = (torch.randn(a.S, (a.heads + 2 * a.kv_heads) * a.D, device=dev, generator=g) * 0.5).to(torch.bfloat16)
     codes = CODES
@@ -111,7 +115,8 @@ def main(argv=None):
         buf = k.flash_bwd2_trace_buffer(dev, a.ctas)
         k.flash_bwd(do, qkv, out, lse, 1, a.S, a.heads, a.kv_heads, a.D, True, a.window, version=2, trace=buf,
                     trace_ctas=a.ctas)
-    torch.cuda.synchronize()
+    if dev == "cuda":
+        torch.cuda.synchronize()
     k.check_status()
     host = buf.cpu().tolist()
     summ = summarize(host, a.cta, codes)
