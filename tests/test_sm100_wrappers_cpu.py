@@ -215,3 +215,27 @@ def test_attention_trace_tool_runs_and_copes_with_an_empty_trace(lib, monkeypatc
     attn_trace.main(["--kernel", kernel, "--S", "256", "--heads", "2", "--kv_heads", "2", "--D", "64", "--ctas", "2",
                      "--device", "cpu", "--out", str(out)])
     assert out.exists() and capsys.readouterr().out.strip()
+
+
+def test_a_whole_step_with_every_candidate_version_selected(lib, monkeypatch):
+    """The same dry run with the opt-in kernel versions selected the way their environment switches do:
+    flipping a default must not be what breaks the Python side."""
+    from zorse_b200.config.training_config import parse_pipeline_dict
+    from zorse_b200.trainer import Trainer, TrainerOptions
+
+    monkeypatch.setattr(k, "ATTN_FWD_VERSION", 4)
+    monkeypatch.setattr(k, "ATTN_FWD4_FLAGS", 2)
+    monkeypatch.setattr(k, "ATTN_BWD_VERSION", 2)
+    monkeypatch.setattr(k, "NORM_FWD_VERSION", 2)
+    monkeypatch.setattr(k, "NORM_BWD_VERSION", 2)
+    monkeypatch.setattr(k, "GEMM_ACC_PREFETCH", True)
+    cfg = parse_pipeline_dict({"model_name": "tiny_llama", "global_batch_size": 4, "microbatch_size": 2,
+                               "sequence_length": 256, "vocab_size": 512, "autocast_dtype": "bfloat16",
+                               "reduce_dtype": "bfloat16",
+                               "pipeline_config": [{"gpu_ranks": [0], "num_microbatches_per_rank": [2],
+                                                    "layer_partition": [0, 4], "zero_config": [[0]]}]})
+    tr = Trainer(cfg, TrainerOptions(schedule="1f1b", ops="sm100", activation_recompute=False))
+    tr.train_step_from_host(tr.synthetic_batch())
+    made = {n for n, _ in lib.calls}
+    assert {"zb_flash_fwd4", "zb_flash_bwd2", "zb_norm_fwd2", "zb_norm_bwd2", "zb_gemm2_accpf_bf16"} <= made, sorted(made)
+    assert not ({"zb_flash_fwd", "zb_flash_bwd", "zb_norm_fwd", "zb_norm_bwd"} & made), sorted(made)
