@@ -239,3 +239,29 @@ def test_a_whole_step_with_every_candidate_version_selected(lib, monkeypatch):
     made = {n for n, _ in lib.calls}
     assert {"zb_flash_fwd4", "zb_flash_bwd2", "zb_norm_fwd2", "zb_norm_bwd2", "zb_gemm2_accpf_bf16"} <= made, sorted(made)
     assert not ({"zb_flash_fwd", "zb_flash_bwd", "zb_norm_fwd", "zb_norm_bwd"} & made), sorted(made)
+
+
+def test_kernel_bench_with_candidate_rows_runs_end_to_end(lib, monkeypatch, tmp_path, capsys):
+    """The timing tool, candidate rows included, on the stand-in library with small shapes; its output must
+    also be what perf_check reads."""
+    from zorse_b200.profiler import kernel_bench as KB
+    from zorse_b200.profiler import perf_check
+
+    monkeypatch.setenv("ZORSE_BENCH_CANDIDATES", "1")
+    monkeypatch.setattr(KB, "DEV", "cpu")
+    monkeypatch.setattr(KB, "_flush", None)
+    monkeypatch.setattr(KB, "FLUSH_BYTES", 1024)
+    monkeypatch.setattr(KB, "GEMM_SHAPES", [("small", 256, 384, 128)])
+    monkeypatch.setattr(KB, "ATTN_CASES", [("small", 1, 256, 4, 2, 64, 0), ("window", 1, 256, 4, 2, 64, 64)])
+    monkeypatch.setattr(KB, "ELEMENTWISE_DIMS", (64, 256, 512, 1000, 4096))
+    monkeypatch.setattr(k, "check_status", lambda device=None: None)
+    out = tmp_path / "kb.json"
+    KB.main(["--out", str(out)])
+    import json
+
+    rows = json.loads(out.read_text())["rows"]
+    ops_seen = {r["op"] for r in rows}
+    assert {"gemm wgrad+= 2cta_accpf", "flash fwd v4 mode2", "flash bwd v2", "rmsnorm fwd v2", "rmsnorm bwd v2",
+            "gemm fwd 2cta", "flash fwd", "adam (bf16 grad)"} <= ops_seen, sorted(ops_seen)
+    assert capsys.readouterr().out.count("\n") == len(rows)
+    assert perf_check.main([str(out)]) in (0, 1)          # rows without a recorded baseline are reported, not fatal

@@ -31,42 +31,53 @@ def _peaks():
 
 
 _flush = None
+DEV = "cuda"            # "cpu" only in the tool's own dry-run test (stand-in library, small shapes)
+FLUSH_BYTES = 256 * 1024 * 1024
+GEMM_SHAPES = [
+    # name, M(tokens), N, K
+    ("7b qkv", 4096, 12288, 4096), ("7b o", 4096, 4096, 4096), ("7b gate_up", 4096, 22016, 4096),
+    ("7b down", 4096, 4096, 11008), ("7b head", 4096, 32000, 4096),
+    ("1b gate_up", 2048, 16384, 2048), ("square 8192", 8192, 8192, 8192),
+]
+ATTN_CASES = [("7b", 1, 4096, 32, 32, 128, 0), ("1b", 1, 2048, 32, 8, 64, 0), ("mistral", 1, 8192, 32, 8, 128, 4096)]
+ELEMENTWISE_DIMS = (4096, 4096, 11008, 32000, 202_383_360 // 2)      # tokens, hidden, ffn, vocab, Adam elements
 
 
 def time_fn(fn, warmup=3, iters=10):
     global _flush
-    if _flush is None:
-        _flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    if _flush is None or _flush.device.type != DEV:
+        _flush = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device=DEV)
     for _ in range(warmup):
         fn()
     ts = []
     for _ in range(iters):
         _flush.zero_()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fn()
-        b.record()
-        torch.cuda.synchronize()
-        ts.append(a.elapsed_time(b))
+        if DEV == "cuda":
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        else:
+            import time
+
+            t0 = time.perf_counter()
+            fn()
+            ts.append(max((time.perf_counter() - t0) * 1e3, 1e-6))
     return statistics.median(ts)
 
 
 def bench_gemm(k, peaks, rows):
-    shapes = [
-        # name, M(tokens), N, K
-        ("7b qkv", 4096, 12288, 4096), ("7b o", 4096, 4096, 4096), ("7b gate_up", 4096, 22016, 4096),
-        ("7b down", 4096, 4096, 11008), ("7b head", 4096, 32000, 4096),
-        ("1b gate_up", 2048, 16384, 2048), ("square 8192", 8192, 8192, 8192),
-    ]
-    for name, M, N, K in shapes:
-        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
-        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
-        dy = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
-        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        dx = torch.empty(M, K, device="cuda", dtype=torch.bfloat16)
-        gw = torch.zeros(N, K, device="cuda", dtype=torch.float32)
+    for name, M, N, K in GEMM_SHAPES:
+        a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+        dy = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+        out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        dx = torch.empty(M, K, device=DEV, dtype=torch.bfloat16)
+        gw = torch.zeros(N, K, device=DEV, dtype=torch.float32)
         fl = 2.0 * M * N * K
-        gw = torch.zeros(N, K, device="cuda", dtype=torch.bfloat16)
+        gw = torch.zeros(N, K, device=DEV, dtype=torch.bfloat16)
         for kern in ("1cta", "2cta"):
             for kind, ours, lib in (
                 ("fwd", lambda: k.gemm(a, w, out, kernel=kern), lambda: torch.matmul(a, w.t(), out=out)),
@@ -90,10 +101,9 @@ def bench_gemm(k, peaks, rows):
 def bench_attn(k, peaks, rows):
     import torch.nn.functional as F
 
-    cases = [("7b", 1, 4096, 32, 32, 128, 0), ("1b", 1, 2048, 32, 8, 64, 0), ("mistral", 1, 8192, 32, 8, 128, 4096)]
-    for name, B, S, Hq, Hkv, D, win in cases:
-        qkv = torch.randn(B * S, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
-        do = torch.randn(B * S, Hq * D, device="cuda", dtype=torch.bfloat16)
+    for name, B, S, Hq, Hkv, D, win in ATTN_CASES:
+        qkv = torch.randn(B * S, (Hq + 2 * Hkv) * D, device=DEV, dtype=torch.bfloat16)
+        do = torch.randn(B * S, Hq * D, device=DEV, dtype=torch.bfloat16)
         out, lse = k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, win)
         x = qkv.view(B, S, Hq + 2 * Hkv, D)
         q = x[:, :, :Hq].transpose(1, 2)
@@ -146,12 +156,12 @@ def bench_attn(k, peaks, rows):
 def bench_elementwise(k, peaks, rows):
     import torch.nn.functional as F
 
-    T, H, Fd, V = 4096, 4096, 11008, 32000
-    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
-    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
-    dy = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    T, H, Fd, V, n_adam = ELEMENTWISE_DIMS
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+    w = torch.ones(H, device=DEV, dtype=torch.bfloat16)
+    dy = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
     y, st = k.norm_fwd(x, w, None, 1e-5, False)
-    gw = torch.zeros(H, device="cuda", dtype=torch.float32)
+    gw = torch.zeros(H, device=DEV, dtype=torch.float32)
 
     def add(op, shape, t_o, t_l, nbytes):
         rows.append({"op": op, "shape": shape, "ours_ms": t_o, "lib_ms": t_l, "ours_gbs": nbytes / t_o / 1e6,
@@ -166,25 +176,25 @@ def bench_elementwise(k, peaks, rows):
             2 * T * H * 2)
         add("rmsnorm bwd v2", f"T{T} H{H}", time_fn(lambda: k.norm_bwd(dy, x, w, st, None, gw, None, False, version=2)),
             None, 3 * T * H * 2)
-    gu = torch.randn(T, 2 * Fd, device="cuda", dtype=torch.bfloat16)
-    dout = torch.randn(T, Fd, device="cuda", dtype=torch.bfloat16)
+    gu = torch.randn(T, 2 * Fd, device=DEV, dtype=torch.bfloat16)
+    dout = torch.randn(T, Fd, device=DEV, dtype=torch.bfloat16)
     add("swiglu fwd", f"T{T} F{Fd}", time_fn(lambda: k.swiglu_fwd(gu)),
         time_fn(lambda: F.silu(gu[:, :Fd]) * gu[:, Fd:]), 3 * T * Fd * 2)
     add("swiglu bwd", f"T{T} F{Fd}", time_fn(lambda: k.swiglu_bwd(gu, dout)), None, 5 * T * Fd * 2)
-    logits = torch.randn(T, V, device="cuda", dtype=torch.bfloat16)
-    tg = torch.randint(0, V, (T,), device="cuda")
+    logits = torch.randn(T, V, device=DEV, dtype=torch.bfloat16)
+    tg = torch.randint(0, V, (T,), device=DEV)
     add("cross-entropy fwd+bwd", f"T{T} V{V}", time_fn(lambda: k.cross_entropy(logits, tg, 1.0, dlogits=logits)),
         None, 2 * T * V * 2)
-    n = 202_383_360 // 2
-    p, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
-    g = torch.randn(n, device="cuda", dtype=torch.bfloat16)
-    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    n = n_adam
+    p, m, v = (torch.zeros(n, device=DEV) for _ in range(3))
+    g = torch.randn(n, device=DEV, dtype=torch.bfloat16)
+    p16 = torch.empty(n, device=DEV, dtype=torch.bfloat16)
     add("adam (bf16 grad)", f"n{n}", time_fn(lambda: k.adam_step(p, m, v, g, p16, lr=1e-3, beta1=0.9, beta2=0.999,
                                                                    eps=1e-8, weight_decay=0.0, step=1)),
         None, n * (12 + 2 + 12 + 2))
-    qkv = torch.randn(T, 3 * H, device="cuda", dtype=torch.bfloat16)
+    qkv = torch.randn(T, 3 * H, device=DEV, dtype=torch.bfloat16)
     from zorse_b200.ops import ref
-    cs = ref.rope_table(T, 128, 1e4, "cuda")
+    cs = ref.rope_table(T, 128, 1e4, DEV)
     add("rope (q,k in place)", f"T{T} 64 heads d128", time_fn(lambda: k.rope_(qkv, cs, T, 64, 128)), None,
         2 * T * 2 * H * 2)
     k.check_status()
