@@ -22,6 +22,8 @@ class FakeLib:
                 return 10
             if name.endswith("trace_events"):
                 return 16
+            if name.endswith("probe_count"):
+                return 64
             return 0
         return f
 
@@ -265,3 +267,13 @@ def test_kernel_bench_with_candidate_rows_runs_end_to_end(lib, monkeypatch, tmp_
             "gemm fwd 2cta", "flash fwd", "adam (bf16 grad)"} <= ops_seen, sorted(ops_seen)
     assert capsys.readouterr().out.count("\n") == len(rows)
     assert perf_check.main([str(out)]) in (0, 1)          # rows without a recorded baseline are reported, not fatal
+
+
+def test_latency_probe_tool_runs_on_the_stand_in_library(lib, monkeypatch, tmp_path, capsys):
+    from zorse_b200.profiler import sm100_latency
+
+    monkeypatch.setattr(k, "lib", lambda: lib)
+    monkeypatch.setattr(k, "check_status", lambda device=None: None)
+    out = tmp_path / "lat.json"
+    sm100_latency.main(["--runs", "2", "--device", "cpu", "--out", str(out)])
+    assert out.exists() and "clocks" in capsys.readouterr().out

@@ -38,6 +38,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--runs", type=int, default=5)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--device", default="cuda", help=argparse.SUPPRESS)     # "cpu" only for the tool's own dry-run test
     a = ap.parse_args(argv)
     import ctypes
 
@@ -49,14 +50,16 @@ def main(argv=None):
     n = lib.zb_latency_probe_count()
     runs = []
     for _ in range(a.runs):
-        out = torch.zeros(n, dtype=torch.int64, device="cuda")
-        sink = torch.zeros(288, dtype=torch.float32, device="cuda")
+        cuda = a.device == "cuda"
+        out = torch.zeros(n, dtype=torch.int64, device=a.device)
+        sink = torch.zeros(288, dtype=torch.float32, device=a.device)
         rc = lib.zb_latency_probe(ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(sink.data_ptr()),
-                                  ctypes.c_void_p(k.status_word("cuda").data_ptr()),
-                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+                                  ctypes.c_void_p(k.status_word(a.device).data_ptr()),
+                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream if cuda else 0))
         if rc != 0:
             raise RuntimeError(lib.zb_last_error().decode())
-        torch.cuda.synchronize()
+        if cuda:
+            torch.cuda.synchronize()
         k.check_status()
         runs.append(out.cpu().tolist())
     med = {NAMES[i]: statistics.median(r[i] for r in runs) for i in NAMES}
