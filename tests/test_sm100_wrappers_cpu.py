@@ -277,3 +277,52 @@ def test_latency_probe_tool_runs_on_the_stand_in_library(lib, monkeypatch, tmp_p
     out = tmp_path / "lat.json"
     sm100_latency.main(["--runs", "2", "--device", "cpu", "--out", str(out)])
     assert out.exists() and "clocks" in capsys.readouterr().out
+
+
+def test_bench_main_prints_its_json_line(lib, monkeypatch, capsys):
+    """bench.py from argument parsing to the JSON line, one process, on the stand-in library with stand-in CUDA
+    events: every key the benchmark contract names is there."""
+    import importlib.util
+    import json
+    import os
+    import sys
+
+    class Ev:
+        def __init__(self, enable_timing=False):
+            pass
+
+        def record(self, stream=None):
+            pass
+
+        def query(self):
+            return True
+
+        def elapsed_time(self, other):
+            return 12.5
+
+        def synchronize(self):
+            pass
+
+    monkeypatch.setattr(k, "check_status", lambda device=None: None)
+    monkeypatch.setattr(torch.cuda, "Event", Ev)
+    monkeypatch.setattr(torch.cuda, "max_memory_allocated", lambda *a: 0)
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a: None)
+    for var in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR"):
+        monkeypatch.delenv(var, raising=False)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_script", os.path.join(root, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--steps", "2", "--warmup", "3", "--model", "tiny_llama", "--vocab", "512",
+                                      "--seq_len", "128", "--global_batch", "4", "--microbatch", "2"])
+    assert mod.main() == 0
+    line = [ln for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")][-1]
+    out = json.loads(line)
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "clocks", "e2e", "gpu_launches"):
+        assert key in out, key
+    assert out["n_gpus"] == 1 and out["steps"] == 2 and out["warmup"] == 3 and out["ms_per_step"] == 6.25
+    assert out["value"] == pytest.approx(4 * 128 / 6.25e-3) and out["gpu_launches"] > 0
+    assert {"value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step"} <= set(out["e2e"])
+    assert out["e2e"]["h2d_bytes_per_step"] == 2 * 4 * 128 * 8 and out["e2e"]["d2h_bytes_per_step"] == 4
+    assert {"model", "global_batch", "seq_len", "parallelism"} <= set(out["config"])
