@@ -427,3 +427,31 @@ def test_take_and_put_slice_are_inverse_for_random_cuts():
         assert sorted(torch.cat(seen).tolist()) == full.reshape(-1).tolist()
 
     check()
+
+
+def _worker_gpu_ops_dry_run(rank, world, cfg_dict):
+    """One step of a tensor-parallel lane through the GPU op layer on a stand-in library (CPU tensors)."""
+    from test_sm100_wrappers_cpu import FakeLib, c_prototypes
+    from zorse_b200.ops import sm100 as k
+    from zorse_b200.trainer import Trainer, TrainerOptions
+
+    fake = FakeLib()
+    k._lib = fake
+    k._bf16 = lambda t, name: None
+    k.status_word = lambda device=None: torch.zeros(1, dtype=torch.int32)
+    k._stream = lambda: None
+    k.check_status = lambda device=None: None
+    tr = Trainer(parse_pipeline_dict(cfg_dict), TrainerOptions(backend="gloo", schedule="1f1b", ops="sm100",
+                                                               activation_recompute=False))
+    tr.train_step_from_host(tr.synthetic_batch())
+    protos = c_prototypes()
+    bad = [(n, a, protos.get(n)) for n, a in fake.calls if protos.get(n) != a]
+    return {"calls": len(fake.calls), "bad": bad, "names": sorted({n for n, _ in fake.calls})}
+
+
+def test_tp_lane_through_the_gpu_op_layer_dry_run():
+    cfg = tiny_cfg(ONE_LANE, tensor_parallel_size=2, autocast_dtype="bfloat16", reduce_dtype="bfloat16", sequence_length=128)
+    res = run_workers(2, _worker_gpu_ops_dry_run, cfg)
+    for r in res:
+        assert r["calls"] > 100 and not r["bad"], r["bad"]
+        assert "zb_flash_fwd" in r["names"] and "zb_norm_bwd" in r["names"]
