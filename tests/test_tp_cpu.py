@@ -449,8 +449,13 @@ def _worker_gpu_ops_dry_run(rank, world, cfg_dict):
     return {"calls": len(fake.calls), "bad": bad, "names": sorted({n for n, _ in fake.calls})}
 
 
-def test_tp_lane_through_the_gpu_op_layer_dry_run():
-    cfg = tiny_cfg(ONE_LANE, tensor_parallel_size=2, autocast_dtype="bfloat16", reduce_dtype="bfloat16", sequence_length=128)
+@pytest.mark.parametrize("layout", ["tp2", "two_stages", "zero2way"])
+def test_tp_lane_through_the_gpu_op_layer_dry_run(layout):
+    """... and the same for two pipeline stages and for a two-way ZeRO stage (bf16 tensors over gloo)."""
+    from test_dist_cpu import PIPE_1x2, PIPE_2x1
+
+    pipe, tp = {"tp2": (ONE_LANE, 2), "two_stages": (PIPE_2x1, 1), "zero2way": (PIPE_1x2, 1)}[layout]
+    cfg = tiny_cfg(pipe, tensor_parallel_size=tp, autocast_dtype="bfloat16", reduce_dtype="bfloat16", sequence_length=128)
     res = run_workers(2, _worker_gpu_ops_dry_run, cfg)
     for r in res:
         assert r["calls"] > 100 and not r["bad"], r["bad"]
