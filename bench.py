@@ -115,13 +115,15 @@ class ClockSampler(threading.Thread):
 
 
 def reference_arm(args):
-    """The reference is plain Python without any packaging metadata, so the prescribed offline
-    `pip install --target baseline/_ref` cannot build it, and its modules do not import against
-    the installed transformers (models/llama_simple.py:7-13 needs classes removed since)."""
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "reference has no setup.py/pyproject (pip install fails) and does not import with transformers 5.5: "
-                      "LlamaFlashAttention2/LlamaSdpaAttention no longer exist"}))
-    return 0
+    """Runs the unmodified reference (a plain copy of its tree under `baseline/_ref/`, which is
+    git-ignored) through its own entry point on the same model, batch and rank plan, and prints
+    the same JSON line with `"impl": "reference"`.  Nothing of this repository's package or kernel
+    library is imported on this path; `baseline/ref_harness.py` says what is added around the
+    reference (an import shim for names the installed transformers removed, timing marks)."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+    import ref_harness
+
+    return ref_harness.run(args, clock_sampler_cls=ClockSampler)
 
 
 def main():
@@ -150,6 +152,8 @@ def main():
     ap.add_argument("--no_preflight", action="store_true",
                     help="skip the host-side replay of the schedule's p2p program before the first multi-stage step")
     ap.add_argument("--skip_e2e", action="store_true")
+    ap.add_argument("--ref_schedule", default="zero2", choices=["zero2", "layer_major", "no_overlap", "two_stage_sync", "flashflex"],
+                    help="--impl reference only: which of the reference's schedules runs (its flag --zero2_pipeline etc.)")
     ap.add_argument("--stall_timeout", type=float, default=420.0,
                     help="abort (non-zero exit) if no training step completes on the host for this many seconds")
     args = ap.parse_args()
@@ -188,6 +192,14 @@ def main():
                                   "error": f"schedule {schedule} would deadlock on this plan: {stuck}"}), flush=True)
             return 5
     recompute = None if args.recompute == "auto" else (args.recompute == "on")
+    # the planner's prediction for exactly this plan and schedule, made before anything is timed
+    predicted = None
+    try:
+        from zorse_b200.planner.predict import predict_step_ms
+
+        predicted = predict_step_ms(cfg_dict, schedule, recompute=recompute, defer_wgrad=args.defer_wgrad)
+    except Exception as e:      # noqa: BLE001 - a missing profile table must not stop the measurement
+        sys.stderr.write(f"[bench] no planner prediction: {e!r}\n")
     tr = Trainer(cfg, TrainerOptions(schedule=schedule, ops="sm100", optimizer_in_backward=args.optimizer_in_backward,
                                      collectives=args.collectives, activation_recompute=recompute,
                                      defer_wgrad=args.defer_wgrad,
@@ -302,6 +314,9 @@ def main():
                        "l2": "per-step working set (>100 GB of parameters, optimizer state and activations) far exceeds the 126 MB L2; no flush needed"},
             "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches, "loss": loss_val,
             "exposed_comm_ms_per_step": exposed_ms,
+            "planner_predicted_ms": None if predicted is None else predicted["ms"],
+            "measured_over_predicted": None if predicted is None else ms_per_step / predicted["ms"],
+            "planner_terms": None if predicted is None else {k: v for k, v in predicted.items() if k != "ms"},
             "max_memory_allocated_gb_rank0": mem,
         }
         print(json.dumps(out))

@@ -116,10 +116,11 @@ rs_adam_kernel(const RsAdamParams p) {
     s_ok = ok ? 1 : 0;
   }
   __syncthreads();
-  if (!s_ok) return;
+  // A block whose wait ran out (the status word says so) skips the arithmetic but still takes part
+  // in the block count below, so that the counter is back at zero for the unit's next launch.
+  const long nvec = s_ok ? p.shard_n / N : 0;
 
   // 2. reduce + Adam over this rank's slice
-  const long nvec = p.shard_n / N;
   const long lo = long(p.r) * p.shard_n;
   for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < nvec; i += long(gridDim.x) * blockDim.x) {
     float g[N];
@@ -203,7 +204,7 @@ rs_adam_kernel(const RsAdamParams p) {
   if (threadIdx.x == 0) s_last = (atomicAdd(p.counter, 1u) == gridDim.x - 1) ? 1u : 0u;
   __syncthreads();
   if (s_last) {
-    if (threadIdx.x < p.R) {
+    if (s_ok && threadIdx.x < p.R) {
       st_release_sys(p.flags[threadIdx.x] + 1 * p.R + p.r, p.epoch);
       st_release_sys(p.flags[threadIdx.x] + 2 * p.R + p.r, p.epoch);
     }

@@ -253,3 +253,13 @@ def test_recover_replans_for_the_gpus_that_are_left(tmp_path):
     assert cfg.vocab_size == 512 and cfg.autocast_dtype == "float32"
     b = run_workers(1, _resume_cli_like, new, os.path.join(ck, "step_2"))
     assert abs(a[0] - b[0]) < 1e-4, (a, b)
+
+
+def test_fault_injection_is_refused_where_a_leaving_rank_would_fault_its_peers():
+    from zorse_b200.utils.health import injection_refusal
+
+    assert injection_refusal(False, "fused", env={}) is None                       # CPU ranks: always allowed
+    assert "NCCL_NVLS_ENABLE" in injection_refusal(True, "library", env={})
+    assert "collectives" in injection_refusal(True, "fused", env={"NCCL_NVLS_ENABLE": "0"})
+    assert "multimem" in injection_refusal(True, "library", env={"NCCL_NVLS_ENABLE": "0", "ZORSE_RS_ADAM_VARIANT": "3"})
+    assert injection_refusal(True, "library", env={"NCCL_NVLS_ENABLE": "0"}) is None

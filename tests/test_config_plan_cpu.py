@@ -286,3 +286,37 @@ def test_planner_with_tensor_parallel_lanes():
         coarsen(dict(data, gpu_list=mixed), 2)
     with pytest.raises(ValueError):
         coarsen(data, 3)
+
+
+def test_leftover_layers_follow_the_reference_rule():
+    # speeds 0.5 / 0.3 / 0.2 of 32 layers: exact 16 / 9.6 / 6.4, two layers left over
+    t = [1 / 0.5, 1 / 0.3, 1 / 0.2]
+    assert distribute_layers(32, t) == [17, 9, 6]                       # largest share first (reference)
+    assert distribute_layers(32, t, rule="remainder") == [16, 10, 6]    # largest fractional remainder first
+
+
+def test_fixed_plan_prediction_has_the_1f1b_and_gpipe_shapes():
+    from zorse_b200.planner.predict import predict_step_ms
+
+    def cfg(P, layers=32, M=64, R=2):
+        per = layers // P
+        return {"model_name": "llama2_7b", "global_batch_size": M, "microbatch_size": 1, "sequence_length": 4096,
+                "vocab_size": 32000, "autocast_dtype": "bfloat16",
+                "pipeline_config": [{"gpu_ranks": list(range(R * i, R * i + R)), "layer_partition": [i * per, (i + 1) * per],
+                                     "num_microbatches_per_rank": [M // R] * R, "zero_config": [list(range(R * i, R * i + R))]}
+                                    for i in range(P)]}
+
+    table = {"llama2_7b": {"b200": {"4096": {"bfloat16": [[2.0, 0.0], [4.0, 0.0]]}}}}
+    one = predict_step_ms(cfg(1, R=1), "1f1b", table=table)
+    assert one["ramp_ms"] == 0 and abs(one["steady_ms"] - 64 * (32 * 6.0 + one["steady_ms"] / 64 - 32 * 6.0)) < 1e-6
+    four = predict_step_ms(cfg(4), "1f1b", table=table)
+    # ramps: the three stages that are not the bottleneck, one microbatch each; steady: 32 microbatches of the slowest
+    assert 3 * 8 * 6.0 <= four["ramp_ms"] <= 3 * 8 * 6.0 + 2.0
+    assert four["steady_ms"] >= 32 * 8 * 6.0
+    deferred = predict_step_ms(cfg(4), "1f1b", table=table, defer_wgrad=True)
+    assert deferred["ramp_ms"] < four["ramp_ms"] and deferred["steady_ms"] == four["steady_ms"]
+    gp = predict_step_ms(cfg(4), "zero2", table=table)
+    assert gp["recompute"] and gp["form"] == "gpipe" and gp["steady_ms"] > four["steady_ms"] * 1.25
+    # a measured chain overhead scales the block times
+    table["_chain_overhead"] = {"llama2_7b": {"b200": 1.1}}
+    assert abs(predict_step_ms(cfg(4), "1f1b", table=table)["block_fwd_ms"] - 2.2) < 1e-9

@@ -57,6 +57,12 @@ def main(argv=None) -> int:
             log.warning(f"p2p replay skipped: {e!r}")
         if stuck is not None:
             raise SystemExit(f"schedule {name} would deadlock on this plan: {stuck} (try --gloo_p2p, --sync_comm or another schedule)")
+    if args.inject_fault:
+        from ..utils.health import injection_refusal
+
+        refusal = injection_refusal(torch.cuda.is_available() and args.backend != "gloo", opt.collectives)
+        if refusal:
+            raise SystemExit(refusal)
     tr = Trainer(cfg, opt)
     log.info(f"rank {tr.rank}/{tr.world} on {tr.device}; schedule {tr.schedule.name}; ops {tr.ops.name}; "
              f"stages {[s.stage_id for s in tr.stages]}", leader_only=False)

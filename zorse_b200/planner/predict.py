@@ -1,0 +1,108 @@
+"""Predicted iteration time of a GIVEN training config (stages, ranks, layer ranges, microbatch
+counts) under a named schedule — what the trainer and `bench.py` print next to the measured time.
+
+The stage-2 optimizer's `pipeline_latency` models the reference's schedules: every stage runs all
+its forwards, then all its backwards (reference zorse_optimizer/optimizer.py:215-505).  The true
+1F1B schedules of this repository have another shape, so this module adds their closed form:
+
+    per stage s:  F_s = n_s * f + [last] head_f + [first] emb_f        (one microbatch, forward)
+                  B_s = n_s * b + [last] head_b + [first] emb_b  (+ F_s when layers are recomputed)
+    1F1B:         T = (m - 1) * max_s (F_s + B_s) + sum_s (F_s + B_s) + 2 (P - 1) * p2p
+    deferred weight gradients shorten the ramps by the weight-gradient time W_s of every stage that
+    is not the bottleneck; v-way interleaving divides the ramps by v.
+
+On top: the all-gather of the first layer (nothing to hide it behind), the reduce-scatter of the
+layer that finishes last, and the optimizer pass over each rank's shard (HBM-bound, 28 bytes per
+parameter: fp32 master + two moments read and written, bf16 copy written).
+
+Block times come from the layer-profile table (`data/model_latencies.json`, one block timed in a
+loop); `chain_overhead` (the ratio of a chain of consecutive blocks to the same number of single
+blocks, stored by the layer profiler under `_chain_overhead`) scales them when it was measured.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+from ..models import registry
+from . import comm_model
+from .latency import head_and_embedding_ms, load_model_compute_latencies_per_gpu, load_table
+
+GPIPE_SHAPED = ("layer_major", "default", "no_overlap", "two_stage_sync", "zero2", "flashflex", "gpipe")
+WGRAD_SHARE_OF_FORWARD = 0.75      # weight-gradient GEMMs ~ the forward GEMMs; the rest of a forward block is attention
+
+
+def chain_overhead(table: dict, model: str, gpu: str) -> float:
+    try:
+        return float(table["_chain_overhead"][model][gpu])
+    except (KeyError, TypeError, ValueError):
+        return 1.0
+
+
+def predict_step_ms(cfg: dict, schedule: str, *, recompute: Optional[bool] = None, gpu: str = "b200",
+                    table: Optional[dict] = None, defer_wgrad: bool = False, optimizer_gbs: float = 6000.0,
+                    p2p_gbs: float = 700.0, p2p_latency_ms: float = 0.02, collective_gbs: float = 600.0,
+                    collective_latency_ms: float = 0.03) -> dict:
+    """`cfg` is a training_config dict.  Returns {"ms": total, ...terms}."""
+    table = load_table() if table is None else table
+    model = cfg["model_name"]
+    seq, mbs, vocab = int(cfg["sequence_length"]), int(cfg["microbatch_size"]), int(cfg.get("vocab_size", 32000))
+    dtype = cfg.get("autocast_dtype", "bfloat16")
+    stats = registry.get_model_stats(model, vocab=vocab)
+    lat = load_model_compute_latencies_per_gpu(model, [gpu], seq, dtype, mbs, table)[gpu]
+    oh = chain_overhead(table, model, gpu)
+    f, b = lat.forward * oh, lat.backward * oh
+    (hf, hb), (ef, eb) = head_and_embedding_ms(model, gpu, seq, mbs, vocab)
+    sched = (schedule or "layer_major").lower()
+    gpipe = sched in GPIPE_SHAPED
+    if recompute is None:
+        recompute = gpipe
+    stages = sorted(cfg["pipeline_config"], key=lambda s: s["layer_partition"][0])
+    # interleaved plans list v chunks per rank group: fold them into one entry per group for the stage sums
+    groups: dict = {}
+    for i, s in enumerate(stages):
+        key = tuple(s["gpu_ranks"])
+        g = groups.setdefault(key, {"n": 0, "first": False, "last": False, "m": max(s["num_microbatches_per_rank"]),
+                                    "R": len(s["gpu_ranks"]), "chunks": 0})
+        g["n"] += s["layer_partition"][1] - s["layer_partition"][0]
+        g["first"] |= i == 0
+        g["last"] |= i == len(stages) - 1
+        g["chunks"] += 1
+    G = list(groups.values())
+    v = max(g["chunks"] for g in G)
+    P = len(G)
+    bytes_per = comm_model.DTYPE_BYTES.get(dtype, 2)
+    p2p = p2p_latency_ms + mbs * seq * stats["hidden_size"] * bytes_per / (p2p_gbs * 1e9) * 1e3
+    layer_bytes = stats["parameters_per_layer"] * bytes_per
+
+    def coll(R):
+        return 0.0 if R <= 1 else collective_latency_ms + layer_bytes * (R - 1) / R / (collective_gbs * 1e9) * 1e3
+
+    T, W = [], []
+    for g in G:
+        F = g["n"] * f + (hf if g["last"] else 0.0) + (ef if g["first"] else 0.0)
+        B = g["n"] * b + (hb if g["last"] else 0.0) + (eb if g["first"] else 0.0) + (F if recompute else 0.0)
+        T.append(F + B)
+        W.append(g["n"] * f * WGRAD_SHARE_OF_FORWARD)
+    m = max(g["m"] for g in G)
+    k = max(range(P), key=lambda i: T[i] * G[i]["m"])
+    if gpipe:
+        # all forwards, then all backwards: the ramps are the other stages' single-microbatch passes too
+        ramp = sum(T[i] for i in range(P) if i != k)
+    else:
+        ramp = sum(T[i] - (W[i] if defer_wgrad else 0.0) for i in range(P) if i != k) / v
+    steady = G[k]["m"] * T[k]
+    opt = max(g["n"] * stats["parameters_per_layer"] / g["R"] for g in G) * 28 / (optimizer_gbs * 1e9) * 1e3
+    if G[0]["first"]:
+        opt_emb = stats["total_parameters"] - stats["num_layers"] * stats["parameters_per_layer"]
+        opt += opt_emb / max(G[0]["R"], 1) * 28 / (optimizer_gbs * 1e9) * 1e3 * (0.5 if P > 1 else 1.0)
+    zero = max(coll(g["R"]) for g in G) * 2.0          # first gather + last reduction are exposed
+    if gpipe and any(g["R"] > 1 for g in G):
+        # layer-major / ZeRO-2 pipeline shapes re-gather in backward; the gathers overlap unless they are longer
+        # than the compute they hide behind
+        per_layer_compute = min(gg["m"] for gg in G) * f
+        zero += max(0.0, max(coll(g["R"]) for g in G) - per_layer_compute) * max(g["n"] for g in G)
+    comm = 2.0 * (P - 1) * p2p * (v if not gpipe else 1)
+    total = steady + ramp + opt + zero + comm
+    return {"ms": total, "steady_ms": steady, "ramp_ms": ramp, "optimizer_ms": opt, "zero_exposed_ms": zero,
+            "p2p_ms": comm, "block_fwd_ms": f, "block_bwd_ms": b, "chain_overhead": oh, "recompute": bool(recompute),
+            "form": "gpipe" if gpipe else "1f1b"}

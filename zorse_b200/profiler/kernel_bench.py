@@ -6,8 +6,8 @@ shapes of the benchmark configurations.
 
 Timing: CUDA events on the launching stream, `--warmup` untimed runs, then `--iters` timed
 runs with a write larger than L2 between runs so no operand is served from cache; the
-figure reported is the median.  Roofline fractions use the measured peaks in
-MEASURED_PEAKS.json when that file exists next to the repository root.
+figure reported is the median.  Roofline fractions use the peaks given with `--peaks FILE`
+(or `--peak_hbm_gbs` / `--peak_bf16_tflops`), else B200 fallback figures.
 """
 from __future__ import annotations
 
@@ -22,11 +22,14 @@ import torch
 ROOT = Path(__file__).resolve().parents[2]
 
 
-def _peaks():
-    f = ROOT / "MEASURED_PEAKS.json"
-    if f.exists():
-        d = json.loads(f.read_text())
-        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+def _peaks(path=None, hbm_gbs=None, bf16_tflops=None):
+    """Roofline denominators: from `--peaks FILE` (JSON with `hbm_gbs` and `bf16_tflops`, e.g. a copy-bandwidth
+    and library-GEMM measurement taken on the same machine), from the two flags, or B200 fallback figures."""
+    if path:
+        d = json.loads(Path(path).read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    if hbm_gbs and bf16_tflops:
+        return {"hbm_gbs": float(hbm_gbs), "bf16_tflops": float(bf16_tflops), "source": "flags"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -204,11 +207,14 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=None)
     ap.add_argument("--only", default="gemm,attn,elementwise")
+    ap.add_argument("--peaks", default=None, help="JSON file with measured hbm_gbs and bf16_tflops of this machine")
+    ap.add_argument("--peak_hbm_gbs", type=float, default=None)
+    ap.add_argument("--peak_bf16_tflops", type=float, default=None)
     a = ap.parse_args(argv)
     from zorse_b200.ops import sm100 as k
 
     k.lib()
-    peaks = _peaks()
+    peaks = _peaks(a.peaks, a.peak_hbm_gbs, a.peak_bf16_tflops)
     rows: list[dict] = []
     only = a.only.split(",")
     if "gemm" in only:

@@ -128,6 +128,31 @@ def parse_fault(spec: Optional[str]):
     return int(r), int(s), kind
 
 
+def injection_refusal(on_cuda: bool, collectives: str, env=None) -> Optional[str]:
+    """Why host-side fault injection must not run with this set-up, or None if it may.
+
+    A rank that leaves the job while its device memory is bound to an NVLink multicast object
+    raises NVLink faults on the GPUs of the ranks that stay.  Memory gets bound that way by NCCL's
+    NVLS algorithms (on by default on NVSwitch systems) and by the symmetric-memory buffers of the
+    fused collectives (`multimem` variants of the fused reduce-scatter + Adam).  So on CUDA devices
+    injection is only allowed when NCCL_NVLS_ENABLE=0 was set before start-up, the collectives are
+    the library ones, and no multimem kernel variant is selected.  CPU (gloo) ranks are unaffected."""
+    if not on_cuda:
+        return None
+    env = os.environ if env is None else env
+    why = []
+    if env.get("NCCL_NVLS_ENABLE", "") != "0":
+        why.append("NCCL_NVLS_ENABLE=0 is not set in the environment")
+    if collectives != "library":
+        why.append(f"--collectives {collectives} binds symmetric memory that peers map (use --collectives library)")
+    if env.get("ZORSE_RS_ADAM_VARIANT", "0") in ("2", "3"):
+        why.append("ZORSE_RS_ADAM_VARIANT selects a multimem kernel")
+    if not why:
+        return None
+    return ("--inject_fault is refused on CUDA devices: a rank that dies while its memory is bound to an NVLink "
+            "multicast object faults its peers' GPUs; " + "; ".join(why))
+
+
 def maybe_inject(fault, rank: int, step: int, keepalive: Optional[Callable[[int], None]] = None) -> None:
     """Called between steps, with none of this rank's kernels or collectives in flight.
     `keepalive` (the local watchdog's beat) is called while a stalled rank sleeps, so that the

@@ -9,8 +9,6 @@ B200 (nominal dense 2250 TFLOP/s bf16/fp16); iteration time is the max over rank
 """
 from __future__ import annotations
 
-import json
-from pathlib import Path
 from typing import Optional
 
 import torch
@@ -35,16 +33,6 @@ def clean_gpu_name(name: str) -> str:
     if "h100" in n:
         return "h100-nvl" if "nvl" in n else "h100"
     return n.replace("nvidia", "").strip().split(" ")[-1].split("-")[0] if n else "cpu"
-
-
-def measured_peak_tflops() -> Optional[float]:
-    f = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
-    if f.exists():
-        try:
-            return float(json.loads(f.read_text())["bf16_tflops_sustained"])
-        except (OSError, ValueError, KeyError, TypeError):
-            return None
-    return None
 
 
 def compute_model_flops(total_params: int, num_layers: int, hidden: int, seq: int, global_batch: int,
