@@ -320,3 +320,32 @@ def test_fixed_plan_prediction_has_the_1f1b_and_gpipe_shapes():
     # a measured chain overhead scales the block times
     table["_chain_overhead"] = {"llama2_7b": {"b200": 1.1}}
     assert abs(predict_step_ms(cfg(4), "1f1b", table=table)["block_fwd_ms"] - 2.2) < 1e-9
+
+
+def test_drawings_of_the_gpu_graph_and_its_partition(tmp_path):
+    import networkx as nx
+
+    from zorse_b200.planner import visualize as V
+
+    G = nx.Graph()
+    for i in range(4):
+        G.add_node(i, name="NVIDIA B200", machine=f"host{i // 2}", memory_total_mib=183359)
+    for a, b, w in [(0, 1, 900.0), (2, 3, 900.0), (0, 2, 50.0), (1, 3, 50.0)]:
+        G.add_edge(a, b, weight=w)
+    parts = {0: 0, 1: 0, 2: 1, 3: 1}
+    m = V.partition_metrics(G, parts)
+    assert m["cut_weight"] == 100.0 and m["internal_weight"] == 1800.0 and m["balance"] == 1.0
+    assert m["partition_sizes"] == {0: 2, 1: 2} and abs(m["ratio_cut_to_total"] - 100 / 1900) < 1e-12
+    sc = V.scene_partitioned(G, parts)
+    assert sorted(e["dashed"] for e in sc.edges) == [False, False, True, True]
+    assert {n["color"] for n in sc.nodes if parts[n["id"]] == 0} != {n["color"] for n in sc.nodes if parts[n["id"]] == 1}
+    assert all(0.0 <= n["x"] <= 1.0 and 0.0 <= n["y"] <= 1.0 for n in sc.nodes)
+    sm = V.scene_with_metrics(G, parts)
+    assert any("Cut value: 100.00" in ln for ln in sm.side_text) and any("P1: 2 nodes" in ln for ln in sm.side_text)
+    g = V.scene_graph(G)
+    assert len(g.legend) == 2 and g.nodes[0]["label"].startswith("B200\n179.1GB")
+    out = V.visualize_partitions_with_metrics(G, parts, output_file=str(tmp_path / "p.svg"))
+    txt = open(out).read()
+    assert txt.startswith("<svg") and "stroke-dasharray" in txt and "Balance: 1.00" in txt
+    assert V.visualize_partition(G, parts, str(tmp_path / "plan.svg"))
+    assert (tmp_path / "plan_graph.svg").exists() and (tmp_path / "plan_partitioned.svg").exists()

@@ -138,6 +138,28 @@ def test_trace_postprocessing(tmp_path):
     assert s[7]["busy_ms"] == pytest.approx(0.15) and s[7]["gap_ms"] == pytest.approx(0.05) and s[9]["kernels"] == 1
 
 
+def test_trace_streams_are_classified_and_gaps_charged_to_the_other_kind(tmp_path):
+    from zorse_b200.utils.trace import classify_streams, stream_overheads
+
+    k = lambda name, ts, dur, s, cat="kernel": {"cat": cat, "name": name, "ts": ts, "dur": dur, "args": {"stream": s}}
+    ev = [k("zb::gemm2_bf16_kernel", 0, 100, 7), k("zb::gemm2_bf16_kernel", 300, 100, 7),       # compute gap 100..300
+          k("ncclDevKernel_AllGather", 150, 100, 20), k("ncclDevKernel_SendRecv", 180, 40, 21),  # two comm streams overlap
+          k("Memcpy HtoD (Pinned -> Device)", 260, 30, 30, "gpu_memcpy"),
+          {"cat": "cuda_runtime", "name": "cudaMalloc", "ts": 110, "dur": 20},
+          k("zb::rs_adam_kernel<bf16>", 500, 50, 20)]
+    kinds = classify_streams(ev)
+    assert kinds == {7: "compute", 20: "communication", 21: "communication", 30: "copy"}
+    f = tmp_path / "t.json"
+    f.write_text(json.dumps({"traceEvents": ev}))
+    o = stream_overheads(str(f))
+    assert o["compute_gap_ms"] == pytest.approx(0.2)
+    assert o["communication_overhead_for_compute"] == pytest.approx(0.1)     # union of the two streams, not 0.14
+    assert o["copy_overhead_for_compute"] == pytest.approx(0.03)
+    assert o["alloc_overhead_for_compute"] == pytest.approx(0.02)
+    assert o["compute_overhead_for_communication"] == pytest.approx(0.1)     # gap 250..500 holds the second GEMM
+    assert o["compute_ms"] == pytest.approx(0.4)                             # the 200 us gap counts as busy (< 500 us)
+
+
 def test_attn_trace_decode_and_phase_stats():
     from zorse_b200.profiler.attn_trace import decode, format_summary, phase_stats, summarize
 

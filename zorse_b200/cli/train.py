@@ -176,11 +176,36 @@ def main(argv=None) -> int:
     flops = metrics.compute_model_flops(registry.total_params(spec, cfg.sequence_length), spec.layers, spec.hidden,
                                         cfg.sequence_length, cfg.global_batch_size, recompute=tr.schedule.recompute)
     gl = tr.global_loss(loss)
+    predicted = cfg.latency
+    if predicted is None and cuda:
+        try:
+            from ..config.training_config import to_dict
+            from ..planner.predict import predict_step_ms
+
+            predicted = predict_step_ms(to_dict(cfg), tr.schedule.name, recompute=tr.schedule.recompute, gpu=gpu,
+                                        defer_wgrad=opt.defer_wgrad)["ms"]
+        except Exception:      # noqa: BLE001 - no profile table for this model / GPU: print no prediction
+            predicted = None
     if tr.rank == 0:
         print(metrics.format_summary(global_batch=cfg.global_batch_size, seq=cfg.sequence_length, step_ms=step_ms,
                                      flops_per_step=flops, gpu_names=names, dtype=cfg.autocast_dtype,
-                                     max_alloc_gb=[float(o[1]) for o in outs], predicted_ms=cfg.latency, loss=gl,
+                                     max_alloc_gb=[float(o[1]) for o in outs], predicted_ms=predicted, loss=gl,
                                      flashflex_ga=args.flashflex_ga))
+    if args.trace_dir and not args.skip_profile and args.profiling_iterations > 0:
+        # stream-classified trace figures of this rank's profiled iterations (reference utils/train_utils.py:104-221,
+        # printed from print_metrics when analyze_trace is set)
+        from ..utils.trace import newest_trace, stream_overheads
+        import os as _os
+
+        tf = newest_trace(_os.path.join(_os.path.expanduser(args.trace_dir), args.experiment_name, f"GPU_{tr.rank}"))
+        if tf:
+            try:
+                o = stream_overheads(tf, gap_threshold_us=args.gap_threshold)
+                it = max(args.profiling_iterations, 1)
+                log.info("trace: " + ", ".join(f"{k}={v / it:.2f}" for k, v in o.items() if isinstance(v, float))
+                         + f" (ms per profiled iteration; streams {o['streams']})", leader_only=False)
+            except (OSError, ValueError, KeyError) as e:
+                log.warning(f"trace analysis skipped: {e!r}")
     if checker is not None:
         log.info(checker.report(), leader_only=False)
     if watchdog:
