@@ -14,10 +14,13 @@ def main(argv=None):
     ap.add_argument("--reduce_dtype", default="float32")
     ap.add_argument("--model_name", required=True)
     ap.add_argument("--output", default=None, help="latency table to update (default data/model_latencies.json)")
+    ap.add_argument("--chain_blocks", type=int, default=4,
+                    help="also time this many consecutive blocks against single-block runs and store the ratio (0: skip)")
     a = ap.parse_args(argv)
     from zorse_b200.profiler.layer import profile_and_store
 
-    res = profile_and_store(a.model_name, a.seq_length, a.autocast_dtype, a.profile_batches, a.output)
+    res = profile_and_store(a.model_name, a.seq_length, a.autocast_dtype, a.profile_batches, a.output,
+                            chain_blocks=a.chain_blocks)
     print(json.dumps({"model": a.model_name, "seq": a.seq_length, **res}))
 
 

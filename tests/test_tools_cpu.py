@@ -300,3 +300,25 @@ def test_package_exports_load_lazily():
     import pytest
     with pytest.raises(AttributeError):
         zorse_b200.no_such_name
+
+
+def test_layer_profile_stores_activation_bytes_and_chain_overhead(tmp_path):
+    from zorse_b200.planner import latency as L
+    from zorse_b200.planner.memory import estimate_memory_usage, group_memory_bytes
+    import torch
+
+    from zorse_b200.profiler.layer import profile_chain
+
+    t: dict = {}
+    L.store_activation_bytes(t, "m", "b200", 128, "bfloat16", [100, 180, 260, 350])
+    assert L.activation_bytes(t, "m", "b200", 128, "bfloat16", 2) == 180
+    assert L.activation_bytes(t, "m", "b200", 128, "bfloat16", 6) == 350 + 2 * 80      # median increase per sequence
+    assert L.activation_bytes(t, "m", "a100", 128, "bfloat16", 1) is None
+    closed = group_memory_bytes([4], 2, 1000, 1, 128, 64)
+    measured = group_memory_bytes([4], 2, 1000, 1, 128, 64, block_activation_bytes=10 * 128 * 64 * 2)
+    assert measured - closed == (10 - 2) * 128 * 64 * 2
+    e = estimate_memory_usage(10**9, 8, 64, 128, 2, num_shards=4, block_activation_bytes=2**30)
+    assert e["training_state_gib"] == pytest.approx(16e9 / 4 / 2**30) and e["activation_gib"] == pytest.approx(1.0)
+    assert estimate_memory_usage(10**9, 8, 64, 128, 2, block_activation_bytes=2**30, recompute=False)["activation_gib"] == 8.0
+    ch = profile_chain("tiny_llama", 64, torch.float32, blocks=2, iters=2, warmup=1, device=torch.device("cpu"))
+    assert ch["blocks"] == 2 and ch["chain_ms"] > 0 and 0.2 < ch["overhead"] < 5.0

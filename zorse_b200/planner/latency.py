@@ -95,3 +95,27 @@ def head_and_embedding_ms(model: str, gpu: str, seq: int, mbs: int, vocab: int, 
     ce = 2.0 * T * (vocab or spec.vocab) * 2 / hbm * 1e3
     emb = 2.0 * T * spec.hidden * 2 / hbm * 1e3
     return (gemm + 0.5 * ce, 2.0 * gemm + 0.5 * ce), (emb, 2.0 * emb)
+
+
+def store_activation_bytes(table: dict, model: str, gpu: str, seq: int, dtype: str, act_bytes: list) -> None:
+    """Peak bytes one block allocates while running forward + backward at microbatch sizes 1..n (measured by
+    the layer profiler), kept beside the latencies under the `_activation_bytes` key."""
+    table.setdefault("_activation_bytes", {}).setdefault(model, {}).setdefault(gpu, {}).setdefault(str(seq), {})[dtype] = \
+        [int(x) for x in act_bytes]
+
+
+def activation_bytes(table: dict, model: str, gpu: str, seq: int, dtype: str, mbs: int) -> Optional[float]:
+    """Measured activation bytes of one block at microbatch size `mbs`: the measured value when the profile
+    reaches that size, otherwise the value at the largest profiled size plus the median increase per extra
+    sequence (reference utils/runtime_estimator.py:115-160 extrapolates with the same median increase)."""
+    try:
+        a = table["_activation_bytes"][model][gpu][str(seq)][dtype]
+    except (KeyError, TypeError):
+        return None
+    if not a:
+        return None
+    if mbs <= len(a):
+        return float(a[mbs - 1])
+    inc = sorted(y - x for x, y in zip(a, a[1:]))
+    step = inc[len(inc) // 2] if inc else float(a[0])
+    return float(a[-1] + step * (mbs - len(a)))

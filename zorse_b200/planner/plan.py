@@ -17,7 +17,7 @@ from ..models import registry
 from ..utils.metrics import clean_gpu_name
 from . import comm_model
 from .cluster import GPU, GPUGroup, ModelConfig, link_bandwidth, link_latency
-from .latency import head_and_embedding_ms, load_model_compute_latencies_per_gpu
+from .latency import head_and_embedding_ms, load_model_compute_latencies_per_gpu, load_table
 from .partition import build_gpu_graph, partition
 from .stage2 import PipelineOptimizer, PlanResult
 
@@ -104,9 +104,12 @@ def plan_partition(data: dict, pmap: dict, model_name: str, *, global_batch_size
             b.send_recv_latency_prev = t
         gpus = [x.identifier for g in groups for x in g.gpus]
         lat_tbl = load_model_compute_latencies_per_gpu(model_name, gpus, sequence_length, autocast_dtype, mbs, table)
-        # the layer profile times one block in a tight loop; a whole step also pays for launch gaps,
-        # allocator traffic and the small kernels between blocks (7.5 % on the B200 runs used to calibrate)
-        lat_tbl = {g: type(v)(v.forward * compute_overhead, v.backward * compute_overhead) for g, v in lat_tbl.items()}
+        # the layer profile times one block in a tight loop; a whole stage also pays for launch gaps and allocator
+        # traffic between blocks: the profiler measures that ratio on a chain of blocks (`_chain_overhead`)
+        full_table = table if table is not None else load_table()
+        lat_tbl = {g: type(v)(v.forward * _overhead(full_table, model_name, g, compute_overhead),
+                              v.backward * _overhead(full_table, model_name, g, compute_overhead))
+                   for g, v in lat_tbl.items()}
         if tp > 1:
             from .tensor_parallel import lane_collective_ms, lane_latencies
 
@@ -120,7 +123,8 @@ def plan_partition(data: dict, pmap: dict, model_name: str, *, global_batch_size
         res = PipelineOptimizer(groups, model, lat_tbl, mbs, dtype_multiplier=dtype_multiplier,
                                 optimizer_multiplier=optimizer_multiplier, reserved_memory_gb=reserved_memory_gb,
                                 recompute=recompute, optimizer_ms_per_layer=opt_ms, head_ms=head_ms,
-                                embedding_ms=emb_ms).optimize()
+                                embedding_ms=emb_ms, activation_table=table if table is not None else load_table(),
+                                dtype=autocast_dtype).optimize()
         if res is None:
             if best is not None:
                 break   # larger microbatches only need more memory
@@ -128,6 +132,15 @@ def plan_partition(data: dict, pmap: dict, model_name: str, *, global_batch_size
         if best is None or res.latency_ms < best.latency_ms:
             best = res
     return best
+
+
+def _overhead(table: dict, model: str, gpu: str, fallback: float) -> float:
+    """Whole-stage time over the sum of single-block times: the layer profiler's measured chain overhead for this
+    model and GPU when the table has one, else the caller's constant."""
+    try:
+        return float(table["_chain_overhead"][model][gpu])
+    except (KeyError, TypeError, ValueError):
+        return fallback
 
 
 def candidate_ks(data: dict) -> list[int]:

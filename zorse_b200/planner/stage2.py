@@ -69,7 +69,8 @@ class PipelineOptimizer:
     def __init__(self, groups: list[GPUGroup], model: ModelConfig, latencies: dict[str, ModelLatencies], microbatch_size: int,
                  *, dtype_multiplier: float = 2.0, optimizer_multiplier: float = 12.0, reserved_memory_gb: float = 2.0,
                  recompute: bool = True, optimizer_ms_per_layer: float = 0.0, max_interleave: Optional[int] = None,
-                 head_ms: tuple = (0.0, 0.0), embedding_ms: tuple = (0.0, 0.0)):
+                 head_ms: tuple = (0.0, 0.0), embedding_ms: tuple = (0.0, 0.0),
+                 activation_table: Optional[dict] = None, dtype: str = "bfloat16"):
         self.groups = list(groups)
         self.model = model
         self.lat = latencies
@@ -83,6 +84,8 @@ class PipelineOptimizer:
         # projection + loss) on the last stage and of the embedding on the first one; the
         # reference's model treats the network as L identical blocks and leaves both out
         self.head_ms = head_ms
+        # profile table with measured activation bytes per block (memory model); None: closed formula
+        self.act_table, self.dtype = activation_table, dtype
         self.embedding_ms = embedding_ms
 
     # ---- work split ------------------------------------------------------------------
@@ -175,7 +178,8 @@ class PipelineOptimizer:
     def optimize(self) -> Optional[PlanResult]:
         stages, _ = self.generate_stage_configs()
         groups = {g.group_id: g for g in self.groups}
-        ok, mem = validate_memory(stages, groups, self.model, self.mbs, self.dm, self.om, self.reserved)
+        ok, mem = validate_memory(stages, groups, self.model, self.mbs, self.dm, self.om, self.reserved,
+                                   table=self.act_table, dtype=self.dtype)
         if not ok:
             return None
         best = None
@@ -188,7 +192,8 @@ class PipelineOptimizer:
             st = self.interleave(stages, d)
             if st is None:
                 continue
-            ok, mem_d = validate_memory(st, groups, self.model, self.mbs, self.dm, self.om, self.reserved)
+            ok, mem_d = validate_memory(st, groups, self.model, self.mbs, self.dm, self.om, self.reserved,
+                                         table=self.act_table, dtype=self.dtype)
             if not ok:
                 continue
             lat, br = self.pipeline_latency(st)

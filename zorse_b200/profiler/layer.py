@@ -81,6 +81,51 @@ def profile_block(model_name: str, seq: int, dtype: torch.dtype, batches: int = 
     return {"forward_ms": fwd, "backward_ms": bwd, "activation_bytes": act}
 
 
+def profile_chain(model_name: str, seq: int, dtype: torch.dtype, blocks: int = 4, iters: int = 8, warmup: int = 2,
+                  device: Optional[torch.device] = None, ops_name: Optional[str] = None, **overrides) -> dict:
+    """Times `blocks` consecutive blocks (all forwards, then all backwards, microbatch size 1) against the same
+    number of single-block runs: {'chain_ms', 'single_ms', 'overhead'}.  The ratio is what a stage of several
+    layers costs beyond the sum of its blocks timed alone (launch gaps, allocator traffic, cold caches between
+    different weights); the planner multiplies its block latencies by it."""
+    device = device or torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    cuda = device.type == "cuda"
+    ops = get_ops(ops_name or default_ops_for(device))
+    spec = registry.get_spec(model_name, **overrides)
+    blks = []
+    for i in range(blocks):
+        blk = registry.make_block(spec)
+        _, n = blk.layout()
+        flat = torch.empty(n, dtype=torch.float32, device=device)
+        blk.init_flat(flat, i + 1)
+        blk.bind(flat.to(dtype), torch.zeros(n, dtype=torch.float32, device=device))
+        blks.append(blk)
+    x = (torch.randn(seq, spec.hidden, device=device) * 0.5).to(dtype)
+    dy = (torch.randn(seq, spec.hidden, device=device) * 0.5).to(dtype)
+    ctx = {"B": 1, "S": seq}
+
+    def chain():
+        saved, h = [], x
+        for blk in blks:
+            sv: dict = {}
+            h = blk.forward(h, ctx, ops, sv)
+            saved.append(sv)
+        g = dy
+        for blk, sv in zip(reversed(blks), reversed(saved)):
+            g = blk.backward(g, ctx, ops, sv)
+
+    def single():
+        for _ in range(blocks):
+            sv: dict = {}
+            blks[0].forward(x, ctx, ops, sv)
+            blks[0].backward(dy, ctx, ops, sv)
+
+    for _ in range(warmup):
+        chain()
+        single()
+    c, s = _time(chain, iters, cuda), _time(single, iters, cuda)
+    return {"chain_ms": c, "single_ms": s, "overhead": c / s if s > 0 else 1.0, "blocks": blocks}
+
+
 def profile_optimizer(n_params: int, shards=(1, 2, 4, 8), device=None, ops_name=None, iters: int = 10) -> dict:
     """Fused Adam time (ms) on a 1/shards slice of a unit (reference utils/runtime_estimator.py:256-279)."""
     device = device or torch.device("cuda" if torch.cuda.is_available() else "cpu")
@@ -98,7 +143,7 @@ def profile_optimizer(n_params: int, shards=(1, 2, 4, 8), device=None, ops_name=
 
 
 def profile_and_store(model_name: str, seq: int, dtype_name: str, batches: int = 4, path: Optional[str] = None,
-                      device=None, ops_name=None) -> dict:
+                      device=None, ops_name=None, chain_blocks: int = 0) -> dict:
     from ..config.training_config import dtype_from_str
 
     device = device or torch.device("cuda" if torch.cuda.is_available() else "cpu")
@@ -107,6 +152,13 @@ def profile_and_store(model_name: str, seq: int, dtype_name: str, batches: int =
     p = Path(path) if path else lat_tbl.latencies_path()
     table = lat_tbl.load_table(p)
     lat_tbl.store(table, model_name, gpu, seq, dtype_name, res["forward_ms"], res["backward_ms"])
+    if any(res["activation_bytes"]):
+        # peak bytes one block adds while it runs forward + backward, per microbatch size: read by the memory model
+        lat_tbl.store_activation_bytes(table, model_name, gpu, seq, dtype_name, res["activation_bytes"])
+    if chain_blocks > 1:
+        ch = profile_chain(model_name, seq, dtype_from_str(dtype_name), chain_blocks, device=device, ops_name=ops_name)
+        table.setdefault("_chain_overhead", {}).setdefault(model_name, {})[gpu] = round(ch["overhead"], 4)
+        res = {**res, "chain": ch}
     p.parent.mkdir(parents=True, exist_ok=True)
     p.write_text(json.dumps(table, indent=1))
     return {"gpu": gpu, **res}
