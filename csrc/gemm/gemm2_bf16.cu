@@ -104,13 +104,17 @@ struct Gemm2Extra {
 // SCATTER: the epilogue sends every output row to the staging slot of the rank that owns it in a
 // row-wise reduce-scatter (plain stores over NVLink, tile by tile while the main loop goes on) and
 // the last CTA raises the arrival flags; the owners add the slots up (csrc/comm/tp_rs.cu).
+// FUSED_AG (Params = GemmAgParams): four more warps per CTA pull the peers' parameter shards into the local
+// unsharded buffer while the tiles whose B rows are already present run; each CTA's producer waits for the
+// chunks that cover its own 128 rows of B.
 template <bool A_MN, bool B_MN, typename Params = GemmParams>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(std::is_same<Params, GemmAgParams>::value ? 320 : 192, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const Params p, const Gemm2Extra ex) {
   using Cfg = Gemm2Cfg;
   constexpr bool SCATTER = std::is_same<Params, GemmScatterParams>::value;
   constexpr bool ACCPF = std::is_same<Params, GemmAccPrefetchParams>::value;
+  constexpr bool FUSED_AG = std::is_same<Params, GemmAgParams>::value;
   constexpr int BK = Cfg::BK, STAGES = Cfg::STAGES, BN = Cfg::BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -164,6 +168,21 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         const int m0 = (tile % tiles_m) * Cfg::BM + int(cta) * 128;
         const int n0 = (tile / tiles_m) * BN + int(cta) * 128;
+        if constexpr (FUSED_AG) {
+          if (p.gate_flags != nullptr && n0 < p.N) {
+            // rows [n0, n0 + 128) of B inside the flat buffer: wait for every chunk of a peer's shard they touch
+            const long b0 = p.gate_base + long(n0) * p.gate_row_bytes;
+            const long b1 = p.gate_base + long(min(n0 + 128, p.N)) * p.gate_row_bytes - 1;
+            const long i0 = (b0 / p.gate_shard_bytes) * p.gate_cps + (b0 % p.gate_shard_bytes) / p.gate_chunk_bytes;
+            const long i1 = (b1 / p.gate_shard_bytes) * p.gate_cps + (b1 % p.gate_shard_bytes) / p.gate_chunk_bytes;
+            for (long c = i0; c <= i1 && ok; ++c) {
+              if (int(c / p.gate_cps) == p.gate_self) continue;
+              ok = flag_wait_ge(p.gate_flags + c, p.gate_epoch, ZB_WAIT_NS, p.status, ST_TIMEOUT_FLAG);
+            }
+            if (!ok) { *abort_flag = 1; break; }
+            asm volatile("fence.proxy.async.global;" ::: "memory");   // the gathered rows were written with plain stores
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, wctx, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
@@ -220,7 +239,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (ok) umma_commit_pair(&tmem_full[buf]);
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------ epilogue (own 128 rows) ------------------------------
     const int q = warp & 3;
     const EpilogueCfg ecfg = epilogue_cfg(p);
@@ -297,6 +316,52 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if constexpr (SCATTER) __threadfence_system();   // this thread's rows are visible to their owners before the flags
   }
 
+  if constexpr (FUSED_AG) if (warp >= 6) {
+    // ------------------------------ all-gather copy warps ------------------------------
+    const AgParams& ag = p.ag;
+    const int ct = threadIdx.x - 192;  // 0..127
+    __shared__ int s_peer_ok;
+    const int total = (ag.R - 1) * ag.cps;
+    const long chunk16 = ag.chunk_bytes / 16;
+    const long shard16 = ag.shard_bytes / 16;
+    int checked_peer = -1;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+      // ascending chunk order inside each peer, peers visited starting after this rank
+      const int c = w / (ag.R - 1);
+      const int pi = w % (ag.R - 1);
+      const int peer = (ag.r + 1 + pi) % ag.R;
+      if (peer != checked_peer) {
+        if (ct == 0)
+          s_peer_ok = flag_wait_ge(ag.version_flags + peer, ag.need_version, ZB_WAIT_NS, p.status, ST_TIMEOUT_FLAG) ? 1 : 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        ok = s_peer_ok != 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        checked_peer = peer;
+        if (!ok) break;
+      }
+      const long beg = long(c) * chunk16;
+      const long end = min(beg + chunk16, shard16);
+      const uint4* src = ag.src[peer];
+      uint4* dst = ag.dst + long(peer) * shard16;
+      long i = beg + ct;
+      for (; i + 7 * 128 < end; i += 8 * 128) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = ld_v4_relaxed_sys(src + i + u * 128);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) dst[i + u * 128] = v[u];
+      }
+      for (; i < end; i += 128) dst[i] = ld_v4_relaxed_sys(src + i);
+      // the rows go from these stores (generic proxy) to the TMA loads of some CTA's producer (async proxy)
+      __threadfence();
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ct == 0) st_release_sys(ag.chunk_flags + peer * ag.cps + c, ag.epoch);
+    }
+    if (!ok) *abort_flag = 1;
+  }
+
   // ------------------------------ teardown ------------------------------
   __syncwarp();
   if (*abort_flag) {
@@ -353,7 +418,7 @@ static int launch_gemm2(const void* A, const void* B, const Params& p, int lda, 
   int pairs = num_sms() / 2;
   if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   if (tiles < pairs) pairs = tiles;
-  kern<<<2 * pairs, 192, Cfg::SMEM_BYTES, stream>>>(ta, tb, p, ex);
+  kern<<<2 * pairs, std::is_same<Params, GemmAgParams>::value ? 320 : 192, Cfg::SMEM_BYTES, stream>>>(ta, tb, p, ex);
   ZB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -442,4 +507,49 @@ extern "C" int zb_gemm2_accpf_bf16(const void* A, const void* B, void* C, int M,
   if (!a_mn_major && b_mn_major) return launch_gemm2<false, true, GemmAccPrefetchParams>(A, B, p, lda, ldb, max_ctas, stream);
   if (a_mn_major && b_mn_major) return launch_gemm2<true, true, GemmAccPrefetchParams>(A, B, p, lda, ldb, max_ctas, stream);
   return launch_gemm2<true, false, GemmAccPrefetchParams>(A, B, p, lda, ldb, max_ctas, stream);
+}
+
+
+// All-gather fused with the GEMM that first consumes the gathered weights, on the 2-CTA core
+// (same contract as zb_ag_gemm_bf16 in gemm_bf16.cu): C[M,N] = A[M,K] * B[N,K]^T (+bias)(+addend),
+// B = a [N,K] weight inside the unit's flat unsharded buffer `full` at byte offset b_offset_bytes.
+extern "C" int zb_ag_gemm2_bf16(const void* A, void* full, long b_offset_bytes, void* C, int M, int N, int K, int lda,
+                                int ldc, const void* bias, const void* addend, int ld_addend, int flags,
+                                const void* const* shard_ptrs, int R, int r, long shard_bytes, int chunk_bytes,
+                                int* chunk_flags, int epoch, const int* version_flags, int need_version, int* status,
+                                cudaStream_t stream) {
+  using namespace zb;
+  if (M <= 0 || N <= 0 || K <= 0) ZB_FAIL(-1, "ag_gemm2: empty problem %d x %d x %d", M, N, K);
+  if (R < 2 || R > AG_MAX_R) ZB_FAIL(-1, "ag_gemm2: group size %d unsupported (2..%d)", R, AG_MAX_R);
+  if (shard_bytes % 16 || chunk_bytes % 2048 || chunk_bytes <= 0) ZB_FAIL(-1, "ag_gemm2: bad shard/chunk size");
+  if (b_offset_bytes % 16 || (long(K) * 2) % 16) ZB_FAIL(-1, "ag_gemm2: weight offset / row size not 16-byte aligned");
+  GemmAgParams p;
+  p.C = C;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.addend = static_cast<const __nv_bfloat16*>(addend);
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc; p.ld_addend = ld_addend;
+  p.flags = flags;
+  p.status = status;
+  AgParams& ag = p.ag;
+  for (int i = 0; i < AG_MAX_R; ++i) ag.src[i] = i < R ? static_cast<const uint4*>(shard_ptrs[i]) : nullptr;
+  ag.dst = static_cast<uint4*>(full);
+  ag.shard_bytes = shard_bytes;
+  ag.R = R; ag.r = r;
+  ag.chunk_bytes = chunk_bytes;
+  ag.cps = int((shard_bytes + chunk_bytes - 1) / chunk_bytes);
+  ag.chunk_flags = chunk_flags;
+  ag.epoch = epoch;
+  ag.version_flags = version_flags;
+  ag.need_version = need_version;
+  p.gate_flags = chunk_flags;
+  p.gate_epoch = epoch;
+  p.gate_base = b_offset_bytes;
+  p.gate_row_bytes = long(K) * 2;
+  p.gate_shard_bytes = shard_bytes;
+  p.gate_chunk_bytes = chunk_bytes;
+  p.gate_cps = ag.cps;
+  p.gate_self = r;
+  const void* B = static_cast<const char*>(full) + b_offset_bytes;
+  return launch_gemm2<false, false, GemmAgParams>(A, B, p, lda, K, 0, stream);
 }

@@ -21,22 +21,6 @@
 
 namespace zb {
 
-// All-gather half of the fused kernel: four extra warps per CTA pull the peers' shards of
-// the unit into the local unsharded buffer with plain 16-byte peer loads, chunk by chunk,
-// and publish a per-chunk flag that the TMA producers above wait for.
-constexpr int AG_MAX_R = 8;
-struct AgParams {
-  const uint4* src[AG_MAX_R];  // shard base of every rank of the group (peer-mapped)
-  uint4* dst;                  // local unsharded buffer
-  long shard_bytes;
-  int R, r;
-  int chunk_bytes, cps;        // chunk size and chunks per shard
-  int* chunk_flags;            // local, [R * cps]
-  int epoch;
-  const int* version_flags;    // local, [R]: peers publish the epoch of their bf16 shard here
-  int need_version;
-};
-
 template <int BN>
 struct GemmCfg {
   static constexpr int BM = 128;

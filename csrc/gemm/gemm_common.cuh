@@ -47,6 +47,28 @@ struct GemmScatterParams : GemmParams {
 };
 
 
+// All-gather half of a fused all-gather + GEMM kernel: extra warps of the GEMM pull the peers' shards of
+// the unit into the local unsharded buffer with plain 16-byte peer loads, chunk by chunk, and publish a
+// per-chunk flag that the TMA producers wait for (gate_* fields of GemmParams).
+constexpr int AG_MAX_R = 8;
+struct AgParams {
+  const uint4* src[AG_MAX_R];  // shard base of every rank of the group (peer-mapped)
+  uint4* dst;                  // local unsharded buffer
+  long shard_bytes;
+  int R, r;
+  int chunk_bytes, cps;        // chunk size and chunks per shard
+  int* chunk_flags;            // local, [R * cps]
+  int epoch;
+  const int* version_flags;    // local, [R]: peers publish the epoch of their bf16 shard here
+  int need_version;
+};
+
+// Selects the 2-CTA kernel with the four all-gather copy warps per CTA.
+struct GemmAgParams : GemmParams {
+  AgParams ag;
+};
+
+
 // Selects the kernels whose accumulate epilogue (C += result, bf16) reads the old C tile before the tile's
 // accumulators are ready, so that the read latency hides behind the main loop (weight gradients).
 struct GemmAccPrefetchParams : GemmParams {};

@@ -113,35 +113,41 @@ def fused_kernels(variant: int = 0):
         assert (m - rmm).abs().max().item() < 1e-2
         assert int(flags[2 * R:3 * R].min()) == 1, flags[: 3 * R]
         dist.barrier()
-    # all-gather fused GEMM
+    # all-gather fused GEMM: the 2-CTA core (default for M, N >= 256) and the 1-CTA kernel, weight at offset 0 and
+    # behind 4096 leading elements (norm weights in a real unit)
+    import os
+
     N, K, M = 1536, 512, 300
-    n = ((N * K + 64 * R - 1) // (64 * R)) * (64 * R)
-    sn = n // R
-    full = symm.empty(n, dtype=torch.bfloat16, device=dev)
-    vflags = symm.empty(64, dtype=torch.int32, device=dev)
-    full.zero_(); vflags.zero_()
-    gen = torch.Generator(device=dev).manual_seed(7)
-    w_all = (torch.randn(n, device=dev, generator=gen) * 0.05).to(torch.bfloat16)
-    full[rank * sn:(rank + 1) * sn].copy_(w_all[rank * sn:(rank + 1) * sn])
-    torch.cuda.synchronize()
-    hfull = symm.rendezvous(full, dist.group.WORLD)
-    symm.rendezvous(vflags, dist.group.WORLD)
-    dist.barrier()
-    a = (torch.randn(M, K, device=dev, generator=torch.Generator(device=dev).manual_seed(9))).to(torch.bfloat16)
-    out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-    chunk = 1 << 14
-    cps = (sn * 2 + chunk - 1) // chunk
-    cflags = torch.zeros(R * cps, dtype=torch.int32, device=dev)
-    k.ag_gemm(a, full, 0, (N, K), out, shard_ptrs=[int(hfull.buffer_ptrs[q]) + q * sn * 2 for q in range(R)], R=R,
-              r=rank, shard_elems=sn, chunk_bytes=chunk, chunk_flags=cflags, epoch=1, version_flags=vflags[2 * R:],
-              need_version=0)
-    torch.cuda.synchronize()
-    k.check_status()
-    assert torch.equal(full, w_all), "gathered parameters differ"
-    want = a.float() @ w_all[: N * K].view(N, K).float().t()
-    err = (out.float() - want).abs().max().item()
-    assert err < 0.05 * max(1.0, want.abs().max().item()), err
-    dist.barrier()
+    for kern, lead in (("2cta", 0), ("1cta", 0), ("2cta", 4096)):
+        os.environ["ZORSE_AG_GEMM"] = kern
+        n = ((lead + N * K + 64 * R - 1) // (64 * R)) * (64 * R)
+        sn = n // R
+        full = symm.empty(n, dtype=torch.bfloat16, device=dev)
+        vflags = symm.empty(64, dtype=torch.int32, device=dev)
+        full.zero_(); vflags.zero_()
+        gen = torch.Generator(device=dev).manual_seed(7)
+        w_all = (torch.randn(n, device=dev, generator=gen) * 0.05).to(torch.bfloat16)
+        full[rank * sn:(rank + 1) * sn].copy_(w_all[rank * sn:(rank + 1) * sn])
+        torch.cuda.synchronize()
+        hfull = symm.rendezvous(full, dist.group.WORLD)
+        symm.rendezvous(vflags, dist.group.WORLD)
+        dist.barrier()
+        a = (torch.randn(M, K, device=dev, generator=torch.Generator(device=dev).manual_seed(9))).to(torch.bfloat16)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        chunk = 1 << 14
+        cps = (sn * 2 + chunk - 1) // chunk
+        cflags = torch.zeros(R * cps, dtype=torch.int32, device=dev)
+        k.ag_gemm(a, full, lead, (N, K), out, shard_ptrs=[int(hfull.buffer_ptrs[q]) + q * sn * 2 for q in range(R)],
+                  R=R, r=rank, shard_elems=sn, chunk_bytes=chunk, chunk_flags=cflags, epoch=1,
+                  version_flags=vflags[2 * R:], need_version=0)
+        torch.cuda.synchronize()
+        k.check_status()
+        assert torch.equal(full, w_all), f"gathered parameters differ ({kern}, lead {lead})"
+        want = a.float() @ w_all[lead: lead + N * K].view(N, K).float().t()
+        err = (out.float() - want).abs().max().item()
+        assert err < 0.05 * max(1.0, want.abs().max().item()), (kern, lead, err)
+        dist.barrier()
+    os.environ.pop("ZORSE_AG_GEMM", None)
 
 
 def tp_kernels():

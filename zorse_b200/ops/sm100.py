@@ -387,7 +387,10 @@ def ag_gemm(a: torch.Tensor, full: torch.Tensor, w_offset: int, w_shape, out: to
     N, K = w_shape
     M = a.shape[0]
     assert out.shape == (M, N) and a.shape[1] == K and out.dtype == torch.bfloat16
-    rc = lib().zb_ag_gemm_bf16(_p(a), _p(full), c_long(w_offset * 2), _p(out), c_int(M), c_int(N), c_int(K),
+    # the 2-CTA core (256 x 256 tiles per CTA pair) when the problem has at least one such tile, like `gemm`
+    two_cta = GEMM_KERNEL == "2cta" and M >= 256 and N >= 256 and os.environ.get("ZORSE_AG_GEMM", "2cta") != "1cta"
+    fn = lib().zb_ag_gemm2_bf16 if two_cta else lib().zb_ag_gemm_bf16
+    rc = fn(_p(a), _p(full), c_long(w_offset * 2), _p(out), c_int(M), c_int(N), c_int(K),
                                c_int(a.stride(0)), c_int(out.stride(0)), _p(bias), _p(addend),
                                c_int(0 if addend is None else addend.stride(0)), c_int(0), _ptr_array(shard_ptrs),
                                c_int(R), c_int(r), c_long(shard_elems * 2), c_int(chunk_bytes), _p(chunk_flags),
