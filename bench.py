@@ -268,11 +268,15 @@ def main():
     # ---- exposed communication: one extra step with every compute-stream wait on comm bracketed ----
     tr.measure_exposed_comm(True)
     tr.train_step(inputs, targets)
-    exposed = torch.tensor([tr.exposed_comm_ms()], device=tr.device)
+    parts = tr.exposed_comm_breakdown()
+    exposed = torch.tensor([parts["zero"] + parts["pipeline"], parts["zero"], parts["pipeline"]], device=tr.device)
     tr.measure_exposed_comm(False)
     if world > 1:
         dist.all_reduce(exposed, op=dist.ReduceOp.MAX)
-    exposed_ms = float(exposed.item())
+    exposed_ms = float(exposed[0].item())
+    exposed_parts = {"zero_collectives_ms": float(exposed[1].item()), "pipeline_recv_wait_ms": float(exposed[2].item()),
+                     "note": "max over ranks; the pipeline part is the wait for the neighbouring stage's tensor "
+                             "(its compute = the pipeline bubble, plus the transfer)"}
     beat()
 
     # ---- end to end through the public API: H2D of the inputs + D2H of the loss every step ----
@@ -313,7 +317,7 @@ def main():
                        "reduce_dtype": args.reduce_dtype, "collectives": args.collectives, "defer_wgrad": args.defer_wgrad,
                        "l2": "per-step working set (>100 GB of parameters, optimizer state and activations) far exceeds the 126 MB L2; no flush needed"},
             "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches, "loss": loss_val,
-            "exposed_comm_ms_per_step": exposed_ms,
+            "exposed_comm_ms_per_step": exposed_ms, "exposed_comm_breakdown": exposed_parts,
             "planner_predicted_ms": None if predicted is None else predicted["ms"],
             "measured_over_predicted": None if predicted is None else ms_per_step / predicted["ms"],
             "planner_terms": None if predicted is None else {k: v for k, v in predicted.items() if k != "ms"},

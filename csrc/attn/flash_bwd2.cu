@@ -52,6 +52,10 @@ __device__ __forceinline__ void red_add_v4_f32(float* p, float a, float b, float
                : "memory");
 }
 
+__device__ __forceinline__ void red_add_f32(float* p, float a) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(a) : "memory");
+}
+
 template <int D, bool TRACE>
 __global__ void __launch_bounds__(32 * BWD2_WARPS, 1)
 flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -165,7 +169,8 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     if (lane == 0 && n_iters > 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, false, false);  // K-major A and B
       constexpr uint32_t idesc_dkv = umma_idesc_bf16(128, D, false, true);   // A from TMEM, B = [q rows][d] (N-major)
-      constexpr uint32_t idesc_dq = umma_idesc_bf16(128, D, true, true);     // A = dS^T tile (M-major), B = K (N-major)
+      // D = 128: A = K (M = head dim, M-major), B = dS^T tile (N = queries, N-major); D = 64: A = dS^T tile, B = K
+      constexpr uint32_t idesc_dq = umma_idesc_bf16(128, D == 128 ? 128 : D, true, true);
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), ds_addr = smem_u32(sDS);
       const uint32_t r_s = tmem_base, r_dp = tmem_base + Cfg::DP_COL;
       bool ok = mbar_wait(kv_full, 0, wctx, ST_TIMEOUT_FULL);
@@ -213,11 +218,19 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
                       (it | kk) != 0 ? 1u : 0u);
         }
         umma_commit(&qdo_empty[st]);
-        // F: dQ = dS K  (reduction over the 128 keys) into R_dP, right behind E which read dS^T from it
+        // F: dQ = dS K  (reduction over the 128 keys) into R_dP, right behind E which read dS^T from it.
+        // For D = 128 the product is formed transposed, dQ^T = K^T dS^T (same two shared-memory tiles with
+        // the operand roles swapped): head-dim index on the TMEM lanes, so that the 32 lanes of a warp add
+        // to 32 consecutive floats of one query row (one full 128-byte line per instruction) in G.
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)
-          umma_f16_ss(r_dp, umma_desc_mnmajor(ds_addr + kk * 2048, BLK), umma_desc_mnmajor(k_addr + kk * 2048, BLK),
-                      idesc_dq, kk != 0 ? 1u : 0u);
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          if constexpr (D == 128)
+            umma_f16_ss(r_dp, umma_desc_mnmajor(k_addr + kk * 2048, BLK), umma_desc_mnmajor(ds_addr + kk * 2048, BLK),
+                        idesc_dq, kk != 0 ? 1u : 0u);
+          else
+            umma_f16_ss(r_dp, umma_desc_mnmajor(ds_addr + kk * 2048, BLK), umma_desc_mnmajor(k_addr + kk * 2048, BLK),
+                        idesc_dq, kk != 0 ? 1u : 0u);
+        }
         umma_commit(dq_full);
         tr(TB_MMA_DEF_ISSUED);
         if (it + 1 < n_iters) {
@@ -336,6 +349,21 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       if (!__all_sync(0xffffffffu, mbar_wait(dq_full, uint32_t(it) & 1, wctx, ST_TIMEOUT_TMEM_FULL))) { ok = false; break; }
       tr(TB_DQ_READY);
       tc_fence_after();
+      if constexpr (D == 128) {
+        // lanes = head-dim index t, columns = queries: this thread adds element t of 64 query rows
+        const size_t row_stride = size_t(p.Hq) * D;
+        float* dq_col = p.dq_acc + (size_t(batch) * p.S + q0) * row_stride + size_t(head) * D + t;
+#pragma unroll 1
+        for (int c = half * 2; c < half * 2 + 2; ++c) {
+          uint32_t r[32];
+          tmem_ld32(lane_addr + uint32_t(Cfg::DP_COL + c * 32), r);
+          tmem_wait_ld();
+          const int nq = min(32, p.S - (q0 + c * 32));   // query rows of this chunk that exist (warp-uniform)
+#pragma unroll
+          for (int k = 0; k < 32; ++k)
+            if (k < nq) red_add_f32(dq_col + size_t(c * 32 + k) * row_stride, __uint_as_float(r[k]));
+        }
+      } else {
       const int qrow = q0 + t;
       float* dq_row = p.dq_acc + (size_t(batch) * p.S + qrow) * (size_t(p.Hq) * D) + size_t(head) * D;
 #pragma unroll 1
@@ -349,6 +377,7 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             red_add_v4_f32(dq_row + c * 32 + v4 * 4, __uint_as_float(r[v4 * 4 + 0]), __uint_as_float(r[v4 * 4 + 1]),
                            __uint_as_float(r[v4 * 4 + 2]), __uint_as_float(r[v4 * 4 + 3]));
         }
+      }
       }
       tc_fence_before();
       __syncwarp();

@@ -46,8 +46,12 @@ struct AttnFwd4Params {
 
 constexpr int FWD4_TRACE_EV = 256;
 constexpr int FWD4_WARPS = 12;
-constexpr int FWD4_SOFTMAX_REGS = 216;  // 2 * 128 * 216 + 128 * 80 = 65536 registers
-constexpr int FWD4_OTHER_REGS = 80;
+// setmaxnreg moves registers inside what the CTA was given at launch: 384 threads x 168 registers
+// (the launch bound) = 64512.  The three warpgroups must add up to exactly that, or the second
+// `inc` waits for registers that never come: 2 * 128 * 208 + 128 * 88 = 64512.
+constexpr int FWD4_SOFTMAX_REGS = 208;
+constexpr int FWD4_OTHER_REGS = 88;
+static_assert(2 * 128 * FWD4_SOFTMAX_REGS + 128 * FWD4_OTHER_REGS == 384 * 168, "register budget of the three warpgroups");
 
 template <int N>
 __device__ __forceinline__ void setmaxnreg_inc() {

@@ -36,7 +36,7 @@ def train_case(case):
     cfg = cfg_for(case, int(dist.get_world_size()) if dist.is_initialized() else 1)
     sched = "1f1b" if "1f1b" in case else ("zero2" if "pp" in case else "layer_major")
     tr = Trainer(cfg, TrainerOptions(schedule=sched, ops="sm100", collectives="fused" if fused else "library",
-                                     optimizer_in_backward=sched != "1f1b", lr=1e-3))
+                                     optimizer_in_backward=sched != "1f1b", lr=1e-3, gloo_p2p="gloo" in case))
     batch = tr.synthetic_batch()
     losses = []
     for _ in range(3):
@@ -213,6 +213,7 @@ def main():
         losses, masters, tr = train_case(case)
         # same job with the other collectives mode must land on the same parameters
         other = {"dp2_uneven_library": "dp2_library", "pp2_1f1b": "pp2", "pp2dp2_1f1b_library": "pp2dp2_library",
+                 "pp2_gloo": "pp2", "dp2_1f1b_fused": "dp2_library", "pp2dp2_1f1b_fused": "pp2dp2_library",
                  "tp2_library": "dp2_library" if dist.get_world_size() == 2 else "pp2dp2_library"}.get(case)
         if case.endswith("fused") or other:
             l2, m2, _ = train_case(other or case.replace("fused", "library"))

@@ -27,7 +27,8 @@ def _run(nproc, *args, timeout=600, **extra_env):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("case", ["dp2_library", "dp2_fused", "pp2", "fused_kernels"])
+@pytest.mark.parametrize("case", ["dp2_library", "dp2_fused", "pp2", "fused_kernels", "pp2_1f1b", "dp2_uneven_library",
+                                  "pp2_gloo", "dp2_1f1b_fused"])
 def test_two_gpus(case):
     out = _run(2, case)
     assert "WORKER_OK" in out
@@ -37,8 +38,7 @@ CANDIDATES = os.environ.get("ZORSE_TEST_CANDIDATES") == "1"   # paths that have 
 
 
 @pytest.mark.skipif(_ngpu() < 2 or not CANDIDATES, reason="needs 2 GPUs and ZORSE_TEST_CANDIDATES=1")
-@pytest.mark.parametrize("case", ["dp2_uneven_library", "pp2_1f1b", "fused_kernels_v1", "fused_kernels_v2",
-                                  "fused_kernels_v3"])
+@pytest.mark.parametrize("case", ["fused_kernels_v1", "fused_kernels_v2", "fused_kernels_v3"])
 def test_two_gpus_candidates(case):
     out = _run(2, case, timeout=300)
     assert "WORKER_OK" in out
@@ -50,12 +50,6 @@ def test_two_gpus_nvls_training(variant):
     """Fused collectives with the in-switch reduction (2) and with the parameter push that replaces
     the all-gather (3) must land on the parameters of the library-collectives run."""
     out = _run(2, "dp2_fused", timeout=300, ZORSE_RS_ADAM_VARIANT=variant)
-    assert "WORKER_OK" in out
-
-
-@pytest.mark.skipif(_ngpu() < 4 or not CANDIDATES, reason="needs 4 GPUs and ZORSE_TEST_CANDIDATES=1")
-def test_four_gpus_1f1b():
-    out = _run(4, "pp2dp2_1f1b_library", timeout=300)
     assert "WORKER_OK" in out
 
 
@@ -87,7 +81,7 @@ def test_tensor_parallel_four_gpus():
 
 
 @pytest.mark.skipif(_ngpu() < 4, reason="needs 4 GPUs")
-@pytest.mark.parametrize("case", ["pp2dp2_library", "pp2dp2_fused"])
+@pytest.mark.parametrize("case", ["pp2dp2_library", "pp2dp2_fused", "pp2dp2_1f1b_library", "pp2dp2_1f1b_fused"])
 def test_four_gpus(case):
     out = _run(4, case)
     assert "WORKER_OK" in out

@@ -111,7 +111,7 @@ def test_gemm_large_vs_fp32(k):
 CANDIDATES = os.environ.get("ZORSE_TEST_CANDIDATES") == "1"   # kernel versions not yet validated on hardware
 
 
-@pytest.mark.parametrize("bwd_version", [1] + ([2] if CANDIDATES else []))
+@pytest.mark.parametrize("bwd_version", [1, 2])
 @pytest.mark.parametrize("T,H", [(5, 512), (300, 4096), (64, 2048), (33, 5120), (1000, 4096)])
 @pytest.mark.parametrize("ln", [False, True])
 def test_norm(k, T, H, ln, bwd_version):
@@ -259,8 +259,8 @@ ATTN_CASES = [
 ]
 
 
-# (version, flags); kernel versions that have not yet passed on hardware join the matrix only on request
-FWD_VERSIONS = [(1, 0), (2, 0)] + ([(4, 0), (4, 1), (4, 2)] if CANDIDATES else [])
+# (version, flags)
+FWD_VERSIONS = [(1, 0), (2, 0), (4, 0), (4, 1), (4, 2)]
 
 
 @pytest.mark.parametrize("version,flags", FWD_VERSIONS)
@@ -287,7 +287,24 @@ def test_flash_fwd(k, B, S, Hq, Hkv, D, causal, window, version, flags):
     _close(lse, want_lse, atol=2e-2, rtol=1e-2)
 
 
-BWD_VERSIONS = [1] + ([2] if CANDIDATES else [])
+def test_flash_default_versions_on_a_large_problem(k):
+    """The size-based default picks the two-tile forward here (20 heads x 8 pairs of query tiles >= 148 CTAs);
+    forward and backward defaults against the fp32 oracle, grouped-query heads, 2048 tokens."""
+    B, S, Hq, Hkv, D = 1, 2048, 20, 4, 128
+    assert k._auto_fwd_version(B, S, Hq) == 4 and k._auto_fwd_version(1, 1000, 8) == 1
+    qkv = _rand(B * S, (Hq + 2 * Hkv) * D, seed=11)
+    do = _rand(B * S, Hq * D, seed=12)
+    q = qkv.float().requires_grad_(True)
+    want_o = ref.attention(q, B, S, Hq, Hkv, D, True, 0)
+    (want,) = torch.autograd.grad(want_o, q, do.float())
+    out, lse = k.flash_fwd(qkv.cuda(), B, S, Hq, Hkv, D, True, 0)
+    got = k.flash_bwd(do.cuda(), qkv.cuda(), out, lse, B, S, Hq, Hkv, D, True, 0)
+    k.check_status()
+    _close(out, want_o.detach(), atol=2e-2, rtol=2e-2)
+    _close(got, want, atol=4e-2, rtol=3e-2)
+
+
+BWD_VERSIONS = [1, 2]
 
 
 @pytest.mark.parametrize("version", BWD_VERSIONS)

@@ -96,9 +96,12 @@ class Streams:
         self.measure_exposed = False
         self.exposed_events: list = []  # (start, end) pairs bracketing compute-stream waits on comm / p2p
 
-    def wait_event(self, ev) -> None:
+    def wait_event(self, ev, kind: str = "zero") -> None:
         """Compute stream waits for `ev`; when measuring, the wait is bracketed by timing events so
-        the time the compute stream sat idle on communication can be summed up after the step."""
+        the time the compute stream sat idle on communication can be summed up after the step.
+        `kind`: "zero" (gathers, reductions, optimizer, offload copies) or "pipeline" (a receive from
+        the neighbouring stage: that wait also contains the time the neighbour needed to produce the
+        tensor, i.e. the pipeline bubble, not only the transfer)."""
         cur = torch.cuda.current_stream()
         if not self.measure_exposed:
             cur.wait_event(ev)
@@ -107,9 +110,9 @@ class Streams:
         a.record(cur)
         cur.wait_event(ev)
         b.record(cur)
-        self.exposed_events.append((a, b))
+        self.exposed_events.append((a, b, kind))
 
-    def wait_stream(self, other) -> None:
+    def wait_stream(self, other, kind: str = "zero") -> None:
         cur = torch.cuda.current_stream()
         if not self.measure_exposed:
             cur.wait_stream(other)
@@ -118,14 +121,16 @@ class Streams:
         a.record(cur)
         cur.wait_stream(other)
         b.record(cur)
-        self.exposed_events.append((a, b))
+        self.exposed_events.append((a, b, kind))
 
-    def exposed_ms(self, clear: bool = True) -> float:
-        """Sum of the bracketed waits (call after a device synchronisation)."""
-        t = sum(a.elapsed_time(b) for a, b in self.exposed_events)
+    def exposed_ms(self, clear: bool = True, by_kind: bool = False):
+        """Sum of the bracketed waits (call after a device synchronisation); with `by_kind` a dict per kind."""
+        out: dict = {}
+        for a, b, kind in self.exposed_events:
+            out[kind] = out.get(kind, 0.0) + a.elapsed_time(b)
         if clear:
             self.exposed_events.clear()
-        return t
+        return out if by_kind else sum(out.values())
 
 
 @dataclass

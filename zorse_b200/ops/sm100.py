@@ -169,7 +169,7 @@ def norm_fwd(x, w, b, eps: float, layernorm: bool, version: Optional[int] = None
     return y, stats
 
 
-NORM_BWD_VERSION = int(os.environ.get("ZORSE_NORM_BWD", "1"))
+NORM_BWD_VERSION = int(os.environ.get("ZORSE_NORM_BWD", "2"))
 
 
 def norm_bwd(dy, x, w, stats, dres, dw, db, layernorm: bool, accumulate: bool = True, version: Optional[int] = None):
@@ -270,26 +270,33 @@ def adam_step(p, m, v, g, p16, *, lr, beta1, beta2, eps, weight_decay, step, gra
 
 
 # --------------------------------------------------------------------------- attention
-ATTN_FWD_VERSION = int(os.environ.get("ZORSE_ATTN_FWD", "1"))
+# 0 = by problem size: version 4 (two query tiles per CTA, 256 query rows) when that still gives every SM a
+# CTA, version 1 (one 128-row tile per CTA) for smaller problems; 1 / 2 / 4 force a version.
+ATTN_FWD_VERSION = int(os.environ.get("ZORSE_ATTN_FWD", "0"))
 
 
-ATTN_FWD4_FLAGS = int(os.environ.get("ZORSE_ATTN_FWD4_FLAGS", "0"))
+ATTN_FWD4_FLAGS = int(os.environ.get("ZORSE_ATTN_FWD4_FLAGS", "1"))
+
+
+def _auto_fwd_version(B: int, S: int, Hq: int) -> int:
+    return 4 if B * Hq * ((S + 255) // 256) >= 148 else 1
 
 
 def flash_fwd(qkv, B: int, S: int, Hq: int, Hkv: int, D: int, causal: bool = True, window: int = 0,
               scale: Optional[float] = None, version: Optional[int] = None, flags: Optional[int] = None,
               trace: Optional[torch.Tensor] = None, trace_ctas: int = 0):
     """qkv: packed [B*S, (Hq+2Hkv)*D]. Returns (out [B*S, Hq*D], lse [B, Hq, S]).
-    version 1 (default, the faster one as measured): one query tile per CTA, S double-buffered in
-    TMEM, P staged through shared memory; version 2: two query tiles per CTA, P kept in TMEM;
-    version 4: two query tiles, one MMA issuer, score rows in registers (`flags` 1: two-wide
+    version 1: one query tile per CTA, S double-buffered in TMEM, P staged through shared memory (default
+    for problems with fewer than 148 pairs of query tiles); version 2: two query tiles per CTA, P kept in
+    TMEM; version 4 (default otherwise, 1.36-1.44x faster than version 1 on 4096-token sequences): two
+    query tiles, one MMA issuer, score rows in registers (`flags` 1: two-wide
     fp32 math, 2: also a quarter of the exponentials as a polynomial on the fma pipe; `trace`: zeroed int64 buffer from `flash_fwd4_trace_buffer` for a phase timeline)."""
     _bf16(qkv, "qkv")
     assert qkv.shape == (B * S, (Hq + 2 * Hkv) * D) and qkv.is_contiguous()
     out = torch.empty(B * S, Hq * D, dtype=qkv.dtype, device=qkv.device)
     lse = torch.empty(B, Hq, S, dtype=torch.float32, device=qkv.device)
     sc = (1.0 / math.sqrt(D)) if scale is None else scale
-    ver = version or ATTN_FWD_VERSION
+    ver = version or ATTN_FWD_VERSION or _auto_fwd_version(B, S, Hq)
     if ver == 4:
         fl = ATTN_FWD4_FLAGS if flags is None else flags
         _check(lib().zb_flash_fwd4(_p(qkv), _p(out), _p(lse), c_int(B), c_int(S), c_int(Hq), c_int(Hkv), c_int(D),
@@ -341,7 +348,8 @@ def flash_fwd4_trace_buffer(device, ctas: int) -> torch.Tensor:
 _attn_scratch: dict = {}
 
 
-ATTN_BWD_VERSION = int(os.environ.get("ZORSE_ATTN_BWD", "1"))
+# 0 = by head dimension: version 2 for d = 64 (1.38x faster there), version 1 otherwise; 1 / 2 force a version
+ATTN_BWD_VERSION = int(os.environ.get("ZORSE_ATTN_BWD", "0"))
 
 
 def flash_bwd(do, qkv, o, lse, B: int, S: int, Hq: int, Hkv: int, D: int, causal: bool = True, window: int = 0,
@@ -354,7 +362,7 @@ def flash_bwd(do, qkv, o, lse, B: int, S: int, Hq: int, Hkv: int, D: int, causal
     (`trace`: zeroed buffer from `flash_bwd2_trace_buffer`)."""
     _bf16(do, "do"); _bf16(qkv, "qkv")
     assert do.is_contiguous() and qkv.is_contiguous() and o.is_contiguous()
-    if (version or ATTN_BWD_VERSION) == 2:
+    if (version or ATTN_BWD_VERSION or (2 if D == 64 else 1)) == 2:
         return _flash_bwd2(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale, trace, trace_ctas)
     key = (qkv.device.index, B, S, Hq, D)
     if key not in _attn_scratch:

@@ -58,13 +58,21 @@ class NcclP2P:
     def _group(self, kind: str, src: int, dst: int):
         return self.groups[(kind, dst > src)]
 
+    @staticmethod
+    def _post(op, tensor, peer: int, group):
+        """One send or receive as a batch of one: the batched form runs inside an NCCL group call on the
+        process group's communicator, which is what torch wants for p2p on an eagerly initialised group
+        (the unbatched form is treated as a collective of the whole group there, with a warning per call).
+        Ordering is unchanged: one queue per process group and device either way."""
+        return dist.batch_isend_irecv([dist.P2POp(op, tensor, peer, group=group)])[-1]
+
     def send(self, t: torch.Tensor, dst: int, tag: int, kind: str = "act") -> Handle:
         cur = torch.cuda.current_stream()
         SC.wrote(("p2p_src", id(t)), cur)
         self.send_stream.wait_stream(cur)
         with torch.cuda.stream(self.send_stream):
             SC.read(("p2p_src", id(t)), label="NCCL send of a tensor the compute stream produced")
-            work = dist.isend(t, dst, group=self._group(kind, self.rank, dst))
+            work = self._post(dist.isend, t, dst, self._group(kind, self.rank, dst))
         t.record_stream(self.send_stream)
         self.bytes_sent += t.numel() * t.element_size()
         self._pending.append((work, t))
@@ -75,7 +83,7 @@ class NcclP2P:
         buf = torch.empty(shape, dtype=dtype, device=self.device)
         self.recv_stream.wait_stream(cur)
         with torch.cuda.stream(self.recv_stream):
-            work = dist.irecv(buf, src, group=self._group(kind, src, self.rank))
+            work = self._post(dist.irecv, buf, src, self._group(kind, src, self.rank))
         buf.record_stream(self.recv_stream)
 
         def wait():
@@ -83,7 +91,7 @@ class NcclP2P:
                 work.wait()
                 SC.wrote(("p2p_dst", id(buf)))
             if self.streams is not None:
-                self.streams.wait_stream(self.recv_stream)
+                self.streams.wait_stream(self.recv_stream, kind="pipeline")
             else:
                 torch.cuda.current_stream().wait_stream(self.recv_stream)
             SC.read(("p2p_dst", id(buf)), label="compute on a received tensor")

@@ -199,6 +199,14 @@ class Trainer:
         self.synchronize()
         return self.streams.exposed_ms() if self.device.type == "cuda" else 0.0
 
+    def exposed_comm_breakdown(self) -> dict:
+        """The same time split by cause (ms): `zero` = waits on gathers, reductions, optimizer and offload
+        copies; `pipeline` = waits on receives from the neighbouring stage, which contain the time that
+        stage needed to produce the tensor (the pipeline bubble) as well as the transfer."""
+        self.synchronize()
+        d = self.streams.exposed_ms(by_kind=True) if self.device.type == "cuda" else {}
+        return {"zero": float(d.get("zero", 0.0)), "pipeline": float(d.get("pipeline", 0.0))}
+
     def synchronize(self):
         if self.device.type == "cuda":
             torch.cuda.synchronize()
