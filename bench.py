@@ -229,9 +229,14 @@ def main():
     tokens_per_step = args.global_batch * args.seq_len
 
     # ---- device-timed region -------------------------------------------------------------
-    for _ in range(args.warmup):
-        tr.train_step(inputs, targets)
+    first_loss = None
+    for w in range(args.warmup):
+        l = tr.train_step(inputs, targets)
         tr.synchronize()
+        if w == 0:
+            # loss of the very first step (random-init weights, before any update): must be ~ln(vocab) and the same
+            # for every parallel plan, which pins that all plans run the same model on the same data
+            first_loss = tr.global_loss(l)
         beat()
     tr.check_kernels()
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
@@ -316,7 +321,7 @@ def main():
                        "optimizer": "Adam fp32 master+moments, step inside the timed region",
                        "reduce_dtype": args.reduce_dtype, "collectives": args.collectives, "defer_wgrad": args.defer_wgrad,
                        "l2": "per-step working set (>100 GB of parameters, optimizer state and activations) far exceeds the 126 MB L2; no flush needed"},
-            "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches, "loss": loss_val,
+            "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches, "loss": loss_val, "loss_first_step": first_loss,
             "exposed_comm_ms_per_step": exposed_ms, "exposed_comm_breakdown": exposed_parts,
             "planner_predicted_ms": None if predicted is None else predicted["ms"],
             "measured_over_predicted": None if predicted is None else ms_per_step / predicted["ms"],

@@ -56,7 +56,9 @@ __device__ __forceinline__ void red_add_f32(float* p, float a) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(a) : "memory");
 }
 
-template <int D, bool TRACE>
+// DQ = false: the key-tile half of the two-kernel backward (dK and dV only): no dS^T copy in shared memory,
+// no dQ product and no atomics; dQ then comes from flash_bwd_dq.cu.
+template <int D, bool TRACE, bool DQ>
 __global__ void __launch_bounds__(32 * BWD2_WARPS, 1)
 flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -153,13 +155,21 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         const uint32_t ph = uint32_t(it / QS) & 1;
         const int head = kv_head * rep + it / per_head;
         const int q0 = (i_lo + it % per_head) * BM;
+        if (!zb_in_bounds(q0 >= 0 && q0 < p.S && head < p.Hq && kv0 < p.S, p.status, 8)) break;
         if (!mbar_wait(&qdo_empty[st], ph ^ 1, wctx, ST_TIMEOUT_EMPTY)) break;
         tr(TB_TMA_STAGE_FREE);
-        mbar_expect_tx(&qdo_full[st], 2 * Cfg::TILE_BYTES);
+        mbar_expect_tx(&qdo_full[st], 2 * Cfg::TILE_BYTES + (DQ ? 0 : 1024));
 #pragma unroll
         for (int b = 0; b < DB; ++b) {
           tma_load_4d(sQ + st * Cfg::TILE_BYTES + b * BLK, &tmap_q, &qdo_full[st], b * 64, head, q0, batch);
           tma_load_4d(sDO + st * Cfg::TILE_BYTES + b * BLK, &tmap_do, &qdo_full[st], b * 64, head, q0, batch);
+        }
+        if constexpr (!DQ) {
+          // lse (log2 units) and delta of the tile's 128 queries: 512 bytes each, next to the stage they belong to
+          // (rows of the statistics buffer are padded to a multiple of 128 entries, q0 is a multiple of 128)
+          const float* row = stats + (size_t(batch) * p.Hq + head) * 2 * size_t(s_pad) + q0;
+          bulk_load_1d(sDS + st * 1024, row, 512, &qdo_full[st]);
+          bulk_load_1d(sDS + st * 1024 + 512, row + s_pad, 512, &qdo_full[st]);
         }
         tr(TB_TMA_ISSUED);
       }
@@ -218,6 +228,10 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
                       (it | kk) != 0 ? 1u : 0u);
         }
         umma_commit(&qdo_empty[st]);
+        if constexpr (!DQ) {
+          if (it + 1 == n_iters) umma_commit(dq_full);   // every dK / dV product is done: the write-out may start
+        }
+        if constexpr (DQ) {
         // F: dQ = dS K  (reduction over the 128 keys) into R_dP, right behind E which read dS^T from it.
         // For D = 128 the product is formed transposed, dQ^T = K^T dS^T (same two shared-memory tiles with
         // the operand roles swapped): head-dim index on the TMEM lanes, so that the 32 lanes of a warp add
@@ -232,6 +246,7 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
                         idesc_dq, kk != 0 ? 1u : 0u);
         }
         umma_commit(dq_full);
+        }
         tr(TB_MMA_DEF_ISSUED);
         if (it + 1 < n_iters) {
           const int sn = (it + 1) % QS;
@@ -240,9 +255,12 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           tc_fence_after();
           issue_a(smem_u32(sQ + sn * Cfg::TILE_BYTES));
           tr(TB_MMA_A_ISSUED);
-          if (!mbar_wait(dq_empty, uint32_t(it) & 1, wctx, ST_TIMEOUT_TMEM_EMPTY)) break;
-          tr(TB_MMA_DQ_EMPTY);
-          tc_fence_after();
+          if constexpr (DQ) {
+            // dQ_it sits in R_dP until the compute warps have drained it
+            if (!mbar_wait(dq_empty, uint32_t(it) & 1, wctx, ST_TIMEOUT_TMEM_EMPTY)) break;
+            tr(TB_MMA_DQ_EMPTY);
+            tc_fence_after();
+          }
           issue_b(smem_u32(sDO + sn * Cfg::TILE_BYTES));
           tr(TB_MMA_B_ISSUED);
         }
@@ -260,9 +278,17 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     for (int it = 0; it < n_iters; ++it) {
       const int head = kv_head * rep + it / per_head;
       const int q0 = (i_lo + it % per_head) * BM;
+      const int qc0 = q0 + half * 64;            // first query column of this thread
+      // statistics of the tile's queries: global rows indexed by the absolute query (one-kernel form), or the
+      // copy the producer placed in shared memory with the stage, indexed from the tile's first query
       const float* lse_q = stats + (size_t(batch) * p.Hq + head) * 2 * size_t(s_pad);
       const float* delta_q = lse_q + s_pad;
-      const int qc0 = q0 + half * 64;            // first query column of this thread
+      if constexpr (!DQ) {
+        const int st = it % QS;
+        if (!__all_sync(0xffffffffu, mbar_wait(&qdo_full[st], uint32_t(it / QS) & 1, wctx, ST_TIMEOUT_FULL))) { ok = false; break; }
+        lse_q = reinterpret_cast<const float*>(sDS + st * 1024) - q0;
+        delta_q = reinterpret_cast<const float*>(sDS + st * 1024 + 512) - q0;
+      }
       const bool need_mask = (p.causal && kv0 + BN - 1 > q0) || (p.window > 0 && kv0 < q0 + BM - p.window) ||
                              (kv0 + BN > p.S) || (q0 + BM > p.S);
       // ---- C1: P^T = exp2(S^T c - lse_q), kept as packed bf16 pairs (queries 2i, 2i+1) ----
@@ -272,7 +298,7 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       // lse_q (already in log2 units) and delta_q are the same for every lane: 16-byte loads from the
       // padded statistics rows
       auto load4 = [&](const float* base, int q, float (&v)[4]) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(base + q));
+        const float4 a = DQ ? __ldg(reinterpret_cast<const float4*>(base + q)) : *reinterpret_cast<const float4*>(base + q);
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
       };
       uint32_t pp[32];
@@ -332,19 +358,22 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         // the other half's threads read columns [64 h', 64 h' + 64) only, so writing the packed
         // values over this half's own first 32 columns cannot disturb them
         tmem_st16(lane_addr + uint32_t(Cfg::DP_COL + half * 64 + c * 16), ds);
+        if constexpr (DQ) {
 #pragma unroll
         for (int v4 = 0; v4 < 4; ++v4) {
           const int ch = c * 4 + v4;  // 16-byte chunk (8 queries) within the 128-byte row
           uint4 u = make_uint4(ds[v4 * 4 + 0], ds[v4 * 4 + 1], ds[v4 * 4 + 2], ds[v4 * 4 + 3]);
           *reinterpret_cast<uint4*>(ds_row + ((ch ^ (t & 7)) << 4)) = u;
         }
+        }
       }
       tmem_wait_st();
-      fence_proxy_async_smem();
+      if constexpr (DQ) fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
       tr(TB_DS_DONE);
+      if constexpr (DQ) {
       // ---- G: dQ tile (lanes = query rows now) -> global fp32 accumulator ----
       if (!__all_sync(0xffffffffu, mbar_wait(dq_full, uint32_t(it) & 1, wctx, ST_TIMEOUT_TMEM_FULL))) { ok = false; break; }
       tr(TB_DQ_READY);
@@ -383,6 +412,12 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_empty);
       tr(TB_DQ_DRAINED);
+      }
+    }
+    if constexpr (!DQ) {
+      // the single dq_full arrival follows the last dK / dV product
+      if (ok && n_iters > 0) ok = mbar_wait(dq_full, 0, wctx, ST_TIMEOUT_TMEM_FULL);
+      tc_fence_after();
     }
     // ------------------------------ dK / dV write-out ------------------------------
     // the last dq_full arrival also covers every dK / dV MMA issued before it
@@ -466,7 +501,7 @@ static int make_head_tmap_bwd2(CUtensorMap* out, const __nv_bfloat16* base, int 
   return make_tmap_nd_bf16(out, base, 4, dims, strides, box);
 }
 
-template <int D, bool TRACE>
+template <int D, bool TRACE, bool DQ = true>
 static int launch_bwd2(const __nv_bfloat16* qkv, const __nv_bfloat16* d_o, const AttnBwdParams& p, const float* stats,
                        int s_pad, unsigned long long* trace, int trace_ctas, cudaStream_t stream) {
   using Cfg = AttnBwd2Cfg<D>;
@@ -477,7 +512,7 @@ static int launch_bwd2(const __nv_bfloat16* qkv, const __nv_bfloat16* d_o, const
   if ((rc = make_head_tmap_bwd2(&tk, qkv + size_t(p.Hq) * D, p.B, p.S, p.Hkv, D, width))) return rc;
   if ((rc = make_head_tmap_bwd2(&tv, qkv + size_t(p.Hq + p.Hkv) * D, p.B, p.S, p.Hkv, D, width))) return rc;
   if ((rc = make_head_tmap_bwd2(&tdo, d_o, p.B, p.S, p.Hq, D, p.Hq * D))) return rc;
-  auto kern = flash_bwd2_kernel<D, TRACE>;
+  auto kern = flash_bwd2_kernel<D, TRACE, DQ>;
   static bool attr_set = false;
   if (!attr_set) {
     ZB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
@@ -488,6 +523,9 @@ static int launch_bwd2(const __nv_bfloat16* qkv, const __nv_bfloat16* d_o, const
   ZB_CUDA_OK(cudaGetLastError());
   return 0;
 }
+
+int attn_bwd_dq(const __nv_bfloat16* qkv, const __nv_bfloat16* d_o, const AttnBwdParams& p, const float* stats, int s_pad,
+                int D, cudaStream_t stream);   // flash_bwd_dq.cu
 
 }  // namespace zb
 
@@ -534,6 +572,44 @@ int zb_flash_bwd2(const void* d_o, const void* qkv, const void* o, const float* 
                 : launch_bwd2<64, false>(QKV, DO, p, stats, s_pad, nullptr, 0, stream);
   if (rc) return rc;
   return attn_bwd_finish_dq(dq_acc, p.dqkv, B, S, Hq, Hkv, D, stream);
+}
+
+// Two-kernel backward without atomics: statistics pass, then dK / dV per key tile (this file's kernel without
+// its dQ part) and dQ per query tile (flash_bwd_dq.cu); the two main kernels are independent of each other.
+// Scratch: stats fp32 [zb_flash_bwd2_stats_floats(B, S, Hq)], zeroed once by the caller.
+int zb_flash_bwd3(const void* d_o, const void* qkv, const void* o, const float* lse, void* dqkv, float* stats,
+                  int B, int S, int Hq, int Hkv, int D, int causal, int window, float softmax_scale, int* status,
+                  int parts, cudaStream_t stream) {
+  // parts: 3 = the whole backward; 1 = statistics + dK / dV kernel only, 2 = dQ kernel only (needs the
+  // statistics of an earlier call) - for timing the two halves separately
+  using namespace zb;
+  if (B <= 0 || S <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv != 0) ZB_FAIL(-1, "attention: Hq=%d not a multiple of Hkv=%d", Hq, Hkv);
+  if (D != 64 && D != 128) ZB_FAIL(-1, "attention: head dim %d unsupported (64 or 128)", D);
+  auto DO = static_cast<const __nv_bfloat16*>(d_o);
+  auto O = static_cast<const __nv_bfloat16*>(o);
+  auto QKV = static_cast<const __nv_bfloat16*>(qkv);
+  const int s_pad = (S + 127) / 128 * 128;
+  if (parts & 1) {
+    const long warps = long(B) * S * Hq;
+    const long blocks = (warps * 32 + 255) / 256;
+    attn_bwd2_stats_kernel<<<(unsigned)blocks, 256, 0, stream>>>(O, DO, lse, stats, B, S, Hq, D, s_pad);
+    ZB_CUDA_OK(cudaGetLastError());
+  }
+  AttnBwdParams p;
+  p.lse = lse; p.delta = nullptr; p.dq_acc = nullptr;
+  p.dqkv = static_cast<__nv_bfloat16*>(dqkv);
+  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.window = window; p.causal = causal;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = status;
+  int rc = 0;
+  if (parts & 1)
+    rc = (D == 128) ? launch_bwd2<128, false, false>(QKV, DO, p, stats, s_pad, nullptr, 0, stream)
+                    : launch_bwd2<64, false, false>(QKV, DO, p, stats, s_pad, nullptr, 0, stream);
+  if (rc) return rc;
+  return (parts & 2) ? attn_bwd_dq(QKV, DO, p, stats, s_pad, D, stream) : 0;
 }
 
 }  // extern "C"

@@ -183,6 +183,7 @@ flash_fwd4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           const int slot = t % NSLOT;
           const uint32_t ph = uint32_t(t / NSLOT) & 1;
           const int kv0 = (j_lo + (t >> 1)) * BN;
+          if (!zb_in_bounds(kv0 >= 0 && kv0 < p.S && kv_head < p.Hkv && batch < p.B, p.status, 8)) break;
           if (!mbar_wait(&r_empty[slot], ph ^ 1, wctx, ST_TIMEOUT_EMPTY)) break;
           tr(TR_TMA_SLOT_FREE);
           mbar_expect_tx(&r_full[slot], Cfg::TILE_BYTES);

@@ -123,6 +123,7 @@ rs_adam_kernel(const RsAdamParams p) {
   // 2. reduce + Adam over this rank's slice
   const long lo = long(p.r) * p.shard_n;
   for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < nvec; i += long(gridDim.x) * blockDim.x) {
+    if (!zb_in_bounds(lo + (i + 1) * N <= long(p.R) * p.shard_n && p.r >= 0 && p.r < p.R, p.status, 5)) break;
     float g[N];
     float pm[N], mm[N], vv[N];
 #pragma unroll

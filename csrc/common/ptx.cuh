@@ -22,7 +22,29 @@ enum : int {
   ST_TIMEOUT_FLAG = 5,       // wait on a global/peer flag ran out
   ST_BAD_ARG = 6,
   ST_TIMEOUT_MISC = 7,
+  ST_BOUNDS = 8,             // debug build only: an index or address left its tensor; the access was skipped
 };
+
+// Debug build (-DZB_DEBUG_BOUNDS=1, `python -m zorse_b200.ops.build --debug-bounds`): every kernel checks its
+// tile coordinates, shard offsets and flag indices against the extents it was given.  A failed check records
+// {ST_BOUNDS, site, block} in the status word and returns false so that the caller skips the access; nothing
+// traps.  In the normal build the function is `true` and the checks compile away.
+// Sites: 1 GEMM tile origin, 2 GEMM epilogue row / column, 3 gather chunk, 4 gather flag index, 5 optimizer
+// slice, 6 embedding row, 7 loss target, 8 attention row, 9 norm row.
+#ifndef ZB_DEBUG_BOUNDS
+#define ZB_DEBUG_BOUNDS 0
+#endif
+__device__ __forceinline__ bool zb_in_bounds(bool cond, int* status, int site) {
+#if ZB_DEBUG_BOUNDS
+  if (!cond) {
+    if (status) atomicCAS(status, 0, ST_BOUNDS | (site << 4) | (int(blockIdx.x) << 8));
+    return false;
+  }
+#else
+  (void)cond; (void)status; (void)site;
+#endif
+  return true;
+}
 
 #ifndef ZB_WAIT_NS
 #define ZB_WAIT_NS 2000000000ull  // 2 s per wait
@@ -147,6 +169,15 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, ui
       :
       : "r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
+}
+
+// Untiled bulk copy global -> this CTA's shared memory, completion counted on an mbarrier. Both addresses must
+// be 16-byte aligned and `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :
+               : "r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 
 // ---------------------------------------------------------------------------

@@ -168,6 +168,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         const int m0 = (tile % tiles_m) * Cfg::BM + int(cta) * 128;
         const int n0 = (tile / tiles_m) * BN + int(cta) * 128;
+        // (the second CTA's half may start past the edge of a ragged tile: its loads then read the fill value)
+        if (!zb_in_bounds(m0 - int(cta) * 128 < p.M && n0 - int(cta) * 128 < p.N && tile >= 0, p.status, 1)) break;
         if constexpr (FUSED_AG) {
           if (p.gate_flags != nullptr && n0 < p.N) {
             // rows [n0, n0 + 128) of B inside the flat buffer: wait for every chunk of a peer's shard they touch
@@ -342,6 +344,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       }
       const long beg = long(c) * chunk16;
       const long end = min(beg + chunk16, shard16);
+      if (!zb_in_bounds(peer >= 0 && peer < ag.R && peer != ag.r && beg >= 0 && end <= shard16 && beg <= end, p.status, 3)) break;
+      if (!zb_in_bounds(peer * ag.cps + c < ag.R * ag.cps && c >= 0, p.status, 4)) break;
       const uint4* src = ag.src[peer];
       uint4* dst = ag.dst + long(peer) * shard16;
       long i = beg + ct;

@@ -91,6 +91,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % tiles_m) * BM;
         const int n0 = (tile / tiles_m) * BN;
+        if (!zb_in_bounds(m0 < p.M && n0 < p.N && tile >= 0, p.status, 1)) break;
         if (p.gate_flags != nullptr) {
           const long b0 = p.gate_base + long(n0) * p.gate_row_bytes;
           const long b1 = p.gate_base + long(min(n0 + BN, p.N)) * p.gate_row_bytes - 1;
@@ -228,6 +229,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       const long beg = long(c) * chunk16;
       const long end = min(beg + chunk16, shard16);
+      if (!zb_in_bounds(peer >= 0 && peer < ag.R && peer != ag.r && beg >= 0 && end <= shard16 && beg <= end, p.status, 3)) break;
+      if (!zb_in_bounds(peer * ag.cps + c < ag.R * ag.cps && c >= 0, p.status, 4)) break;
       const uint4* src = ag.src[peer];
       uint4* dst = ag.dst + long(peer) * shard16;
       long i = beg + ct;

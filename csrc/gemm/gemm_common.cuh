@@ -98,6 +98,7 @@ __device__ __forceinline__ EpilogueCfg epilogue_cfg(const GemmParams& p) {
 __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const EpilogueCfg& e, int row, int col0,
                                                      const uint32_t (&r)[32]) {
   const bool out_f32 = e.out_f32, accum = e.accum, vec_ok = e.vec_ok;
+  if (!zb_in_bounds(row >= 0 && row < p.M && col0 >= 0 && col0 < p.N && p.C != nullptr, p.status, 2)) return;
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);

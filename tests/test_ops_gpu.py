@@ -304,7 +304,7 @@ def test_flash_default_versions_on_a_large_problem(k):
     _close(got, want, atol=4e-2, rtol=3e-2)
 
 
-BWD_VERSIONS = [1, 2]
+BWD_VERSIONS = [1, 2, 3]
 
 
 @pytest.mark.parametrize("version", BWD_VERSIONS)
@@ -371,3 +371,38 @@ def test_accumulate_prefetch_gemm_matches_the_default(k, M, N, K, a_mn, b_mn):
         k.gemm(a, b, got, a_mn=a_mn, b_mn=b_mn, accumulate=True, kernel="2cta_accpf")
     k.check_status()
     assert torch.equal(got, want)
+
+
+def test_checking_build_gives_the_same_results_and_a_clean_status():
+    """The debug build (-DZB_DEBUG_BOUNDS=1: kernels verify tile coordinates, shard offsets and flag indices and
+    report through the status word) runs a GEMM with ragged edges and attention forward + backward in a child
+    process and must agree with the fp32 oracle with no check tripped."""
+    import subprocess
+    import sys
+
+    code = r'''
+import math, torch
+from zorse_b200.ops import sm100 as k
+assert str(k.lib()._name).endswith("libzorse_sm100_dbg.so"), k.lib()._name
+g = torch.Generator().manual_seed(3)
+rnd = lambda *s: (torch.randn(*s, generator=g) * 0.5).to(torch.bfloat16)
+a, b = rnd(300, 520), rnd(1320, 520)
+out = torch.empty(300, 1320, dtype=torch.bfloat16, device="cuda")
+k.gemm(a.cuda(), b.cuda(), out)
+k.check_status()
+want = a.float() @ b.float().t()
+assert (out.float().cpu() - want).abs().max() < 0.15
+B, S, Hq, Hkv, D = 1, 600, 4, 2, 128
+qkv, do = rnd(B * S, (Hq + 2 * Hkv) * D).cuda(), rnd(B * S, Hq * D).cuda()
+o1, l1 = k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, 0, version=1)
+o4, l4 = k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, 0, version=4)
+d1 = k.flash_bwd(do, qkv, o1, l1, B, S, Hq, Hkv, D, True, 0, version=1)
+d3 = k.flash_bwd(do, qkv, o1, l1, B, S, Hq, Hkv, D, True, 0, version=3)
+k.check_status()
+assert (o1.float() - o4.float()).abs().max() < 3e-2 and (d1.float() - d3.float()).abs().max() < 6e-2
+print("CHECKING_BUILD_OK")
+'''
+    env = dict(os.environ, ZORSE_DEBUG_BOUNDS="1")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, env=env,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0 and "CHECKING_BUILD_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

@@ -248,7 +248,7 @@ def test_candidate_report_parent_side(monkeypatch, capsys):
     """Case list, child-failure handling and the table of the candidate report (no GPU: children are faked)."""
     from zorse_b200.profiler import candidates as C
 
-    assert len(C.CASES) == len(set(C.CASES)) == 27
+    assert len(C.CASES) == len(set(C.CASES)) == 30
     fake = {"flash_bwd2:7b": {"case": "flash_bwd2:7b", "agrees": True, "max_diff": 0.01, "tolerance": 0.06, "status_word": 0,
                               "ms_default": 0.9, "ms_candidate": 0.45},
             "norm_bwd2_rms:7b": {"case": "norm_bwd2_rms:7b", "agrees": False, "max_diff": 0.5, "tolerance": 0.03,
@@ -322,3 +322,19 @@ def test_layer_profile_stores_activation_bytes_and_chain_overhead(tmp_path):
     assert estimate_memory_usage(10**9, 8, 64, 128, 2, block_activation_bytes=2**30, recompute=False)["activation_gib"] == 8.0
     ch = profile_chain("tiny_llama", 64, torch.float32, blocks=2, iters=2, warmup=1, device=torch.device("cpu"))
     assert ch["blocks"] == 2 and ch["chain_ms"] > 0 and 0.2 < ch["overhead"] < 5.0
+
+
+def test_status_word_of_the_checking_build_is_decoded(monkeypatch):
+    """A bounds report {code 8, site, block} from the checking build reads as a KernelError naming the site."""
+    import torch
+
+    from zorse_b200.ops import sm100 as k
+
+    word = torch.tensor([8 | (2 << 4) | (37 << 8)], dtype=torch.int32)
+    monkeypatch.setattr(k, "status_word", lambda device=None: word)
+    with pytest.raises(k.KernelError, match=r"site 2 \(GEMM epilogue row / column\) in block 37"):
+        k.check_status()
+    assert int(word.item()) == 0
+    word[0] = 5 | (3 << 8)
+    with pytest.raises(k.KernelError, match=r"status 5 \(flag wait ran out\) in block 3"):
+        k.check_status()

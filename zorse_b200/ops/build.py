@@ -50,8 +50,8 @@ def _newest_header_mtime() -> float:
     return max((h.stat().st_mtime for h in hs), default=0.0)
 
 
-def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
-    cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool, extra=()) -> str:
+    cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
@@ -63,7 +63,20 @@ def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
     return r.stderr
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+DEBUG_LIB = OUT_DIR / "libzorse_sm100_dbg.so"
+
+
+def build(force: bool = False, verbose: bool = False, debug_bounds: bool = False) -> Path:
+    """`debug_bounds`: the checking build (`-DZB_DEBUG_BOUNDS=1`, own object directory and library name):
+    kernels compare tile coordinates, shard offsets and flag indices with the extents they were given and
+    report through the status word instead of touching memory outside them.  Loaded instead of the normal
+    library when ZORSE_DEBUG_BOUNDS=1."""
+    if debug_bounds:
+        return _build(force, verbose, OUT_DIR / "obj_dbg", DEBUG_LIB, ["-DZB_DEBUG_BOUNDS=1"], write_log=False)
+    return _build(force, verbose, OBJ_DIR, LIB, [], write_log=True)
+
+
+def _build(force: bool, verbose: bool, OBJ_DIR: Path, LIB: Path, extra: list, write_log: bool) -> Path:
     nvcc = find_nvcc()
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     hdr_m = _newest_header_mtime()
@@ -77,11 +90,12 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             jobs.append((src, obj))
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
-            futs = [ex.submit(_compile_one, nvcc, s, o, verbose) for s, o in jobs]
+            futs = [ex.submit(_compile_one, nvcc, s, o, verbose, tuple(extra)) for s, o in jobs]
             for f in futs:
                 f.result()
         # registers / spills / shared memory of every kernel, one section per source file
-        (OUT_DIR / "ptxas.log").write_text("\n".join(o.with_suffix(".log").read_text() for o in objs
+        if write_log:
+            (OUT_DIR / "ptxas.log").write_text("\n".join(o.with_suffix(".log").read_text() for o in objs
                                                       if o.with_suffix(".log").exists()))
     if jobs or not LIB.exists():
         cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"]
@@ -95,8 +109,9 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--debug-bounds", action="store_true", help="the checking build (libzorse_sm100_dbg.so)")
     a = ap.parse_args(argv)
-    lib = build(force=a.force, verbose=a.verbose)
+    lib = build(force=a.force, verbose=a.verbose, debug_bounds=a.debug_bounds)
     print(lib)
     return 0
 

@@ -48,11 +48,17 @@ def lib():
     """Loads (building if needed) the kernel library. Raises if it cannot be had."""
     global _lib
     if _lib is None:
-        if not _LIB_PATH.exists():
+        path = _LIB_PATH
+        if os.environ.get("ZORSE_DEBUG_BOUNDS", "0") == "1":
+            # the checking build: same entry points, kernels verify their indices (see csrc/common/ptx.cuh)
+            from . import build as _build
+
+            path = _build.build(debug_bounds=True)
+        elif not path.exists():
             from . import build as _build
 
             _build.build()
-        _lib = ctypes.CDLL(str(_LIB_PATH))
+        _lib = ctypes.CDLL(str(path))
         _lib.zb_last_error.restype = ctypes.c_char_p
         if os.environ.get("ZORSE_RS_ADAM_VARIANT", "0") != "0":      # candidate, see csrc/comm/rs_adam.cu
             _lib.zb_set_rs_adam_variant(c_int(int(os.environ["ZORSE_RS_ADAM_VARIANT"])))
@@ -85,12 +91,21 @@ _STATUS_NAMES = {
 }
 
 
+_BOUNDS_SITES = {1: "GEMM tile origin", 2: "GEMM epilogue row / column", 3: "all-gather chunk", 4: "all-gather flag index",
+                 5: "optimizer slice", 8: "attention tile"}
+
+
 def check_status(device=None) -> None:
     """Synchronising read of the status word; raises KernelError if a kernel gave up."""
     s = status_word(device)
     v = int(s.item())
     if v != 0:
         s.zero_()
+        code = v & 0xf
+        if code == 8:
+            site = (v >> 4) & 0xf
+            raise KernelError(f"sm100 kernel (checking build) found an index outside its tensor: site {site} "
+                              f"({_BOUNDS_SITES.get(site, '?')}) in block {v >> 8}; the access was skipped")
         raise KernelError(
             f"sm100 kernel reported status {v & 0xff} ({_STATUS_NAMES.get(v & 0xff, '?')}) in block {v >> 8}")
 
@@ -333,6 +348,25 @@ def _flash_bwd2(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale, trace,
     return dqkv
 
 
+def _flash_bwd3(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale, parts: int = 3):
+    key = (qkv.device.index, B, S, Hq)
+    if key not in _attn_scratch3:
+        n = lib().zb_flash_bwd2_stats_floats(c_int(B), c_int(S), c_int(Hq))
+        _attn_scratch3[key] = torch.zeros(n, dtype=torch.float32, device=qkv.device)   # padding stays zero
+    stats = _attn_scratch3[key]
+    dqkv = torch.empty_like(qkv)
+    sc = (1.0 / math.sqrt(D)) if scale is None else scale
+    _check(lib().zb_flash_bwd3(_p(do), _p(qkv), _p(o), _p(lse), _p(dqkv), _p(stats), c_int(B), c_int(S), c_int(Hq),
+                               c_int(Hkv), c_int(D), c_int(int(causal)), c_int(window), c_float(sc),
+                               _p(status_word(qkv.device)), c_int(parts), _stream()), "flash_bwd3")
+    global _launches
+    _launches += 2  # statistics + the second main kernel
+    return dqkv
+
+
+_attn_scratch3: dict = {}
+
+
 def flash_bwd2_trace_buffer(device, ctas: int) -> torch.Tensor:
     w, e = lib().zb_flash_bwd2_trace_warps(), lib().zb_flash_bwd2_trace_events()
     return torch.zeros(ctas, w, e, dtype=torch.int64, device=device)
@@ -359,10 +393,14 @@ def flash_bwd(do, qkv, o, lse, B: int, S: int, Hq: int, Hkv: int, D: int, causal
     and device; the accumulator is left zeroed by the kernel that converts it to bf16.
     version 1 (default): scores with queries on the TMEM lanes, P and dS staged through shared
     memory; version 2: transposed scores, P^T / dS^T consumed from tensor memory, two Q/dO stages
-    (`trace`: zeroed buffer from `flash_bwd2_trace_buffer`)."""
+    (`trace`: zeroed buffer from `flash_bwd2_trace_buffer`); version 3: two kernels without atomics, dK / dV per
+    key tile and dQ per query tile (scores are formed twice; no fp32 dQ accumulator)."""
     _bf16(do, "do"); _bf16(qkv, "qkv")
     assert do.is_contiguous() and qkv.is_contiguous() and o.is_contiguous()
-    if (version or ATTN_BWD_VERSION or (2 if D == 64 else 1)) == 2:
+    ver = version or ATTN_BWD_VERSION or (2 if D == 64 else 1)
+    if ver == 3:
+        return _flash_bwd3(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale)
+    if ver == 2:
         return _flash_bwd2(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale, trace, trace_ctas)
     key = (qkv.device.index, B, S, Hq, D)
     if key not in _attn_scratch:

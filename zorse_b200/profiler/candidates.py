@@ -30,7 +30,7 @@ ATTN_SHAPES = {   # name: (B, S, Hq, Hkv, D, window)
 NORM_SHAPES = {"7b": (4096, 4096), "gqa64": (4096, 2048), "ragged_window": (1000, 5120)}
 WGRAD_SHAPES = {"7b_qkv": (4096, 12288, 4096), "7b_gate_up": (4096, 22016, 4096), "ragged": (1000, 1320, 520)}   # tokens, N, K
 
-CASES = [f"{k}:{s}" for k in ("flash_fwd4_f0", "flash_fwd4_f1", "flash_fwd4_f2", "flash_bwd2") for s in ATTN_SHAPES] + \
+CASES = [f"{k}:{s}" for k in ("flash_fwd4_f0", "flash_fwd4_f1", "flash_fwd4_f2", "flash_bwd2", "flash_bwd3") for s in ATTN_SHAPES] + \
         [f"{k}:{s}" for k in ("norm_fwd2_rms", "norm_fwd2_ln", "norm_bwd2_rms", "norm_bwd2_ln") for s in NORM_SHAPES] + \
         [f"gemm_accpf:{s}" for s in WGRAD_SHAPES]
 
@@ -100,7 +100,8 @@ def run_case(case: str, dev: str = "cuda", flush_floats: int = 64 * 1024 * 1024)
             res["max_diff"] = max(_diff(out4, out1), _diff(lse4, lse1))
             res["tolerance"] = 3e-2 if fl < 2 else 4e-2
         else:
-            cand = lambda: k.flash_bwd(do, qkv, out1, lse1, B, S, Hq, Hkv, D, True, win, version=2)
+            bv = int(kind[-1])
+            cand = lambda: k.flash_bwd(do, qkv, out1, lse1, B, S, Hq, Hkv, D, True, win, version=bv)
             base = lambda: k.flash_bwd(do, qkv, out1, lse1, B, S, Hq, Hkv, D, True, win, version=1)
             d1, d2 = base(), cand()
             sync()

@@ -9,8 +9,11 @@ For a Llama-2-7B block (202 383 360 bf16 parameters) on R ranks:
 * `ag_gemm`: fused all-gather + QKV GEMM (4096 tokens) vs `all_gather_into_tensor` + the plain
   GEMM. Roofline = slower of GEMM FLOPs at the measured bf16 peak and inbound bytes
   (R-1)/R * N * 2 at link bandwidth.
-Link bandwidth: 770 GB/s per direction per GPU (measured peer copy on this pool; 900 nominal).
-Times are CUDA-event medians, max over ranks.
+Link bandwidth: every fraction is given twice, against the nominal 900 GB/s per direction per GPU and
+against 770 GB/s (the peer-copy rate measured on B200 / NVSwitch systems).  `--rs_adam_variants 0,1,2`
+times several variants of the reduce-scatter kernel in one run (0 = loads per peer in turn, 1 = all
+loads issued up front, 2 = in-switch reduction through the multicast address); `ag_gemm` is timed on
+the 2-CTA and the 1-CTA GEMM core and for two chunk sizes.  Times are CUDA-event medians, max over ranks.
 """
 from __future__ import annotations
 
@@ -21,7 +24,8 @@ import statistics
 import torch
 import torch.distributed as dist
 
-LINK_GBS = 770.0
+LINK_GBS = 900.0            # nominal NVLink 5, per direction per GPU
+LINK_GBS_MEASURED = 770.0   # peer copy
 
 
 def _time(fn, pre=None, iters=8, warmup=3):
@@ -48,7 +52,8 @@ def main(argv=None):
     ap.add_argument("--out", default=None)
     ap.add_argument("--params", type=int, default=202_383_360)
     ap.add_argument("--tokens", type=int, default=4096)
-    ap.add_argument("--rs_adam_variant", type=int, default=0, help="1 = early-load candidate of the rs_adam kernel, 2 = in-switch (NVLS) reduction candidate")
+    ap.add_argument("--rs_adam_variants", default="0", help="comma-separated: 0, 1 (loads up front), 2 (in-switch reduction)")
+    ap.add_argument("--peaks", default=None, help="JSON with measured hbm_gbs / bf16_tflops of this machine")
     a = ap.parse_args(argv)
     import torch.distributed._symmetric_memory as symm
 
@@ -57,17 +62,19 @@ def main(argv=None):
     from zorse_b200.profiler.kernel_bench import _peaks
 
     dev = dist_init()
-    k.set_rs_adam_variant(a.rs_adam_variant)
     rank, R = dist.get_rank(), dist.get_world_size()
-    peaks = _peaks()
+    peaks = _peaks(a.peaks)
+    variants = [int(v) for v in a.rs_adam_variants.split(",")]
     q = 64 * R
     n = (a.params + q - 1) // q * q
     sn = n // R
-    res = {"R": R, "params": n, "link_gbs": LINK_GBS, "peaks": peaks}
+    res = {"R": R, "params": n, "link_gbs": LINK_GBS, "link_gbs_measured": LINK_GBS_MEASURED, "peaks": peaks}
     hyper = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0)
 
     # ---------------------------------------------------------------- rs_adam
-    for gdt, name in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
+    for variant in variants:
+      k.set_rs_adam_variant(variant)
+      for gdt, name in ((torch.bfloat16, "bf16"), (torch.float32, "fp32")):
         grad = symm.empty(n, dtype=gdt, device=dev)
         flags = symm.empty(64, dtype=torch.int32, device=dev)
         grad.normal_()
@@ -81,14 +88,15 @@ def main(argv=None):
         epoch = [0]
 
         mc = int(getattr(hg, "multicast_ptr", 0) or 0)
-        if a.rs_adam_variant == 2 and mc == 0:
-            raise SystemExit("--rs_adam_variant 2 needs NVLS multicast; this group's symmetric memory has none")
+        if variant == 2 and mc == 0:
+            res[f"rs_adam_v2_{name}"] = {"skipped": "no NVLS multicast address for this group"}
+            continue
 
         def fused():
             epoch[0] += 1
             kw = dict(step=epoch[0], grad_scale=1.0, grad_f32=gdt == torch.float32, epoch=epoch[0], counter=counter,
                       **hyper)
-            if a.rs_adam_variant == 2:
+            if variant == 2:
                 k.rs_adam_nvls(mc, [int(x) for x in hf.buffer_ptrs], R, rank, sn, master, m, v, p16, **kw)
             else:
                 k.rs_adam([int(x) for x in hg.buffer_ptrs], [int(x) for x in hf.buffer_ptrs], R, rank, sn, master, m,
@@ -102,12 +110,20 @@ def main(argv=None):
         t_f, t_l = _time(fused), _time(library)
         k.check_status()
         gb = grad.element_size()
-        link_ms = (R - 1) / R * n * gb / (LINK_GBS * 1e9) * 1e3
-        hbm_ms = (sn * (12 + 14) + n * gb) / (peaks["hbm_gbs"] * 1e9) * 1e3   # state r/w + all R slices read once
-        res[f"rs_adam_{name}"] = {"fused_ms": t_f, "nccl_plus_adam_ms": t_l, "nvlink_roofline_ms": link_ms,
-                                  "hbm_term_ms": hbm_ms, "frac_of_nvlink_roofline": link_ms / t_f,
-                                  "frac_of_max_term": max(link_ms, hbm_ms) / t_f}
+        inbound = (R - 1) / R * n * gb
+        if variant == 2:
+            inbound = n / R * gb * 1.0      # the switch delivers the sum: one slice's worth of bytes comes in
+        link_ms = inbound / (LINK_GBS * 1e9) * 1e3
+        link_ms_meas = inbound / (LINK_GBS_MEASURED * 1e9) * 1e3
+        # optimizer state read + written (fp32 master, two moments: 24 B; bf16 copy written: 2 B) and the
+        # gradient slices this rank reads (its own from HBM)
+        hbm_ms = (sn * 26 + sn * gb) / (peaks["hbm_gbs"] * 1e9) * 1e3
+        res[f"rs_adam_v{variant}_{name}"] = {
+            "fused_ms": t_f, "nccl_plus_adam_ms": t_l, "nvlink_ms_at_900": link_ms, "nvlink_ms_at_770": link_ms_meas,
+            "hbm_term_ms": hbm_ms, "frac_of_roofline_900": max(link_ms, hbm_ms) / t_f,
+            "frac_of_roofline_770": max(link_ms_meas, hbm_ms) / t_f}
         dist.barrier()
+    k.set_rs_adam_variant(0)
 
     # ---------------------------------------------------------------- ag_gemm (QKV of a 7B block)
     N, K, M = 12288, 4096, a.tokens
@@ -120,20 +136,10 @@ def main(argv=None):
     symm.rendezvous(vflags, dist.group.WORLD)
     x = torch.randn(M, K, device=dev).to(torch.bfloat16)
     out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-    chunk = 1 << 15
-    cps = (sn * 2 + chunk - 1) // chunk
-    cflags = torch.zeros(R * cps, dtype=torch.int32, device=dev)
-    shard_ptrs = [int(hfull.buffer_ptrs[qq]) + qq * sn * 2 for qq in range(R)]
-    off = 4096  # the norm weight precedes the QKV weight in a block's flat layout
-    ep = [0]
-
-    def fused_ag():
-        ep[0] += 1
-        k.ag_gemm(x, full, off, (N, K), out, shard_ptrs=shard_ptrs, R=R, r=rank, shard_elems=sn, chunk_bytes=chunk,
-                  chunk_flags=cflags, epoch=ep[0], version_flags=vflags[2 * R:], need_version=0)
-
     shard = full[rank * sn:(rank + 1) * sn].clone()
     gathered = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    off = 4096  # the norm weight precedes the QKV weight in a block's flat layout
+    shard_ptrs = [int(hfull.buffer_ptrs[qq]) + qq * sn * 2 for qq in range(R)]
 
     def library_ag():
         dist.all_gather_into_tensor(gathered, shard)
@@ -142,12 +148,32 @@ def main(argv=None):
     def gemm_only():
         k.gemm(x, full[off:off + N * K].view(N, K), out)
 
-    t_f, t_l, t_g = _time(fused_ag), _time(library_ag), _time(gemm_only)
-    k.check_status()
-    link_ms = (R - 1) / R * n * 2 / (LINK_GBS * 1e9) * 1e3
+    t_l, t_g = _time(library_ag), _time(gemm_only)
+    inbound = (R - 1) / R * n * 2
+    link_ms, link_ms_meas = inbound / (LINK_GBS * 1e9) * 1e3, inbound / (LINK_GBS_MEASURED * 1e9) * 1e3
     gemm_ms = 2.0 * M * N * K / (peaks["bf16_tflops"] * 1e12) * 1e3
-    res["ag_gemm"] = {"fused_ms": t_f, "nccl_plus_gemm_ms": t_l, "gemm_alone_ms": t_g, "nvlink_roofline_ms": link_ms,
-                      "gemm_roofline_ms": gemm_ms, "frac_of_roofline": max(link_ms, gemm_ms) / t_f}
+    res["ag_gemm"] = {"nccl_plus_gemm_ms": t_l, "gemm_alone_ms": t_g, "nvlink_ms_at_900": link_ms,
+                      "nvlink_ms_at_770": link_ms_meas, "gemm_roofline_ms": gemm_ms}
+    import os
+
+    for kern in ("2cta", "1cta"):
+        for chunk in (1 << 15, 1 << 18):
+            os.environ["ZORSE_AG_GEMM"] = kern
+            cps = (sn * 2 + chunk - 1) // chunk
+            cflags = torch.zeros(R * cps, dtype=torch.int32, device=dev)
+            ep = [0]
+
+            def fused_ag():
+                ep[0] += 1
+                k.ag_gemm(x, full, off, (N, K), out, shard_ptrs=shard_ptrs, R=R, r=rank, shard_elems=sn,
+                          chunk_bytes=chunk, chunk_flags=cflags, epoch=ep[0], version_flags=vflags[2 * R:], need_version=0)
+
+            t_f = _time(fused_ag)
+            k.check_status()
+            res["ag_gemm"][f"{kern}_chunk{chunk >> 10}k"] = {
+                "fused_ms": t_f, "frac_of_roofline_900": max(link_ms, gemm_ms) / t_f,
+                "frac_of_roofline_770": max(link_ms_meas, gemm_ms) / t_f}
+    os.environ.pop("ZORSE_AG_GEMM", None)
     if rank == 0:
         print(json.dumps(res, indent=1))
         if a.out:

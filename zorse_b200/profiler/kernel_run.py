@@ -3,7 +3,8 @@
 zorse_b200.profiler.kernel_run <case>`).  Holds well under a few GB on the device.
 
 cases: gemm_fwd | gemm_dgrad | gemm_wgrad | flash_fwd1 | flash_fwd2 | flash_fwd4 | flash_fwd4p | flash_fwd4q | flash_bwd | flash_bwd2 |
-       rmsnorm | adam | ce
+       flash_bwd3 | flash_bwd3_dkv | flash_bwd3_dq | rmsnorm | adam | ce
+Prints the median CUDA-event time of the repetitions (a 256 MB write between them keeps operands out of L2).
 """
 from __future__ import annotations
 
@@ -38,7 +39,12 @@ def main(argv=None):
               "flash_fwd4p": lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, 0, version=4, flags=1),
               "flash_fwd4q": lambda: k.flash_fwd(qkv, B, S, Hq, Hkv, D, True, 0, version=4, flags=2),
               "flash_bwd": lambda: k.flash_bwd(do, qkv, out, lse, B, S, Hq, Hkv, D, True, 0, version=1),
-              "flash_bwd2": lambda: k.flash_bwd(do, qkv, out, lse, B, S, Hq, Hkv, D, True, 0, version=2)}[case]
+              "flash_bwd2": lambda: k.flash_bwd(do, qkv, out, lse, B, S, Hq, Hkv, D, True, 0, version=2),
+              "flash_bwd3": lambda: k.flash_bwd(do, qkv, out, lse, B, S, Hq, Hkv, D, True, 0, version=3),
+              "flash_bwd3_dkv": lambda: k._flash_bwd3(do, qkv, out, lse, B, S, Hq, Hkv, D, True, 0, None, parts=1),
+              "flash_bwd3_dq": lambda: k._flash_bwd3(do, qkv, out, lse, B, S, Hq, Hkv, D, True, 0, None, parts=2)}[case]
+        if case == "flash_bwd3_dq":
+            k.flash_bwd(do, qkv, out, lse, B, S, Hq, Hkv, D, True, 0, version=3)   # fills the statistics
     elif case == "rmsnorm":
         x, w = rnd(32768, 4096), torch.ones(4096, device=dev, dtype=torch.bfloat16)
         fn = lambda: k.norm_fwd(x, w, None, 1e-5, False)
@@ -52,11 +58,18 @@ def main(argv=None):
         fn = lambda: k.cross_entropy(lg, tg, 1.0, dlogits=lg)
     else:
         raise SystemExit(__doc__)
+    flush = torch.zeros(64 * 1024 * 1024, device=dev)
+    ts = []
     for _ in range(reps):
+        flush.add_(1.0)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
         fn()
-    torch.cuda.synchronize()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
     k.check_status()
-    print("ok", case)
+    print("ok", case, f"median {sorted(ts)[len(ts) // 2]:.4f} ms over {reps} runs")
 
 
 if __name__ == "__main__":
