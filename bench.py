@@ -139,7 +139,10 @@ def main():
     ap.add_argument("--vocab", type=int, default=32000)
     ap.add_argument("--schedule", default="auto")
     ap.add_argument("--reduce_dtype", default="bfloat16")
-    ap.add_argument("--collectives", default="library", choices=["library", "fused"])
+    ap.add_argument("--collectives", default="auto", choices=["auto", "library", "fused"],
+                    help="ZeRO collectives inside a stage's data-parallel group: this repository's fused NVLink kernels "
+                         "(all-gather + GEMM, reduce-scatter + Adam) or NCCL + separate kernels; auto = fused when "
+                         "every stage has at least two data-parallel ranks")
     ap.add_argument("--optimizer_in_backward", action="store_true")
     ap.add_argument("--recompute", default="auto", choices=["auto", "on", "off"])
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the JSON line says so)")
@@ -177,6 +180,8 @@ def main():
     cfg_dict, par = build_config(args.gpus, args.model, args.global_batch, args.microbatch, args.seq_len, args.vocab,
                                  args.reduce_dtype, schedule, args.layers, args.interleave, args.tp)
     cfg = parse_pipeline_dict(cfg_dict)
+    if args.collectives == "auto":
+        args.collectives = "fused" if (args.tp == 1 and all(len(s.gpu_ranks) >= 2 for s in cfg.stages)) else "library"
     if world > 1 and len(cfg.stages) > 1 and not args.no_preflight:
         # a p2p program that cannot complete would leave the GPUs spinning in NCCL kernels: replay it on the host first
         stuck = None

@@ -221,6 +221,18 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           umma_f16_ts(tmem_base + Cfg::DV_COL, r_s + acol, umma_desc_mnmajor(do_addr + kk * 2048, BLK), idesc_dkv,
                       (it | kk) != 0 ? 1u : 0u);
         }
+        if constexpr (!DQ) {
+          // S^T of the next step right behind D (which was P^T's last reader), ahead of E: the next step's
+          // exponentials then start 8 products earlier, while E and B are still running
+          if (it + 1 < n_iters) {
+            const int sn = (it + 1) % QS;
+            if (!mbar_wait(&qdo_full[sn], uint32_t((it + 1) / QS) & 1, wctx, ST_TIMEOUT_FULL)) break;
+            tr(TB_MMA_QDO_READY);
+            tc_fence_after();
+            issue_a(smem_u32(sQ + sn * Cfg::TILE_BYTES));
+            tr(TB_MMA_A_ISSUED);
+          }
+        }
 #pragma unroll
         for (int kk = 0; kk < BM / 16; ++kk) {
           const uint32_t acol = uint32_t(kk / 4) * 64 + uint32_t(kk % 4) * 8;
@@ -230,6 +242,12 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         umma_commit(&qdo_empty[st]);
         if constexpr (!DQ) {
           if (it + 1 == n_iters) umma_commit(dq_full);   // every dK / dV product is done: the write-out may start
+          tr(TB_MMA_DEF_ISSUED);
+          if (it + 1 < n_iters) {
+            issue_b(smem_u32(sDO + ((it + 1) % QS) * Cfg::TILE_BYTES));   // overwrites R_dP behind E, its last reader
+            tr(TB_MMA_B_ISSUED);
+          }
+          continue;
         }
         if constexpr (DQ) {
         // F: dQ = dS K  (reduction over the 128 keys) into R_dP, right behind E which read dS^T from it.
@@ -308,21 +326,32 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         tmem_ld32(lane_addr + uint32_t(half * 64 + c * 32), rs);
         tmem_wait_ld();
 #pragma unroll
-        for (int k = 0; k < 32; k += 4) {
-          float l4[4], e[4];
-          load4(lse_q, qc0 + c * 32 + k, l4);
+        // the mask test is hoisted out of the element loop: one branch per chunk, not one per element
+        if (need_mask) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int q = qc0 + c * 32 + k + u;
-            float pe = exp2f(fmaf(__uint_as_float(rs[k + u]), p.scale_log2, -l4[u]));
-            if (need_mask) {
+          for (int k = 0; k < 32; k += 4) {
+            float l4[4], e[4];
+            load4(lse_q, qc0 + c * 32 + k, l4);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int q = qc0 + c * 32 + k + u;
+              const float pe = exp2f(fmaf(__uint_as_float(rs[k + u]), p.scale_log2, -l4[u]));
               const bool vis = key_ok && (q < p.S) && (!p.causal || key <= q) && (p.window <= 0 || q - key < p.window);
-              pe = vis ? pe : 0.f;
+              e[u] = vis ? pe : 0.f;
             }
-            e[u] = pe;
+            pp[c * 16 + (k >> 1)] = pack_bf16x2(e[0], e[1]);
+            pp[c * 16 + (k >> 1) + 1] = pack_bf16x2(e[2], e[3]);
           }
-          pp[c * 16 + (k >> 1)] = pack_bf16x2(e[0], e[1]);
-          pp[c * 16 + (k >> 1) + 1] = pack_bf16x2(e[2], e[3]);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; k += 4) {
+            float l4[4], e[4];
+            load4(lse_q, qc0 + c * 32 + k, l4);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) e[u] = exp2f(fmaf(__uint_as_float(rs[k + u]), p.scale_log2, -l4[u]));
+            pp[c * 16 + (k >> 1)] = pack_bf16x2(e[0], e[1]);
+            pp[c * 16 + (k >> 1) + 1] = pack_bf16x2(e[2], e[3]);
+          }
         }
       }
       {
@@ -579,7 +608,7 @@ int zb_flash_bwd2(const void* d_o, const void* qkv, const void* o, const float* 
 // Scratch: stats fp32 [zb_flash_bwd2_stats_floats(B, S, Hq)], zeroed once by the caller.
 int zb_flash_bwd3(const void* d_o, const void* qkv, const void* o, const float* lse, void* dqkv, float* stats,
                   int B, int S, int Hq, int Hkv, int D, int causal, int window, float softmax_scale, int* status,
-                  int parts, cudaStream_t stream) {
+                  int parts, unsigned long long* trace, int trace_ctas, cudaStream_t stream) {
   // parts: 3 = the whole backward; 1 = statistics + dK / dV kernel only, 2 = dQ kernel only (needs the
   // statistics of an earlier call) - for timing the two halves separately
   using namespace zb;
@@ -605,9 +634,13 @@ int zb_flash_bwd3(const void* d_o, const void* qkv, const void* o, const float* 
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
   int rc = 0;
-  if (parts & 1)
-    rc = (D == 128) ? launch_bwd2<128, false, false>(QKV, DO, p, stats, s_pad, nullptr, 0, stream)
-                    : launch_bwd2<64, false, false>(QKV, DO, p, stats, s_pad, nullptr, 0, stream);
+  const bool trc = trace != nullptr && trace_ctas > 0;     // phase trace of the dK / dV kernel (as in zb_flash_bwd2)
+  if (parts & 1) {
+    if (D == 128) rc = trc ? launch_bwd2<128, true, false>(QKV, DO, p, stats, s_pad, trace, trace_ctas, stream)
+                           : launch_bwd2<128, false, false>(QKV, DO, p, stats, s_pad, nullptr, 0, stream);
+    else rc = trc ? launch_bwd2<64, true, false>(QKV, DO, p, stats, s_pad, trace, trace_ctas, stream)
+                  : launch_bwd2<64, false, false>(QKV, DO, p, stats, s_pad, nullptr, 0, stream);
+  }
   if (rc) return rc;
   return (parts & 2) ? attn_bwd_dq(QKV, DO, p, stats, s_pad, D, stream) : 0;
 }

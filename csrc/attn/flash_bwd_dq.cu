@@ -225,38 +225,49 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       if (!__all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], uint32_t(i >> 1) & 1, wctx, ST_TIMEOUT_TMEM_FULL))) { ok = false; break; }
       tc_fence_after();
       float pr[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32];
-        tmem_ld32(s_col + uint32_t(c * 32), rs);
+      {
+        // both 32-column chunks in flight before the first is used; the mask test is hoisted out of the
+        // element loops (one branch per tile, not per element)
+        uint32_t rs0[32], rs1[32];
+        tmem_ld32(s_col, rs0);
+        tmem_ld32(s_col + 32u, rs1);
         tmem_wait_ld();
+        const float nl = -lse_r;
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          float pe = exp2f(fmaf(__uint_as_float(rs[k]), p.scale_log2, -lse_r));
-          if (need_mask) {
-            const int col = kv0 + half * 64 + c * 32 + k;
+          pr[k] = exp2f(fmaf(__uint_as_float(rs0[k]), p.scale_log2, nl));
+          pr[32 + k] = exp2f(fmaf(__uint_as_float(rs1[k]), p.scale_log2, nl));
+        }
+        if (need_mask) {
+          const int col0 = kv0 + half * 64;
+#pragma unroll
+          for (int k = 0; k < 64; ++k) {
+            const int col = col0 + k;
             const bool vis = row_ok && (col < p.S) && (!p.causal || col <= row) && (p.window <= 0 || row - col < p.window);
-            pe = vis ? pe : 0.f;
+            pr[k] = vis ? pr[k] : 0.f;
           }
-          pr[c * 32 + k] = pe;
         }
       }
       if (!__all_sync(0xffffffffu, mbar_wait(dp_full, uint32_t(i) & 1, wctx, ST_TIMEOUT_TMEM_FULL))) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rd[32];
-        tmem_ld32(lane_addr + uint32_t(Cfg::DP_COL + half * 64 + c * 32), rd);
+      {
+        uint32_t rd0[32], rd1[32];
+        tmem_ld32(lane_addr + uint32_t(Cfg::DP_COL + half * 64), rd0);
+        tmem_ld32(lane_addr + uint32_t(Cfg::DP_COL + half * 64 + 32), rd1);
         tmem_wait_ld();
-        uint32_t ds[16];
+        uint32_t ds0[16], ds1[16];
+        // dS = P (dP - delta) scale = (P scale) dP - (P scale) delta: one multiply and one fma per element
+        const float nd = -delta_r;
 #pragma unroll
         for (int k = 0; k < 32; k += 2) {
-          const float s0 = pr[c * 32 + k] * (__uint_as_float(rd[k]) - delta_r) * p.scale;
-          const float s1 = pr[c * 32 + k + 1] * (__uint_as_float(rd[k + 1]) - delta_r) * p.scale;
-          ds[k >> 1] = pack_bf16x2(s0, s1);
+          const float a0 = pr[k] * p.scale, a1 = pr[k + 1] * p.scale;
+          const float b0 = pr[32 + k] * p.scale, b1 = pr[32 + k + 1] * p.scale;
+          ds0[k >> 1] = pack_bf16x2(a0 * (__uint_as_float(rd0[k]) + nd), a1 * (__uint_as_float(rd0[k + 1]) + nd));
+          ds1[k >> 1] = pack_bf16x2(b0 * (__uint_as_float(rd1[k]) + nd), b1 * (__uint_as_float(rd1[k + 1]) + nd));
         }
         // packed bf16 over this half's own first 32 columns: the other half's threads only touch their own 64
-        tmem_st16(s_col + uint32_t(c * 16), ds);
+        tmem_st16(s_col, ds0);
+        tmem_st16(s_col + 16u, ds1);
       }
       tmem_wait_st();
       tc_fence_before();

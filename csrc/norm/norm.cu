@@ -182,6 +182,12 @@ colsum_partial_kernel(const __nv_bfloat16* __restrict__ dy, int T, int N, int ld
 
 }  // namespace zb
 
+namespace zb {
+int norm_bwd_with_scratch(const void* dy, const void* x, const void* w, const float* stats, const void* dres, void* dx,
+                          float* part_dw, float* part_db, int P, void* dw, void* db, int T, int H, int ln, int grad_f32,
+                          int accumulate, cudaStream_t stream);
+}  // namespace zb
+
 extern "C" {
 
 int zb_norm_partial_rows(int T) {
@@ -213,32 +219,8 @@ int zb_norm_bwd(const void* dy, const void* x, const void* w, const float* stats
   using namespace zb;
   if (H % 8 != 0 || H > NORM_THREADS * NORM_MAXV * 8) ZB_FAIL(-1, "norm: H=%d unsupported", H);
   if (T <= 0) return 0;
-  const int P = zb_norm_partial_rows(T);
-  auto DY = static_cast<const __nv_bfloat16*>(dy);
-  auto X = static_cast<const __nv_bfloat16*>(x);
-  auto W = static_cast<const __nv_bfloat16*>(w);
-  auto DR = static_cast<const __nv_bfloat16*>(dres);
-  auto DX = static_cast<__nv_bfloat16*>(dx);
-  // rows up to 4096 wide need two 16-byte chunks per thread: half the registers, two CTAs per SM
-  if (H <= NORM_THREADS * 2 * 8) {
-    if (ln) norm_bwd_kernel<true, 2><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, part_db, T, H);
-    else norm_bwd_kernel<false, 2><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, nullptr, T, H);
-  } else {
-    if (ln) norm_bwd_kernel<true, NORM_MAXV><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, part_db, T, H);
-    else norm_bwd_kernel<false, NORM_MAXV><<<P, NORM_THREADS, 0, stream>>>(DY, X, W, stats, DR, DX, part_dw, nullptr, T, H);
-  }
-  ZB_CUDA_OK(cudaGetLastError());
-  const int nb = (H + 255) / 256;
-  if (dw != nullptr) {
-    if (grad_f32) colsum_accumulate_kernel<float><<<nb, 256, 0, stream>>>(part_dw, P, H, static_cast<float*>(dw), accumulate);
-    else colsum_accumulate_kernel<__nv_bfloat16><<<nb, 256, 0, stream>>>(part_dw, P, H, static_cast<__nv_bfloat16*>(dw), accumulate);
-  }
-  if (ln && db != nullptr) {
-    if (grad_f32) colsum_accumulate_kernel<float><<<nb, 256, 0, stream>>>(part_db, P, H, static_cast<float*>(db), accumulate);
-    else colsum_accumulate_kernel<__nv_bfloat16><<<nb, 256, 0, stream>>>(part_db, P, H, static_cast<__nv_bfloat16*>(db), accumulate);
-  }
-  ZB_CUDA_OK(cudaGetLastError());
-  return 0;
+  return norm_bwd_with_scratch(dy, x, w, stats, dres, dx, part_dw, part_db, zb_norm_partial_rows(T), dw, db, T, H, ln,
+                               grad_f32, accumulate, stream);
 }
 
 // Bias gradient: out[n] (+)= sum_t dy[t, n]. part: fp32 scratch [64, N].

@@ -56,3 +56,8 @@ extern "C" int zb_norm_bwd_noalloc(const void* dy, const void* x, const void* w,
   return zb::norm_bwd_with_scratch(dy, x, w, stats, dres, dx, part_dw, part_db, P, dw, db, T, H, ln, grad_f32,
                                    accumulate, stream);
 }
+
+extern "C" int zb_norm_bwd_noalloc_init(void) {
+  int err = 0;
+  return scratch_for_current_device(&err) != nullptr ? 0 : err;
+}

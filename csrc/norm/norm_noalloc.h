@@ -27,7 +27,12 @@ extern "C" {
 //
 // * Calls no cudaMalloc / cudaFree and no allocating library routine.
 // * The first call on each device looks up the device address of the scratch array (with that
-//   device current); make that first call outside of any stream capture.
+//   device current).  With lazy module loading that lookup is also the moment the driver loads the
+//   module, reserves the 8 MiB and takes its own locks: treat the first call per device as a
+//   start-up call - make it outside of any stream capture AND outside the restricted contexts this
+//   entry point is meant for (not from an allocator callback, not from a thread that must stay off
+//   the allocator's lock).  `zb_norm_bwd_noalloc_init()` does only this lookup, for start-up code
+//   that has nothing to compute yet.
 // * All calls share the one scratch array, and the array keeps the previous call's contents
 //   (every call overwrites what it later reads, so nothing needs clearing by the caller).
 //   Two calls that overlap on the GPU - different streams, or different host threads - race on
@@ -35,6 +40,10 @@ extern "C" {
 int zb_norm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* stats, const void* dres,
                         void* dx, void* dw, void* db, int T, int H, int ln, int grad_f32, int accumulate,
                         cudaStream_t stream);
+
+// Resolves (and caches) the scratch address for the current device without launching anything.
+// Returns 0 on success, -2 on a CUDA error.  Call once per device at start-up.
+int zb_norm_bwd_noalloc_init(void);
 
 #ifdef __cplusplus
 }

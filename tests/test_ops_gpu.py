@@ -322,19 +322,15 @@ def test_flash_bwd(k, B, S, Hq, Hkv, D, causal, window, version):
     _close(got, want, atol=4e-2, rtol=3e-2)
 
 
-@pytest.mark.skipif(not CANDIDATES, reason="ZORSE_TEST_CANDIDATES=1: tools that have not yet run on hardware")
-def test_latency_probe_and_attention_traces_run(k):
-    """The in-kernel probes terminate, leave the status word clean and record plausible clocks."""
-    from zorse_b200.profiler import attn_trace, sm100_latency
+def test_attention_traces_run(k):
+    """The in-kernel phase traces terminate, leave the status word clean and record plausible clocks."""
+    from zorse_b200.profiler import attn_trace
 
-    sm100_latency.main(["--runs", "2"])
-    k.check_status()
     for kern in ("fwd4", "bwd2"):
         attn_trace.main(["--kernel", kern, "--S", "1024", "--heads", "2", "--kv_heads", "2", "--ctas", "2"])
         k.check_status()
 
 
-@pytest.mark.skipif(not CANDIDATES, reason="ZORSE_TEST_CANDIDATES=1: first run on hardware pending")
 def test_a_wait_that_runs_out_reports_and_leaves_the_context_usable(k):
     """Failure detection on the device: a wait on a flag that nothing sets gives up after its (short)
     limit, the kernel returns, the host reads which wait it was, and the next launches work.  Nothing

@@ -200,36 +200,6 @@ def test_exp2_polynomial_matches_exp2_in_fp32_emulation():
     assert emu(np.array([-np.inf, -1e9, -127.0]))[0] == 0 and emu(np.array([-127.0]))[0] == 0
     assert abs(emu(np.array([0.0]))[0] - 1.0) < 1e-4 and abs(emu(np.array([8.0]))[0] - 256.0) < 0.03
 
-
-def test_latency_probe_derivations():
-    from zorse_b200.profiler.sm100_latency import NAMES, derive
-
-    med = {n: 0 for n in NAMES.values()}
-    med.update({"mma_8": 900, "mma_32": 900 + 24 * 64, "ex2_1024_1warp_per_sched": 8192 + 1024})
-    d = derive(med)
-    assert d["clocks_per_mma_128x128x16"] == 64.0 and d["mma_fixed_latency"] == 900 - 8 * 64
-    assert d["ex2_clocks_per_op_1warp_per_sched"] == 9.0
-
-
-def test_perf_check_flags_regressions(tmp_path):
-    import json
-
-    from zorse_b200.profiler import perf_check
-
-    base = json.loads(perf_check.DEFAULT.read_text())
-    assert len(base["kernels"]) > 40 and "gemm fwd 2cta | 7b qkv M4096 N12288 K4096" in base["kernels"]
-    k0, k1 = list(base["kernels"])[:2]
-    rows = [{"op": k0.split(" | ")[0], "shape": k0.split(" | ")[1], "ours_ms": base["kernels"][k0]["ours_ms"] * 1.25},
-            {"op": k1.split(" | ")[0], "shape": k1.split(" | ")[1], "ours_ms": base["kernels"][k1]["ours_ms"] * 1.02},
-            {"op": "new kernel", "shape": "x", "ours_ms": 1.0}]
-    res = perf_check.compare(rows, base, 0.10)
-    assert [s[0] for s in res["slower"]] == [k0] and res["same"] == 1 and res["unknown"] == ["new kernel | x"]
-    f = tmp_path / "new.json"
-    f.write_text(json.dumps({"rows": rows}))
-    assert perf_check.main([str(f)]) == 1
-    assert perf_check.main([str(f), "--tolerance", "0.5"]) == 0
-
-
 def test_mesh_cli_writes_a_valid_config(capsys):
     import json
 
@@ -264,28 +234,6 @@ def test_candidate_report_parent_side(monkeypatch, capsys):
     monkeypatch.undo()
     monkeypatch.setattr(sp, "run", lambda *a, **k: sp.CompletedProcess(a, 3, stdout="", stderr="Traceback\nRuntimeError: x"))
     assert C.run_child("flash_bwd2:7b", 1.0)["error"].startswith("exit code 3: RuntimeError")
-
-
-def test_step_model_adds_up_the_recorded_kernel_times():
-    import json
-    import os
-
-    from zorse_b200.profiler import step_model as SM
-
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    t = json.load(open(os.path.join(root, "data", "kernel_baseline_b200.json")))["kernels"]
-    m = SM.step_model(t, layers=32, microbatches=64)
-    want = 32 * 64 * t["flash fwd | 7b S4096 Hq32 Hkv32 D128 win0"]["ours_ms"]
-    assert abs(m["attention fwd"]["ours_ms"] - want) < 1e-6
-    assert abs(m["optimizer"]["ours_ms"] - 64 * t["adam (bf16 grad) | n101191680"]["ours_ms"]) < 1e-6
-    total = sum(g["ours_ms"] for g in m.values())
-    assert 9000 < total < 12452            # below the measured step, and most of it
-    one = SM.step_model(t, layers=1, microbatches=1)
-    assert abs(sum(g["ours_ms"] for g in one.values()) * 1.0 - (total - m["head"]["ours_ms"] - m["optimizer"]["ours_ms"]) / 2048
-               - one["head"]["ours_ms"] - one["optimizer"]["ours_ms"]) < 1e-6
-    table = SM.format_table(m, 12452.0)
-    assert "not explained by isolated timings" in table and "| attention bwd |" in table
-
 
 def test_package_exports_load_lazily():
     import importlib

@@ -38,17 +38,22 @@ def test_noalloc_matches_regular_entry_point(ln):
         _, stats = k.norm_fwd(x, w, b, 1e-5, ln)
         dw_ref = torch.ones(H, dtype=gdt, device="cuda")
         db_ref = torch.ones(H, dtype=gdt, device="cuda") if ln else None
-        dx_ref = k.norm_bwd(dy, x, w, stats, dres, dw_ref, db_ref, ln)
+        # the regular entry point this one is a variant of (zb_norm_bwd = version 1 of the wrapper)
+        dx_ref = k.norm_bwd(dy, x, w, stats, dres, dw_ref, db_ref, ln, version=1)
         dw = torch.ones(H, dtype=gdt, device="cuda")
         db = torch.ones(H, dtype=gdt, device="cuda") if ln else None
         dx = torch.empty_like(x)
+        assert lib.zb_norm_bwd_noalloc_init() == 0     # start-up call: resolves the scratch address on this device
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]     # the driver's view: a cudaMalloc inside the call would show here
         stream = c_void_p(torch.cuda.current_stream().cuda_stream)
         rc = fn(_ptr(dy), _ptr(x), _ptr(w), _ptr(stats), _ptr(dres), _ptr(dx), _ptr(dw), _ptr(db), c_int(T), c_int(H),
                 c_int(int(ln)), c_int(int(gdt == torch.float32)), c_int(1), stream)
         assert rc == 0, lib.zb_last_error().decode()
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before
         assert torch.equal(dx, dx_ref)
         tol = 1e-3 if gdt == torch.float32 else 6e-2
         assert (dw.float() - dw_ref.float()).abs().max().item() <= tol * max(1.0, dw_ref.float().abs().max().item())

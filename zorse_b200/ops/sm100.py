@@ -348,7 +348,7 @@ def _flash_bwd2(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale, trace,
     return dqkv
 
 
-def _flash_bwd3(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale, parts: int = 3):
+def _flash_bwd3(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale, parts: int = 3, trace=None, trace_ctas: int = 0):
     key = (qkv.device.index, B, S, Hq)
     if key not in _attn_scratch3:
         n = lib().zb_flash_bwd2_stats_floats(c_int(B), c_int(S), c_int(Hq))
@@ -358,7 +358,8 @@ def _flash_bwd3(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale, parts:
     sc = (1.0 / math.sqrt(D)) if scale is None else scale
     _check(lib().zb_flash_bwd3(_p(do), _p(qkv), _p(o), _p(lse), _p(dqkv), _p(stats), c_int(B), c_int(S), c_int(Hq),
                                c_int(Hkv), c_int(D), c_int(int(causal)), c_int(window), c_float(sc),
-                               _p(status_word(qkv.device)), c_int(parts), _stream()), "flash_bwd3")
+                               _p(status_word(qkv.device)), c_int(parts), _p(trace),
+                               c_int(trace_ctas if trace is not None else 0), _stream()), "flash_bwd3")
     global _launches
     _launches += 2  # statistics + the second main kernel
     return dqkv
@@ -382,7 +383,8 @@ def flash_fwd4_trace_buffer(device, ctas: int) -> torch.Tensor:
 _attn_scratch: dict = {}
 
 
-# 0 = by head dimension: version 2 for d = 64 (1.38x faster there), version 1 otherwise; 1 / 2 force a version
+# 0 = default = version 3 (two kernels, no atomics: 1.46x faster than version 1 at 4096 tokens, d = 128);
+# 1 / 2 / 3 force a version
 ATTN_BWD_VERSION = int(os.environ.get("ZORSE_ATTN_BWD", "0"))
 
 
@@ -391,15 +393,15 @@ def flash_bwd(do, qkv, o, lse, B: int, S: int, Hq: int, Hkv: int, D: int, causal
               trace_ctas: int = 0):
     """Returns dqkv packed like qkv. Scratch (fp32 dQ accumulator, delta) is cached per shape
     and device; the accumulator is left zeroed by the kernel that converts it to bf16.
-    version 1 (default): scores with queries on the TMEM lanes, P and dS staged through shared
+    version 1: scores with queries on the TMEM lanes, P and dS staged through shared
     memory; version 2: transposed scores, P^T / dS^T consumed from tensor memory, two Q/dO stages
-    (`trace`: zeroed buffer from `flash_bwd2_trace_buffer`); version 3: two kernels without atomics, dK / dV per
+    (`trace`: zeroed buffer from `flash_bwd2_trace_buffer`); version 3 (default): two kernels without atomics, dK / dV per
     key tile and dQ per query tile (scores are formed twice; no fp32 dQ accumulator)."""
     _bf16(do, "do"); _bf16(qkv, "qkv")
     assert do.is_contiguous() and qkv.is_contiguous() and o.is_contiguous()
-    ver = version or ATTN_BWD_VERSION or (2 if D == 64 else 1)
+    ver = version or ATTN_BWD_VERSION or 3
     if ver == 3:
-        return _flash_bwd3(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale)
+        return _flash_bwd3(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale, trace=trace, trace_ctas=trace_ctas)
     if ver == 2:
         return _flash_bwd2(do, qkv, o, lse, B, S, Hq, Hkv, D, causal, window, scale, trace, trace_ctas)
     key = (qkv.device.index, B, S, Hq, D)

@@ -80,7 +80,8 @@ def format_summary(summary: dict) -> str:
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default="fwd4", choices=["fwd4", "bwd2"])
+    ap.add_argument("--kernel", default="fwd4", choices=["fwd4", "bwd2", "bwd3"],
+                    help="bwd3: the dK / dV kernel of the two-kernel backward (same phase codes as bwd2, no dQ phases)")
     ap.add_argument("--S", type=int, default=4096)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv_heads", type=int, default=32)
@@ -110,10 +111,11 @@ def main(argv=None):
         codes = BWD_CODES
         do = (torch.randn(a.S, a.heads * a.D, device=dev, generator=g) * 0.5).to(torch.bfloat16)
         out, lse = k.flash_fwd(qkv, 1, a.S, a.heads, a.kv_heads, a.D, True, a.window)
+        ver = 3 if a.kernel == "bwd3" else 2
         for _ in range(2):
-            k.flash_bwd(do, qkv, out, lse, 1, a.S, a.heads, a.kv_heads, a.D, True, a.window, version=2)
+            k.flash_bwd(do, qkv, out, lse, 1, a.S, a.heads, a.kv_heads, a.D, True, a.window, version=ver)
         buf = k.flash_bwd2_trace_buffer(dev, a.ctas)
-        k.flash_bwd(do, qkv, out, lse, 1, a.S, a.heads, a.kv_heads, a.D, True, a.window, version=2, trace=buf,
+        k.flash_bwd(do, qkv, out, lse, 1, a.S, a.heads, a.kv_heads, a.D, True, a.window, version=ver, trace=buf,
                     trace_ctas=a.ctas)
     if dev == "cuda":
         torch.cuda.synchronize()

@@ -3,7 +3,8 @@
 zorse_b200.profiler.kernel_run <case>`).  Holds well under a few GB on the device.
 
 cases: gemm_fwd | gemm_dgrad | gemm_wgrad | flash_fwd1 | flash_fwd2 | flash_fwd4 | flash_fwd4p | flash_fwd4q | flash_bwd | flash_bwd2 |
-       flash_bwd3 | flash_bwd3_dkv | flash_bwd3_dq | rmsnorm | adam | ce
+       flash_bwd3 | flash_bwd3_dkv | flash_bwd3_dq | rmsnorm | rmsnorm_bwd | layernorm_bwd | rope | swiglu_fwd | swiglu_bwd |
+       embedding_fwd | embedding_bwd | adam | ce
 Prints the median CUDA-event time of the repetitions (a 256 MB write between them keeps operands out of L2).
 """
 from __future__ import annotations
@@ -48,6 +49,29 @@ def main(argv=None):
     elif case == "rmsnorm":
         x, w = rnd(32768, 4096), torch.ones(4096, device=dev, dtype=torch.bfloat16)
         fn = lambda: k.norm_fwd(x, w, None, 1e-5, False)
+    elif case in ("rmsnorm_bwd", "layernorm_bwd"):
+        ln = case.startswith("layer")
+        x, w, dy, dres = rnd(32768, 4096), torch.ones(4096, device=dev, dtype=torch.bfloat16), rnd(32768, 4096), rnd(32768, 4096)
+        b = torch.zeros(4096, device=dev, dtype=torch.bfloat16) if ln else None
+        _, st = k.norm_fwd(x, w, b, 1e-5, ln)
+        dw = torch.zeros(4096, device=dev)
+        db = torch.zeros(4096, device=dev) if ln else None
+        fn = lambda: k.norm_bwd(dy, x, w, st, dres, dw, db, ln)
+    elif case == "rope":
+        S, H, D = 4096, 64, 128                                  # q and k heads of a 7B block, 8 sequences: 537 MB
+        buf = rnd(8 * S, 3 * 32 * D)
+        pos = torch.arange(S, device=dev, dtype=torch.float32)[:, None]
+        inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device=dev, dtype=torch.float32) / D))[None, :]
+        cs = torch.cat([torch.cos(pos * inv), torch.sin(pos * inv)], dim=1).contiguous()
+        fn = lambda: k.rope_(buf, cs, S, H, D)
+    elif case in ("swiglu_fwd", "swiglu_bwd"):
+        gu, dh = rnd(16384, 2 * 11008), rnd(16384, 11008)        # 721 MB + 361 MB
+        fn = (lambda: k.swiglu_fwd(gu)) if case.endswith("fwd") else (lambda: k.swiglu_bwd(gu, dh))
+    elif case in ("embedding_fwd", "embedding_bwd"):
+        ids = torch.randint(0, 32000, (65536,), device=dev)
+        table, dout = rnd(32000, 4096), rnd(65536, 4096)
+        dtable = torch.zeros(32000, 4096, device=dev)
+        fn = (lambda: k.embedding_fwd(ids, table)) if case.endswith("fwd") else (lambda: k.embedding_bwd(ids, dout, dtable))
     elif case == "adam":
         n = 64 * 1024 * 1024
         p, m, v = (torch.zeros(n, device=dev) for _ in range(3))
