@@ -349,3 +349,37 @@ def test_drawings_of_the_gpu_graph_and_its_partition(tmp_path):
     assert txt.startswith("<svg") and "stroke-dasharray" in txt and "Balance: 1.00" in txt
     assert V.visualize_partition(G, parts, str(tmp_path / "plan.svg"))
     assert (tmp_path / "plan_graph.svg").exists() and (tmp_path / "plan_partitioned.svg").exists()
+
+
+def test_latency_driven_microbatch_routing():
+    """Ranks of unequal speed: the first stage hands its microbatches on in the order they finish, the next stage
+    feeds the rank with most work ahead first (reference zorse_utils/pipeline_comm.py:193-303); equal ranks reduce to
+    round-robin; the plan stays a valid many-to-many routing and the 1F1B order built on it completes."""
+    from zorse_b200.parallel.p2p_plan import create_static_comm_plans, latency_owners, plan_1f1b_order
+    from zorse_b200.parallel.p2p_sim import preflight
+
+    assert latency_owners([2, 2], [1.0, 1.0], receiver=False) == [0, 1, 0, 1]
+    assert latency_owners([2, 2], [1.0, 1.0], receiver=True) == [1, 0, 1, 0]
+    # a rank twice as fast with three times the microbatches: it finishes 0, 1, 2 at t = 0, 1, 2; the slow one at 0
+    assert latency_owners([3, 1], [1.0, 2.0], receiver=False) == [1, 0, 0, 0]
+    # receiving side: work ahead 3, 2, 1 (fast rank) and 2 (slow rank): fast, then the tie goes to the slower rank
+    assert latency_owners([3, 1], [1.0, 2.0], receiver=True) == [0, 1, 0, 0]
+    d = {"model_name": "tiny_llama", "global_batch_size": 8, "microbatch_size": 1, "sequence_length": 64,
+         "comm_plan": "latency", "rank_latency_ms": {"0": 1.0, "1": 2.0, "2": 1.5, "3": 1.5},
+         "pipeline_config": [
+             {"gpu_ranks": [0, 1], "num_microbatches_per_rank": [6, 2], "layer_partition": [0, 2], "zero_config": [[0, 1]]},
+             {"gpu_ranks": [2, 3], "num_microbatches_per_rank": [4, 4], "layer_partition": [2, 4], "zero_config": [[2, 3]]}]}
+    cfg = tc.parse_pipeline_dict(d)
+    assert cfg.comm_plan == "latency" and cfg.rank_latency_ms[1] == 2.0
+    assert tc.to_dict(cfg)["rank_latency_ms"] == {"0": 1.0, "1": 2.0, "2": 1.5, "3": 1.5}
+    plans = create_static_comm_plans(cfg)            # validates mirror-image sends / receives and counts
+    assert len(plans[0].stages[0].microbatches) == 6 and len(plans[1].stages[0].microbatches) == 2
+    # per microbatch rank 0 needs 2 ms (2 layers x 1.0), rank 1 needs 4 ms: completions at 0, 2, 4, 6, 8, 10 and 0, 4;
+    # ties go to the slower rank first (the reference sorts (time, -latency, rank) tuples)
+    assert plans[0].stages[0].microbatches == [1, 2, 4, 5, 6, 7] and plans[1].stages[0].microbatches == [0, 3]
+    base = tc.parse_pipeline_dict({k: v for k, v in d.items() if k not in ("comm_plan", "rank_latency_ms")})
+    assert create_static_comm_plans(base)[1].stages[0].microbatches == [2, 6]          # by counts alone
+    order = plan_1f1b_order(cfg)
+    assert sorted(op for op, _ in order[1]) == ["B", "B", "F", "F"]
+    for sched in ("layer_major", "zero2", "1f1b"):
+        assert preflight(cfg, sched) is None, sched      # the p2p program of every schedule completes under NCCL's rules

@@ -133,6 +133,19 @@ def test_mixed_widths_and_hybrid(schedule):
     _check(res, cfg)
 
 
+@pytest.mark.parametrize("schedule", ["zero2", "1f1b"])
+def test_latency_driven_routing_trains_like_the_oracle(schedule):
+    """The same 4-rank plan with the microbatches routed by per-rank latencies (a slow rank on each stage): the
+    routing changes who carries which microbatch, not the result."""
+    pipe = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [3, 1], "layer_partition": [0, 1], "zero_config": [[0, 1]]},
+            {"gpu_ranks": [2, 3], "num_microbatches_per_rank": [1, 3], "layer_partition": [1, 4], "zero_config": [[2], [3]]}]
+    cfg = tiny_cfg(pipe)
+    cfg["comm_plan"] = "latency"
+    cfg["rank_latency_ms"] = {"0": 1.0, "1": 2.5, "2": 3.0, "3": 1.0}
+    res = run_workers(4, _worker, cfg, {"schedule": schedule}, 2)
+    _check(res, cfg)
+
+
 def test_interleaved_stages_three_ranks():
     """1 -> 2 -> 1 widths with rank 0 hosting the first and the last stage."""
     pipe = [{"gpu_ranks": [0], "num_microbatches_per_rank": [4], "layer_partition": [0, 1], "zero_config": [[0]]},

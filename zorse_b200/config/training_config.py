@@ -134,6 +134,11 @@ class PipelineConfig:
     grad_norm_compat: str = "mean"
     unused_ranks: tuple[int, ...] = ()   # ranks of the job that own no stage (the planner may leave a slow GPU out)
     tensor_parallel_size: int = 1        # processes per rank number of this file (see the module docstring)
+    # "interleave": microbatches are dealt to a stage's ranks by their counts alone; "latency": by the ranks'
+    # per-layer latencies as well (reference zorse_utils/pipeline_comm.py:193-303), from `rank_latency_ms`
+    # (rank -> ms per layer and microbatch) or, when absent, from the profile table and the ranks' GPU models
+    comm_plan: str = "interleave"
+    rank_latency_ms: Optional[dict] = None
     extra: dict = field(default_factory=dict)
 
     @property
@@ -228,7 +233,7 @@ def parse_pipeline_dict(d: dict[str, Any]) -> PipelineConfig:
              "fused_optimizer", "interleave_degree", "latency", "autocast_dtype", "reduce_dtype",
              "split_microbatches_evenly", "skip_compute_sync", "interleave_stage_sync", "gloo_batch_recv",
              "alternate_nccl_gloo", "large_model_init", "schedule", "activation_recompute", "activation_offload",
-             "grad_norm_compat", "zero_level", "unused_ranks", "tensor_parallel_size"}
+             "grad_norm_compat", "zero_level", "unused_ranks", "tensor_parallel_size", "comm_plan", "rank_latency_ms"}
     cfg = PipelineConfig(
         model_name=str(d["model_name"]), global_batch_size=gbs, microbatch_size=mbs,
         sequence_length=int(d["sequence_length"]), stages=stages, vocab_size=int(d.get("vocab_size", 49152)),
@@ -243,6 +248,8 @@ def parse_pipeline_dict(d: dict[str, Any]) -> PipelineConfig:
         grad_norm_compat=str(d.get("grad_norm_compat", "mean")),
         unused_ranks=tuple(int(r) for r in d.get("unused_ranks", ())),
         tensor_parallel_size=int(d.get("tensor_parallel_size", 1)),
+        comm_plan=str(d.get("comm_plan", "interleave")),
+        rank_latency_ms={int(k): float(v) for k, v in d["rank_latency_ms"].items()} if d.get("rank_latency_ms") else None,
         extra={k: v for k, v in d.items() if k not in known})
     cfg.validate()
     return cfg
@@ -290,5 +297,9 @@ def to_dict(cfg: PipelineConfig) -> dict[str, Any]:
         d["activation_offload"] = cfg.activation_offload
     if cfg.grad_norm_compat != "mean":
         d["grad_norm_compat"] = cfg.grad_norm_compat
+    if cfg.comm_plan != "interleave":
+        d["comm_plan"] = cfg.comm_plan
+    if cfg.rank_latency_ms:
+        d["rank_latency_ms"] = {str(k): v for k, v in cfg.rank_latency_ms.items()}
     d.update(cfg.extra)
     return d

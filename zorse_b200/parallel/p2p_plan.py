@@ -57,9 +57,34 @@ class RankCommPlan:
     stages: dict[int, StageCommPattern] = field(default_factory=dict)
 
 
-def stage_owners(stage) -> list[int]:
-    """Global rank owning each global microbatch on `stage`."""
-    idx = interleave_owners(stage.num_microbatches_per_rank)
+def latency_owners(counts: Sequence[int], latency: Sequence[float], receiver: bool) -> list[int]:
+    """Owner (index into the stage's rank list) of each microbatch when the ranks differ in speed
+    (reference zorse_utils/pipeline_comm.py:193-303, a greedy matching per stage boundary).
+
+    A rank with `latency` ms per microbatch finishes its i-th microbatch at `latency * i`.  On the sending
+    side of a boundary the g-th microbatch is the g-th to finish (`receiver=False`: sorted by completion
+    time, slower rank first on ties, as the reference's tuples sort); on the receiving side it goes to the rank with the g-th largest amount
+    of work still ahead of it, `latency * (count - i)` (`receiver=True`), so the ranks that need longest are
+    fed first.  Equal ranks with equal counts get the plain round-robin either way."""
+    items = []
+    for k, (c, lat) in enumerate(zip(counts, latency)):
+        for i in range(c):
+            items.append(((-lat * (c - i), -lat, -k) if receiver else (lat * i, -lat, k)))
+    items.sort()
+    return [abs(k) for _, _, k in items]
+
+
+def stage_owners(stage, cfg=None, position: int = 0) -> list[int]:
+    """Global rank owning each global microbatch on `stage`.  With `cfg.comm_plan == "latency"` and per-rank
+    latencies in `cfg.rank_latency_ms`, the first stage deals its microbatches in the order they finish and every
+    later stage takes them in the order of the work its ranks still have ahead (see `latency_owners`)."""
+    lat = getattr(cfg, "rank_latency_ms", None) if cfg is not None else None
+    if cfg is not None and getattr(cfg, "comm_plan", "interleave") == "latency" and lat \
+            and all(r in lat for r in stage.gpu_ranks):
+        idx = latency_owners(stage.num_microbatches_per_rank, [lat[r] * stage.num_layers for r in stage.gpu_ranks],
+                             receiver=position > 0)
+    else:
+        idx = interleave_owners(stage.num_microbatches_per_rank)
     return [stage.gpu_ranks[k] for k in idx]
 
 
@@ -67,7 +92,7 @@ def create_static_comm_plans(cfg) -> dict[int, RankCommPlan]:
     """rank -> plan, for every rank named in the config."""
     stages = cfg.stages
     M = cfg.num_microbatches
-    owners = [stage_owners(s) for s in stages]
+    owners = [stage_owners(s, cfg, i) for i, s in enumerate(stages)]
     plans: dict[int, RankCommPlan] = {}
     for si, st in enumerate(stages):
         for r in st.gpu_ranks:
@@ -159,7 +184,7 @@ def plan_1f1b_order(cfg, f_cost: float = 1.0, b_cost: float = 2.0) -> dict[int, 
     itself is one valid execution.  Ranks host one stage each."""
     stages = cfg.stages
     P, M = len(stages), cfg.num_microbatches
-    owners = [stage_owners(s) for s in stages]
+    owners = [stage_owners(s, cfg, i) for i, s in enumerate(stages)]
     stage_of: dict[int, int] = {}
     for si, s in enumerate(stages):
         for r in s.gpu_ranks:

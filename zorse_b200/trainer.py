@@ -92,6 +92,8 @@ class Trainer:
             self.transport = LaneTransport(self.transport, tp, self.tp_index)
             if self.gloo_transport is not None:
                 self.gloo_transport = LaneTransport(self.gloo_transport, tp, self.tp_index)
+        if cfg.comm_plan == "latency" and not cfg.rank_latency_ms:
+            cfg.rank_latency_ms = self._rank_latencies(cfg, tp)
         plans = create_static_comm_plans(cfg)
         self.plan = plans.get(self.lane)     # None on a rank the plan leaves idle
         offload_act = cfg.activation_offload if opt.activation_offload is None else opt.activation_offload
@@ -188,6 +190,22 @@ class Trainer:
             dist.all_reduce(t)
             v = t.cpu()
         return float(v[0])
+
+    def _rank_latencies(self, cfg, tp: int) -> dict:
+        """ms per layer and microbatch of every rank of the plan, for the latency-driven microbatch routing: every
+        process reports its GPU model, the profile table (data/model_latencies.json) gives forward + backward time of
+        one block of this model on that GPU (reference zorse_utils/pipeline_comm.py:176-191, 214-226)."""
+        from .planner.latency import load_model_compute_latencies_per_gpu
+        from .utils.metrics import clean_gpu_name
+
+        name = clean_gpu_name(torch.cuda.get_device_name(self.device)) if self.device.type == "cuda" else "cpu"
+        names = [name] * self.world
+        if G.is_dist():
+            names = [None] * self.world
+            dist.all_gather_object(names, name, group=self.gloo_group)
+        lat = load_model_compute_latencies_per_gpu(cfg.model_name, sorted(set(names)), cfg.sequence_length,
+                                                   cfg.autocast_dtype, cfg.microbatch_size)
+        return {lane: lat[names[lane * tp]].total for lane in range(self.world // tp)}
 
     def measure_exposed_comm(self, on: bool = True) -> None:
         """Brackets every compute-stream wait on a collective or a p2p receive with timing events."""
