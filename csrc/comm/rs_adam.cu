@@ -213,6 +213,103 @@ rs_adam_kernel(const RsAdamParams p) {
   }
 }
 
+// Default variant.  All loads of an iteration - optimizer state and the R gradient slices of V vectors per thread -
+// are issued before anything is consumed, so one NVLink round trip covers them all and a thread keeps V * (R + 6)
+// 16-byte requests in flight.  RT bounds R at compile time (register arrays sized for the group, not for 8).
+// Same protocol, same summation order (rank 0, 1, ...) and same arithmetic as the generic kernel above.
+template <typename GT, int RT, int V>
+__global__ void __launch_bounds__(256)
+rs_adam_early_kernel(const RsAdamParams p) {
+  constexpr int N = GradVec<GT>::N;
+  __shared__ int s_ok;
+  if (blockIdx.x == 0 && threadIdx.x < p.R) {
+    __threadfence_system();
+    st_release_sys(p.flags[threadIdx.x] + 0 * p.R + p.r, p.epoch);
+  }
+  if (threadIdx.x == 0) {
+    bool ok = true;
+    for (int q = 0; q < p.R && ok; ++q)
+      ok = flag_wait_ge(p.flags[p.r] + 0 * p.R + q, p.epoch, p.wait_ns, p.status, ST_TIMEOUT_FLAG);
+    s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  const long nvec = s_ok ? p.shard_n / N : 0;
+  const long lo = long(p.r) * p.shard_n;
+  const long stride = long(gridDim.x) * blockDim.x;
+  for (long i0 = blockIdx.x * long(blockDim.x) + threadIdx.x; i0 < nvec; i0 += stride * V) {
+    float pm[V][N], mm[V][N], vv[V][N];
+    uint4 raw[V][RT];
+    bool on[V];
+#pragma unroll
+    for (int u = 0; u < V; ++u) {
+      const long i = i0 + u * stride;
+      on[u] = i < nvec && zb_in_bounds(lo + (i + 1) * N <= long(p.R) * p.shard_n, p.status, 5);
+      if (on[u]) {
+#pragma unroll
+        for (int q = 0; q < RT; ++q)
+          if (q < p.R) raw[u][q] = ld_v4_relaxed_sys(static_cast<const GT*>(p.grad[q]) + lo + i * N);
+#pragma unroll
+        for (int k = 0; k < N; k += 4) {
+          *reinterpret_cast<float4*>(pm[u] + k) = *reinterpret_cast<const float4*>(p.master + i * N + k);
+          *reinterpret_cast<float4*>(mm[u] + k) = *reinterpret_cast<const float4*>(p.m + i * N + k);
+          *reinterpret_cast<float4*>(vv[u] + k) = *reinterpret_cast<const float4*>(p.v + i * N + k);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < V; ++u) {
+      const long i = i0 + u * stride;
+      if (!on[u]) continue;
+      float g[N];
+#pragma unroll
+      for (int k = 0; k < N; ++k) g[k] = 0.f;
+#pragma unroll
+      for (int q = 0; q < RT; ++q) {
+        if (q < p.R) {
+          float t[N];
+          GradVec<GT>::unpack(raw[u][q], t);
+#pragma unroll
+          for (int k = 0; k < N; ++k) g[k] += t[k];
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        float gg = g[k] * p.grad_scale;
+        if (p.weight_decay != 0.f) gg += p.weight_decay * pm[u][k];
+        mm[u][k] = p.beta1 * mm[u][k] + (1.f - p.beta1) * gg;
+        vv[u][k] = p.beta2 * vv[u][k] + (1.f - p.beta2) * gg * gg;
+        pm[u][k] -= (p.lr / p.bc1) * (mm[u][k] / (sqrtf(vv[u][k]) / p.bc2_sqrt + p.eps));
+      }
+#pragma unroll
+      for (int k = 0; k < N; k += 4) {
+        *reinterpret_cast<float4*>(p.master + i * N + k) = *reinterpret_cast<float4*>(pm[u] + k);
+        *reinterpret_cast<float4*>(p.m + i * N + k) = *reinterpret_cast<float4*>(mm[u] + k);
+        *reinterpret_cast<float4*>(p.v + i * N + k) = *reinterpret_cast<float4*>(vv[u] + k);
+      }
+      if (N == 8) {
+        uint4 o;
+        o.x = pack_bf16x2(pm[u][0], pm[u][1]); o.y = pack_bf16x2(pm[u][2], pm[u][3]);
+        o.z = pack_bf16x2(pm[u][4], pm[u][5]); o.w = pack_bf16x2(pm[u][6], pm[u][7]);
+        *reinterpret_cast<uint4*>(p.p16 + i * N) = o;
+      } else {
+        *reinterpret_cast<uint2*>(p.p16 + i * N) = make_uint2(pack_bf16x2(pm[u][0], pm[u][1]), pack_bf16x2(pm[u][2], pm[u][3]));
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ unsigned int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(p.counter, 1u) == gridDim.x - 1) ? 1u : 0u;
+  __syncthreads();
+  if (s_last) {
+    if (s_ok && threadIdx.x < p.R) {
+      st_release_sys(p.flags[threadIdx.x] + 1 * p.R + p.r, p.epoch);
+      st_release_sys(p.flags[threadIdx.x] + 2 * p.R + p.r, p.epoch);
+    }
+    if (threadIdx.x == 0) *p.counter = 0u;
+  }
+}
+
 // Waits until flags[which*R + q] >= epoch for every q (one thread; bounded).
 __global__ void wait_flags_kernel(const int* flags, int R, int which, int epoch, unsigned long long wait_ns,
                                   int* status) {
@@ -237,7 +334,7 @@ peer_pull_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long n1
 
 }  // namespace zb
 
-static int g_rs_adam_variant = 0;
+static int g_rs_adam_variant = 1;   // 1 = loads issued up front (default), 0 = one peer after another
 
 static int rs_adam_launch(const void* const* grad_ptrs, const void* grad_mc, void* p16_mc, int* const* flag_ptrs, int R, int r,
                           long shard_n, float* master, float* m, float* v, void* p16, float lr, float beta1,
@@ -272,8 +369,15 @@ static int rs_adam_launch(const void* const* grad_ptrs, const void* grad_mc, voi
     if (grad_f32) rs_adam_kernel<float, RS_NVLS><<<blocks, 256, 0, stream>>>(p);
     else rs_adam_kernel<__nv_bfloat16, RS_NVLS><<<blocks, 256, 0, stream>>>(p);
   } else if (g_rs_adam_variant == 1) {
-    if (grad_f32) rs_adam_kernel<float, RS_EARLY><<<blocks, 256, 0, stream>>>(p);
-    else rs_adam_kernel<__nv_bfloat16, RS_EARLY><<<blocks, 256, 0, stream>>>(p);
+#define ZB_EARLY(GT_)                                                                              \
+    do {                                                                                           \
+      if (R <= 2) rs_adam_early_kernel<GT_, 2, 2><<<blocks, 256, 0, stream>>>(p);                  \
+      else if (R <= 4) rs_adam_early_kernel<GT_, 4, 1><<<blocks, 256, 0, stream>>>(p);             \
+      else rs_adam_early_kernel<GT_, 8, 1><<<blocks, 256, 0, stream>>>(p);                         \
+    } while (0)
+    if (grad_f32) ZB_EARLY(float);
+    else ZB_EARLY(__nv_bfloat16);
+#undef ZB_EARLY
   } else {
     if (grad_f32) rs_adam_kernel<float, RS_PLAIN><<<blocks, 256, 0, stream>>>(p);
     else rs_adam_kernel<__nv_bfloat16, RS_PLAIN><<<blocks, 256, 0, stream>>>(p);
@@ -284,7 +388,7 @@ static int rs_adam_launch(const void* const* grad_ptrs, const void* grad_mc, voi
 
 extern "C" {
 
-// 0 = measured kernel, 1 = candidate that requests the optimizer state and all R slices up front.
+// 1 (default) = the optimizer state and all R slices are requested up front; 0 = one peer after another.
 void zb_set_rs_adam_variant(int v) { g_rs_adam_variant = v; }
 
 // grad_ptrs / flag_ptrs: host arrays of R device pointers (peer-mapped), ordered by rank in

@@ -208,7 +208,11 @@ def main():
     if case == "tp_kernels":
         tp_kernels()
     elif case.startswith("fused_kernels"):
-        fused_kernels(int(case[-1]) if case[-2:] in ("v1", "v2", "v3") else 0)
+        if case[-2:] in ("v2", "v3"):
+            fused_kernels(int(case[-1]))
+        else:
+            fused_kernels(1)      # the default reduce-scatter kernel (loads issued up front)
+            fused_kernels(0)      # one peer after another
     else:
         losses, masters, tr = train_case(case)
         # same job with the other collectives mode must land on the same parameters

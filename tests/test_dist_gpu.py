@@ -38,7 +38,7 @@ CANDIDATES = os.environ.get("ZORSE_TEST_CANDIDATES") == "1"   # paths that have 
 
 
 @pytest.mark.skipif(_ngpu() < 2 or not CANDIDATES, reason="needs 2 GPUs and ZORSE_TEST_CANDIDATES=1")
-@pytest.mark.parametrize("case", ["fused_kernels_v1", "fused_kernels_v2", "fused_kernels_v3"])
+@pytest.mark.parametrize("case", ["fused_kernels_v2", "fused_kernels_v3"])
 def test_two_gpus_candidates(case):
     out = _run(2, case, timeout=300)
     assert "WORKER_OK" in out

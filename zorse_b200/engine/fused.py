@@ -38,7 +38,7 @@ CHUNK_BYTES = int(os.environ.get("ZORSE_AG_CHUNK_BYTES", str(1 << 18)))
 # candidates of the reduce-scatter + Adam kernel that use NVSwitch multicast (csrc/comm/rs_adam.cu):
 # 2 = gradient slice summed inside the switch; 3 = as 2, and the refreshed bf16 shard is stored through
 # the multicast address of the unsharded buffers, so that no all-gather follows an update at all
-RS_ADAM_MODE = int(os.environ.get("ZORSE_RS_ADAM_VARIANT", "0"))
+RS_ADAM_MODE = int(os.environ.get("ZORSE_RS_ADAM_VARIANT", "1"))
 
 
 @dataclass

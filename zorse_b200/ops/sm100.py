@@ -60,7 +60,7 @@ def lib():
             _build.build()
         _lib = ctypes.CDLL(str(path))
         _lib.zb_last_error.restype = ctypes.c_char_p
-        if os.environ.get("ZORSE_RS_ADAM_VARIANT", "0") != "0":      # candidate, see csrc/comm/rs_adam.cu
+        if "ZORSE_RS_ADAM_VARIANT" in os.environ:      # 0 / 1 select a peer-load kernel (1 is the library default)
             _lib.zb_set_rs_adam_variant(c_int(int(os.environ["ZORSE_RS_ADAM_VARIANT"])))
     return _lib
 
