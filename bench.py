@@ -83,6 +83,28 @@ def build_config(n, model, gbs, mbs, seq, vocab, reduce_dtype, schedule, layers_
     return cfg, par
 
 
+def baseline_config(n_cfg: int, world: int):
+    """The other configurations of the benchmark set (all on 8 GPUs), run through this same harness with
+    `--baseline_config N`: (model, global batch, microbatch, sequence, vocabulary, stages, stage extras, schedule,
+    trainer options).  2: Llama-3.2-1B, 2 stages x 4-way ZeRO-2, optimizer in backward, ZeRO-2 pipeline schedule.
+    4: Mistral-7B (sliding window 4096), 2 stages x 4-way ZeRO-3 with the uneven 14 / 18 layer split, sequence 8192.
+    5: OPT-13B, 8 stages x 1, parameters offloaded to pinned host memory, optimizer in backward, layer-major schedule."""
+    if world != 8:
+        raise SystemExit(f"--baseline_config {n_cfg} is an 8-GPU configuration (WORLD_SIZE={world})")
+    if n_cfg == 2:
+        return dict(model="llama3.2_1b", gbs=128, mbs=2, seq=2048, vocab=128256, schedule="zero2", par="pp2xdp4-zero2",
+                    stages=[([0, 1, 2, 3], 0, 8), ([4, 5, 6, 7], 8, 16)], extra={"zero_level": 2},
+                    opts=dict(optimizer_in_backward=True))
+    if n_cfg == 4:
+        return dict(model="mistral_7b", gbs=32, mbs=1, seq=8192, vocab=32000, schedule="1f1b", par="pp2xdp4-zero3-14/18",
+                    stages=[([0, 1, 2, 3], 0, 14), ([4, 5, 6, 7], 14, 32)], extra={}, opts={})
+    if n_cfg == 5:
+        return dict(model="opt_13b", gbs=128, mbs=2, seq=2048, vocab=50272, schedule="layer_major", par="pp8xdp1-offload",
+                    stages=[([i], 5 * i, 5 * i + 5) for i in range(8)], extra={},
+                    opts=dict(optimizer_in_backward=True, offload_model_params=True))
+    raise SystemExit("--baseline_config takes 2, 4 or 5 (3 is the default benchmark, 1 is the CPU test configuration)")
+
+
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons with nvidia-smi (read-only) during the timed region."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -154,6 +176,8 @@ def main():
                     help="1F1B: input gradients are sent upstream before the weight-gradient GEMMs (same arithmetic)")
     ap.add_argument("--no_preflight", action="store_true",
                     help="skip the host-side replay of the schedule's p2p program before the first multi-stage step")
+    ap.add_argument("--baseline_config", type=int, default=0,
+                    help="run configuration 2, 4 or 5 of the benchmark set (8 GPUs) instead of the headline one")
     ap.add_argument("--skip_e2e", action="store_true")
     ap.add_argument("--ref_schedule", default="zero2", choices=["zero2", "layer_major", "no_overlap", "two_stage_sync", "flashflex"],
                     help="--impl reference only: which of the reference's schedules runs (its flag --zero2_pipeline etc.)")
@@ -177,11 +201,28 @@ def main():
     schedule = args.schedule
     if schedule == "auto":
         schedule = "1f1b_interleaved" if (args.interleave > 1 and args.gpus >= 4) else "1f1b"
-    cfg_dict, par = build_config(args.gpus, args.model, args.global_batch, args.microbatch, args.seq_len, args.vocab,
-                                 args.reduce_dtype, schedule, args.layers, args.interleave, args.tp)
+    extra_opts = {}
+    if args.baseline_config:
+        bc = baseline_config(args.baseline_config, world)
+        args.model, args.global_batch, args.microbatch, args.seq_len, args.vocab = bc["model"], bc["gbs"], bc["mbs"], bc["seq"], bc["vocab"]
+        schedule, par, extra_opts = (bc["schedule"] if args.schedule == "auto" else schedule), bc["par"], bc["opts"]
+        M = args.global_batch // args.microbatch
+        pipe = []
+        for ranks, a, b in bc["stages"]:
+            base, rem = divmod(M, len(ranks))
+            pipe.append({"gpu_ranks": ranks, "num_microbatches_per_rank": [base + (1 if i < rem else 0) for i in range(len(ranks))],
+                         "layer_partition": [a, b], "zero_config": [ranks], **bc["extra"]})
+        cfg_dict = {"model_name": args.model, "global_batch_size": args.global_batch, "microbatch_size": args.microbatch,
+                    "sequence_length": args.seq_len, "vocab_size": args.vocab, "fused_optimizer": True,
+                    "autocast_dtype": "bfloat16", "reduce_dtype": args.reduce_dtype, "pipeline_config": pipe,
+                    "schedule": schedule}
+    else:
+        cfg_dict, par = build_config(args.gpus, args.model, args.global_batch, args.microbatch, args.seq_len, args.vocab,
+                                     args.reduce_dtype, schedule, args.layers, args.interleave, args.tp)
     cfg = parse_pipeline_dict(cfg_dict)
     if args.collectives == "auto":
-        args.collectives = "fused" if (args.tp == 1 and all(len(s.gpu_ranks) >= 2 for s in cfg.stages)) else "library"
+        fused_ok = args.tp == 1 and all(len(s.gpu_ranks) >= 2 for s in cfg.stages) and not extra_opts.get("offload_model_params")
+        args.collectives = "fused" if fused_ok else "library"
     if world > 1 and len(cfg.stages) > 1 and not args.no_preflight:
         # a p2p program that cannot complete would leave the GPUs spinning in NCCL kernels: replay it on the host first
         stuck = None
@@ -205,10 +246,11 @@ def main():
         predicted = predict_step_ms(cfg_dict, schedule, recompute=recompute, defer_wgrad=args.defer_wgrad)
     except Exception as e:      # noqa: BLE001 - a missing profile table must not stop the measurement
         sys.stderr.write(f"[bench] no planner prediction: {e!r}\n")
-    tr = Trainer(cfg, TrainerOptions(schedule=schedule, ops="sm100", optimizer_in_backward=args.optimizer_in_backward,
-                                     collectives=args.collectives, activation_recompute=recompute,
-                                     defer_wgrad=args.defer_wgrad,
-                                     model_overrides={} if args.layers is None else {"layers": args.layers}))
+    topt = dict(schedule=schedule, ops="sm100", optimizer_in_backward=args.optimizer_in_backward,
+                collectives=args.collectives, activation_recompute=recompute, defer_wgrad=args.defer_wgrad,
+                model_overrides={} if args.layers is None else {"layers": args.layers})
+    topt.update(extra_opts)
+    tr = Trainer(cfg, TrainerOptions(**topt))
     from zorse_b200.ops import sm100
     from zorse_b200.utils.health import Watchdog
 
@@ -320,6 +362,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
             "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights", "impl": "ours",
+            "baseline_config": args.baseline_config or 3,
             "config": {"model": args.model + ("" if args.layers is None else f"[layers={args.layers} DEBUG]"),
                        "global_batch": args.global_batch, "seq_len": args.seq_len, "microbatch": args.microbatch,
                        "parallelism": par, "schedule": schedule, "activation_recompute": tr.schedule.recompute,

@@ -349,12 +349,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const uint4* src = ag.src[peer];
       uint4* dst = ag.dst + long(peer) * shard16;
       long i = beg + ct;
-      for (; i + 7 * 128 < end; i += 8 * 128) {
-        uint4 v[8];
+      // 16 requests of 16 bytes in flight per thread (32 KiB per CTA, 4.7 MB per GPU): enough to cover the
+      // ~3 us NVLink round trip at the link rate while the tensor-core warps take most of the issue slots
+      for (; i + 15 * 128 < end; i += 16 * 128) {
+        uint4 v[16];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = ld_v4_relaxed_sys(src + i + u * 128);
+        for (int u = 0; u < 16; ++u) v[u] = ld_v4_relaxed_sys(src + i + u * 128);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) dst[i + u * 128] = v[u];
+        for (int u = 0; u < 16; ++u) dst[i + u * 128] = v[u];
       }
       for (; i < end; i += 128) dst[i] = ld_v4_relaxed_sys(src + i);
       // the rows go from these stores (generic proxy) to the TMA loads of some CTA's producer (async proxy)

@@ -86,12 +86,12 @@ def main(argv=None):
     ts = []
     for _ in range(reps):
         flush.add_(1.0)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
         fn()
-        b.record()
+        ev1.record()
         torch.cuda.synchronize()
-        ts.append(a.elapsed_time(b))
+        ts.append(ev0.elapsed_time(ev1))
     k.check_status()
     print("ok", case, f"median {sorted(ts)[len(ts) // 2]:.4f} ms over {reps} runs")
 
