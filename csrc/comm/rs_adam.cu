@@ -372,7 +372,7 @@ static int rs_adam_launch(const void* const* grad_ptrs, const void* grad_mc, voi
 #define ZB_EARLY(GT_)                                                                              \
     do {                                                                                           \
       if (R <= 2) rs_adam_early_kernel<GT_, 2, 2><<<blocks, 256, 0, stream>>>(p);                  \
-      else if (R <= 4) rs_adam_early_kernel<GT_, 4, 1><<<blocks, 256, 0, stream>>>(p);             \
+      else if (R <= 4) rs_adam_early_kernel<GT_, 4, 2><<<blocks, 256, 0, stream>>>(p);             \
       else rs_adam_early_kernel<GT_, 8, 1><<<blocks, 256, 0, stream>>>(p);                         \
     } while (0)
     if (grad_f32) ZB_EARLY(float);

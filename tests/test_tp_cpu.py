@@ -459,4 +459,5 @@ def test_tp_lane_through_the_gpu_op_layer_dry_run(layout):
     res = run_workers(2, _worker_gpu_ops_dry_run, cfg)
     for r in res:
         assert r["calls"] > 100 and not r["bad"], r["bad"]
-        assert "zb_flash_fwd" in r["names"] and "zb_norm_bwd" in r["names"]
+        names = set(r["names"])
+        assert names & {"zb_flash_fwd", "zb_flash_fwd4"} and names & {"zb_norm_bwd", "zb_norm_bwd2"}   # whichever versions are default
