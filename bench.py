@@ -174,6 +174,8 @@ def main():
                     help="tensor-parallel processes per lane (not the baseline configuration; the JSON line says so)")
     ap.add_argument("--defer_wgrad", action="store_true",
                     help="1F1B: input gradients are sent upstream before the weight-gradient GEMMs (same arithmetic)")
+    ap.add_argument("--defer_tail_wgrad", type=int, default=0,
+                    help="1F1B: weight gradients of the last stage's last N layers (head first) run after its last backward")
     ap.add_argument("--no_preflight", action="store_true",
                     help="skip the host-side replay of the schedule's p2p program before the first multi-stage step")
     ap.add_argument("--baseline_config", type=int, default=0,
@@ -248,6 +250,7 @@ def main():
         sys.stderr.write(f"[bench] no planner prediction: {e!r}\n")
     topt = dict(schedule=schedule, ops="sm100", optimizer_in_backward=args.optimizer_in_backward,
                 collectives=args.collectives, activation_recompute=recompute, defer_wgrad=args.defer_wgrad,
+                defer_tail_wgrad=args.defer_tail_wgrad,
                 model_overrides={} if args.layers is None else {"layers": args.layers})
     topt.update(extra_opts)
     tr = Trainer(cfg, TrainerOptions(**topt))
@@ -368,6 +371,7 @@ def main():
                        "parallelism": par, "schedule": schedule, "activation_recompute": tr.schedule.recompute,
                        "optimizer": "Adam fp32 master+moments, step inside the timed region",
                        "reduce_dtype": args.reduce_dtype, "collectives": args.collectives, "defer_wgrad": args.defer_wgrad,
+                       "defer_tail_wgrad": args.defer_tail_wgrad,
                        "l2": "per-step working set (>100 GB of parameters, optimizer state and activations) far exceeds the 126 MB L2; no flush needed"},
             "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches, "loss": loss_val, "loss_first_step": first_loss,
             "exposed_comm_ms_per_step": exposed_ms, "exposed_comm_breakdown": exposed_parts,

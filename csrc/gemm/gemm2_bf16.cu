@@ -349,14 +349,26 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const uint4* src = ag.src[peer];
       uint4* dst = ag.dst + long(peer) * shard16;
       long i = beg + ct;
-      // 16 requests of 16 bytes in flight per thread (32 KiB per CTA, 4.7 MB per GPU): enough to cover the
-      // ~3 us NVLink round trip at the link rate while the tensor-core warps take most of the issue slots
-      for (; i + 15 * 128 < end; i += 16 * 128) {
-        uint4 v[16];
+      // Software-pipelined copy: the 8 requests of the next batch are issued before the 8 values of the current one are
+      // stored, so a thread always has 8 - 16 peer loads of 16 bytes in flight (up to 32 KiB per CTA, 4.7 MB per GPU)
+      // instead of draining to zero between batches.
+      constexpr int UB = 8;
+      const long step = long(UB) * 128;
+      if (i + (UB - 1) * 128 < end) {
+        uint4 cur[UB], nxt[UB];
 #pragma unroll
-        for (int u = 0; u < 16; ++u) v[u] = ld_v4_relaxed_sys(src + i + u * 128);
+        for (int u = 0; u < UB; ++u) cur[u] = ld_v4_relaxed_sys(src + i + u * 128);
+        for (; i + step + (UB - 1) * 128 < end; i += step) {
 #pragma unroll
-        for (int u = 0; u < 16; ++u) dst[i + u * 128] = v[u];
+          for (int u = 0; u < UB; ++u) nxt[u] = ld_v4_relaxed_sys(src + i + step + u * 128);
+#pragma unroll
+          for (int u = 0; u < UB; ++u) dst[i + u * 128] = cur[u];
+#pragma unroll
+          for (int u = 0; u < UB; ++u) cur[u] = nxt[u];
+        }
+#pragma unroll
+        for (int u = 0; u < UB; ++u) dst[i + u * 128] = cur[u];
+        i += step;
       }
       for (; i < end; i += 128) dst[i] = ld_v4_relaxed_sys(src + i);
       // the rows go from these stores (generic proxy) to the TMA loads of some CTA's producer (async proxy)

@@ -33,7 +33,8 @@ def main(argv=None) -> int:
         offload_model_params=args.offload_model_params, gloo_p2p=args.gloo_p2p, collectives=args.collectives,
         activation_recompute=False if args.no_recompute else None,
         activation_offload=True if args.offload_activations_to_host else None, lr=args.lr, seed=args.seed,
-        backend=args.backend, pipeline_log=plog, shift_labels=args.shift_labels, defer_wgrad=args.defer_wgrad)
+        backend=args.backend, pipeline_log=plog, shift_labels=args.shift_labels, defer_wgrad=args.defer_wgrad,
+        defer_tail_wgrad=args.defer_tail_wgrad)
     if args.nvtx:
         from ..utils import ranges
 

@@ -21,11 +21,14 @@ class ScheduleBase:
     recompute_default = True
 
     def __init__(self, stages: list[PipelineStage], cfg, *, recompute: Optional[bool] = None, pipeline_log=None,
-                 defer_wgrad: bool = False):
+                 defer_wgrad: bool = False, defer_tail_wgrad: int = 0):
         self.stages = sorted(stages, key=lambda s: s.stage_id)
         self.cfg = cfg
         # 1F1B schedules: send a microbatch's input gradient upstream before computing its weight gradients
         self.defer_wgrad = defer_wgrad
+        # 1F1B, last stage: the weight gradients of the output head and of this many blocks before it run after the
+        # stage's last backward, in the time the last stage otherwise idles while the other stages drain
+        self.defer_tail_wgrad = int(defer_tail_wgrad)
         self.recompute = self.recompute_default if recompute is None else recompute
         self.log = pipeline_log
         self.device = stages[0].device if stages else torch.device("cpu")

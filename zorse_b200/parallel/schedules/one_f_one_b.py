@@ -37,6 +37,15 @@ class OneFOneBSchedule(ScheduleBase):
         st.engine.prefetch_all()
         stage_pos = [s.stage_id for s in self.cfg.stages].index(st.stage_id)
         warm = min(len(self.cfg.stages) - stage_pos - 1, M)
+        # The last stage carries the output head on top of its blocks, so it sets the pipeline's period, and it
+        # is also the stage that idles longest at the end of a step (while the other stages drain).  With
+        # `defer_tail_wgrad = k` the weight-gradient GEMMs of its last k layers (the head first) are taken out of
+        # every microbatch's backward and run once, after the stage's last backward, inside that idle time.  The
+        # operands (dlogits, layer inputs) of all microbatches stay alive until then.  Same additions in the same
+        # order per bucket entry, so the result is bit-identical.
+        hold = set()
+        if self.defer_tail_wgrad > 0 and st.is_last and len(self.cfg.stages) > 1 and st.can_defer_wgrad():
+            hold = set(range(max(L - self.defer_tail_wgrad, 0), L))
         # Receives are posted when they are needed, never ahead: torch serialises the p2p
         # operations of one process group on each rank, so a receive posted one microbatch early
         # would sit in front of this rank's own send of the current microbatch, and across four
@@ -65,8 +74,8 @@ class OneFOneBSchedule(ScheduleBase):
             for li in reversed(range(L)):
                 units[li].acquire()
                 units[li].grad_views()
-                dy = st.backward_layer(li, mbl, dy, self._tgt(st, targets, mbl), self.recompute)
-                if last and asynchronous:
+                dy = st.backward_layer(li, mbl, dy, self._tgt(st, targets, mbl), self.recompute, hold_wgrad=li in hold)
+                if last and asynchronous and li not in hold:
                     units[li].reduce_grads()
             if not st.is_first:
                 st.send_bwd(mbl, dy)
@@ -75,7 +84,8 @@ class OneFOneBSchedule(ScheduleBase):
                 st.wgrad.flush()
             if last and not asynchronous:
                 for li in reversed(range(L)):
-                    units[li].reduce_grads()
+                    if li not in hold:
+                        units[li].reduce_grads()
 
         if self.order is not None:
             for op, i in self.order:
@@ -88,12 +98,21 @@ class OneFOneBSchedule(ScheduleBase):
                 bwd(i)
             for i in range(M - warm, M):
                 bwd(i)
+        if hold and M > 0:
+            # the held-back weight gradients, then the reductions of the layers they belong to (last layer first,
+            # the order every rank of the stage uses)
+            st.wgrad_tail.active = False
+            st.wgrad_tail.flush()
+            for li in sorted(hold, reverse=True):
+                units[li].acquire()
+                units[li].grad_views()
+                units[li].reduce_grads()
         if M == 0:
             # a rank without microbatches still joins every reduction, in the order its peers use
-            # (last layer first)
-            for u in reversed(units):
-                u.grad_views()
-                u.reduce_grads()
+            # (last layer first; layers whose weight gradients are held back come after the others)
+            for li in [i for i in reversed(range(L)) if i not in hold] + sorted(hold, reverse=True):
+                units[li].grad_views()
+                units[li].reduce_grads()
         st.flush()
         st.engine.optimizer_step()
         st.engine.finish_step()

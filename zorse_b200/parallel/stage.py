@@ -168,6 +168,7 @@ class PipelineStage:
                                   hidden=self.hidden, kernels=ops.k)
         self.act_dtype = engine_cfg.compute_dtype
         self.wgrad = DeferredWgrad(ops)      # what backward_layer hands to the layers as their ops
+        self.wgrad_tail = DeferredWgrad(ops)  # weight gradients held back until the stage's last backward is done
         self.stash = ActivationStash(device, activation_offload, streams.copy)
         self.saved: dict = {}
         self.loss_sum: Optional[torch.Tensor] = None
@@ -282,7 +283,9 @@ class PipelineStage:
             return None
         return y
 
-    def backward_layer(self, li: int, mbl: int, dy, targets, recompute: bool):
+    def backward_layer(self, li: int, mbl: int, dy, targets, recompute: bool, hold_wgrad: bool = False):
+        """`hold_wgrad`: this layer's weight-gradient GEMMs go to the tail queue (`wgrad_tail`), which the schedule
+        flushes once, after the stage's last backward."""
         layer = self.layers[li]
         c = self.ctx(mbl, targets if layer.kind == "head" else None)
         if recompute:
@@ -298,4 +301,7 @@ class PipelineStage:
         else:
             sv = self.saved.pop((li, mbl))
         with phase("bwd." + layer.kind):
+            if hold_wgrad:
+                self.wgrad_tail.active = True
+                return layer.backward(dy, c, self.wgrad_tail, sv)
             return layer.backward(dy, c, self.wgrad if self.wgrad.active else self.ops, sv)

@@ -46,6 +46,7 @@ class TrainerOptions:
     model_overrides: dict = field(default_factory=dict)
     pipeline_log: object = None
     defer_wgrad: bool = False              # 1F1B: input gradients are sent upstream before the weight-gradient GEMMs run
+    defer_tail_wgrad: int = 0              # 1F1B, last stage: head (+ this many - 1 blocks) weight gradients after its last backward; 0 = off
     shift_labels: bool = False             # synthetic targets = next token of the inputs (last position ignored)
 
 
@@ -111,7 +112,7 @@ class Trainer:
         recompute = cfg.activation_recompute if opt.activation_recompute is None else opt.activation_recompute
         name = cfg.schedule or opt.schedule
         self.schedule = build_schedule(name, self.stages, cfg, recompute=recompute, pipeline_log=opt.pipeline_log,
-                                       defer_wgrad=opt.defer_wgrad)
+                                       defer_wgrad=opt.defer_wgrad, defer_tail_wgrad=opt.defer_tail_wgrad)
         self.step_idx = 0
 
     # ------------------------------------------------------------------ data
