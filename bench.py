@@ -30,7 +30,14 @@ import time
 BASELINE_TOKENS_PER_S = None  # the reference publishes no B200 number
 
 
-def parallel_plan(n: int, layers: int):
+def parallel_plan(n: int, layers: int, pp: int = 0):
+    if pp:
+        # not the benchmark's plan: pp equal stages of n / pp data-parallel ranks each (the JSON line names it)
+        if n % pp or layers < pp:
+            raise SystemExit(f"--pp {pp} does not divide {n} GPUs / {layers} layers")
+        d, q = n // pp, layers // pp
+        return ([(list(range(i * d, (i + 1) * d)), i * q, (i + 1) * q if i < pp - 1 else layers) for i in range(pp)],
+                f"pp{pp}xdp{d}" + ("-zero3" if d > 1 else ""))
     if n == 1:
         return [(list(range(1)), 0, layers)], "pp1xdp1"
     if n == 2:
@@ -57,13 +64,13 @@ def interleave_plan(stages, layers: int, v: int):
     return out
 
 
-def build_config(n, model, gbs, mbs, seq, vocab, reduce_dtype, schedule, layers_override=None, interleave=1, tp=1):
+def build_config(n, model, gbs, mbs, seq, vocab, reduce_dtype, schedule, layers_override=None, interleave=1, tp=1, pp=0):
     from zorse_b200.models import registry
 
     spec = registry.get_spec(model, layers=layers_override)
     if n % tp:
         raise SystemExit(f"--tp {tp} does not divide --gpus {n}")
-    stages, par = parallel_plan(n // tp, spec.layers)     # with tp > 1 the plan numbers lanes of tp processes
+    stages, par = parallel_plan(n // tp, spec.layers, pp)  # with tp > 1 the plan numbers lanes of tp processes
     if tp > 1:
         par += f"-tp{tp}"
     if interleave > 1 and len(stages) > 1:
@@ -172,6 +179,8 @@ def main():
                     help="model chunks per rank group (>1 selects the interleaved 1F1B schedule on 4 and 8 GPUs)")
     ap.add_argument("--tp", type=int, default=1,
                     help="tensor-parallel processes per lane (not the baseline configuration; the JSON line says so)")
+    ap.add_argument("--pp", type=int, default=0,
+                    help="pipeline stages (not the baseline plan for this GPU count; the JSON line says so)")
     ap.add_argument("--defer_wgrad", action="store_true",
                     help="1F1B: input gradients are sent upstream before the weight-gradient GEMMs (same arithmetic)")
     ap.add_argument("--defer_tail_wgrad", type=int, default=0,
@@ -220,7 +229,7 @@ def main():
                     "schedule": schedule}
     else:
         cfg_dict, par = build_config(args.gpus, args.model, args.global_batch, args.microbatch, args.seq_len, args.vocab,
-                                     args.reduce_dtype, schedule, args.layers, args.interleave, args.tp)
+                                     args.reduce_dtype, schedule, args.layers, args.interleave, args.tp, args.pp)
     cfg = parse_pipeline_dict(cfg_dict)
     if args.collectives == "auto":
         fused_ok = args.tp == 1 and all(len(s.gpu_ranks) >= 2 for s in cfg.stages) and not extra_opts.get("offload_model_params")

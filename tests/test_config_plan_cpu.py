@@ -317,6 +317,20 @@ def test_fixed_plan_prediction_has_the_1f1b_and_gpipe_shapes():
     assert deferred["ramp_ms"] < four["ramp_ms"] and deferred["steady_ms"] == four["steady_ms"]
     gp = predict_step_ms(cfg(4), "zero2", table=table)
     assert gp["recompute"] and gp["form"] == "gpipe" and gp["steady_ms"] > four["steady_ms"] * 1.25
+    # layer-major on several stages: a stage passes microbatches on only from its last layer, so a stage starts
+    # when its predecessor is in its last layer: with two stages of one layer each the passes pipeline perfectly,
+    # with many layers per stage the stages run almost one after the other
+    lm1 = predict_step_ms(cfg(2, layers=2, M=8, R=1), "layer_major", table=table)
+    assert lm1["form"] == "layer_major"
+    body = 8 * 2.0 + 2.0 + 8 * 6.0 + 6.0       # forward of 8 microbatches + one hand-over, backward with recompute likewise
+    from zorse_b200.planner.latency import head_and_embedding_ms
+    (hf, hb), (ef, eb) = head_and_embedding_ms("llama2_7b", "b200", 4096, 1, 32000)
+    ends = 9 * (2 * hf + hb + 2 * ef + eb) + 1.0          # head and embedding (recomputed once) per microbatch, transfers
+    assert body <= lm1["steady_ms"] + lm1["ramp_ms"] <= body + ends
+    lm = predict_step_ms(cfg(4, M=64, R=1), "layer_major", table=table)
+    serial = 32 * 64 * (2.0 + 6.0)               # every block on every microbatch, nothing overlapped
+    assert 0.85 * serial < lm["steady_ms"] + lm["ramp_ms"] < 1.02 * serial
+    assert predict_step_ms(cfg(1, R=1), "layer_major", table=table)["form"] == "gpipe"      # one stage: nothing to replay
     # a measured chain overhead scales the block times
     table["_chain_overhead"] = {"llama2_7b": {"b200": 1.1}}
     assert abs(predict_step_ms(cfg(4), "1f1b", table=table)["block_fwd_ms"] - 2.2) < 1e-9

@@ -28,7 +28,7 @@ def _run(nproc, *args, timeout=600, **extra_env):
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("case", ["dp2_library", "dp2_fused", "pp2", "fused_kernels", "pp2_1f1b", "dp2_uneven_library",
-                                  "pp2_gloo", "dp2_1f1b_fused"])
+                                  "pp2_gloo", "dp2_1f1b_fused", "pp2_1f1b_tail"])
 def test_two_gpus(case):
     out = _run(2, case)
     assert "WORKER_OK" in out
@@ -81,7 +81,8 @@ def test_tensor_parallel_four_gpus():
 
 
 @pytest.mark.skipif(_ngpu() < 4, reason="needs 4 GPUs")
-@pytest.mark.parametrize("case", ["pp2dp2_library", "pp2dp2_fused", "pp2dp2_1f1b_library", "pp2dp2_1f1b_fused"])
+@pytest.mark.parametrize("case", ["pp2dp2_library", "pp2dp2_fused", "pp2dp2_1f1b_library", "pp2dp2_1f1b_fused",
+                                  "pp2dp2_1f1b_tail_fused"])
 def test_four_gpus(case):
     out = _run(4, case)
     assert "WORKER_OK" in out

@@ -10,6 +10,8 @@ its forwards, then all its backwards (reference zorse_optimizer/optimizer.py:215
     1F1B:         T = (m - 1) * max_s (F_s + B_s) + sum_s (F_s + B_s) + 2 (P - 1) * p2p
     deferred weight gradients shorten the ramps by the weight-gradient time W_s of every stage that
     is not the bottleneck; v-way interleaving divides the ramps by v.
+    layer-major schedules on several stages: a replay of the loop (a stage passes microbatches on only from its last
+    layer, so the stages run almost one after the other).
 
 On top: the all-gather of the first layer (nothing to hide it behind), the reduce-scatter of the
 layer that finishes last, and the optimizer pass over each rank's shard (HBM-bound, 28 bytes per
@@ -27,6 +29,9 @@ from ..models import registry
 from . import comm_model
 from .latency import head_and_embedding_ms, load_model_compute_latencies_per_gpu, load_table
 
+# "for layer: for microbatch" on every stage: a stage hands its first microbatch downstream only while it runs its LAST
+# layer, so consecutive stages overlap by one layer's pass at most (see `_layer_major_ms`)
+LAYER_MAJOR_SHAPED = ("layer_major", "default", "no_overlap", "two_stage_sync")
 GPIPE_SHAPED = ("layer_major", "default", "no_overlap", "two_stage_sync", "zero2", "flashflex", "gpipe")
 WGRAD_SHARE_OF_FORWARD = 0.75      # weight-gradient GEMMs ~ the forward GEMMs; the rest of a forward block is attention
 
@@ -36,6 +41,47 @@ def chain_overhead(table: dict, model: str, gpu: str) -> float:
         return float(table["_chain_overhead"][model][gpu])
     except (KeyError, TypeError, ValueError):
         return 1.0
+
+
+def _layer_major_ms(G, f, b, head, emb, p2p, recompute) -> float:
+    """Replays the layer-major loop of every stage under the block-time model: stage s runs layer 0 on microbatch j
+    once stage s-1 has finished its last layer on that microbatch (plus the transfer), then every further layer on all
+    microbatches; backward mirrors it from the last stage (which turns around at once).  Returns the time at which
+    the first stage finishes its backward (reference loop: zorse_utils/pipeline_schedule_v2.py:202-374)."""
+    (hf, hb), (ef, eb) = head, emb
+
+    def feed(up_out, m):
+        if up_out is None:
+            return [0.0] * m
+        mu = len(up_out)
+        return [up_out[min(mu - 1, ((j + 1) * mu + m - 1) // m - 1)] + p2p for j in range(m)]
+
+    fwd_end, out = [], None
+    for g in G:
+        arr, t = feed(out, g["m"]), 0.0
+        for l in range(g["n"]):
+            c = f + (ef if g["first"] and l == 0 else 0.0) + (hf if g["last"] and l == g["n"] - 1 else 0.0)
+            out = []
+            for j in range(g["m"]):
+                t = max(t, arr[j]) if l == 0 else t
+                t += c
+                out.append(t)
+        fwd_end.append(t)
+    out = None
+    for g, t0 in zip(reversed(G), reversed(fwd_end)):
+        arr, t = feed(out, g["m"]), t0
+        for l in reversed(range(g["n"])):
+            c = b + (f if recompute else 0.0)
+            if g["last"] and l == g["n"] - 1:
+                c += hb + (hf if recompute else 0.0)
+            if g["first"] and l == 0:
+                c += eb + (ef if recompute else 0.0)
+            out = []
+            for j in range(g["m"]):
+                t = max(t, arr[j]) if l == g["n"] - 1 else t
+                t += c
+                out.append(t)
+    return t
 
 
 def predict_step_ms(cfg: dict, schedule: str, *, recompute: Optional[bool] = None, gpu: str = "b200",
@@ -85,12 +131,15 @@ def predict_step_ms(cfg: dict, schedule: str, *, recompute: Optional[bool] = Non
         W.append(g["n"] * f * WGRAD_SHARE_OF_FORWARD)
     m = max(g["m"] for g in G)
     k = max(range(P), key=lambda i: T[i] * G[i]["m"])
-    if gpipe:
+    steady = G[k]["m"] * T[k]
+    layer_major = sched in LAYER_MAJOR_SHAPED and v == 1 and P > 1
+    if layer_major:
+        ramp = _layer_major_ms(G, f, b, (hf, hb), (ef, eb), p2p, recompute) - steady
+    elif gpipe:
         # all forwards, then all backwards: the ramps are the other stages' single-microbatch passes too
         ramp = sum(T[i] for i in range(P) if i != k)
     else:
         ramp = sum(T[i] - (W[i] if defer_wgrad else 0.0) for i in range(P) if i != k) / v
-    steady = G[k]["m"] * T[k]
     opt = max(g["n"] * stats["parameters_per_layer"] / g["R"] for g in G) * 28 / (optimizer_gbs * 1e9) * 1e3
     if G[0]["first"]:
         opt_emb = stats["total_parameters"] - stats["num_layers"] * stats["parameters_per_layer"]
@@ -101,8 +150,8 @@ def predict_step_ms(cfg: dict, schedule: str, *, recompute: Optional[bool] = Non
         # than the compute they hide behind
         per_layer_compute = min(gg["m"] for gg in G) * f
         zero += max(0.0, max(coll(g["R"]) for g in G) - per_layer_compute) * max(g["n"] for g in G)
-    comm = 2.0 * (P - 1) * p2p * (v if not gpipe else 1)
+    comm = 0.0 if layer_major else 2.0 * (P - 1) * p2p * (v if not gpipe else 1)     # layer-major: inside the replay
     total = steady + ramp + opt + zero + comm
     return {"ms": total, "steady_ms": steady, "ramp_ms": ramp, "optimizer_ms": opt, "zero_exposed_ms": zero,
             "p2p_ms": comm, "block_fwd_ms": f, "block_bwd_ms": b, "chain_overhead": oh, "recompute": bool(recompute),
-            "form": "gpipe" if gpipe else "1f1b"}
+            "form": "layer_major" if layer_major else "gpipe" if gpipe else "1f1b"}
