@@ -183,8 +183,10 @@ def main():
                     help="pipeline stages (not the baseline plan for this GPU count; the JSON line says so)")
     ap.add_argument("--defer_wgrad", action="store_true",
                     help="1F1B: input gradients are sent upstream before the weight-gradient GEMMs (same arithmetic)")
-    ap.add_argument("--defer_tail_wgrad", type=int, default=0,
-                    help="1F1B: weight gradients of the last stage's last N layers (head first) run after its last backward")
+    ap.add_argument("--defer_tail_wgrad", type=int, default=-1,
+                    help="1F1B: weight gradients of the last stage's last N layers (head first) run after its last backward, "
+                         "in the time the other stages need to drain; -1 = what the planner's rule picks for the plan "
+                         "(2 on the 4-stage plan of 8 GPUs, 0 on the others), 0 = off")
     ap.add_argument("--no_preflight", action="store_true",
                     help="skip the host-side replay of the schedule's p2p program before the first multi-stage step")
     ap.add_argument("--baseline_config", type=int, default=0,
@@ -252,11 +254,16 @@ def main():
     # the planner's prediction for exactly this plan and schedule, made before anything is timed
     predicted = None
     try:
-        from zorse_b200.planner.predict import predict_step_ms
+        from zorse_b200.planner.predict import best_tail_deferral, predict_step_ms
 
-        predicted = predict_step_ms(cfg_dict, schedule, recompute=recompute, defer_wgrad=args.defer_wgrad)
+        if args.defer_tail_wgrad < 0:
+            args.defer_tail_wgrad = (best_tail_deferral(cfg_dict, schedule, recompute=recompute, defer_wgrad=args.defer_wgrad)
+                                     if schedule == "1f1b" and args.tp == 1 else 0)
+        predicted = predict_step_ms(cfg_dict, schedule, recompute=recompute, defer_wgrad=args.defer_wgrad,
+                                    defer_tail_wgrad=args.defer_tail_wgrad)
     except Exception as e:      # noqa: BLE001 - a missing profile table must not stop the measurement
         sys.stderr.write(f"[bench] no planner prediction: {e!r}\n")
+    args.defer_tail_wgrad = max(args.defer_tail_wgrad, 0)
     topt = dict(schedule=schedule, ops="sm100", optimizer_in_backward=args.optimizer_in_backward,
                 collectives=args.collectives, activation_recompute=recompute, defer_wgrad=args.defer_wgrad,
                 defer_tail_wgrad=args.defer_tail_wgrad,

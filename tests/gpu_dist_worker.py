@@ -220,6 +220,7 @@ def main():
         other = {"dp2_uneven_library": "dp2_library", "pp2_1f1b": "pp2", "pp2dp2_1f1b_library": "pp2dp2_library",
                  "pp2_gloo": "pp2", "dp2_1f1b_fused": "dp2_library", "pp2dp2_1f1b_fused": "pp2dp2_library",
                  "pp2_1f1b_tail": "pp2_1f1b", "pp2dp2_1f1b_tail_fused": "pp2dp2_1f1b_library",
+                 "dp2_1f1b_tail_fused": "dp2_library",
                  "tp2_library": "dp2_library" if dist.get_world_size() == 2 else "pp2dp2_library"}.get(case)
         if case.endswith("fused") or other:
             l2, m2, _ = train_case(other or case.replace("fused", "library"))

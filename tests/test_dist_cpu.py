@@ -283,14 +283,15 @@ def _worker_defer(rank, world, cfg_dict, opts, steps):
         DeferredWgrad.flush = orig
 
 
-@pytest.mark.parametrize("pipe_name,k", [("PIPE_2x1", 1), ("PIPE_2x1", 2), ("MIXED", 2)])
+@pytest.mark.parametrize("pipe_name,k", [("PIPE_2x1", 1), ("PIPE_2x1", 2), ("MIXED", 2), ("PIPE_1x2_UNEVEN", 2)])
 def test_tail_deferred_weight_gradients_give_the_same_training(pipe_name, k):
     """1F1B with the last stage's head (k = 1) or head + last block (k = 2) weight gradients held back until the
     stage's last backward: same losses and parameters as the oracle (two stages x 1, and two stages x 2-way shard with
-    uneven microbatch counts, where a reduction order shared by the stage's ranks matters)."""
+    uneven microbatch counts, where a reduction order shared by the stage's ranks matters; one stage x 2: allowed,
+    pointless)."""
     mixed = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [3, 1], "layer_partition": [0, 2], "zero_config": [[0, 1]]},
              {"gpu_ranks": [2, 3], "num_microbatches_per_rank": [1, 3], "layer_partition": [2, 4], "zero_config": [[2, 3]]}]
-    pipe = PIPE_2x1 if pipe_name == "PIPE_2x1" else mixed
+    pipe = {"PIPE_2x1": PIPE_2x1, "PIPE_1x2_UNEVEN": PIPE_1x2_UNEVEN}.get(pipe_name, mixed)
     cfg = tiny_cfg(pipe)
-    res = run_workers(2 if pipe_name == "PIPE_2x1" else 4, _worker, cfg, {"schedule": "1f1b", "defer_tail_wgrad": k}, 2)
+    res = run_workers(4 if pipe_name == "MIXED" else 2, _worker, cfg, {"schedule": "1f1b", "defer_tail_wgrad": k}, 2)
     _check(res, cfg)

@@ -28,7 +28,8 @@ def _run(nproc, *args, timeout=600, **extra_env):
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("case", ["dp2_library", "dp2_fused", "pp2", "fused_kernels", "pp2_1f1b", "dp2_uneven_library",
-                                  "pp2_gloo", "dp2_1f1b_fused", "pp2_1f1b_tail"])
+                                  "pp2_gloo", "dp2_1f1b_fused", "pp2_1f1b_tail",
+                                  "dp2_1f1b_tail_fused"])
 def test_two_gpus(case):
     out = _run(2, case)
     assert "WORKER_OK" in out

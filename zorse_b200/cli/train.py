@@ -35,6 +35,19 @@ def main(argv=None) -> int:
         activation_offload=True if args.offload_activations_to_host else None, lr=args.lr, seed=args.seed,
         backend=args.backend, pipeline_log=plog, shift_labels=args.shift_labels, defer_wgrad=args.defer_wgrad,
         defer_tail_wgrad=args.defer_tail_wgrad)
+    if opt.defer_tail_wgrad < 0:
+        # -1: the planner's rule decides (held-back work must fit into the time the other stages drain)
+        opt.defer_tail_wgrad = 0
+        if (cfg.schedule or opt.schedule) == "1f1b" and cfg.tensor_parallel_size == 1:
+            try:
+                from ..config.training_config import to_dict
+                from ..planner.predict import best_tail_deferral
+
+                opt.defer_tail_wgrad = best_tail_deferral(to_dict(cfg), "1f1b", recompute=opt.activation_recompute,
+                                                          defer_wgrad=opt.defer_wgrad)
+            except Exception as e:      # noqa: BLE001 - no profile table for this model / GPU: leave it off
+                log.warning(f"--defer_tail_wgrad -1: no prediction for this model ({e!r}); off")
+        log.info(f"defer_tail_wgrad = {opt.defer_tail_wgrad}")
     if args.nvtx:
         from ..utils import ranges
 
@@ -184,7 +197,7 @@ def main(argv=None) -> int:
             from ..planner.predict import predict_step_ms
 
             predicted = predict_step_ms(to_dict(cfg), tr.schedule.name, recompute=tr.schedule.recompute, gpu=gpu,
-                                        defer_wgrad=opt.defer_wgrad)["ms"]
+                                        defer_wgrad=opt.defer_wgrad, defer_tail_wgrad=opt.defer_tail_wgrad)["ms"]
         except Exception:      # noqa: BLE001 - no profile table for this model / GPU: print no prediction
             predicted = None
     if tr.rank == 0:

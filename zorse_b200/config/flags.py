@@ -76,7 +76,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="skip the host-side replay of the schedule's p2p program before a multi-stage NCCL job starts")
     p.add_argument("--defer_tail_wgrad", type=int, default=0,
                    help="1F1B: weight gradients of the last stage's last N layers (the output head first) run after the "
-                        "stage's last backward, in the time it otherwise idles while the other stages drain")
+                        "stage's last backward, in the time it otherwise idles while the other stages drain "
+                        "(-1: the planner's rule picks N for the plan)")
     p.add_argument("--defer_wgrad", action="store_true",
                    help="1F1B schedules: send each microbatch's input gradient upstream before its weight-gradient GEMMs run")
     p.add_argument("--heartbeat_timeout", type=float, default=0.0, help="seconds; 0 disables the watchdog")

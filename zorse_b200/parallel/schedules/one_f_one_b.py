@@ -42,9 +42,11 @@ class OneFOneBSchedule(ScheduleBase):
         # `defer_tail_wgrad = k` the weight-gradient GEMMs of its last k layers (the head first) are taken out of
         # every microbatch's backward and run once, after the stage's last backward, inside that idle time.  The
         # operands (dlogits, layer inputs) of all microbatches stay alive until then.  Same additions in the same
-        # order per bucket entry, so the result is bit-identical.
+        # order per bucket entry, so the result is bit-identical.  Whether it pays is the caller's question
+        # (`planner.predict.best_tail_deferral`): the held-back work has to fit into the time the other stages
+        # need to drain, and with one stage there is nothing to gain.
         hold = set()
-        if self.defer_tail_wgrad > 0 and st.is_last and len(self.cfg.stages) > 1 and st.can_defer_wgrad():
+        if self.defer_tail_wgrad > 0 and st.is_last and st.can_defer_wgrad():
             hold = set(range(max(L - self.defer_tail_wgrad, 0), L))
         # Receives are posted when they are needed, never ahead: torch serialises the p2p
         # operations of one process group on each rank, so a receive posted one microbatch early

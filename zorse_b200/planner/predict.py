@@ -27,7 +27,7 @@ from typing import Optional
 
 from ..models import registry
 from . import comm_model
-from .latency import head_and_embedding_ms, load_model_compute_latencies_per_gpu, load_table
+from .latency import activation_bytes, head_and_embedding_ms, load_model_compute_latencies_per_gpu, load_table
 
 # "for layer: for microbatch" on every stage: a stage hands its first microbatch downstream only while it runs its LAST
 # layer, so consecutive stages overlap by one layer's pass at most (see `_layer_major_ms`)
@@ -85,7 +85,8 @@ def _layer_major_ms(G, f, b, head, emb, p2p, recompute) -> float:
 
 
 def predict_step_ms(cfg: dict, schedule: str, *, recompute: Optional[bool] = None, gpu: str = "b200",
-                    table: Optional[dict] = None, defer_wgrad: bool = False, optimizer_gbs: float = 6000.0,
+                    table: Optional[dict] = None, defer_wgrad: bool = False, defer_tail_wgrad: int = 0,
+                    optimizer_gbs: float = 6000.0,
                     p2p_gbs: float = 700.0, p2p_latency_ms: float = 0.02, collective_gbs: float = 600.0,
                     collective_latency_ms: float = 0.03) -> dict:
     """`cfg` is a training_config dict.  Returns {"ms": total, ...terms}."""
@@ -129,6 +130,13 @@ def predict_step_ms(cfg: dict, schedule: str, *, recompute: Optional[bool] = Non
         B = g["n"] * b + (hb if g["last"] else 0.0) + (eb if g["first"] else 0.0) + (F if recompute else 0.0)
         T.append(F + B)
         W.append(g["n"] * f * WGRAD_SHARE_OF_FORWARD)
+    tail = 0.0
+    if defer_tail_wgrad > 0 and not gpipe and P > 1 and v == 1:
+        # the last stage's head (+ blocks) weight gradients leave every microbatch's backward and run after its last
+        # one, inside the time the stages before it need to finish (see `best_tail_deferral`)
+        w = max(hb - hf, 0.0) + (min(defer_tail_wgrad, G[-1]["n"] + 1) - 1) * f * WGRAD_SHARE_OF_FORWARD
+        T[-1] -= w
+        tail = max(0.0, G[-1]["m"] * w - sum(g["n"] * b for g in G[:-1]))
     m = max(g["m"] for g in G)
     k = max(range(P), key=lambda i: T[i] * G[i]["m"])
     steady = G[k]["m"] * T[k]
@@ -151,7 +159,51 @@ def predict_step_ms(cfg: dict, schedule: str, *, recompute: Optional[bool] = Non
         per_layer_compute = min(gg["m"] for gg in G) * f
         zero += max(0.0, max(coll(g["R"]) for g in G) - per_layer_compute) * max(g["n"] for g in G)
     comm = 0.0 if layer_major else 2.0 * (P - 1) * p2p * (v if not gpipe else 1)     # layer-major: inside the replay
-    total = steady + ramp + opt + zero + comm
+    total = steady + ramp + opt + zero + comm + tail
     return {"ms": total, "steady_ms": steady, "ramp_ms": ramp, "optimizer_ms": opt, "zero_exposed_ms": zero,
-            "p2p_ms": comm, "block_fwd_ms": f, "block_bwd_ms": b, "chain_overhead": oh, "recompute": bool(recompute),
-            "form": "layer_major" if layer_major else "gpipe" if gpipe else "1f1b"}
+            "p2p_ms": comm, "tail_wgrad_ms": tail, "block_fwd_ms": f, "block_bwd_ms": b, "chain_overhead": oh, "recompute": bool(recompute),
+            "form": "layer_major" if layer_major else "gpipe" if gpipe else "1f1b",
+            "stage_ms": T, "stage_layers": [g["n"] for g in G], "stage_microbatches": [g["m"] for g in G],
+            "interleave": v, "head_wgrad_ms": max(hb - hf, 0.0), "block_wgrad_ms": f * WGRAD_SHARE_OF_FORWARD}
+
+
+def best_tail_deferral(cfg: dict, schedule: str, *, recompute: Optional[bool] = None, table: Optional[dict] = None,
+                       max_layers: int = 2, min_gain: float = 0.015, window_share: float = 0.8,
+                       max_hold_gib: float = 32.0, **kw) -> int:
+    """How many layers of the last stage (the head first) should hold their weight-gradient GEMMs back until the
+    stage's last backward (`defer_tail_wgrad` of the 1F1B schedule); 0 = none.
+
+    The last stage carries the head on top of its blocks and so sets the period of a balanced 1F1B pipeline; it is also
+    the stage that idles longest at the end of a step, while the stages before it finish their last backward one after
+    the other.  Holding back w ms of weight gradients per microbatch shortens the period to max(T_last - w, T_others)
+    and moves m * w ms into that idle window.  Chosen: the deepest k <= max_layers whose held-back work fits into
+    `window_share` of the window, if the predicted gain is at least `min_gain` of the step.  (Measured on 4 stages
+    of 8 Llama-2-7B blocks, 32 microbatches: k = 2 -> 1548 to 1484 ms, k = 3 -> 1511 ms; at 2 stages with 64
+    microbatches k = 2 does not fit the window and costs 0.6 %.)  The operands of the held-back GEMMs stay alive for
+    every microbatch (the logits' gradient, and per block about 1.8x its stored activations): at most
+    `max_hold_gib` of them."""
+    p = predict_step_ms(cfg, schedule, recompute=recompute, table=table, **kw)
+    T, P = p["stage_ms"], len(p["stage_ms"])
+    if p["form"] != "1f1b" or p["interleave"] > 1 or P < 2 or p["recompute"]:
+        return 0
+    m = p["stage_microbatches"][-1]
+    others = max(T[:-1])
+    if T[-1] <= others:
+        return 0
+    window = window_share * sum(n * p["block_bwd_ms"] for n in p["stage_layers"][:-1])
+    seq, mbs, vocab = int(cfg["sequence_length"]), int(cfg["microbatch_size"]), int(cfg.get("vocab_size", 32000))
+    stats = registry.get_model_stats(cfg["model_name"], vocab=vocab)
+    tokens = seq * mbs
+    head_bytes = tokens * (vocab + stats["hidden_size"]) * 2
+    act = activation_bytes(load_table() if table is None else table, cfg["model_name"], kw.get("gpu", "b200"), seq,
+                           cfg.get("autocast_dtype", "bfloat16"), mbs)
+    block_bytes = 1.8 * (act if act else 34 * tokens * stats["hidden_size"])
+    best, best_gain = 0, 0.0
+    for k in range(1, min(max_layers, p["stage_layers"][-1] + 1) + 1):
+        w = p["head_wgrad_ms"] + (k - 1) * p["block_wgrad_ms"]
+        if m * w > window or m * (head_bytes + (k - 1) * block_bytes) > max_hold_gib * 2 ** 30:
+            break
+        gain = m * (T[-1] - max(T[-1] - w, others))
+        if gain > best_gain:
+            best, best_gain = k, gain
+    return best if best_gain >= min_gain * p["ms"] else 0
