@@ -364,6 +364,31 @@ def test_tail_deferral_rule_follows_the_drain_window():
     assert late["tail_wgrad_ms"] > 50.0
 
 
+def test_planner_cli_writes_schedule_and_tail_deferral(tmp_path):
+    """`zorse_planner.py --schedule 1f1b` writes the schedule, this repository's prediction for it and the depth of the
+    tail deferral into the file; the key survives a parse / to_dict round trip and reaches the schedule object."""
+    import importlib.util
+    import json
+    import os
+
+    from zorse_b200.config.training_config import parse_pipeline_config, parse_pipeline_dict, to_dict
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("planner_cli", os.path.join(root, "zorse_planner.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    out = tmp_path / "tc.json"
+    rc = mod.main(["--cluster_info_file", os.path.join(root, "example", "cluster_info.json"), "--model_name", "llama2_7b",
+                   "--global_batch_size", "64", "--sequence_length", "4096", "--num_stages", "4", "--microbatch_size", "1",
+                   "--no_recompute", "--schedule", "1f1b", "--output", str(out)])
+    assert rc == 0
+    d = json.loads(out.read_text())
+    assert d["schedule"] == "1f1b" and d["defer_tail_wgrad"] == 2 and 1400 < d["latency"] < 1650
+    cfg = parse_pipeline_config(out)
+    assert cfg.defer_tail_wgrad == 2 and to_dict(cfg)["defer_tail_wgrad"] == 2
+    assert parse_pipeline_dict({k: v for k, v in d.items() if k != "defer_tail_wgrad"}).defer_tail_wgrad is None
+
+
 def test_drawings_of_the_gpu_graph_and_its_partition(tmp_path):
     import networkx as nx
 

@@ -292,6 +292,12 @@ def test_tail_deferred_weight_gradients_give_the_same_training(pipe_name, k):
     mixed = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [3, 1], "layer_partition": [0, 2], "zero_config": [[0, 1]]},
              {"gpu_ranks": [2, 3], "num_microbatches_per_rank": [1, 3], "layer_partition": [2, 4], "zero_config": [[2, 3]]}]
     pipe = {"PIPE_2x1": PIPE_2x1, "PIPE_1x2_UNEVEN": PIPE_1x2_UNEVEN}.get(pipe_name, mixed)
-    cfg = tiny_cfg(pipe)
-    res = run_workers(4 if pipe_name == "MIXED" else 2, _worker, cfg, {"schedule": "1f1b", "defer_tail_wgrad": k}, 2)
-    _check(res, cfg)
+    # k = 1 on the two-stage plan comes from the config file's key, the others from the trainer option
+    by_key = pipe_name == "PIPE_2x1" and k == 1
+    cfg = tiny_cfg(pipe, **({"defer_tail_wgrad": k} if by_key else {}))
+    opts = {"schedule": "1f1b"} if by_key else {"schedule": "1f1b", "defer_tail_wgrad": k}
+    res = run_workers(4 if pipe_name == "MIXED" else 2, _worker_defer, cfg, opts, 2)
+    _check([r["result"] for r in res], cfg)
+    if pipe_name == "PIPE_2x1":
+        # the last stage's rank held back one GEMM (head) or five (head + the block's four) per microbatch and step
+        assert [r["deferred"] for r in res] == [0, 2 * 4 * (1 if k == 1 else 5)]

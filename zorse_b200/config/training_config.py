@@ -139,6 +139,9 @@ class PipelineConfig:
     # (rank -> ms per layer and microbatch) or, when absent, from the profile table and the ranks' GPU models
     comm_plan: str = "interleave"
     rank_latency_ms: Optional[dict] = None
+    # 1F1B: weight gradients of the last stage's last N layers (the head first) run after its last backward
+    # (schedules/one_f_one_b.py); written by the planner when asked for a 1F1B plan, a trainer flag overrides it
+    defer_tail_wgrad: Optional[int] = None
     extra: dict = field(default_factory=dict)
 
     @property
@@ -233,7 +236,8 @@ def parse_pipeline_dict(d: dict[str, Any]) -> PipelineConfig:
              "fused_optimizer", "interleave_degree", "latency", "autocast_dtype", "reduce_dtype",
              "split_microbatches_evenly", "skip_compute_sync", "interleave_stage_sync", "gloo_batch_recv",
              "alternate_nccl_gloo", "large_model_init", "schedule", "activation_recompute", "activation_offload",
-             "grad_norm_compat", "zero_level", "unused_ranks", "tensor_parallel_size", "comm_plan", "rank_latency_ms"}
+             "grad_norm_compat", "zero_level", "unused_ranks", "tensor_parallel_size", "comm_plan", "rank_latency_ms",
+             "defer_tail_wgrad"}
     cfg = PipelineConfig(
         model_name=str(d["model_name"]), global_batch_size=gbs, microbatch_size=mbs,
         sequence_length=int(d["sequence_length"]), stages=stages, vocab_size=int(d.get("vocab_size", 49152)),
@@ -250,6 +254,7 @@ def parse_pipeline_dict(d: dict[str, Any]) -> PipelineConfig:
         tensor_parallel_size=int(d.get("tensor_parallel_size", 1)),
         comm_plan=str(d.get("comm_plan", "interleave")),
         rank_latency_ms={int(k): float(v) for k, v in d["rank_latency_ms"].items()} if d.get("rank_latency_ms") else None,
+        defer_tail_wgrad=int(d["defer_tail_wgrad"]) if d.get("defer_tail_wgrad") is not None else None,
         extra={k: v for k, v in d.items() if k not in known})
     cfg.validate()
     return cfg
@@ -301,5 +306,7 @@ def to_dict(cfg: PipelineConfig) -> dict[str, Any]:
         d["comm_plan"] = cfg.comm_plan
     if cfg.rank_latency_ms:
         d["rank_latency_ms"] = {str(k): v for k, v in cfg.rank_latency_ms.items()}
+    if cfg.defer_tail_wgrad is not None:
+        d["defer_tail_wgrad"] = cfg.defer_tail_wgrad
     d.update(cfg.extra)
     return d

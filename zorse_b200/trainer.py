@@ -112,7 +112,8 @@ class Trainer:
         recompute = cfg.activation_recompute if opt.activation_recompute is None else opt.activation_recompute
         name = cfg.schedule or opt.schedule
         self.schedule = build_schedule(name, self.stages, cfg, recompute=recompute, pipeline_log=opt.pipeline_log,
-                                       defer_wgrad=opt.defer_wgrad, defer_tail_wgrad=opt.defer_tail_wgrad)
+                                       defer_wgrad=opt.defer_wgrad,
+                                       defer_tail_wgrad=opt.defer_tail_wgrad or cfg.defer_tail_wgrad or 0)
         self.step_idx = 0
 
     # ------------------------------------------------------------------ data

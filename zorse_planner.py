@@ -39,6 +39,10 @@ def main(argv=None) -> int:
                          "the lane model is not calibrated against measurements yet")
     ap.add_argument("--compute_overhead", type=float, default=1.075,
                     help="whole-step time over the sum of profiled layer times (launch gaps, small kernels)")
+    ap.add_argument("--schedule", default=None,
+                    help="write this schedule into the config (the trainer then needs no schedule flag) together with "
+                         "this repository's prediction for it; with 1f1b also how many of the last stage's layers hold "
+                         "their weight gradients back (defer_tail_wgrad)")
     ap.add_argument("--draw", default=None, help="write a PNG of the partitioned GPU graph (needs matplotlib)")
     a = ap.parse_args(argv)
 
@@ -66,6 +70,22 @@ def main(argv=None) -> int:
                         a.reduce_dtype, a.output_file,
                         total_ranks=(int(data.get("total_gpus", 0)) // a.tensor_parallel_size) or None,
                         tensor_parallel_size=a.tensor_parallel_size)
+    if a.schedule:
+        from zorse_b200.planner.predict import best_tail_deferral, predict_step_ms
+
+        cfg["schedule"] = a.schedule
+        recompute = False if a.no_recompute else None
+        try:
+            if a.schedule == "1f1b" and a.tensor_parallel_size == 1 and res.interleave_degree == 1:
+                cfg["defer_tail_wgrad"] = best_tail_deferral(cfg, a.schedule, recompute=recompute)
+            cfg["latency"] = predict_step_ms(cfg, a.schedule, recompute=recompute,
+                                             defer_tail_wgrad=cfg.get("defer_tail_wgrad", 0))["ms"]
+            print(f"schedule {a.schedule}: predicted {cfg['latency']:.2f} ms"
+                  + (f", defer_tail_wgrad {cfg['defer_tail_wgrad']}" if "defer_tail_wgrad" in cfg else ""))
+        except Exception as e:      # noqa: BLE001 - no profile rows for this model on this GPU type
+            print(f"schedule {a.schedule}: no prediction ({e!r}); the stage-2 estimate stays in the file", file=sys.stderr)
+        with open(a.output_file, "w") as f:
+            json.dump(cfg, f, indent=4)
     if cfg.get("unused_ranks"):
         print(f"ranks {cfg['unused_ranks']} own no stage (too slow to be given a layer); they idle during training")
     print(f"best: {len(res.stages)} stages, microbatch {res.microbatch_size}, interleave {res.interleave_degree}, "
