@@ -389,6 +389,36 @@ def test_planner_cli_writes_schedule_and_tail_deferral(tmp_path):
     assert parse_pipeline_dict({k: v for k, v in d.items() if k != "defer_tail_wgrad"}).defer_tail_wgrad is None
 
 
+def test_plan_ranks_candidates_by_the_schedule_the_trainer_will_run():
+    """`plan(schedule=...)`: every candidate carries the stage-2 figure and the schedule-specific prediction; the
+    winner is the one with the smallest schedule-specific prediction.  A cluster with two GPU models (no single
+    profile row set) falls back to the stage-2 figure."""
+    import json
+    import os
+
+    from zorse_b200.planner.cluster import load_cluster_info
+    from zorse_b200.planner.plan import export_config, plan
+    from zorse_b200.planner.predict import predict_step_ms
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    data = load_cluster_info(os.path.join(root, "example", "cluster_info.json"))
+    kw = dict(global_batch_size=64, sequence_length=4096, microbatch_size=1, recompute=False)
+    best, tried = plan(data, "llama2_7b", schedule="1f1b", **kw)
+    assert all(t["schedule_ms"] is not None and t["latency_ms"] is not None for t in tried)
+    win = min(tried, key=lambda t: t["schedule_ms"])
+    assert len({tuple(s.gpu_ranks) for s in best.stages}) == win["k"]
+    cfg = export_config(best, "llama2_7b", 64, 4096, 32000, "bfloat16", "float32")
+    assert abs(predict_step_ms(cfg, "1f1b", recompute=False)["ms"] - win["schedule_ms"]) < 1e-6
+    # layer-major on several stages runs them almost one after the other: the ranking must prefer few stages
+    _, lm = plan(data, "llama2_7b", schedule="layer_major", global_batch_size=64, sequence_length=4096, microbatch_size=1)
+    by_k = {t["k"]: t["schedule_ms"] for t in lm}
+    assert by_k[1] < by_k[2] < by_k[4] < by_k[8]
+    mixed = json.loads(json.dumps(data))
+    mixed["gpu_list"][0]["name"] = "h100"
+    _, tr2 = plan(mixed, "llama2_7b", schedule="1f1b", ks=[8], **kw)
+    assert "schedule_ms" not in tr2[0]
+
+
 def test_drawings_of_the_gpu_graph_and_its_partition(tmp_path):
     import networkx as nx
 

@@ -156,16 +156,22 @@ def plan(data: dict, model_name: str, *, global_batch_size: int, sequence_length
          dtype_multiplier: float = 2.0, optimizer_multiplier: float = 12.0, reserved_memory_gb: float = 2.0,
          recompute: bool = True, measured_agrs: Optional[dict] = None, table: Optional[dict] = None,
          ks: Optional[list[int]] = None, microbatch_size: Optional[int] = None,
-         compute_overhead: float = 1.075, tensor_parallel_size: int = 1) -> tuple[Optional[PlanResult], list[dict]]:
+         compute_overhead: float = 1.075, tensor_parallel_size: int = 1,
+         schedule: Optional[str] = None) -> tuple[Optional[PlanResult], list[dict]]:
     """tensor_parallel_size t > 1 plans for lanes of t GPUs; the ranks of the result are lane numbers, which is
-    what the trainer's config means when it carries `tensor_parallel_size` (export_config writes it)."""
+    what the trainer's config means when it carries `tensor_parallel_size` (export_config writes it).
+
+    `schedule`: the schedule the trainer will run.  The stage-2 optimizer costs every candidate with the reference's
+    all-forward-then-all-backward model; with a schedule name, and a cluster of one GPU model that the profile table
+    covers, the candidates (one per number of groups) are ranked by `predict.predict_step_ms` for that schedule
+    instead (1F1B ramps, layer-major replay, tail deferral), and each entry of the returned list carries both figures."""
     full_data, lane_members = data, None
     if tensor_parallel_size > 1:
         from .tensor_parallel import coarsen
 
         data, lane_members = coarsen(data, tensor_parallel_size)
     G = build_gpu_graph(data)
-    best, tried = None, []
+    best, best_score, tried = None, None, []
     for k in (ks or candidate_ks(data)):
         pmap = partition(G, k, partition_algorithm)
         res = plan_partition(data, pmap, model_name, global_batch_size=global_batch_size,
@@ -174,12 +180,38 @@ def plan(data: dict, model_name: str, *, global_batch_size: int, sequence_length
                              reserved_memory_gb=reserved_memory_gb, recompute=recompute, measured_agrs=measured_agrs,
                              table=table, microbatch_size=microbatch_size, compute_overhead=compute_overhead,
                              tensor_parallel_size=tensor_parallel_size, lane_members=lane_members, full_data=full_data)
-        tried.append({"k": k, "latency_ms": None if res is None else res.latency_ms,
-                      "microbatch_size": None if res is None else res.microbatch_size,
-                      "interleave_degree": None if res is None else res.interleave_degree})
-        if res is not None and (best is None or res.latency_ms < best.latency_ms):
-            best = res
+        entry = {"k": k, "latency_ms": None if res is None else res.latency_ms,
+                 "microbatch_size": None if res is None else res.microbatch_size,
+                 "interleave_degree": None if res is None else res.interleave_degree}
+        score = None if res is None else res.latency_ms
+        if res is not None and schedule and tensor_parallel_size == 1:
+            ms = _schedule_ms(res, data, model_name, global_batch_size, sequence_length, vocab_size, autocast_dtype,
+                              reduce_dtype, schedule, recompute, table)
+            if ms is not None:
+                entry["schedule_ms"] = score = ms
+        tried.append(entry)
+        if res is not None and (best is None or score < best_score):
+            best, best_score = res, score
     return best, tried
+
+
+def _schedule_ms(res: PlanResult, data: dict, model_name: str, gbs: int, seq: int, vocab: int, autocast_dtype: str,
+                 reduce_dtype: str, schedule: str, recompute: bool, table: Optional[dict]) -> Optional[float]:
+    """Predicted step of a candidate plan under `schedule`, or None when the predictor does not cover the cluster
+    (several GPU models, or no profile rows)."""
+    from .predict import best_tail_deferral, predict_step_ms
+
+    kinds = {g["name"] if isinstance(g, dict) else str(g) for g in data.get("gpu_list", [])}
+    if len(kinds) != 1:
+        return None
+    gpu = next(iter(kinds)).lower()
+    cfg = export_config(res, model_name, gbs, seq, vocab, autocast_dtype, reduce_dtype)
+    rc = None if recompute else False
+    try:
+        k = best_tail_deferral(cfg, schedule, recompute=rc, table=table, gpu=gpu) if schedule == "1f1b" else 0
+        return float(predict_step_ms(cfg, schedule, recompute=rc, table=table, gpu=gpu, defer_tail_wgrad=k)["ms"])
+    except Exception:      # noqa: BLE001 - no rows for this model / GPU / sequence length
+        return None
 
 
 def export_config(res: PlanResult, model_name: str, global_batch_size: int, sequence_length: int, vocab_size: int,

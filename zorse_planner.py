@@ -40,9 +40,9 @@ def main(argv=None) -> int:
     ap.add_argument("--compute_overhead", type=float, default=1.075,
                     help="whole-step time over the sum of profiled layer times (launch gaps, small kernels)")
     ap.add_argument("--schedule", default=None,
-                    help="write this schedule into the config (the trainer then needs no schedule flag) together with "
-                         "this repository's prediction for it; with 1f1b also how many of the last stage's layers hold "
-                         "their weight gradients back (defer_tail_wgrad)")
+                    help="the schedule the trainer will run: candidate plans are ranked by this repository's prediction "
+                         "for that schedule, and the file gets the schedule, that prediction and, with 1f1b, how many "
+                         "of the last stage's layers hold their weight gradients back (defer_tail_wgrad)")
     ap.add_argument("--draw", default=None, help="write a PNG of the partitioned GPU graph (needs matplotlib)")
     a = ap.parse_args(argv)
 
@@ -60,9 +60,10 @@ def main(argv=None) -> int:
                       optimizer_multiplier=a.optimizer_multiplier, reserved_memory_gb=a.reserved_memory_gb,
                       recompute=not a.no_recompute, measured_agrs=measured,
                       ks=[a.num_stages] if a.num_stages else None, microbatch_size=a.microbatch_size, compute_overhead=a.compute_overhead,
-                      tensor_parallel_size=a.tensor_parallel_size)
+                      tensor_parallel_size=a.tensor_parallel_size, schedule=a.schedule)
     for t in tried:
-        print(f"k={t['k']}: predicted {t['latency_ms']} ms (microbatch {t['microbatch_size']}, interleave {t['interleave_degree']})")
+        print(f"k={t['k']}: predicted {t['latency_ms']} ms (microbatch {t['microbatch_size']}, interleave {t['interleave_degree']})"
+              + (f"; under {a.schedule}: {t['schedule_ms']:.1f} ms" if t.get("schedule_ms") is not None else ""))
     if res is None:
         print("no plan fits in memory", file=sys.stderr)
         return 1
