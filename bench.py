@@ -187,6 +187,8 @@ def main():
                     help="1F1B: weight gradients of the last stage's last N layers (head first) run after its last backward, "
                          "in the time the other stages need to drain; -1 = what the planner's rule picks for the plan "
                          "(2 on the 4-stage plan of 8 GPUs, 0 on the others), 0 = off")
+    ap.add_argument("--prepost_recv", action="store_true",
+                    help="1F1B: post the next operation's receive ahead (per-boundary p2p groups); not measured on hardware")
     ap.add_argument("--no_preflight", action="store_true",
                     help="skip the host-side replay of the schedule's p2p program before the first multi-stage step")
     ap.add_argument("--baseline_config", type=int, default=0,
@@ -242,7 +244,7 @@ def main():
         try:
             from zorse_b200.parallel.p2p_sim import preflight
 
-            stuck = preflight(cfg, schedule, defer_wgrad=args.defer_wgrad)
+            stuck = preflight(cfg, schedule, defer_wgrad=args.defer_wgrad, prepost_recv=args.prepost_recv)
         except Exception as e:      # noqa: BLE001 - the replay is a safety net, not a precondition
             sys.stderr.write(f"[bench] p2p replay skipped: {e!r}\n")
         if stuck is not None:
@@ -266,7 +268,7 @@ def main():
     args.defer_tail_wgrad = max(args.defer_tail_wgrad, 0)
     topt = dict(schedule=schedule, ops="sm100", optimizer_in_backward=args.optimizer_in_backward,
                 collectives=args.collectives, activation_recompute=recompute, defer_wgrad=args.defer_wgrad,
-                defer_tail_wgrad=args.defer_tail_wgrad,
+                defer_tail_wgrad=args.defer_tail_wgrad, prepost_recv=args.prepost_recv,
                 model_overrides={} if args.layers is None else {"layers": args.layers})
     topt.update(extra_opts)
     tr = Trainer(cfg, TrainerOptions(**topt))
@@ -387,7 +389,7 @@ def main():
                        "parallelism": par, "schedule": schedule, "activation_recompute": tr.schedule.recompute,
                        "optimizer": "Adam fp32 master+moments, step inside the timed region",
                        "reduce_dtype": args.reduce_dtype, "collectives": args.collectives, "defer_wgrad": args.defer_wgrad,
-                       "defer_tail_wgrad": args.defer_tail_wgrad,
+                       "defer_tail_wgrad": args.defer_tail_wgrad, "prepost_recv": args.prepost_recv,
                        "l2": "per-step working set (>100 GB of parameters, optimizer state and activations) far exceeds the 126 MB L2; no flush needed"},
             "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches, "loss": loss_val, "loss_first_step": first_loss,
             "exposed_comm_ms_per_step": exposed_ms, "exposed_comm_breakdown": exposed_parts,

@@ -301,3 +301,17 @@ def test_tail_deferred_weight_gradients_give_the_same_training(pipe_name, k):
     if pipe_name == "PIPE_2x1":
         # the last stage's rank held back one GEMM (head) or five (head + the block's four) per microbatch and step
         assert [r["deferred"] for r in res] == [0, 2 * 4 * (1 if k == 1 else 5)]
+
+
+@pytest.mark.parametrize("pipe_name", ["PIPE_2x1", "CHAIN4", "MIXED"])
+def test_1f1b_with_preposted_receives_gives_the_same_training(pipe_name):
+    """Receives posted one operation ahead (`prepost_recv`, per-boundary groups): two stages, a chain of four stages
+    (middle ranks hold two receives in flight) and two stages x 2 with uneven counts all match the oracle."""
+    chain4 = [{"gpu_ranks": [k], "num_microbatches_per_rank": [4], "layer_partition": [k, k + 1], "zero_config": [[k]]}
+              for k in range(4)]
+    mixed = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [3, 1], "layer_partition": [0, 2], "zero_config": [[0, 1]]},
+             {"gpu_ranks": [2, 3], "num_microbatches_per_rank": [1, 3], "layer_partition": [2, 4], "zero_config": [[2, 3]]}]
+    pipe = {"PIPE_2x1": PIPE_2x1, "CHAIN4": chain4, "MIXED": mixed}[pipe_name]
+    cfg = tiny_cfg(pipe)
+    res = run_workers(2 if pipe_name == "PIPE_2x1" else 4, _worker, cfg, {"schedule": "1f1b", "prepost_recv": True}, 2)
+    _check(res, cfg)

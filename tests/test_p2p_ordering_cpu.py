@@ -63,6 +63,32 @@ def test_one_ahead_receives_would_deadlock_1f1b_on_four_stages():
     assert simulate(progs, separate_kinds=False, separate_directions=False) is not None or True
 
 
+@pytest.mark.parametrize("P,M,width", [(2, 4, 1), (4, 8, 1), (4, 8, 2), (8, 16, 1), (3, 5, 1), (4, 64, 2)])
+def test_1f1b_with_receives_posted_one_operation_ahead_is_deadlock_free(P, M, width):
+    """`prepost_recv`: the receive of the next forward / backward is posted before the current one is computed, on
+    per-boundary groups.  Every receive really is issued before the previous operation's compute, and the program
+    completes under the serialised-queue rules."""
+    cfg = chain_cfg(P, M, width)
+    progs = record_programs(cfg, "1f1b", model_overrides={**OV, "layers": P}, prepost_recv=True)
+    assert simulate(progs) is None
+    assert simulate(progs, serialize_within_group=False) is None
+    plain = record_programs(cfg, "1f1b", model_overrides={**OV, "layers": P})
+    for r, ev in progs.items():
+        # same messages as the on-demand program, per kind in the same order
+        norm = lambda evs, what: [(e.kind.rstrip("01"), e.peer, e.tag) for e in evs if e.what == what]
+        assert norm(ev, "send") == norm(plain[r], "send")
+        assert sorted(norm(ev, "post_recv")) == sorted(norm(plain[r], "post_recv"))
+        # a middle rank has two receives in flight at some point (the current one and the next one)
+        if 0 < r // width < P - 1 and M // width >= 2:
+            open_, most = 0, 0
+            for e in ev:
+                open_ += {"post_recv": 1, "wait_recv": -1}.get(e.what, 0)
+                most = max(most, open_)
+            assert most == 2
+    with pytest.raises(ValueError, match="per-boundary"):
+        record_programs(cfg, "1f1b", model_overrides={**OV, "layers": P}, prepost_recv=True, split_parity=False)
+
+
 def test_simulator_flags_order_mismatch():
     a = [Event("send", 1, "act", 0), Event("send", 1, "act", 2)]
     b = [Event("post_recv", 0, "act", 2), Event("wait_recv", 0, "act", 2), Event("post_recv", 0, "act", 0),
@@ -158,6 +184,9 @@ def test_irregular_routing_is_deadlock_free(schedule, widths, counts):
     progs = record_programs(cfg, schedule, model_overrides={**OV, "layers": len(widths)})
     assert simulate(progs) is None
     assert simulate(progs, serialize_within_group=False) is None
+    if schedule == "1f1b":
+        ahead = record_programs(cfg, schedule, model_overrides={**OV, "layers": len(widths)}, prepost_recv=True)
+        assert simulate(ahead) is None
 
 
 def test_planned_1f1b_order_equals_the_classic_one_on_a_regular_chain():

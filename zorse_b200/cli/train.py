@@ -34,7 +34,7 @@ def main(argv=None) -> int:
         activation_recompute=False if args.no_recompute else None,
         activation_offload=True if args.offload_activations_to_host else None, lr=args.lr, seed=args.seed,
         backend=args.backend, pipeline_log=plog, shift_labels=args.shift_labels, defer_wgrad=args.defer_wgrad,
-        defer_tail_wgrad=args.defer_tail_wgrad)
+        defer_tail_wgrad=args.defer_tail_wgrad, prepost_recv=args.prepost_recv)
     if opt.defer_tail_wgrad < 0:
         # -1: the planner's rule decides (held-back work must fit into the time the other stages drain)
         opt.defer_tail_wgrad = 0
@@ -66,7 +66,7 @@ def main(argv=None) -> int:
         name = cfg.schedule or opt.schedule
         stuck = None
         try:
-            stuck = preflight(cfg, name, defer_wgrad=opt.defer_wgrad)
+            stuck = preflight(cfg, name, defer_wgrad=opt.defer_wgrad, prepost_recv=opt.prepost_recv)
         except Exception as e:      # noqa: BLE001 - the replay is a safety net, not a precondition
             log.warning(f"p2p replay skipped: {e!r}")
         if stuck is not None:

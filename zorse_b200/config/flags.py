@@ -74,6 +74,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--resume", type=str, default=None)
     p.add_argument("--no_preflight", action="store_true",
                    help="skip the host-side replay of the schedule's p2p program before a multi-stage NCCL job starts")
+    p.add_argument("--prepost_recv", action="store_true",
+                   help="1F1B: post the receive of the next forward / backward before computing the current one "
+                        "(stage boundaries then use their own process groups); not measured on hardware")
     p.add_argument("--defer_tail_wgrad", type=int, default=0,
                    help="1F1B: weight gradients of the last stage's last N layers (the output head first) run after the "
                         "stage's last backward, in the time it otherwise idles while the other stages drain "

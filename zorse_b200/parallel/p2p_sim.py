@@ -147,9 +147,13 @@ def simulate(programs: dict[int, list[Event]], *, separate_kinds: bool = True, s
     return None if not stuck else "deadlock: " + "; ".join(stuck[:8])
 
 
-def record_programs(cfg, schedule_name: str, model_overrides: Optional[dict] = None, **schedule_kw) -> dict[int, list[Event]]:
+def record_programs(cfg, schedule_name: str, model_overrides: Optional[dict] = None,
+                    split_parity: Optional[bool] = None, **schedule_kw) -> dict[int, list[Event]]:
     """Runs one step of `schedule_name` for every rank of `cfg` in isolation (CPU, PyTorch ops,
-    shard groups of one rank) and returns the recorded p2p programs."""
+    shard groups of one rank) and returns the recorded p2p programs.  `split_parity`: as `PipelineStage`
+    (None: per-boundary groups only for irregular plans, and for schedules asked to post receives ahead)."""
+    if split_parity is None and schedule_kw.get("prepost_recv"):
+        split_parity = True
     from ..engine.zero import EngineConfig, Streams
     from ..ops.api import get_ops
     from .groups import Group, StageGroups
@@ -174,7 +178,7 @@ def record_programs(cfg, schedule_name: str, model_overrides: Optional[dict] = N
         stages = [PipelineStage(cfg, st, rank=r, device=dev, ops=ops, engine_cfg=ecfg,
                                 groups=StageGroups(Group((r,)), Group((r,))), streams=streams,
                                 pattern=plans[r].stages[st.stage_id], transport=tp, model_overrides=model_overrides,
-                                local_mailbox=box)
+                                local_mailbox=box, split_parity=split_parity)
                   for st in cfg.stages_of_rank(r)]
         sched = build_schedule(schedule_name, stages, cfg, **schedule_kw)
         sched.step(0, inputs, inputs)

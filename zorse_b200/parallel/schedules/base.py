@@ -21,7 +21,7 @@ class ScheduleBase:
     recompute_default = True
 
     def __init__(self, stages: list[PipelineStage], cfg, *, recompute: Optional[bool] = None, pipeline_log=None,
-                 defer_wgrad: bool = False, defer_tail_wgrad: int = 0):
+                 defer_wgrad: bool = False, defer_tail_wgrad: int = 0, prepost_recv: bool = False):
         self.stages = sorted(stages, key=lambda s: s.stage_id)
         self.cfg = cfg
         # 1F1B schedules: send a microbatch's input gradient upstream before computing its weight gradients
@@ -29,6 +29,9 @@ class ScheduleBase:
         # 1F1B, last stage: the weight gradients of the output head and of this many blocks before it run after the
         # stage's last backward, in the time the last stage otherwise idles while the other stages drain
         self.defer_tail_wgrad = int(defer_tail_wgrad)
+        # 1F1B: the receive of the NEXT forward / backward is posted before the current one is computed, so the transfer
+        # and its handshake run under compute (needs per-boundary process groups: `PipelineStage.split_parity`)
+        self.prepost_recv = bool(prepost_recv)
         self.recompute = self.recompute_default if recompute is None else recompute
         self.log = pipeline_log
         self.device = stages[0].device if stages else torch.device("cpu")

@@ -48,14 +48,32 @@ class OneFOneBSchedule(ScheduleBase):
         hold = set()
         if self.defer_tail_wgrad > 0 and st.is_last and st.can_defer_wgrad():
             hold = set(range(max(L - self.defer_tail_wgrad, 0), L))
-        # Receives are posted when they are needed, never ahead: torch serialises the p2p
+        # By default receives are posted when they are needed, never ahead: torch serialises the p2p
         # operations of one process group on each rank, so a receive posted one microbatch early
         # would sit in front of this rank's own send of the current microbatch, and across four
         # or more stages those extra "send waits for the next receive" edges close a cycle
         # (stage 0's first backward would wait for a forward it runs only afterwards).
+        # `prepost_recv` posts the receive of the next operation (one operation ahead, not one microbatch) before
+        # the current one is computed.  It is only allowed with per-boundary groups (the stage's `split_parity`),
+        # where a group carries one direction of one boundary on a rank, so that by construction an early receive
+        # stands in front of nothing but later receives of that boundary; the host-side replay checks the program
+        # all the same before a job starts.
+        if self.prepost_recv and not st.split_parity:
+            raise ValueError("prepost_recv needs per-boundary process groups (PipelineStage(split_parity=True))")
+        posted: dict = {}
+
+        def post(op, mbl):
+            # the receive operation `op` on microbatch `mbl` will wait for, if it has one and it is not posted yet
+            if (op, mbl) in posted or (st.is_first if op == "F" else st.is_last):
+                return
+            posted[(op, mbl)] = st.recv_fwd(mbl) if op == "F" else st.recv_bwd(mbl)
+
+        def take(op, mbl):
+            post(op, mbl)
+            return posted.pop((op, mbl)).wait()
 
         def fwd(mbl):
-            x = self._inp(st, inputs, mbl) if st.is_first else st.recv_fwd(mbl).wait()
+            x = self._inp(st, inputs, mbl) if st.is_first else take("F", mbl)
             for li in range(L):
                 units[li].acquire()
                 x = st.forward_layer(li, mbl, x, self._tgt(st, targets, mbl), self.recompute)
@@ -63,7 +81,7 @@ class OneFOneBSchedule(ScheduleBase):
                 st.send_fwd(mbl, x)
 
         def bwd(mbl):
-            dy = None if st.is_last else st.recv_bwd(mbl).wait()
+            dy = None if st.is_last else take("B", mbl)
             # On CUDA the reduction of a layer is queued on the communication stream as soon as its last
             # backward is issued and overlaps the rest of that backward.  Host-blocking collectives (gloo)
             # must wait until this microbatch's gradient has been sent upstream: a rank that finishes early
@@ -90,16 +108,18 @@ class OneFOneBSchedule(ScheduleBase):
                         units[li].reduce_grads()
 
         if self.order is not None:
-            for op, i in self.order:
-                (fwd if op == "F" else bwd)(i)
+            seq = list(self.order)
         else:
-            for i in range(warm):
-                fwd(i)
+            seq = [("F", i) for i in range(warm)]
             for i in range(M - warm):
-                fwd(warm + i)
-                bwd(i)
-            for i in range(M - warm, M):
-                bwd(i)
+                seq += [("F", warm + i), ("B", i)]
+            seq += [("B", i) for i in range(M - warm, M)]
+        for j, (op, i) in enumerate(seq):
+            if self.prepost_recv:
+                post(op, i)
+                if j + 1 < len(seq):
+                    post(*seq[j + 1])
+            (fwd if op == "F" else bwd)(i)
         if hold and M > 0:
             # the held-back weight gradients, then the reductions of the layers they belong to (last layer first,
             # the order every rank of the stage uses)

@@ -116,7 +116,7 @@ class PipelineStage:
     def __init__(self, cfg: PipelineConfig, st: StageConfig, *, rank: int, device: torch.device, ops,
                  engine_cfg: EngineConfig, groups: StageGroups, streams: Streams, pattern: StageCommPattern,
                  transport, gloo_transport=None, activation_offload: bool = False, model_overrides: Optional[dict] = None,
-                 local_mailbox=None, process_rank: Optional[int] = None):
+                 local_mailbox=None, process_rank: Optional[int] = None, split_parity: Optional[bool] = None):
         # `rank` is the number the config and the p2p plan know this process by (its lane with tensor
         # parallelism); `process_rank` its rank in torch.distributed, which the groups are made of
         self.cfg, self.st, self.rank, self.device, self.ops = cfg, st, rank, device, ops
@@ -147,7 +147,8 @@ class PipelineStage:
         # irregular routing (mixed widths / uneven counts): traffic of even and odd stage boundaries goes
         # through different process groups, so that a rank's receives (boundary b - 1) and sends (boundary b)
         # never share a serialised queue; regular plans keep the four groups they were measured with
-        self.split_parity = not is_regular(cfg)
+        # (`split_parity=True`: asked for by a schedule that posts receives ahead, which needs the same separation)
+        self.split_parity = (not is_regular(cfg)) if split_parity is None else bool(split_parity)
         self.pos = [s.stage_id for s in cfg.stages].index(st.stage_id)
         self.transport = transport
         self.gloo_transport = gloo_transport

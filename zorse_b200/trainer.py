@@ -47,6 +47,7 @@ class TrainerOptions:
     pipeline_log: object = None
     defer_wgrad: bool = False              # 1F1B: input gradients are sent upstream before the weight-gradient GEMMs run
     defer_tail_wgrad: int = 0              # 1F1B, last stage: head (+ this many - 1 blocks) weight gradients after its last backward; 0 = off
+    prepost_recv: bool = False             # 1F1B: post the next operation's receive ahead (per-boundary p2p groups)
     shift_labels: bool = False             # synthetic targets = next token of the inputs (last position ignored)
 
 
@@ -87,7 +88,7 @@ class Trainer:
         # can alternate between them by stage width; on CPU ranks there is only Gloo
         both = opt.gloo_p2p and self.device.type == "cuda" and G.is_dist()
         self.transport = make_transport(self.device, use_gloo=opt.gloo_p2p and not both, gloo_group=self.gloo_group,
-                                        streams=self.streams, split_parity=not is_regular(cfg))
+                                        streams=self.streams, split_parity=not is_regular(cfg) or opt.prepost_recv)
         self.gloo_transport = GlooP2P(self.device, self.gloo_group) if both else None
         if tp > 1:
             self.transport = LaneTransport(self.transport, tp, self.tp_index)
@@ -105,7 +106,8 @@ class Trainer:
                           groups=stage_groups[st.stage_id], streams=self.streams, pattern=self.plan.stages[st.stage_id],
                           transport=self.transport, gloo_transport=self.gloo_transport,
                           activation_offload=bool(offload_act),
-                          model_overrides=opt.model_overrides, local_mailbox=mailbox)
+                          model_overrides=opt.model_overrides, local_mailbox=mailbox,
+                          split_parity=True if opt.prepost_recv else None)
             for st in cfg.stages_of_rank(self.lane)]
         self.spec = (self.stages[0].spec if self.stages else
                      registry.get_spec(cfg.model_name, vocab=cfg.vocab_size, **(opt.model_overrides or {})))
@@ -113,7 +115,8 @@ class Trainer:
         name = cfg.schedule or opt.schedule
         self.schedule = build_schedule(name, self.stages, cfg, recompute=recompute, pipeline_log=opt.pipeline_log,
                                        defer_wgrad=opt.defer_wgrad,
-                                       defer_tail_wgrad=opt.defer_tail_wgrad or cfg.defer_tail_wgrad or 0)
+                                       defer_tail_wgrad=opt.defer_tail_wgrad or cfg.defer_tail_wgrad or 0,
+                                       prepost_recv=opt.prepost_recv)
         self.step_idx = 0
 
     # ------------------------------------------------------------------ data
