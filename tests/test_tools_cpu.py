@@ -286,3 +286,61 @@ def test_status_word_of_the_checking_build_is_decoded(monkeypatch):
     word[0] = 5 | (3 << 8)
     with pytest.raises(k.KernelError, match=r"status 5 \(flag wait ran out\) in block 3"):
         k.check_status()
+
+
+def test_profile_helpers_memcpy_function_time_and_line_fit(tmp_path):
+    """Readers of a profiler trace by category and by name, the least-squares line the layer profile stores, and the
+    memory line (all zero on a CPU device)."""
+    import json
+
+    from zorse_b200.planner import latency
+    from zorse_b200.utils import metrics, trace
+
+    ev = [{"cat": "kernel", "name": "zb::gemm2_bf16_kernel<1, 0>", "dur": 1500, "ts": 0},
+          {"cat": "kernel", "name": "zb::adam_kernel", "dur": 500, "ts": 2000},
+          {"cat": "gpu_memcpy", "name": "Memcpy HtoD (Pinned -> Device)", "dur": 800, "ts": 100},
+          {"cat": "cpu_op", "name": "zero.adam", "dur": 4000, "ts": 0},
+          {"cat": "cpu_op", "name": "zero.adam", "dur": 2000, "ts": 5000}]
+    f = tmp_path / "t.json"
+    f.write_text(json.dumps({"traceEvents": ev}))
+    assert trace.extract_kernel_runtime(str(f), 2) == pytest.approx(1.0)
+    assert trace.extract_memcpy_runtime(str(f), 2) == pytest.approx(0.4)
+    assert trace.extract_function_runtime("zero.adam", str(f), 2) == pytest.approx(3.0)
+    assert trace.extract_function_runtime("gemm2_bf16_kernel", str(f)) == 0.0
+    assert trace.extract_function_runtime("gemm2_bf16_kernel", str(f), exact=False) == pytest.approx(1.5)
+    s, c = trace.fit_line([3.0, 5.0, 7.0, 9.0])
+    assert s == pytest.approx(2.0) and c == pytest.approx(1.0)
+    assert trace.fit_line([4.0]) == (4.0, 0.0)
+    with pytest.raises(ValueError):
+        trace.fit_line([])
+    table = {}
+    latency.store(table, "m", "b200", 128, "bfloat16", [3.0, 5.0, 7.0], [6.0, 10.0, 14.0])
+    row = table["m"]["b200"]["128"]["bfloat16"]
+    assert row[0] == pytest.approx([2.0, 1.0]) and row[1] == pytest.approx([4.0, 2.0])
+    lines = []
+    st = metrics.print_memory_stats("tag", "cpu", out=lines.append)
+    assert st["max_allocated"] == 0.0 and st["tag"] == "tag" and not lines
+
+
+def test_random_datasets_and_even_split():
+    import torch
+
+    from zorse_b200.utils import data
+
+    ds = data.RandomTokenDataset(100, 16, size=10, targets="next", seed=1)
+    x, y = ds[3]
+    assert len(ds) == 10 and x.dtype == torch.long and torch.equal(y[:-1], x[1:]) and 0 <= int(y[-1]) < 100
+    assert torch.equal(data.RandomTokenDataset(100, 16, size=10, seed=1).inputs, ds.inputs)      # same seed, same data
+    reg = data.RandomTokenDataset(100, 16, size=4, targets="regression")
+    assert reg[0][1].dtype == torch.float32 and float(reg.labels.max()) < 1.0
+    with pytest.raises(ValueError):
+        data.RandomTokenDataset(100, 16, targets="other")
+    img = data.RandomImageDataset(8, size=6, classes=0)
+    assert img[0][0].shape == (3, 8, 8) and img[0][1].dtype == torch.float32
+    assert data.RandomImageDataset(8, size=6, classes=5).labels.dtype == torch.long
+    batches = list(data.get_dataset("tiny_llama", batch_size=4, batches=3, seq_length=8, vocab_size=50))
+    assert len(batches) == 3 and batches[0][0].shape == (4, 8) and int(batches[0][0].max()) < 50
+    xs, ys = data.split_into(torch.arange(10), torch.arange(10), 4)
+    assert [len(a) for a in xs] == [3, 3, 2, 2] and torch.equal(torch.cat(ys), torch.arange(10))
+    with pytest.raises(ValueError):
+        data.split_into(torch.arange(2), torch.arange(2), 4)

@@ -154,9 +154,8 @@ def main(argv=None) -> int:
             heartbeat.beat(step)
         if step == args.warmup_iterations - 3:
             # same point as the reference (zorse.py:170-172): three steps before the timed region
-            mem = metrics.memory_stats(tr.device)
-            log.info("memory: " + ", ".join(f"{k}={v:.2f}" if isinstance(v, float) else f"{k}={v}" for k, v in mem.items()),
-                     leader_only=False)
+            metrics.print_memory_stats("before the timed steps", tr.device, rank=tr.rank,
+                                       out=lambda line: log.info(line, leader_only=False))
         iter_ms.append(ms)
         log.info(f"Iteration {step} Time {ms:.2f} ms" + (f" loss {float(loss):.4f}" if loss is not None else ""))
         if prof is not None and step == args.warmup_iterations - 1:

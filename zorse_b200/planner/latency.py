@@ -70,15 +70,9 @@ def load_model_compute_latencies_per_gpu(model: str, gpus: list[str], seq: int, 
 
 def store(table: dict, model: str, gpu: str, seq: int, dtype: str, fwd_ms: list[float], bwd_ms: list[float]) -> None:
     """Adds a profile (times at microbatch sizes 1..n) with its least-squares line."""
-    def fit(ys):
-        n = len(ys)
-        if n == 1:
-            return [ys[0], 0.0]
-        xs = list(range(1, n + 1))
-        mx, my = sum(xs) / n, sum(ys) / n
-        sl = sum((x - mx) * (y - my) for x, y in zip(xs, ys)) / sum((x - mx) ** 2 for x in xs)
-        return [sl, my - sl * mx]
+    from ..utils.trace import fit_line
 
+    fit = lambda ys: list(fit_line(ys))
     table.setdefault(model, {}).setdefault(gpu, {}).setdefault(str(seq), {})[dtype] = [fit(fwd_ms), fit(bwd_ms),
                                                                                       list(fwd_ms), list(bwd_ms)]
 

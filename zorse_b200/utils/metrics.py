@@ -68,6 +68,26 @@ def memory_stats(device) -> dict:
             "alloc_retries": st.get("num_alloc_retries", 0)}
 
 
+def print_memory_stats(tag: str, device, rank: int = 0, skip: bool = False, out=print) -> dict:
+    """One line per call with allocated / peak allocated / peak reserved memory in GiB and as a share of the device,
+    and the allocator's retry count (a non-zero count means the step ran against the memory limit); returns the
+    figures (reference utils/profile.py:16-48).  On a CPU device, or with `skip`, everything is zero and nothing
+    is printed."""
+    st = {"tag": tag, "allocated": 0.0, "max_allocated": 0.0, "max_reserved": 0.0, "cuda_malloc_retries": 0}
+    if skip or torch.device(device).type != "cuda":
+        return st
+    torch.cuda.synchronize(device)
+    m = memory_stats(device)
+    total = torch.cuda.get_device_properties(device).total_memory / 2**30
+    st.update(allocated=m["allocated_gb"], max_allocated=m["max_allocated_gb"], max_reserved=m["max_reserved_gb"],
+              cuda_malloc_retries=m["alloc_retries"])
+    out(f"rank {rank} {tag}: {st['allocated']:.2f} GiB allocated ({100 * st['allocated'] / total:.2f}%), "
+        f"{st['max_allocated']:.2f} GiB max allocated ({100 * st['max_allocated'] / total:.2f}%), "
+        f"{st['max_reserved']:.2f} GiB max reserved ({100 * st['max_reserved'] / total:.2f}%), "
+        f"{st['cuda_malloc_retries']} cuda malloc retries")
+    return st
+
+
 def format_summary(*, global_batch: int, seq: int, step_ms: float, flops_per_step: float, gpu_names: list[str],
                    dtype: str, max_alloc_gb: list[float], predicted_ms: Optional[float] = None,
                    exposed_comm_ms: Optional[float] = None, loss: Optional[float] = None, flashflex_ga: int = 1) -> str:

@@ -32,6 +32,36 @@ def extract_kernel_runtime(trace_file: str, iterations: int = 1, cat: str = "ker
     return sum(e.get("dur", 0) for e in ev if e.get("cat") == cat) / 1e3 / max(iterations, 1)
 
 
+def extract_memcpy_runtime(trace_file: str, iterations: int = 1) -> float:
+    """Copy-engine time per iteration in ms (reference utils/profile.py:133-158)."""
+    return extract_kernel_runtime(trace_file, iterations, cat="gpu_memcpy")
+
+
+def extract_function_runtime(name: str, trace_file: str, iterations: int = 1, exact: bool = True) -> float:
+    """Time per iteration (ms) of the trace events called `name` (any category: a kernel, a CPU operator, a
+    `record_function` / NVTX range); `exact=False` matches the name as a substring, which is what kernel names with
+    template arguments need (reference utils/profile.py:161-182 matches exactly)."""
+    with open(trace_file) as f:
+        ev = json.load(f).get("traceEvents", [])
+    hit = (lambda n: n == name) if exact else (lambda n: name in n)
+    return sum(e.get("dur", 0) for e in ev if hit(str(e.get("name", "")))) / 1e3 / max(iterations, 1)
+
+
+def fit_line(ys) -> tuple[float, float]:
+    """Least-squares (slope, intercept) of ys over x = 1..n, the form in which the layer profiler stores how a
+    latency grows with the microbatch size (reference utils/profile.py:124-130); one point gives (y, 0)."""
+    ys = [float(y) for y in ys]
+    n = len(ys)
+    if n == 0:
+        raise ValueError("fit_line needs at least one value")
+    if n == 1:
+        return ys[0], 0.0
+    mx, my = (n + 1) / 2.0, sum(ys) / n
+    sxx = sum((x - mx) ** 2 for x in range(1, n + 1))
+    slope = sum((x - mx) * (y - my) for x, y in zip(range(1, n + 1), ys)) / sxx
+    return slope, my - slope * mx
+
+
 def stream_busy_and_gaps(trace_file: str, gap_threshold_us: float = 0.0) -> dict:
     """Per CUDA stream: busy time and idle gaps between consecutive kernels (ms)."""
     with open(trace_file) as f:
