@@ -315,3 +315,57 @@ def test_1f1b_with_preposted_receives_gives_the_same_training(pipe_name):
     cfg = tiny_cfg(pipe)
     res = run_workers(2 if pipe_name == "PIPE_2x1" else 4, _worker, cfg, {"schedule": "1f1b", "prepost_recv": True}, 2)
     _check(res, cfg)
+
+
+def _worker_patterns(rank, world):
+    """Every collective pattern once on 4 gloo ranks arranged as 2 nodes x 2: results on all-ones inputs."""
+    import torch.distributed as dist
+
+    from zorse_b200.parallel.groups import dist_init
+    from zorse_b200.profiler import collectives as C
+
+    dist_init("gloo")
+    dev, f32 = torch.device("cpu"), torch.float32
+    groups = C.node_groups(local_size=2)
+    intra, inter = groups
+    assert dist.get_process_group_ranks(intra) == [rank // 2 * 2, rank // 2 * 2 + 1]
+    assert dist.get_process_group_ranks(inter) == [rank % 2, rank % 2 + 2]
+    out = {}
+    n = 64
+    p = C.AllReduce(n, f32, device=dev); p.execute(); out["all_reduce"] = float(p.full[0])
+    p = C.AllGather(n, f32, device=dev); p.execute(); out["all_gather"] = (p.full.numel(), float(p.full.sum()))
+    p = C.ReduceScatter(n, f32, device=dev); p.execute(); out["reduce_scatter"] = (p.shard.numel(), float(p.shard[0]))
+    p = C.Broadcast(n, f32, device=dev); p.execute(); out["broadcast"] = float(p.full[0])
+    p = C.IntraNodeAllGather(n, f32, dev, groups); p.execute(); out["intra_ag"] = (p.name, p.shard.numel(), p.full.numel())
+    p = C.InterNodeAllGather(n, f32, dev, groups); p.execute(); out["inter_ag"] = (p.name, p.shard.numel(), p.full.numel())
+    p = C.IntraNodeReduceScatter(n, f32, dev, groups); p.execute(); out["intra_rs"] = (p.name, float(p.shard[0]))
+    p = C.InterNodeReduceScatter(n, f32, dev, groups); p.execute(); out["inter_rs"] = (p.name, float(p.shard[0]))
+    p = C.HybridReduceScatter(n, f32, intra, inter, dev); p.execute(); out["hybrid"] = (p.shard.numel(), float(p.shard[0]))
+    p = C.ReduceScatter2Hop(n, f32, intra, inter, dev); p.execute()
+    out["two_hop"] = (p.name, p.shard2.numel(), float(p.shard2[0]), float(p.shard[0]))
+    p = C.Zero25(n, f32, intra, inter, dev); p.execute(); out["zero25"] = (p.name, float(p.shard[0]), float(p.shard[-1]))
+    p = C.Zero25Global(n, f32, device=dev); p.execute(); out["zero25g"] = (p.name, float(p.full[0]), float(p.full[-1]))
+    p = C.UnevenAllGather(n, [4, 2, 1, 1], f32, device=dev); p.execute(); out["uneven_ag"] = [t.numel() for t in p.parts]
+    p = C.UnevenReduceScatter(n, None, f32, device=dev, sizes=[10, 20, 30, 4]); p.execute()
+    out["uneven_rs"] = (p.mine.numel(), float(p.mine[0]))
+    t = C.time_pattern(C.Zero25(n, f32, intra, inter, dev), warmup=1, trials=2)
+    out["timed"] = sorted(t)
+    return out
+
+
+def test_collective_patterns_on_two_by_two_gloo_ranks():
+    """The benchmark patterns (world-wide, per node, across nodes, hybrid, 2-hop with and without the gather back,
+    list-based) compute what their names say (reference utils/comm_patterns.py)."""
+    res = run_workers(4, _worker_patterns)
+    for r, o in enumerate(res):
+        assert o["all_reduce"] == 4.0 and o["all_gather"] == (64, 64.0) and o["reduce_scatter"] == (16, 4.0)
+        assert o["broadcast"] == 1.0
+        assert o["intra_ag"] == ("intra_node_all_gather", 16, 32) and o["inter_ag"] == ("inter_node_all_gather", 16, 32)
+        assert o["intra_rs"] == ("intra_node_reduce_scatter", 2.0) and o["inter_rs"] == ("inter_node_reduce_scatter", 2.0)
+        assert o["hybrid"] == (32, 4.0)                     # summed over the node, then over the nodes
+        assert o["two_hop"] == ("reduce_scatter_2hop", 16, 4.0, 2.0)       # outer shard fully reduced, inner shard not
+        assert o["zero25"] == ("zero_2_5", 4.0, 4.0)                         # gathered back: whole inner shard reduced
+        assert o["zero25g"] == ("zero_2_5_global", 4.0, 4.0)
+        assert o["uneven_ag"] == [32, 16, 8, 8]
+        assert o["uneven_rs"] == ([10, 20, 30, 4][r], 4.0)
+        assert {"avg_time_ms", "bandwidth_mbps", "world_size"} <= set(o["timed"])

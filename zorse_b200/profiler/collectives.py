@@ -1,10 +1,12 @@
 """Collective benchmarks: the patterns the planner needs to cost ZeRO traffic.
 
 Classes with `.execute()` as in the reference's research tool (utils/comm_patterns.py:1-403):
-all-reduce, all-gather, reduce-scatter, hybrid reduce-scatter (reduce-scatter inside a group
-+ all-reduce across groups), 2-hop reduce-scatter, uneven (list based) all-gather /
-reduce-scatter, broadcast — timed with CUDA events (max over ranks) instead of profiler
-traces.  `fit_switch_model` turns timings at several sizes into the alpha / bandwidth pair
+all-reduce, all-gather, reduce-scatter, broadcast; all-gather / reduce-scatter restricted to the
+ranks of one node or to the ranks of equal local index across nodes (`node_groups`); hybrid
+reduce-scatter (reduce-scatter inside a group + all-reduce across groups); 2-hop reduce-scatter
+and "ZeRO 2.5" (the same with an all-gather back across the outer group); its world-wide
+list-based form; uneven (list based) all-gather / reduce-scatter by ratios or by sizes — timed
+with CUDA events (max over ranks) instead of profiler traces.  `fit_switch_model` turns timings at several sizes into the alpha / bandwidth pair
 of `planner/comm_model.switch_collective_ms`.
 """
 from __future__ import annotations
@@ -79,10 +81,79 @@ class HybridReduceScatter(Pattern):
             dist.all_reduce(self.shard, group=self.replicate_group)
 
 
+def node_groups(local_size: int | None = None):
+    """(intra-node group of this rank, inter-node group of this rank): the ranks of this rank's node, and the ranks
+    with this rank's local index on every node (reference utils/comm.py:124-160).  Collective: every rank creates
+    every group, in the same order.  `local_size` defaults to LOCAL_WORLD_SIZE, else the whole job is one node."""
+    import os
+
+    world, me = dist.get_world_size(), dist.get_rank()
+    local = int(local_size or os.environ.get("LOCAL_WORLD_SIZE", world))
+    if world % local:
+        raise ValueError(f"{world} ranks do not split into nodes of {local}")
+    intra = inter = None
+    for node in range(world // local):
+        g = dist.new_group(list(range(node * local, (node + 1) * local)))
+        if me // local == node:
+            intra = g
+    for idx in range(local):
+        g = dist.new_group(list(range(idx, world, local)))
+        if me % local == idx:
+            inter = g
+    return intra, inter
+
+
+class ScopedAllGather(Pattern):
+    """All-gather of a world-wide message's pieces inside one scope: with the intra-node group every rank
+    contributes 1 / world of the message and ends up with its node's part; with the inter-node group 1 / world
+    again, gathered across the nodes (reference IntraNodeAllGather / InterNodeAllGather)."""
+    name = "scoped_all_gather"
+
+    def __init__(self, numel, dtype=torch.bfloat16, scope_group=None, device=None, name=None):
+        super().__init__(numel, dtype, scope_group, device)
+        world = dist.get_world_size()
+        piece = max(self.numel // world, 1)
+        self.shard = torch.ones(piece, dtype=dtype, device=self.device)
+        self.full = torch.ones(piece * self.R, dtype=dtype, device=self.device)
+        if name:
+            self.name = name
+
+    def bytes(self) -> int:
+        return self.full.numel() * self.full.element_size()
+
+    def execute(self):
+        dist.all_gather_into_tensor(self.full, self.shard, group=self.group)
+
+
+class ScopedReduceScatter(ScopedAllGather):
+    name = "scoped_reduce_scatter"
+
+    def execute(self):
+        dist.reduce_scatter_tensor(self.shard, self.full, group=self.group)
+
+
+def IntraNodeAllGather(numel, dtype=torch.bfloat16, device=None, groups=None):
+    return ScopedAllGather(numel, dtype, (groups or node_groups())[0], device, "intra_node_all_gather")
+
+
+def InterNodeAllGather(numel, dtype=torch.bfloat16, device=None, groups=None):
+    return ScopedAllGather(numel, dtype, (groups or node_groups())[1], device, "inter_node_all_gather")
+
+
+def IntraNodeReduceScatter(numel, dtype=torch.bfloat16, device=None, groups=None):
+    return ScopedReduceScatter(numel, dtype, (groups or node_groups())[0], device, "intra_node_reduce_scatter")
+
+
+def InterNodeReduceScatter(numel, dtype=torch.bfloat16, device=None, groups=None):
+    return ScopedReduceScatter(numel, dtype, (groups or node_groups())[1], device, "inter_node_reduce_scatter")
+
+
 class ReduceScatter2Hop(Pattern):
-    """Reduce-scatter inside the inner group, reduce-scatter of the result across the outer
-    group, all-gather back across the outer group (the reference's "ZeRO 2.5" pattern)."""
+    """Reduce-scatter inside the inner group, then reduce-scatter of the result across the outer group; with
+    `gather_back` the outer shards are all-gathered again, so that every rank of the inner group ends with its
+    fully reduced inner shard (the reference's `Zero_2_5`; without it, its `ReduceScatter2Hop`)."""
     name = "reduce_scatter_2hop"
+    gather_back = False
 
     def __init__(self, numel, dtype=torch.bfloat16, inner_group=None, outer_group=None, device=None):
         super().__init__(numel, dtype, inner_group, device)
@@ -96,29 +167,72 @@ class ReduceScatter2Hop(Pattern):
         dist.reduce_scatter_tensor(self.shard, self.full, group=self.group)
         if self.outer is not None and self.Ro > 1:
             dist.reduce_scatter_tensor(self.shard2, self.shard[: self.n2], group=self.outer)
-            dist.all_gather_into_tensor(self.shard[: self.n2], self.shard2, group=self.outer)
+            if self.gather_back:
+                dist.all_gather_into_tensor(self.shard[: self.n2], self.shard2, group=self.outer)
+
+
+class Zero25(ReduceScatter2Hop):
+    name = "zero_2_5"
+    gather_back = True
+
+
+class Zero25Global(Pattern):
+    """The same result over one flat group: list-based reduce-scatter of the whole message over every rank, then
+    an all-gather of the reduced pieces (reference `Zero_2_5_Global`)."""
+    name = "zero_2_5_global"
+
+    def __init__(self, numel, dtype=torch.bfloat16, group=None, device=None):
+        super().__init__(numel, dtype, group, device)
+        self.pieces = list(self.full.split(self.numel // self.R))
+
+    def execute(self):
+        dist.reduce_scatter(self.shard, self.pieces, group=self.group)
+        dist.all_gather_into_tensor(self.full, self.shard, group=self.group)
 
 
 class UnevenAllGather(Pattern):
     """List-based all-gather with per-rank shard sizes given by `ratios`."""
     name = "uneven_all_gather"
 
-    def __init__(self, numel, ratios: Sequence[float], dtype=torch.bfloat16, group=None, device=None):
+    def __init__(self, numel, ratios: Sequence[float] | None = None, dtype=torch.bfloat16, group=None, device=None,
+                 sizes: Sequence[int] | None = None):
+        """Per-rank piece sizes: `sizes` (elements) when given, else `numel` split by `ratios`."""
         super().__init__(numel, dtype, group, device)
-        tot = sum(ratios)
-        sizes = [max(int(self.numel * r / tot), 1) for r in ratios]
+        if sizes is None:
+            tot = sum(ratios)
+            sizes = [max(int(self.numel * r / tot), 1) for r in ratios]
+        if len(sizes) != self.R:
+            raise ValueError(f"{len(sizes)} piece sizes for a group of {self.R}")
         self.parts = [torch.ones(s, dtype=dtype, device=self.device) for s in sizes]
         self.mine = self.parts[dist.get_rank(group)].clone()
 
+    def _owner(self, q: int) -> int:
+        return dist.get_global_rank(self.group, q) if self.group is not None else q
+
     def execute(self):
-        dist.all_gather(self.parts, self.mine, group=self.group)
+        if self.device.type == "cuda":
+            dist.all_gather(self.parts, self.mine, group=self.group)
+            return
+        # Gloo has no list form with unequal sizes: one broadcast per piece (what the ZeRO engine does for
+        # unequal shards on CPU ranks)
+        self.parts[dist.get_rank(self.group)].copy_(self.mine)
+        for q, part in enumerate(self.parts):
+            dist.broadcast(part, src=self._owner(q), group=self.group)
 
 
 class UnevenReduceScatter(UnevenAllGather):
     name = "uneven_reduce_scatter"
 
     def execute(self):
-        dist.reduce_scatter(self.mine, self.parts, group=self.group)
+        if self.device.type == "cuda":
+            dist.reduce_scatter(self.mine, self.parts, group=self.group)
+            return
+        me = dist.get_rank(self.group)
+        for q, part in enumerate(self.parts):
+            buf = part.clone()
+            dist.reduce(buf, dst=self._owner(q), group=self.group)
+            if q == me:
+                self.mine.copy_(buf)
 
 
 def time_pattern(p: Pattern, warmup: int = 3, trials: int = 10) -> dict:
