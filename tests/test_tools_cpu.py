@@ -344,3 +344,35 @@ def test_random_datasets_and_even_split():
     assert [len(a) for a in xs] == [3, 3, 2, 2] and torch.equal(torch.cat(ys), torch.arange(10))
     with pytest.raises(ValueError):
         data.split_into(torch.arange(2), torch.arange(2), 4)
+
+
+def _groups(pmap):
+    out = {}
+    for n, p in pmap.items():
+        out.setdefault(p, []).append(n)
+    return list(out.values())
+
+
+def test_mixed_graph_weighting_keeps_alike_gpus_together():
+    """One switch domain with two GPU generations: bandwidth alone ties every cut (contiguous blocks in rank order,
+    which mix the generations here); with the mixed weighting the clustering partitioner puts the four fast and the four
+    slow GPUs into one group each."""
+    from zorse_b200.planner.partition import build_gpu_graph, partition
+
+    names = ["b200", "h100", "b200", "h100", "b200", "h100", "b200", "h100"]
+    data = {"machines": [{"machine": "n0", "machine_index": 0}],
+            "gpu_list": [{"id": f"gpu_{i}", "name": n, "memory_total_mib": 183359 if n == "b200" else 81559,
+                          "machine": "n0", "global_rank": i} for i, n in enumerate(names)],
+            "bandwidth": {"intranode_bandwidth": {"0": 700.0}, "internode_bandwidth": {}}}
+    plain = partition(build_gpu_graph(data), 2)
+    assert {plain[f"gpu_{i}"] for i in range(4)} == {plain["gpu_0"]}               # ranks 0..3 together: mixed models
+    G = build_gpu_graph(data, weighting="mixed", gpu_latency_ms={"b200": 5.3, "h100": 11.0})
+    assert G["gpu_0"]["gpu_2"]["weight"] == 100 and G["gpu_0"]["gpu_1"]["weight"] < 90
+    mixed = partition(G, 2, "clustering")
+    assert len({mixed[f"gpu_{i}"] for i in (0, 2, 4, 6)}) == 1 and len({mixed[f"gpu_{i}"] for i in (1, 3, 5, 7)}) == 1
+    assert mixed["gpu_0"] != mixed["gpu_1"]
+    # (a minimum cut of a dense graph peels off single GPUs whatever the weights: the cut partitioners are made for
+    # clusters whose machines are islands of bandwidth)
+    assert sorted(map(len, _groups(partition(G, 2, "min_k_cut_split")))) == [1, 7]
+    with pytest.raises(ValueError):
+        build_gpu_graph(data, weighting="other")

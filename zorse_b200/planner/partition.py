@@ -15,14 +15,35 @@ import networkx as nx
 from .cluster import link_bandwidth
 
 
-def build_gpu_graph(data: dict) -> nx.Graph:
+def build_gpu_graph(data: dict, weighting: str = "bandwidth", gpu_latency_ms: dict | None = None) -> nx.Graph:
+    """`weighting="bandwidth"` (default, the reference's live path): an edge weighs its link bandwidth in GB/s.
+    `weighting="mixed"`: 0.7 x bandwidth (min-max normalised over the cluster's links) + 0.2 x memory similarity
+    (1 - difference over the cluster's range) + 0.1 x compute similarity (square root of the ratio of the two GPUs'
+    block latencies, from `gpu_latency_ms`: GPU name -> ms), scaled to 1..100 — the combination the reference carries
+    switched off (zorse_planner.py:44-71, 136-141).  It keeps alike GPUs together where bandwidth alone ties, which
+    is the case inside one NVSwitch domain that mixes GPU generations."""
+    if weighting not in ("bandwidth", "mixed"):
+        raise ValueError(f"weighting must be bandwidth or mixed, not {weighting!r}")
     G = nx.Graph()
     for g in data["gpu_list"]:
         G.add_node(g["id"], **{k: g[k] for k in ("id", "name", "memory_total_mib", "machine", "global_rank") if k in g})
     gl = data["gpu_list"]
-    for i in range(len(gl)):
-        for j in range(i + 1, len(gl)):
-            G.add_edge(gl[i]["id"], gl[j]["id"], weight=int(max(link_bandwidth(data, gl[i], gl[j]), 1)))
+    pairs = [(i, j) for i in range(len(gl)) for j in range(i + 1, len(gl))]
+    bw = {p: link_bandwidth(data, gl[p[0]], gl[p[1]]) for p in pairs}
+    if weighting == "bandwidth":
+        for (i, j), b in bw.items():
+            G.add_edge(gl[i]["id"], gl[j]["id"], weight=int(max(b, 1)))
+        return G
+    lo_b, hi_b = (min(bw.values()), max(bw.values())) if bw else (0.0, 0.0)
+    mem = [float(g.get("memory_total_mib", 0)) for g in gl]
+    lo_m, hi_m = min(mem), max(mem)
+    lat = {str(k).lower(): float(v) for k, v in (gpu_latency_ms or {}).items()}
+    for i, j in pairs:
+        b = 1.0 if hi_b == lo_b else (bw[(i, j)] - lo_b) / (hi_b - lo_b)
+        m = 1.0 if hi_m == lo_m else 1.0 - abs(mem[i] - mem[j]) / (hi_m - lo_m)
+        a, c = lat.get(str(gl[i].get("name", "")).lower()), lat.get(str(gl[j].get("name", "")).lower())
+        sim = 1.0 if not a or not c else (min(a, c) / max(a, c)) ** 0.5
+        G.add_edge(gl[i]["id"], gl[j]["id"], weight=int(max(round(100 * (0.7 * b + 0.2 * m + 0.1 * sim)), 1)))
     return G
 
 

@@ -157,7 +157,7 @@ def plan(data: dict, model_name: str, *, global_batch_size: int, sequence_length
          recompute: bool = True, measured_agrs: Optional[dict] = None, table: Optional[dict] = None,
          ks: Optional[list[int]] = None, microbatch_size: Optional[int] = None,
          compute_overhead: float = 1.075, tensor_parallel_size: int = 1,
-         schedule: Optional[str] = None) -> tuple[Optional[PlanResult], list[dict]]:
+         schedule: Optional[str] = None, graph_weighting: str = "bandwidth") -> tuple[Optional[PlanResult], list[dict]]:
     """tensor_parallel_size t > 1 plans for lanes of t GPUs; the ranks of the result are lane numbers, which is
     what the trainer's config means when it carries `tensor_parallel_size` (export_config writes it).
 
@@ -170,7 +170,16 @@ def plan(data: dict, model_name: str, *, global_batch_size: int, sequence_length
         from .tensor_parallel import coarsen
 
         data, lane_members = coarsen(data, tensor_parallel_size)
-    G = build_gpu_graph(data)
+    gpu_ms = None
+    if graph_weighting == "mixed":
+        # compute similarity of two GPUs = how alike their block latencies for this model are
+        names = sorted({str(g.get("name", "")).lower() for g in data["gpu_list"]})
+        try:
+            lat = load_model_compute_latencies_per_gpu(model_name, names, sequence_length, autocast_dtype, 1, table)
+            gpu_ms = {n: v.total for n, v in lat.items()}
+        except Exception:      # noqa: BLE001 - no profile for some GPU model: that term stays neutral
+            gpu_ms = None
+    G = build_gpu_graph(data, weighting=graph_weighting, gpu_latency_ms=gpu_ms)
     best, best_score, tried = None, None, []
     for k in (ks or candidate_ks(data)):
         pmap = partition(G, k, partition_algorithm)

@@ -39,6 +39,9 @@ def main(argv=None) -> int:
                          "the lane model is not calibrated against measurements yet")
     ap.add_argument("--compute_overhead", type=float, default=1.075,
                     help="whole-step time over the sum of profiled layer times (launch gaps, small kernels)")
+    ap.add_argument("--graph_weighting", default="bandwidth", choices=["bandwidth", "mixed"],
+                    help="edge weights of the GPU graph: link bandwidth alone, or mixed with memory and compute "
+                         "similarity (keeps alike GPUs together where bandwidth ties; use with the clustering partitioner)")
     ap.add_argument("--schedule", default=None,
                     help="the schedule the trainer will run: candidate plans are ranked by this repository's prediction "
                          "for that schedule, and the file gets the schedule, that prediction and, with 1f1b, how many "
@@ -60,7 +63,8 @@ def main(argv=None) -> int:
                       optimizer_multiplier=a.optimizer_multiplier, reserved_memory_gb=a.reserved_memory_gb,
                       recompute=not a.no_recompute, measured_agrs=measured,
                       ks=[a.num_stages] if a.num_stages else None, microbatch_size=a.microbatch_size, compute_overhead=a.compute_overhead,
-                      tensor_parallel_size=a.tensor_parallel_size, schedule=a.schedule)
+                      tensor_parallel_size=a.tensor_parallel_size, schedule=a.schedule,
+                      graph_weighting=a.graph_weighting)
     for t in tried:
         print(f"k={t['k']}: predicted {t['latency_ms']} ms (microbatch {t['microbatch_size']}, interleave {t['interleave_degree']})"
               + (f"; under {a.schedule}: {t['schedule_ms']:.1f} ms" if t.get("schedule_ms") is not None else ""))
