@@ -32,6 +32,26 @@ def test_reference_example_round_trip():
     assert tc.to_dict(cfg)["latency"] == REF_EXAMPLE["latency"]
 
 
+def test_shipped_example_configs_parse():
+    """Every training config under example/ parses, and the CPU one is the two-stage plan of the first benchmark
+    configuration (tiny decoder: 4 layers, hidden 512, 8 heads, FFN 1376, vocabulary 32000, fp32)."""
+    import glob
+    import os
+
+    from zorse_b200.models import registry
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "example")
+    files = sorted(glob.glob(os.path.join(root, "training_config*.json")))
+    assert len(files) >= 2
+    for f in files:
+        tc.parse_pipeline_config(f)
+    cpu = tc.parse_pipeline_config(os.path.join(root, "training_config_cpu_2stage.json"))
+    spec = registry.get_spec(cpu.model_name)
+    assert (spec.layers, spec.hidden, spec.heads, spec.ffn) == (4, 512, 8, 1376)
+    assert (cpu.global_batch_size, cpu.microbatch_size, cpu.sequence_length, cpu.vocab_size) == (8, 2, 128, 32000)
+    assert [s.gpu_ranks for s in cpu.stages] == [(0,), (1,)] and cpu.autocast_dtype == "float32"
+
+
 @pytest.mark.parametrize("mutate,msg", [
     (lambda d: d["pipeline_config"][0].update(layer_partition=[1, 22]), "starts at"),
     (lambda d: d["pipeline_config"][0].update(num_microbatches_per_rank=[1, 1, 1, 1]), "microbatches"),
