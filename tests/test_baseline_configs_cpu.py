@@ -1,4 +1,4 @@
-"""Scaled-down versions of the named benchmark configurations 2, 4 and 5 on CPU ranks (gloo):
+"""Scaled-down versions of the named benchmark configurations 2, 3, 4 and 5 on CPU ranks (gloo):
 same model families, parallel plans and engine options, tiny dimensions; each must reproduce
 the single-process oracle (loss and parameters after two steps)."""
 import torch
@@ -57,6 +57,20 @@ def test_config2_like_gqa_two_stages_zero2_optimizer_in_backward():
              "zero_config": [[2, 3]], "zero_level": 2}]
     cfg = _cfg("llama3.2_1b", pipe, 8, 2, 32, 512)
     res = run_workers(4, _worker, cfg, {"schedule": "zero2", "optimizer_in_backward": True}, ov, 2)
+    _check(res, cfg, ov)
+
+
+def test_config3_like_four_stages_two_way_zero3_as_the_benchmark_runs_it():
+    """The headline plan (4 stages x 2-way ZeRO-3 on 8 ranks) with the options `bench.py` picks for it: 1F1B without
+    recomputation, weight gradients of the head and the last block of the last stage held back to the end of its
+    backward; and once more under the schedule the configuration names (ZeRO-2 pipeline schedule, recomputing)."""
+    ov = {"layers": 8, "hidden": 64, "heads": 4, "kv_heads": 4, "ffn": 128}
+    pipe = [{"gpu_ranks": [2 * i, 2 * i + 1], "num_microbatches_per_rank": [4, 4], "layer_partition": [2 * i, 2 * i + 2],
+             "zero_config": [[2 * i, 2 * i + 1]]} for i in range(4)]
+    cfg = _cfg("llama2_7b", pipe, 8, 1, 32, 512)
+    res = run_workers(8, _worker, cfg, {"schedule": "1f1b", "defer_tail_wgrad": 2, "activation_recompute": False}, ov, 2)
+    _check(res, cfg, ov)
+    res = run_workers(8, _worker, cfg, {"schedule": "zero2"}, ov, 2)
     _check(res, cfg, ov)
 
 
