@@ -263,3 +263,57 @@ def test_fault_injection_is_refused_where_a_leaving_rank_would_fault_its_peers()
     assert "collectives" in injection_refusal(True, "fused", env={"NCCL_NVLS_ENABLE": "0"})
     assert "multimem" in injection_refusal(True, "library", env={"NCCL_NVLS_ENABLE": "0", "ZORSE_RS_ADAM_VARIANT": "3"})
     assert injection_refusal(True, "library", env={"NCCL_NVLS_ENABLE": "0"}) is None
+
+
+def _masters_of(ck_dir):
+    """gid -> whole fp32 master of every unit of a checkpoint, whatever plan wrote it."""
+    from zorse_b200.ckpt.reader import _file_offsets, read_meta, read_range
+
+    meta = read_meta(ck_dir)
+    off = _file_offsets(meta)
+    return meta["step"], {u["gid"]: read_range(ck_dir, meta, off, u, 0, 0, u["numel"]) for u in meta["units"]}
+
+
+def test_supervised_job_survives_the_loss_of_a_rank(tmp_path):
+    """End to end on CPU ranks: a 4-rank job (2 stages x 2) under the supervisor loses rank 1 before step 3 (the rank
+    exits by itself, between steps); the supervisor blames that rank and not the peers that then fail on their
+    connections, plans for the three GPUs that are left, resumes from the newest checkpoint and trains the remaining
+    steps.  The final parameters equal those of the same job run without a failure."""
+    import json
+
+    from zorse_b200.cli import supervise
+
+    gl = [{"index": i, "name": "NVIDIA B200", "memory_total_mib": 183359, "id": f"gpu_{i}", "machine": "m0",
+           "global_rank": i} for i in range(4)]
+    cluster = {"machines": [{"machine": "m0", "num_gpus": 4, "machine_index": 0, "gpus": gl}], "gpu_list": gl,
+               "total_gpus": 4, "bandwidth": {"internode_bandwidth": {}, "intranode_bandwidth": {"0": 770.0},
+                                              "internode_latency": {}, "intranode_latency": {"0": 2e-5}}}
+    pipe = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [2, 2], "layer_partition": [0, 2], "zero_config": [[0, 1]]},
+            {"gpu_ranks": [2, 3], "num_microbatches_per_rank": [2, 2], "layer_partition": [2, 4], "zero_config": [[2, 3]]}]
+    (tmp_path / "cluster.json").write_text(json.dumps(cluster))
+    (tmp_path / "tc.json").write_text(json.dumps(tiny_cfg(pipe)))
+    common = ["--config_file", str(tmp_path / "tc.json"), "--cluster_info_file", str(tmp_path / "cluster.json"),
+              "--train_steps", "5", "--checkpoint_every", "1", "--max_restarts", "1", "--grace", "20"]
+    trainer = ["--", "--backend", "gloo", "--skip_profile", "--lr", "1e-3"]
+    assert supervise.main(common + ["--checkpoint_dir", str(tmp_path / "ck_a"), "--work_dir", str(tmp_path / "run_a")]
+                          + trainer) == 0
+    assert supervise.main(common + ["--checkpoint_dir", str(tmp_path / "ck_b"), "--work_dir", str(tmp_path / "run_b")]
+                          + trainer + ["--inject_fault", "1:3:exit"]) == 0
+    # the second job restarted once, on three ranks, from step 3
+    new_cfg = parse_pipeline_dict(json.loads((tmp_path / "run_b" / "training_config_attempt1.json").read_text()))
+    assert new_cfg.world_size == 3 and new_cfg.global_batch_size == 8
+    assert (tmp_path / "run_b" / "attempt1_rank2.log").exists() and not (tmp_path / "run_b" / "attempt1_rank3.log").exists()
+    assert "resumed from" in (tmp_path / "run_b" / "attempt1_rank0.log").read_text()
+    sa, a = _masters_of(str(tmp_path / "ck_a" / "step_5"))
+    sb, b = _masters_of(str(tmp_path / "ck_b" / "step_5"))
+    assert sa == sb == 5 and set(a) == set(b)
+    for gid in a:
+        assert (a[gid] - b[gid]).abs().max().item() < 5e-5, gid
+    # attribution rules on their own
+    fr = supervise.failed_ranks
+    assert fr({0: 1, 1: 17, 2: 1, 3: -15}, {0: "RuntimeError: Connection closed by peer", 1: "", 2: "recvBytes failed", 3: ""},
+              [1, 0, 2, 3]) == [1]
+    assert fr({0: 3, 1: -15, 2: 3}, {0: "[watchdog] rank 0: no progress for 9s; ranks behind or silent: [1]; dumping", 1: "",
+                                     2: "[watchdog] rank 2: ...; ranks behind or silent: [1]"}, [0, 2, 1]) == [1]
+    assert fr({0: 1, 1: 1}, {0: "Connection reset", 1: "Connection closed by peer"}, [1, 0]) == [1]
+    assert fr({0: 0, 1: 0}, {}, [0, 1]) == []

@@ -78,12 +78,14 @@ def main(argv=None) -> int:
         if refusal:
             raise SystemExit(refusal)
     tr = Trainer(cfg, opt)
+    resumed_step = 0
     log.info(f"rank {tr.rank}/{tr.world} on {tr.device}; schedule {tr.schedule.name}; ops {tr.ops.name}; "
              f"stages {[s.stage_id for s in tr.stages]}", leader_only=False)
     if args.resume:
         from ..ckpt.reader import load_checkpoint
 
-        load_checkpoint(tr, args.resume)
+        resumed_step = load_checkpoint(tr, args.resume)
+        log.info(f"resumed from {args.resume} (step {resumed_step})")
     from ..utils.health import maybe_inject, parse_fault
 
     fault = parse_fault(args.inject_fault)
@@ -120,17 +122,22 @@ def main(argv=None) -> int:
         log.info(f"replay check: identical={rep['identical']} loss={rep['loss']} "
                  f"differing units={[(d['gid'], d['kind'], d['max_abs_diff']) for d in rep['differing_units']]}",
                  leader_only=False)
-    total = args.warmup_iterations + args.iterations
+    # --train_steps: a job that is told how far to train and continues the count of the checkpoint it resumed;
+    # otherwise the benchmark form of the reference (warm-up + timed iterations, counted from 0)
+    first = resumed_step if args.train_steps else 0
+    total = args.train_steps if args.train_steps else args.warmup_iterations + args.iterations
+    if first >= total:
+        log.info(f"checkpoint is at step {first}, --train_steps {total}: nothing left to train")
     iter_ms = []
     prof = None
     loss = None
-    for step in range(total):
+    for step in range(first, total):
         maybe_inject(fault, tr.rank, step, keepalive=watchdog.beat if watchdog else None)
-        if step == args.warmup_iterations:
+        if step - first == args.warmup_iterations:
             tr.synchronize()
             tr.barrier()
         if (not args.skip_profile and args.trace_dir and prof is None
-                and step == args.warmup_iterations - args.profiling_iterations and args.profiling_iterations > 0):
+                and step - first == args.warmup_iterations - args.profiling_iterations and args.profiling_iterations > 0):
             from ..utils.trace import profiler_context
 
             prof = profiler_context(args.trace_dir, args.experiment_name, tr.rank)
@@ -152,13 +159,13 @@ def main(argv=None) -> int:
             watchdog.beat(step)
         if heartbeat is not None:
             heartbeat.beat(step)
-        if step == args.warmup_iterations - 3:
+        if step - first == args.warmup_iterations - 3:
             # same point as the reference (zorse.py:170-172): three steps before the timed region
             metrics.print_memory_stats("before the timed steps", tr.device, rank=tr.rank,
                                        out=lambda line: log.info(line, leader_only=False))
         iter_ms.append(ms)
         log.info(f"Iteration {step} Time {ms:.2f} ms" + (f" loss {float(loss):.4f}" if loss is not None else ""))
-        if prof is not None and step == args.warmup_iterations - 1:
+        if prof is not None and step - first == args.warmup_iterations - 1:
             prof.__exit__(None, None, None)
             prof = None
         if args.checkpoint_dir and args.checkpoint_every and (step + 1) % args.checkpoint_every == 0:
@@ -167,7 +174,7 @@ def main(argv=None) -> int:
             save_checkpoint(tr, args.checkpoint_dir, step + 1)
     # mean of the timed iterations (each one is bracketed by events / a host clock and a device
     # synchronisation above), so checkpoint writes and logging between steps are not counted
-    timed = iter_ms[args.warmup_iterations:]
+    timed = iter_ms[args.warmup_iterations:] or iter_ms[-1:]
     avg_ms = sum(timed) / len(timed) if timed else 0.0
     tr.barrier()
     # max over ranks, memory and GPU names over the host-side group

@@ -72,6 +72,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--checkpoint_dir", type=str, default=None)
     p.add_argument("--checkpoint_every", type=int, default=0)
     p.add_argument("--resume", type=str, default=None)
+    p.add_argument("--train_steps", type=int, default=0,
+                   help="train up to this optimizer step, counting the steps of a resumed checkpoint (checkpoints and "
+                        "--inject_fault then use that global step); 0 = run --warmup_iterations + --iterations steps")
     p.add_argument("--no_preflight", action="store_true",
                    help="skip the host-side replay of the schedule's p2p program before a multi-stage NCCL job starts")
     p.add_argument("--prepost_recv", action="store_true",
