@@ -317,3 +317,47 @@ def test_supervised_job_survives_the_loss_of_a_rank(tmp_path):
                                      2: "[watchdog] rank 2: ...; ranks behind or silent: [1]"}, [0, 2, 1]) == [1]
     assert fr({0: 1, 1: 1}, {0: "Connection reset", 1: "Connection closed by peer"}, [1, 0]) == [1]
     assert fr({0: 0, 1: 0}, {}, [0, 1]) == []
+
+
+def _worker_message_fault(rank, world, cfg_dict, fault):
+    """Step 0 runs clean; before step 1 rank 0 arms a message fault.  Returns (losses, error text or None, seconds)."""
+    import time
+
+    from zorse_b200.parallel.p2p import P2PTimeout
+    from zorse_b200.trainer import Trainer, TrainerOptions
+    from zorse_b200.utils.health import maybe_inject, parse_fault
+
+    tr = Trainer(parse_pipeline_dict(cfg_dict), TrainerOptions(backend="gloo", schedule="1f1b", p2p_timeout_s=4.0,
+                                                               p2p_fault_hooks=True))
+    batch = tr.synthetic_batch()
+    losses, err, t0 = [], None, time.time()
+    for step in range(2):
+        maybe_inject(parse_fault(fault), tr.rank, step, transport=tr.fault_transport)
+        try:
+            losses.append(tr.global_loss(tr.train_step_from_host(batch)))
+        except (P2PTimeout, RuntimeError) as e:
+            err = f"{type(e).__name__}: {e}"
+            break
+    return losses, err, time.time() - t0, list(tr.fault_transport.dropped)
+
+
+def test_dropped_and_delayed_pipeline_messages():
+    """Host-side message faults on Gloo ranks: a delayed activation only costs time; a dropped one ends the step on
+    the receiving rank with an error that names the missing message (sender, tag, kind), within the receive limit,
+    and the sender fails in bounded time too instead of waiting for ever."""
+    from zorse_b200.utils.health import parse_fault
+
+    cfg = tiny_cfg(PIPE_2x1)
+    clean = run_workers(2, _worker_message_fault, cfg, None)
+    late = run_workers(2, _worker_message_fault, cfg, "0:1:delay=1.5")
+    assert [r[1] for r in late] == [None, None] and late[0][0] == pytest.approx(clean[0][0], abs=1e-6)
+    assert late[0][2] > clean[0][2] + 1.0
+    lost = run_workers(2, _worker_message_fault, cfg, "0:1:drop", timeout=120)
+    (l0, e0, t0, d0), (l1, e1, t1, d1) = lost
+    assert len(d0) == 1 and d0[0][0] == 1 and d0[0][2].startswith("act") and not d1
+    assert e1 is not None and "P2PTimeout" in e1 and f"tag {d0[0][1]} from rank 0" in e1 and "act" in e1, e1
+    assert e0 is not None and t0 < 60 and t1 < 60, (e0, t0, t1)
+    assert len(l0) == 1 and len(l1) == 1 and l0[0] == pytest.approx(clean[0][0][0], abs=1e-6)     # step 0 was clean
+    assert parse_fault("3:7:delay=0.5") == (3, 7, "delay=0.5")
+    with pytest.raises(ValueError):
+        parse_fault("0:1:lose")

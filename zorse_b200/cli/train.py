@@ -34,7 +34,9 @@ def main(argv=None) -> int:
         activation_recompute=False if args.no_recompute else None,
         activation_offload=True if args.offload_activations_to_host else None, lr=args.lr, seed=args.seed,
         backend=args.backend, pipeline_log=plog, shift_labels=args.shift_labels, defer_wgrad=args.defer_wgrad,
-        defer_tail_wgrad=args.defer_tail_wgrad, prepost_recv=args.prepost_recv)
+        defer_tail_wgrad=args.defer_tail_wgrad, prepost_recv=args.prepost_recv,
+        p2p_timeout_s=args.p2p_timeout or None,
+        p2p_fault_hooks=bool(args.inject_fault) and (":drop" in args.inject_fault or ":delay=" in args.inject_fault))
     if opt.defer_tail_wgrad < 0:
         # -1: the planner's rule decides (held-back work must fit into the time the other stages drain)
         opt.defer_tail_wgrad = 0
@@ -132,7 +134,8 @@ def main(argv=None) -> int:
     prof = None
     loss = None
     for step in range(first, total):
-        maybe_inject(fault, tr.rank, step, keepalive=watchdog.beat if watchdog else None)
+        maybe_inject(fault, tr.rank, step, keepalive=watchdog.beat if watchdog else None,
+                     transport=getattr(tr, "fault_transport", None))
         if step - first == args.warmup_iterations:
             tr.synchronize()
             tr.barrier()

@@ -110,10 +110,17 @@ class NcclP2P:
         torch.cuda.current_stream().wait_stream(self.send_stream)
 
 
+class P2PTimeout(RuntimeError):
+    """A pipeline message did not arrive in time; the text names the message."""
+
+
 class GlooP2P:
-    def __init__(self, device: torch.device, group=None):
+    def __init__(self, device: torch.device, group=None, recv_timeout_s: float | None = None):
+        """`recv_timeout_s`: how long a receive may wait for its message before `P2PTimeout` is raised with the
+        sender, tag and kind of the missing message (None: the process group's own timeout applies)."""
         self.device = device
         self.group = group
+        self.recv_timeout_s = recv_timeout_s
         self.cuda = device.type == "cuda"
         if self.cuda:
             self.copy_send = torch.cuda.Stream(device=device)
@@ -142,7 +149,16 @@ class GlooP2P:
         work = dist.irecv(host, src, group=self.group, tag=tag)
 
         def wait():
-            work.wait()
+            if self.recv_timeout_s is None:
+                work.wait()
+            else:
+                try:
+                    done = work.wait(datetime.timedelta(seconds=self.recv_timeout_s))
+                except RuntimeError as e:
+                    raise P2PTimeout(f"no {kind} message with tag {tag} from rank {src} within {self.recv_timeout_s:g}s "
+                                     f"({str(e).splitlines()[0][:120]})") from e
+                if done is False:
+                    raise P2PTimeout(f"no {kind} message with tag {tag} from rank {src} within {self.recv_timeout_s:g}s")
             if not self.cuda:
                 return host
             with torch.cuda.stream(self.copy_recv):
@@ -203,6 +219,39 @@ class LoopbackP2P:
         pass
 
 
+class FaultyTransport:
+    """Host-side fault injection on the pipeline's messages (failure-detection tests; nothing on a device is made
+    to fault): the next `drop_next` sends are silently dropped, the next send is delayed by `delay_next_s` seconds."""
+
+    def __init__(self, inner):
+        self.inner = inner
+        self.drop_next = 0
+        self.delay_next_s = 0.0
+        self.dropped: list = []
+
+    def send(self, t, dst, tag, kind="act"):
+        if self.drop_next > 0:
+            self.drop_next -= 1
+            self.dropped.append((dst, tag, kind))
+            return Handle(lambda: None)
+        if self.delay_next_s > 0:
+            import time
+
+            d, self.delay_next_s = self.delay_next_s, 0.0
+            time.sleep(d)
+        return self.inner.send(t, dst, tag, kind)
+
+    def recv(self, shape, dtype, src, tag, kind="act"):
+        return self.inner.recv(shape, dtype, src, tag, kind)
+
+    def flush(self):
+        self.inner.flush()
+
+    @property
+    def bytes_sent(self):
+        return self.inner.bytes_sent
+
+
 class LaneTransport:
     """With tensor parallelism the plan numbers lanes, and slice t of lane a talks to slice t of lane b:
     this wrapper turns lane numbers into process ranks (lane * tp + t) for the transport under it."""
@@ -225,9 +274,9 @@ class LaneTransport:
 
 
 def make_transport(device: torch.device, use_gloo: bool = False, gloo_group=None, streams=None,
-                   split_parity: bool = False):
+                   split_parity: bool = False, recv_timeout_s: float | None = None):
     if not (dist.is_available() and dist.is_initialized()):
         return LoopbackP2P(0, {})
     if device.type == "cuda" and not use_gloo:
         return NcclP2P(device, streams=streams, split_parity=split_parity)
-    return GlooP2P(device, gloo_group)
+    return GlooP2P(device, gloo_group, recv_timeout_s=recv_timeout_s)

@@ -47,6 +47,8 @@ class TrainerOptions:
     pipeline_log: object = None
     defer_wgrad: bool = False              # 1F1B: input gradients are sent upstream before the weight-gradient GEMMs run
     defer_tail_wgrad: int = 0              # 1F1B, last stage: head (+ this many - 1 blocks) weight gradients after its last backward; 0 = off
+    p2p_timeout_s: Optional[float] = None  # Gloo p2p: a receive that waits longer raises, naming the missing message
+    p2p_fault_hooks: bool = False          # wrap the transport so that tests can drop or delay messages (host side)
     prepost_recv: bool = False             # 1F1B: post the next operation's receive ahead (per-boundary p2p groups)
     shift_labels: bool = False             # synthetic targets = next token of the inputs (last position ignored)
 
@@ -88,8 +90,13 @@ class Trainer:
         # can alternate between them by stage width; on CPU ranks there is only Gloo
         both = opt.gloo_p2p and self.device.type == "cuda" and G.is_dist()
         self.transport = make_transport(self.device, use_gloo=opt.gloo_p2p and not both, gloo_group=self.gloo_group,
-                                        streams=self.streams, split_parity=not is_regular(cfg) or opt.prepost_recv)
-        self.gloo_transport = GlooP2P(self.device, self.gloo_group) if both else None
+                                        streams=self.streams, split_parity=not is_regular(cfg) or opt.prepost_recv,
+                                        recv_timeout_s=opt.p2p_timeout_s)
+        if opt.p2p_fault_hooks:
+            from .parallel.p2p import FaultyTransport
+
+            self.transport = self.fault_transport = FaultyTransport(self.transport)
+        self.gloo_transport = GlooP2P(self.device, self.gloo_group, recv_timeout_s=opt.p2p_timeout_s) if both else None
         if tp > 1:
             self.transport = LaneTransport(self.transport, tp, self.tp_index)
             if self.gloo_transport is not None:

@@ -118,13 +118,17 @@ def tcp_heartbeat(rank: int, world: int, port_offset: int = 23, timeout_s: float
 
 
 def parse_fault(spec: Optional[str]):
-    """`rank:step:kind` with kind in stall | raise | exit -> (rank, step, kind); host-side fault
-    injection for failure-detection tests (nothing on the device is made to fault)."""
+    """`rank:step:kind` with kind in stall | raise | exit | drop | delay=<seconds> -> (rank, step, kind); host-side
+    fault injection for failure-detection tests (nothing on the device is made to fault).  `drop` loses the rank's
+    first pipeline message of that step, `delay=<s>` holds it back for s seconds (both need the trainer's
+    `p2p_fault_hooks`)."""
     if not spec:
         return None
     r, s, kind = spec.split(":")
-    if kind not in ("stall", "raise", "exit"):
+    if kind not in ("stall", "raise", "exit", "drop") and not kind.startswith("delay="):
         raise ValueError(f"unknown fault kind {kind!r}")
+    if kind.startswith("delay="):
+        float(kind[6:])
     return int(r), int(s), kind
 
 
@@ -153,13 +157,22 @@ def injection_refusal(on_cuda: bool, collectives: str, env=None) -> Optional[str
             "multicast object faults its peers' GPUs; " + "; ".join(why))
 
 
-def maybe_inject(fault, rank: int, step: int, keepalive: Optional[Callable[[int], None]] = None) -> None:
+def maybe_inject(fault, rank: int, step: int, keepalive: Optional[Callable[[int], None]] = None,
+                 transport=None) -> None:
     """Called between steps, with none of this rank's kernels or collectives in flight.
     `keepalive` (the local watchdog's beat) is called while a stalled rank sleeps, so that the
     stalled rank itself stays silent towards its peers without aborting on its own."""
     if fault is None or fault[0] != rank or fault[1] != step:
         return
     kind = fault[2]
+    if kind == "drop" or kind.startswith("delay="):
+        if transport is None or not hasattr(transport, "drop_next"):
+            raise RuntimeError("message faults need the trainer's p2p_fault_hooks (a FaultyTransport)")
+        if kind == "drop":
+            transport.drop_next = 1
+        else:
+            transport.delay_next_s = float(kind[6:])
+        return
     if kind == "raise":
         raise RuntimeError(f"injected failure on rank {rank} before step {step}")
     if kind == "exit":
