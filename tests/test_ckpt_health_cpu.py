@@ -327,7 +327,7 @@ def _worker_message_fault(rank, world, cfg_dict, fault):
     from zorse_b200.trainer import Trainer, TrainerOptions
     from zorse_b200.utils.health import maybe_inject, parse_fault
 
-    tr = Trainer(parse_pipeline_dict(cfg_dict), TrainerOptions(backend="gloo", schedule="1f1b", p2p_timeout_s=4.0,
+    tr = Trainer(parse_pipeline_dict(cfg_dict), TrainerOptions(backend="gloo", schedule="1f1b", p2p_timeout_s=15.0,
                                                                p2p_fault_hooks=True))
     batch = tr.synthetic_batch()
     losses, err, t0 = [], None, time.time()
@@ -352,11 +352,11 @@ def test_dropped_and_delayed_pipeline_messages():
     late = run_workers(2, _worker_message_fault, cfg, "0:1:delay=1.5")
     assert [r[1] for r in late] == [None, None] and late[0][0] == pytest.approx(clean[0][0], abs=1e-6)
     assert late[0][2] > clean[0][2] + 1.0
-    lost = run_workers(2, _worker_message_fault, cfg, "0:1:drop", timeout=120)
+    lost = run_workers(2, _worker_message_fault, cfg, "0:1:drop", timeout=180)
     (l0, e0, t0, d0), (l1, e1, t1, d1) = lost
     assert len(d0) == 1 and d0[0][0] == 1 and d0[0][2].startswith("act") and not d1
     assert e1 is not None and "P2PTimeout" in e1 and f"tag {d0[0][1]} from rank 0" in e1 and "act" in e1, e1
-    assert e0 is not None and t0 < 60 and t1 < 60, (e0, t0, t1)
+    assert e0 is not None and t0 < 120 and t1 < 120, (e0, t0, t1)
     assert len(l0) == 1 and len(l1) == 1 and l0[0] == pytest.approx(clean[0][0][0], abs=1e-6)     # step 0 was clean
     assert parse_fault("3:7:delay=0.5") == (3, 7, "delay=0.5")
     with pytest.raises(ValueError):
