@@ -84,6 +84,31 @@ def test_heartbeat_names_the_silent_rank():
     assert hbs[0].stale_ranks(limit_s=100.0, min_step=1) == [1]
 
 
+def test_short_or_garbled_store_reads_count_as_silence():
+    """A store that returns a cut-off or mangled heartbeat value (short read) or raises: the rank is reported as
+    silent; the reader does not crash the watchdog that calls it."""
+    class BadStore(DictStore):
+        def __init__(self, bad):
+            super().__init__()
+            self.bad = bad
+
+        def get(self, k):
+            if k in self.bad:
+                v = self.bad[k]
+                if isinstance(v, Exception):
+                    raise v
+                return v
+            return super().get(k)
+
+    now = [50.0]
+    store = BadStore({"hb/1": b"12", "hb/2": "7:", "hb/3": "x:y", "hb/4": RuntimeError("store gone"), "hb/5": b""})
+    hbs = [Heartbeat(store, r, 6, clock=lambda: now[0]) for r in range(6)]
+    for h in hbs:
+        h.beat(3)
+    assert hbs[0].read(0) == (3, 50.0) and all(hbs[0].read(r) is None for r in range(1, 6))
+    assert hbs[0].stale_ranks(limit_s=10.0) == [1, 2, 3, 4, 5]
+
+
 def test_watchdog_fires_on_a_stuck_step():
     fired = []
     w = Watchdog(1.0, on_timeout=lambda step, idle: fired.append((step, idle)), poll_s=0.05)

@@ -39,8 +39,11 @@ class Heartbeat:
             v = v.decode()
         if not v:
             return None
-        s, t = v.split(":")
-        return int(s), float(t)
+        try:                                  # a short or garbled read counts as no heartbeat, not as a crash
+            s, t = v.split(":")
+            return int(s), float(t)
+        except ValueError:
+            return None
 
     def stale_ranks(self, limit_s: float, min_step: Optional[int] = None) -> list[int]:
         """Ranks with no heartbeat, one older than limit_s, or (if given) behind min_step."""
