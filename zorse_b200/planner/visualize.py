@@ -14,7 +14,6 @@ ends in a file; no window or graphics API is involved.
 from __future__ import annotations
 
 import colorsys
-import math
 from dataclasses import dataclass, field
 from typing import Optional
 from xml.sax.saxutils import escape
