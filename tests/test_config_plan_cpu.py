@@ -500,3 +500,35 @@ def test_latency_driven_microbatch_routing():
     assert sorted(op for op, _ in order[1]) == ["B", "B", "F", "F"]
     for sched in ("layer_major", "zero2", "1f1b"):
         assert preflight(cfg, sched) is None, sched      # the p2p program of every schedule completes under NCCL's rules
+
+
+@pytest.mark.parametrize("n,want", [(1, ("1f1b", "library", 0, 1)), (2, ("1f1b", "fused", 0, 1)),
+                                    (4, ("1f1b", "fused", 0, 2)), (8, ("1f1b", "fused", 2, 4))])
+def test_bench_defaults_per_gpu_count(n, want, monkeypatch):
+    """What `bench.py --gpus N` hands to the trainer with no other flag: 1F1B, this repository's fused collectives from
+    two GPUs up, and the tail deferral the planner's rule picks (two layers on the 4-stage plan only)."""
+    import importlib.util
+    import os
+    import sys
+
+    import zorse_b200.trainer as trainer_mod
+
+    class Captured(Exception):
+        pass
+
+    def fake_trainer(cfg, opt):
+        raise Captured((cfg, opt))
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_script_defaults", os.path.join(root, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    monkeypatch.setattr(trainer_mod, "Trainer", fake_trainer)
+    monkeypatch.setenv("WORLD_SIZE", str(n))
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--gpus", str(n)])
+    with pytest.raises(Captured) as e:
+        mod.main()
+    cfg, opt = e.value.args[0]
+    assert (opt.schedule, opt.collectives, opt.defer_tail_wgrad, len(cfg.stages)) == want
+    assert opt.activation_recompute is None and not opt.defer_wgrad and not opt.prepost_recv
+    assert cfg.model_name == "llama2_7b" and cfg.global_batch_size == 64 and cfg.sequence_length == 4096
