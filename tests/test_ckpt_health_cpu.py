@@ -82,6 +82,14 @@ def test_heartbeat_names_the_silent_rank():
     now[0] += 5
     assert hbs[0].stale_ranks(limit_s=8.0) == [1]
     assert hbs[0].stale_ranks(limit_s=100.0, min_step=1) == [1]
+    # ranks 0 and 2 wait inside step 2 for rank 1, which never started it: all three have finished step 1 at best,
+    # but only rank 1 has not entered step 2
+    hbs[1].beat(1)
+    for r in (0, 1, 2):
+        hbs[r].beat_enter(1)
+    hbs[0].beat_enter(2)
+    hbs[2].beat_enter(2)
+    assert hbs[0].not_entered(2) == [1] and hbs[0].not_entered(1) == [] and hbs[0].not_entered(3) == [0, 1, 2]
 
 
 def test_short_or_garbled_store_reads_count_as_silence():
@@ -341,6 +349,10 @@ def test_supervised_job_survives_the_loss_of_a_rank(tmp_path):
     assert fr({0: 3, 1: -15, 2: 3}, {0: "[watchdog] rank 0: no progress for 9s; ranks behind or silent: [1]; dumping", 1: "",
                                      2: "[watchdog] rank 2: ...; ranks behind or silent: [1]"}, [0, 2, 1]) == [1]
     assert fr({0: 1, 1: 1}, {0: "Connection reset", 1: "Connection closed by peer"}, [1, 0]) == [1]
+    # a stalled rank: everybody is "behind" (useless), but only rank 2 has not entered the step the others are in
+    stuck = "[watchdog] rank {r}: no progress for 6.2s after step 2; ranks behind or silent: {b}; ranks that have not entered step 3: [2]"
+    assert fr({0: 3, 1: -6, 2: -15, 3: 3}, {0: stuck.format(r=0, b=[1, 2, 3]), 1: "Connection closed by peer", 2: "",
+                                            3: stuck.format(r=3, b=[0, 1, 2])}, [1, 0, 3, 2]) == [2]
     assert fr({0: 0, 1: 0}, {}, [0, 1]) == []
 
 

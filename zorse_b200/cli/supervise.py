@@ -9,7 +9,8 @@ torchrun job, rendezvous on 127.0.0.1) and waits.  A job that ends with every ra
 is done.  Otherwise the ranks that failed are found from exit codes and logs: a rank that ended
 with an error of its own (not the watchdog's abort code 3, not a signal from the supervisor, and a
 log that does not read like the loss of a peer) is a failed rank; else the ranks the watchdog
-reports name as "behind or silent"; else the rank that ended first.  The failed ranks' GPUs leave
+reports name as not having entered the step the others are in (or as "behind or silent"); else
+the rank that ended first.  The failed ranks' GPUs leave
 the cluster description, the planner runs on what is left (`cli.recover`), and the job starts
 again from the newest complete checkpoint under the new plan (with `--visible_devices`, every
 process pinned to a surviving GPU).  The checkpoint reader re-shards across plans, and
@@ -56,19 +57,22 @@ def failed_ranks(codes: dict, logs: dict, order: Optional[list] = None) -> list[
 
     1. ranks that ended with an error of their own: a non-zero code that is neither the watchdog's abort nor the
        supervisor's SIGTERM / SIGKILL, and a log that does not read like the loss of a peer;
-    2. else the ranks the watchdog reports name as behind or silent;
+    2. else the ranks the watchdog reports name as not having entered the step the others are in, else the ranks
+       they name as behind or silent (a list that names every rank says nothing and is skipped);
     3. else the rank that ended first with an error."""
     errored = [r for r, c in codes.items()
                if c not in (0, None, WATCHDOG_EXIT) and not (c < 0 and -c in (signal.SIGTERM, signal.SIGKILL))]
     own = [r for r in errored if not COLLATERAL.search(logs.get(r) or "")]
     if own:
         return sorted(own)
-    named: set = set()
-    for text in logs.values():
-        for m in re.finditer(r"ranks behind or silent: \[([0-9, ]*)\]", text or ""):
-            named.update(int(x) for x in m.group(1).split(",") if x.strip())
-    if named:
-        return sorted(named)
+    for pattern in (r"ranks that have not entered step \d+: \[([0-9, ]*)\]", r"ranks behind or silent: \[([0-9, ]*)\]"):
+        named: set = set()
+        for text in logs.values():
+            for m in re.finditer(pattern, text or ""):
+                named.update(int(x) for x in m.group(1).split(",") if x.strip())
+        # a list that names every rank of the job says nothing (everybody waits behind the same step)
+        if named and len(named) < len(codes):
+            return sorted(named)
     for r in order or []:
         if r in errored:
             return [r]
@@ -163,8 +167,8 @@ def main(argv=None) -> int:
             return 0
         bad = failed_ranks(codes, logs, order)
         print(f"[supervise] attempt {attempt} failed: exit codes {codes}; failed ranks {bad}", flush=True)
-        if not bad:
-            print("[supervise] no rank can be blamed (see the per-rank logs); not restarting", flush=True)
+        if not bad or len(bad) >= world:
+            print("[supervise] no rank can be singled out (see the per-rank logs); not restarting", flush=True)
             return 1
         if attempt == a.max_restarts:
             break

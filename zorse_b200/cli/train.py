@@ -98,6 +98,7 @@ def main(argv=None) -> int:
         from ..utils.health import Watchdog, tcp_heartbeat
 
         heartbeat = tcp_heartbeat(tr.rank, tr.world)
+        entered = [None]          # the step this rank is in
 
         def stuck(step, idle):
             # name the ranks whose heartbeat is older than ours before giving up
@@ -106,6 +107,11 @@ def main(argv=None) -> int:
                 # half the limit: a peer that beat a moment after this rank's last beat is just as stuck
                 behind = [r for r in heartbeat.stale_ranks(args.heartbeat_timeout / 2, min_step=step) if r != tr.rank]
                 msg += f"; ranks behind or silent: {behind}"
+                if entered[0] is not None:
+                    # everybody who waits for a stuck rank looks "behind"; the rank that never started the step
+                    # the others are in is the one they wait for
+                    late = [r for r in heartbeat.not_entered(entered[0]) if r != tr.rank]
+                    msg += f"; ranks that have not entered step {entered[0]}: {late}"
             sys.stderr.write(msg + "; dumping stacks and aborting\n")
             faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
             sys.stderr.flush()
@@ -136,6 +142,9 @@ def main(argv=None) -> int:
     for step in range(first, total):
         maybe_inject(fault, tr.rank, step, keepalive=watchdog.beat if watchdog else None,
                      transport=getattr(tr, "fault_transport", None))
+        if heartbeat is not None:
+            entered[0] = step
+            heartbeat.beat_enter(step)
         if step - first == args.warmup_iterations:
             tr.synchronize()
             tr.barrier()

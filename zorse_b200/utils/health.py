@@ -25,14 +25,29 @@ class Heartbeat:
         self.store, self.rank, self.world, self.clock = store, rank, world, clock
 
     def beat(self, step: int) -> None:
+        """Step `step` is finished on this rank."""
         self.store.set(f"hb/{self.rank}", f"{step}:{self.clock():.3f}")
 
-    def read(self, rank: int):
+    def beat_enter(self, step: int) -> None:
+        """This rank is about to run step `step`.  When a job stops, every rank that waits for a stuck peer has
+        finished the same step as that peer; what tells them apart is that they have entered the next one."""
+        self.store.set(f"hbin/{self.rank}", f"{step}:{self.clock():.3f}")
+
+    def not_entered(self, step: int) -> list[int]:
+        """Ranks that have not reported entering step `step` (or any later one)."""
+        out = []
+        for r in range(self.world):
+            hb = self.read(r, key="hbin")
+            if hb is None or hb[0] < step:
+                out.append(r)
+        return out
+
+    def read(self, rank: int, key: str = "hb"):
         try:
             check = getattr(self.store, "check", None)     # TCPStore.get blocks on a missing key
-            if check is not None and not check([f"hb/{rank}"]):
+            if check is not None and not check([f"{key}/{rank}"]):
                 return None
-            v = self.store.get(f"hb/{rank}")
+            v = self.store.get(f"{key}/{rank}")
         except (KeyError, RuntimeError, TimeoutError):   # key never written / store gone
             return None
         if isinstance(v, bytes):
