@@ -356,6 +356,34 @@ def test_fixed_plan_prediction_has_the_1f1b_and_gpipe_shapes():
     assert abs(predict_step_ms(cfg(4), "1f1b", table=table)["block_fwd_ms"] - 2.2) < 1e-9
 
 
+def test_prediction_on_a_mixed_cluster_costs_every_rank_with_its_own_gpu():
+    """`gpu` as a rank -> model mapping: a stage's single-microbatch time is its slowest rank's; its share of the
+    steady state is the largest microbatches x time over its ranks, so giving the slow rank fewer microbatches helps
+    exactly as far as it balances the products."""
+    from zorse_b200.planner.predict import predict_step_ms
+
+    table = {"llama2_7b": {"fast": {"4096": {"bfloat16": [[2.0, 0.0], [4.0, 0.0]]}},
+                           "slow": {"4096": {"bfloat16": [[4.0, 0.0], [8.0, 0.0]]}}}}
+
+    def cfg(counts):
+        return {"model_name": "llama2_7b", "global_batch_size": sum(counts), "microbatch_size": 1, "sequence_length": 4096,
+                "vocab_size": 32000, "autocast_dtype": "bfloat16",
+                "pipeline_config": [{"gpu_ranks": [0, 1], "layer_partition": [0, 32], "num_microbatches_per_rank": counts,
+                                     "zero_config": [[0, 1]]}]}
+
+    same = predict_step_ms(cfg([12, 12]), "1f1b", table=table, gpu="fast")
+    assert predict_step_ms(cfg([12, 12]), "1f1b", table=table, gpu={0: "fast", 1: "fast"})["ms"] == same["ms"]
+    even = predict_step_ms(cfg([12, 12]), "1f1b", table=table, gpu={0: "fast", 1: "slow"})
+    fair = predict_step_ms(cfg([16, 8]), "1f1b", table=table, gpu={0: "fast", 1: "slow"})
+    over = predict_step_ms(cfg([20, 4]), "1f1b", table=table, gpu={0: "fast", 1: "slow"})
+    assert even["block_fwd_ms"] == 4.0 and same["block_fwd_ms"] == 2.0
+    t_fast, t_slow = same["stage_ms"][0], even["stage_ms"][0]        # one microbatch through the stage on either GPU
+    assert t_slow - t_fast == pytest.approx(32 * 6.0)                # the blocks double, head and embedding do not change
+    assert same["steady_ms"] == pytest.approx(12 * t_fast) and even["steady_ms"] == pytest.approx(12 * t_slow)
+    assert fair["steady_ms"] == pytest.approx(max(16 * t_fast, 8 * t_slow)) and fair["steady_ms"] < even["steady_ms"]
+    assert over["steady_ms"] == pytest.approx(20 * t_fast) and over["steady_ms"] > fair["steady_ms"]   # the fast rank is the long one now
+
+
 def test_tail_deferral_rule_follows_the_drain_window():
     """The rule that picks how many layers of the last stage hold their weight gradients back: on by two layers for the
     4-stage plan with 32 microbatches per rank (measured: 1548 -> 1484 ms), off where the held-back work does not fit
@@ -433,10 +461,13 @@ def test_plan_ranks_candidates_by_the_schedule_the_trainer_will_run():
     _, lm = plan(data, "llama2_7b", schedule="layer_major", global_batch_size=64, sequence_length=4096, microbatch_size=1)
     by_k = {t["k"]: t["schedule_ms"] for t in lm}
     assert by_k[1] < by_k[2] < by_k[4] < by_k[8]
+    # a mixed cluster: every rank is costed with its own GPU model, so the plan with one slow GPU among its stages is
+    # predicted slower than the all-B200 one
     mixed = json.loads(json.dumps(data))
-    mixed["gpu_list"][0]["name"] = "h100"
+    mixed["gpu_list"][0]["name"] = "NVIDIA H100 80GB HBM3"
     _, tr2 = plan(mixed, "llama2_7b", schedule="1f1b", ks=[8], **kw)
-    assert "schedule_ms" not in tr2[0]
+    _, tr1 = plan(data, "llama2_7b", schedule="1f1b", ks=[8], **kw)
+    assert tr2[0]["schedule_ms"] > tr1[0]["schedule_ms"] * 1.05        # (the slow GPU's stage also gets fewer layers)
 
 
 def test_drawings_of_the_gpu_graph_and_its_partition(tmp_path):

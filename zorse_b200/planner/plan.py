@@ -162,9 +162,9 @@ def plan(data: dict, model_name: str, *, global_batch_size: int, sequence_length
     what the trainer's config means when it carries `tensor_parallel_size` (export_config writes it).
 
     `schedule`: the schedule the trainer will run.  The stage-2 optimizer costs every candidate with the reference's
-    all-forward-then-all-backward model; with a schedule name, and a cluster of one GPU model that the profile table
-    covers, the candidates (one per number of groups) are ranked by `predict.predict_step_ms` for that schedule
-    instead (1F1B ramps, layer-major replay, tail deferral), and each entry of the returned list carries both figures."""
+    all-forward-then-all-backward model; with a schedule name the candidates (one per number of groups) are ranked by
+    `predict.predict_step_ms` for that schedule instead (1F1B ramps, layer-major replay, tail deferral; every rank
+    with its own GPU model's times), and each entry of the returned list carries both figures."""
     full_data, lane_members = data, None
     if tensor_parallel_size > 1:
         from .tensor_parallel import coarsen
@@ -206,14 +206,15 @@ def plan(data: dict, model_name: str, *, global_batch_size: int, sequence_length
 
 def _schedule_ms(res: PlanResult, data: dict, model_name: str, gbs: int, seq: int, vocab: int, autocast_dtype: str,
                  reduce_dtype: str, schedule: str, recompute: bool, table: Optional[dict]) -> Optional[float]:
-    """Predicted step of a candidate plan under `schedule`, or None when the predictor does not cover the cluster
-    (several GPU models, or no profile rows)."""
+    """Predicted step of a candidate plan under `schedule` (every rank costed with its own GPU model's profile, or
+    the analytic estimate where the table has none), or None when the predictor fails."""
     from .predict import best_tail_deferral, predict_step_ms
 
-    kinds = {g["name"] if isinstance(g, dict) else str(g) for g in data.get("gpu_list", [])}
-    if len(kinds) != 1:
+    gpu = {int(g["global_rank"]): clean_gpu_name(g["name"]) for g in data.get("gpu_list", []) if isinstance(g, dict)}
+    if not gpu:
         return None
-    gpu = next(iter(kinds)).lower()
+    if len(set(gpu.values())) == 1:
+        gpu = next(iter(gpu.values()))
     cfg = export_config(res, model_name, gbs, seq, vocab, autocast_dtype, reduce_dtype)
     rc = None if recompute else False
     try:

@@ -43,12 +43,12 @@ def chain_overhead(table: dict, model: str, gpu: str) -> float:
         return 1.0
 
 
-def _layer_major_ms(G, f, b, head, emb, p2p, recompute) -> float:
+def _layer_major_ms(G, p2p, recompute) -> float:
     """Replays the layer-major loop of every stage under the block-time model: stage s runs layer 0 on microbatch j
     once stage s-1 has finished its last layer on that microbatch (plus the transfer), then every further layer on all
     microbatches; backward mirrors it from the last stage (which turns around at once).  Returns the time at which
-    the first stage finishes its backward (reference loop: zorse_utils/pipeline_schedule_v2.py:202-374)."""
-    (hf, hb), (ef, eb) = head, emb
+    the first stage finishes its backward (reference loop: zorse_utils/pipeline_schedule_v2.py:202-374).  Every
+    group entry carries its own block, head and embedding times (those of its slowest GPU)."""
 
     def feed(up_out, m):
         if up_out is None:
@@ -60,7 +60,7 @@ def _layer_major_ms(G, f, b, head, emb, p2p, recompute) -> float:
     for g in G:
         arr, t = feed(out, g["m"]), 0.0
         for l in range(g["n"]):
-            c = f + (ef if g["first"] and l == 0 else 0.0) + (hf if g["last"] and l == g["n"] - 1 else 0.0)
+            c = g["f"] + (g["ef"] if g["first"] and l == 0 else 0.0) + (g["hf"] if g["last"] and l == g["n"] - 1 else 0.0)
             out = []
             for j in range(g["m"]):
                 t = max(t, arr[j]) if l == 0 else t
@@ -71,11 +71,11 @@ def _layer_major_ms(G, f, b, head, emb, p2p, recompute) -> float:
     for g, t0 in zip(reversed(G), reversed(fwd_end)):
         arr, t = feed(out, g["m"]), t0
         for l in reversed(range(g["n"])):
-            c = b + (f if recompute else 0.0)
+            c = g["b"] + (g["f"] if recompute else 0.0)
             if g["last"] and l == g["n"] - 1:
-                c += hb + (hf if recompute else 0.0)
+                c += g["hb"] + (g["hf"] if recompute else 0.0)
             if g["first"] and l == 0:
-                c += eb + (ef if recompute else 0.0)
+                c += g["eb"] + (g["ef"] if recompute else 0.0)
             out = []
             for j in range(g["m"]):
                 t = max(t, arr[j]) if l == g["n"] - 1 else t
@@ -84,21 +84,31 @@ def _layer_major_ms(G, f, b, head, emb, p2p, recompute) -> float:
     return t
 
 
-def predict_step_ms(cfg: dict, schedule: str, *, recompute: Optional[bool] = None, gpu: str = "b200",
+def predict_step_ms(cfg: dict, schedule: str, *, recompute: Optional[bool] = None, gpu="b200",
                     table: Optional[dict] = None, defer_wgrad: bool = False, defer_tail_wgrad: int = 0,
                     optimizer_gbs: float = 6000.0,
                     p2p_gbs: float = 700.0, p2p_latency_ms: float = 0.02, collective_gbs: float = 600.0,
                     collective_latency_ms: float = 0.03) -> dict:
-    """`cfg` is a training_config dict.  Returns {"ms": total, ...terms}."""
+    """`cfg` is a training_config dict.  `gpu`: the GPU model every rank runs on, or a mapping rank -> GPU model for
+    a mixed cluster (a rank's block, head and embedding times are those of its own model; a stage's single-microbatch
+    time is its slowest rank's, its share of the steady state the largest `microbatches x time` over its ranks, which
+    is what unequal microbatch counts per rank are there to balance).  Returns {"ms": total, ...terms}."""
     table = load_table() if table is None else table
     model = cfg["model_name"]
     seq, mbs, vocab = int(cfg["sequence_length"]), int(cfg["microbatch_size"]), int(cfg.get("vocab_size", 32000))
     dtype = cfg.get("autocast_dtype", "bfloat16")
     stats = registry.get_model_stats(model, vocab=vocab)
-    lat = load_model_compute_latencies_per_gpu(model, [gpu], seq, dtype, mbs, table)[gpu]
-    oh = chain_overhead(table, model, gpu)
-    f, b = lat.forward * oh, lat.backward * oh
-    (hf, hb), (ef, eb) = head_and_embedding_ms(model, gpu, seq, mbs, vocab)
+    name_of = (lambda r: str(gpu[r]).lower()) if isinstance(gpu, dict) else (lambda r: gpu)
+    cache: dict = {}
+
+    def times(name):
+        if name not in cache:
+            lat = load_model_compute_latencies_per_gpu(model, [name], seq, dtype, mbs, table)[name]
+            oh = chain_overhead(table, model, name)
+            (hf, hb), (ef, eb) = head_and_embedding_ms(model, name, seq, mbs, vocab)
+            cache[name] = {"f": lat.forward * oh, "b": lat.backward * oh, "hf": hf, "hb": hb, "ef": ef, "eb": eb, "oh": oh}
+        return cache[name]
+
     sched = (schedule or "layer_major").lower()
     gpipe = sched in GPIPE_SHAPED
     if recompute is None:
@@ -109,7 +119,8 @@ def predict_step_ms(cfg: dict, schedule: str, *, recompute: Optional[bool] = Non
     for i, s in enumerate(stages):
         key = tuple(s["gpu_ranks"])
         g = groups.setdefault(key, {"n": 0, "first": False, "last": False, "m": max(s["num_microbatches_per_rank"]),
-                                    "R": len(s["gpu_ranks"]), "chunks": 0})
+                                    "R": len(s["gpu_ranks"]), "chunks": 0, "ranks": list(s["gpu_ranks"]),
+                                    "counts": list(s["num_microbatches_per_rank"])})
         g["n"] += s["layer_partition"][1] - s["layer_partition"][0]
         g["first"] |= i == 0
         g["last"] |= i == len(stages) - 1
@@ -124,25 +135,32 @@ def predict_step_ms(cfg: dict, schedule: str, *, recompute: Optional[bool] = Non
     def coll(R):
         return 0.0 if R <= 1 else collective_latency_ms + layer_bytes * (R - 1) / R / (collective_gbs * 1e9) * 1e3
 
-    T, W = [], []
+    def one_microbatch(g, t, less=0.0):
+        F = g["n"] * t["f"] + (t["hf"] if g["last"] else 0.0) + (t["ef"] if g["first"] else 0.0)
+        B = g["n"] * t["b"] + (t["hb"] if g["last"] else 0.0) + (t["eb"] if g["first"] else 0.0) + (F if recompute else 0.0)
+        return F + B - less
+
+    tail_on = defer_tail_wgrad > 0 and not gpipe and P > 1 and v == 1
+    T, W, S = [], [], []
     for g in G:
-        F = g["n"] * f + (hf if g["last"] else 0.0) + (ef if g["first"] else 0.0)
-        B = g["n"] * b + (hb if g["last"] else 0.0) + (eb if g["first"] else 0.0) + (F if recompute else 0.0)
-        T.append(F + B)
-        W.append(g["n"] * f * WGRAD_SHARE_OF_FORWARD)
-    tail = 0.0
-    if defer_tail_wgrad > 0 and not gpipe and P > 1 and v == 1:
+        per_rank = [times(name_of(r)) for r in g["ranks"]]
+        slow = max(per_rank, key=lambda t: one_microbatch(g, t))
+        g.update(slow)                      # the stage's own block / head / embedding times: its slowest GPU's
         # the last stage's head (+ blocks) weight gradients leave every microbatch's backward and run after its last
         # one, inside the time the stages before it need to finish (see `best_tail_deferral`)
-        w = max(hb - hf, 0.0) + (min(defer_tail_wgrad, G[-1]["n"] + 1) - 1) * f * WGRAD_SHARE_OF_FORWARD
-        T[-1] -= w
-        tail = max(0.0, G[-1]["m"] * w - sum(g["n"] * b for g in G[:-1]))
-    m = max(g["m"] for g in G)
-    k = max(range(P), key=lambda i: T[i] * G[i]["m"])
-    steady = G[k]["m"] * T[k]
+        held = [(max(t["hb"] - t["hf"], 0.0) + (min(defer_tail_wgrad, g["n"] + 1) - 1) * t["f"] * WGRAD_SHARE_OF_FORWARD)
+                if tail_on and g is G[-1] else 0.0 for t in per_rank]
+        per_mb = [one_microbatch(g, t, w) for t, w in zip(per_rank, held)]
+        T.append(max(per_mb))
+        S.append(max(c * x for c, x in zip(g["counts"], per_mb)))
+        W.append(g["n"] * slow["f"] * WGRAD_SHARE_OF_FORWARD)
+        g["held"] = max(c * w for c, w in zip(g["counts"], held))
+    tail = max(0.0, G[-1]["held"] - sum(g["n"] * g["b"] for g in G[:-1])) if tail_on else 0.0
+    k = max(range(P), key=lambda i: S[i])
+    steady = S[k]
     layer_major = sched in LAYER_MAJOR_SHAPED and v == 1 and P > 1
     if layer_major:
-        ramp = _layer_major_ms(G, f, b, (hf, hb), (ef, eb), p2p, recompute) - steady
+        ramp = _layer_major_ms(G, p2p, recompute) - steady
     elif gpipe:
         # all forwards, then all backwards: the ramps are the other stages' single-microbatch passes too
         ramp = sum(T[i] for i in range(P) if i != k)
@@ -156,15 +174,18 @@ def predict_step_ms(cfg: dict, schedule: str, *, recompute: Optional[bool] = Non
     if gpipe and any(g["R"] > 1 for g in G):
         # layer-major / ZeRO-2 pipeline shapes re-gather in backward; the gathers overlap unless they are longer
         # than the compute they hide behind
-        per_layer_compute = min(gg["m"] for gg in G) * f
+        per_layer_compute = min(gg["m"] * gg["f"] for gg in G)
         zero += max(0.0, max(coll(g["R"]) for g in G) - per_layer_compute) * max(g["n"] for g in G)
     comm = 0.0 if layer_major else 2.0 * (P - 1) * p2p * (v if not gpipe else 1)     # layer-major: inside the replay
     total = steady + ramp + opt + zero + comm + tail
+    slowest = max(G, key=lambda g: g["f"] + g["b"])
     return {"ms": total, "steady_ms": steady, "ramp_ms": ramp, "optimizer_ms": opt, "zero_exposed_ms": zero,
-            "p2p_ms": comm, "tail_wgrad_ms": tail, "block_fwd_ms": f, "block_bwd_ms": b, "chain_overhead": oh, "recompute": bool(recompute),
+            "p2p_ms": comm, "tail_wgrad_ms": tail, "block_fwd_ms": slowest["f"], "block_bwd_ms": slowest["b"],
+            "chain_overhead": slowest["oh"], "recompute": bool(recompute),
             "form": "layer_major" if layer_major else "gpipe" if gpipe else "1f1b",
             "stage_ms": T, "stage_layers": [g["n"] for g in G], "stage_microbatches": [g["m"] for g in G],
-            "interleave": v, "head_wgrad_ms": max(hb - hf, 0.0), "block_wgrad_ms": f * WGRAD_SHARE_OF_FORWARD}
+            "stage_block_bwd_ms": [g["b"] for g in G], "interleave": v,
+            "head_wgrad_ms": max(G[-1]["hb"] - G[-1]["hf"], 0.0), "block_wgrad_ms": G[-1]["f"] * WGRAD_SHARE_OF_FORWARD}
 
 
 def best_tail_deferral(cfg: dict, schedule: str, *, recompute: Optional[bool] = None, table: Optional[dict] = None,
@@ -190,7 +211,7 @@ def best_tail_deferral(cfg: dict, schedule: str, *, recompute: Optional[bool] = 
     others = max(T[:-1])
     if T[-1] <= others:
         return 0
-    window = window_share * sum(n * p["block_bwd_ms"] for n in p["stage_layers"][:-1])
+    window = window_share * sum(n * b for n, b in zip(p["stage_layers"][:-1], p["stage_block_bwd_ms"][:-1]))
     seq, mbs, vocab = int(cfg["sequence_length"]), int(cfg["microbatch_size"]), int(cfg.get("vocab_size", 32000))
     stats = registry.get_model_stats(cfg["model_name"], vocab=vocab)
     tokens = seq * mbs
