@@ -214,7 +214,10 @@ def main(argv=None) -> int:
             from ..config.training_config import to_dict
             from ..planner.predict import predict_step_ms
 
-            predicted = predict_step_ms(to_dict(cfg), tr.schedule.name, recompute=tr.schedule.recompute, gpu=gpu,
+            # a job on several GPU models: every rank of the plan is costed with its own model's profile
+            mixed = len(set(names)) > 1 and len(names) == tr.world and cfg.tensor_parallel_size == 1
+            predicted = predict_step_ms(to_dict(cfg), tr.schedule.name, recompute=tr.schedule.recompute,
+                                        gpu={i: n for i, n in enumerate(names)} if mixed else gpu,
                                         defer_wgrad=opt.defer_wgrad, defer_tail_wgrad=opt.defer_tail_wgrad)["ms"]
         except Exception:      # noqa: BLE001 - no profile table for this model / GPU: print no prediction
             predicted = None
