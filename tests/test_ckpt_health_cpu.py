@@ -398,3 +398,34 @@ def test_dropped_and_delayed_pipeline_messages():
     assert parse_fault("3:7:delay=0.5") == (3, 7, "delay=0.5")
     with pytest.raises(ValueError):
         parse_fault("0:1:lose")
+
+
+def test_supervised_job_survives_a_rank_that_stalls(tmp_path):
+    """A rank that stops between steps without exiting (it never joins step 3): the peers' watchdogs end them and
+    report who never entered the step they are stuck in; the supervisor ends the silent rank, restarts on the other
+    three from the newest checkpoint and the job reaches its last step."""
+    import json
+
+    from zorse_b200.cli import supervise
+
+    gl = [{"index": i, "name": "NVIDIA B200", "memory_total_mib": 183359, "id": f"gpu_{i}", "machine": "m0",
+           "global_rank": i} for i in range(4)]
+    cluster = {"machines": [{"machine": "m0", "num_gpus": 4, "machine_index": 0, "gpus": gl}], "gpu_list": gl,
+               "total_gpus": 4, "bandwidth": {"internode_bandwidth": {}, "intranode_bandwidth": {"0": 770.0},
+                                              "internode_latency": {}, "intranode_latency": {"0": 2e-5}}}
+    pipe = [{"gpu_ranks": [0, 1], "num_microbatches_per_rank": [2, 2], "layer_partition": [0, 2], "zero_config": [[0, 1]]},
+            {"gpu_ranks": [2, 3], "num_microbatches_per_rank": [2, 2], "layer_partition": [2, 4], "zero_config": [[2, 3]]}]
+    (tmp_path / "cluster.json").write_text(json.dumps(cluster))
+    (tmp_path / "tc.json").write_text(json.dumps(tiny_cfg(pipe)))
+    rc = supervise.main(["--config_file", str(tmp_path / "tc.json"), "--cluster_info_file", str(tmp_path / "cluster.json"),
+                         "--train_steps", "5", "--checkpoint_every", "1", "--max_restarts", "1", "--grace", "12",
+                         "--checkpoint_dir", str(tmp_path / "ck"), "--work_dir", str(tmp_path / "run"),
+                         "--", "--backend", "gloo", "--skip_profile", "--heartbeat_timeout", "6", "--heartbeat_startup", "90",
+                         "--inject_fault", "2:3:stall"])
+    assert rc == 0
+    logs = "".join((tmp_path / "run" / f"attempt0_rank{r}.log").read_text() for r in (0, 1, 3))
+    assert "ranks that have not entered step 3: [2]" in logs
+    new_cfg = parse_pipeline_dict(json.loads((tmp_path / "run" / "training_config_attempt1.json").read_text()))
+    assert new_cfg.world_size == 3
+    step, _ = _masters_of(str(tmp_path / "ck" / "step_5"))
+    assert step == 5
