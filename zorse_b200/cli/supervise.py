@@ -38,12 +38,24 @@ from typing import Optional
 WATCHDOG_EXIT = 3          # cli/train.py: a rank whose watchdog saw no progress
 
 
-def _free_port() -> int:
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    p = s.getsockname()[1]
-    s.close()
-    return p
+def _free_port(also: int = 23) -> int:
+    """A free rendezvous port whose `also`-th successor is free too (the trainer's heartbeat store listens there)."""
+    for _ in range(50):
+        s = socket.socket()
+        s.bind(("127.0.0.1", 0))
+        p = s.getsockname()[1]
+        s.close()
+        if p + also > 65535:
+            continue
+        t = socket.socket()
+        try:
+            t.bind(("127.0.0.1", p + also))
+        except OSError:
+            continue
+        finally:
+            t.close()
+        return p
+    raise RuntimeError("no pair of free ports found")
 
 
 # what a rank prints when it fails because ANOTHER rank went away or fell silent
