@@ -308,6 +308,8 @@ def test_profile_helpers_memcpy_function_time_and_line_fit(tmp_path):
     assert trace.extract_function_runtime("zero.adam", str(f), 2) == pytest.approx(3.0)
     assert trace.extract_function_runtime("gemm2_bf16_kernel", str(f)) == 0.0
     assert trace.extract_function_runtime("gemm2_bf16_kernel", str(f), exact=False) == pytest.approx(1.5)
+    names = ["NVIDIA B200", "NVIDIA B200", "NVIDIA H100", "NVIDIA B200", "NVIDIA H100"]
+    assert [trace.first_of_its_model(i, names) for i in range(5)] == [True, False, True, False, False]
     s, c = trace.fit_line([3.0, 5.0, 7.0, 9.0])
     assert s == pytest.approx(2.0) and c == pytest.approx(1.0)
     assert trace.fit_line([4.0]) == (4.0, 0.0)

@@ -152,7 +152,8 @@ def main(argv=None) -> int:
                 and step - first == args.warmup_iterations - args.profiling_iterations and args.profiling_iterations > 0):
             from ..utils.trace import profiler_context
 
-            prof = profiler_context(args.trace_dir, args.experiment_name, tr.rank)
+            prof = profiler_context(args.trace_dir, args.experiment_name, tr.rank,
+                                    unique_gpus_only=args.trace_unique_gpus_only)
             prof.__enter__()
         if cuda:
             a = torch.cuda.Event(enable_timing=True)

@@ -72,6 +72,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--checkpoint_dir", type=str, default=None)
     p.add_argument("--checkpoint_every", type=int, default=0)
     p.add_argument("--resume", type=str, default=None)
+    p.add_argument("--trace_unique_gpus_only", action="store_true",
+                   help="profiler traces only on the first GPU of each model per machine (the reference's behaviour); "
+                        "default: every rank records its own")
     p.add_argument("--p2p_timeout", type=float, default=0.0,
                    help="Gloo p2p: seconds a pipeline receive may wait before the job fails with the name of the missing "
                         "message (0: the process group's timeout)")

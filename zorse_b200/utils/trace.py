@@ -10,7 +10,20 @@ import os
 import torch
 
 
-def profiler_context(trace_dir: str, experiment: str, rank: int, detailed: bool = False):
+def first_of_its_model(device_index: int, device_names) -> bool:
+    """Whether the device is the first one of its model among the machine's devices (`device_names` in index order)."""
+    return list(device_names).index(device_names[device_index]) == device_index
+
+
+def profiler_context(trace_dir: str, experiment: str, rank: int, detailed: bool = False, unique_gpus_only: bool = False):
+    """`unique_gpus_only`: on a machine with several GPUs of one model only the first of them records a trace, the
+    others get a context that does nothing (what the reference's trainer does, utils/profile.py:52-63, zorse.py:153)."""
+    if unique_gpus_only and torch.cuda.is_available():
+        import contextlib
+
+        names = [torch.cuda.get_device_name(i) for i in range(torch.cuda.device_count())]
+        if not first_of_its_model(torch.cuda.current_device(), names):
+            return contextlib.nullcontext()
     out = os.path.join(os.path.expanduser(trace_dir), experiment, f"GPU_{rank}")
     os.makedirs(out, exist_ok=True)
     acts = [torch.profiler.ProfilerActivity.CPU]
