@@ -181,9 +181,13 @@ def test_trainer_cli_end_to_end(tmp_path):
     assert "replay check: identical=True" in out
     assert "Throughput:" in out and "Batch Size,Seq_Len,Min_Allocated,Max_Allocated,Latency,Throughput" in out
     assert (ck / "step_5" / "meta.json").exists()
-    r2 = subprocess.run(base + ["--resume", str(ck / "step_5")], capture_output=True, text=True, timeout=300,
-                        env=env, cwd=root)
-    assert r2.returncode == 0, (r2.stdout + r2.stderr)[-3000:]
+    assert out.count("===== zorse-b200 run summary =====") == 1
+    # resumed, with the summary after every timed iteration (two of them: one running block + the final one)
+    r2 = subprocess.run(base + ["--resume", str(ck / "step_5"), "--print_metrics_every_iteration"], capture_output=True,
+                        text=True, timeout=300, env=env, cwd=root)
+    out2 = r2.stdout + r2.stderr
+    assert r2.returncode == 0, out2[-3000:]
+    assert out2.count("===== zorse-b200 run summary =====") == 2 and "resumed from" in out2
 
 
 def _interleaved_pipe(P, v, width, M):

@@ -139,6 +139,47 @@ def main(argv=None) -> int:
     iter_ms = []
     prof = None
     loss = None
+
+    def report(avg_ms, loss):
+        """The summary block (collective: every rank calls it): step time as the max over ranks, memory and GPU names
+        over the host-side group, throughput, MFU, prediction, loss (reference utils/train_utils.py:556-734)."""
+        t = torch.tensor([avg_ms, metrics.memory_stats(tr.device)["max_allocated_gb"]], dtype=torch.float64)
+        gpu = metrics.clean_gpu_name(torch.cuda.get_device_name(tr.device)) if cuda else "cpu"
+        if G.is_dist():
+            grp = tr.gloo_group if tr.gloo_group is not None else None
+            outs = [torch.zeros_like(t) for _ in range(tr.world)]
+            names = [None] * tr.world
+            if grp is not None or dist.get_backend() == "gloo":
+                dist.all_gather(outs, t, group=grp)
+                dist.all_gather_object(names, gpu, group=grp)
+            else:
+                outs, names = [t], [gpu]
+        else:
+            outs, names = [t], [gpu]
+        step_ms = max(float(o[0]) for o in outs)
+        spec = tr.spec
+        flops = metrics.compute_model_flops(registry.total_params(spec, cfg.sequence_length), spec.layers, spec.hidden,
+                                            cfg.sequence_length, cfg.global_batch_size, recompute=tr.schedule.recompute)
+        gl = tr.global_loss(loss)
+        predicted = cfg.latency
+        if predicted is None and cuda:
+            try:
+                from ..config.training_config import to_dict
+                from ..planner.predict import predict_step_ms
+
+                # a job on several GPU models: every rank of the plan is costed with its own model's profile
+                mixed = len(set(names)) > 1 and len(names) == tr.world and cfg.tensor_parallel_size == 1
+                predicted = predict_step_ms(to_dict(cfg), tr.schedule.name, recompute=tr.schedule.recompute,
+                                            gpu={i: n for i, n in enumerate(names)} if mixed else gpu,
+                                            defer_wgrad=opt.defer_wgrad, defer_tail_wgrad=opt.defer_tail_wgrad)["ms"]
+            except Exception:      # noqa: BLE001 - no profile table for this model / GPU: print no prediction
+                predicted = None
+        if tr.rank == 0:
+            print(metrics.format_summary(global_batch=cfg.global_batch_size, seq=cfg.sequence_length, step_ms=step_ms,
+                                         flops_per_step=flops, gpu_names=names, dtype=cfg.autocast_dtype,
+                                         max_alloc_gb=[float(o[1]) for o in outs], predicted_ms=predicted, loss=gl,
+                                         flashflex_ga=args.flashflex_ga), flush=True)
+
     for step in range(first, total):
         maybe_inject(fault, tr.rank, step, keepalive=watchdog.beat if watchdog else None,
                      transport=getattr(tr, "fault_transport", None))
@@ -181,6 +222,11 @@ def main(argv=None) -> int:
         if prof is not None and step - first == args.warmup_iterations - 1:
             prof.__exit__(None, None, None)
             prof = None
+        if args.print_metrics_every_iteration and args.warmup_iterations <= step - first < total - first - 1:
+            # the running mean of the timed iterations so far, after each of them but the last (whose block is the
+            # final one; reference zorse.py:185-196)
+            so_far = iter_ms[args.warmup_iterations:]
+            report(sum(so_far) / len(so_far), loss)
         if args.checkpoint_dir and args.checkpoint_every and (step + 1) % args.checkpoint_every == 0:
             from ..ckpt.writer import save_checkpoint
 
@@ -190,43 +236,7 @@ def main(argv=None) -> int:
     timed = iter_ms[args.warmup_iterations:] or iter_ms[-1:]
     avg_ms = sum(timed) / len(timed) if timed else 0.0
     tr.barrier()
-    # max over ranks, memory and GPU names over the host-side group
-    t = torch.tensor([avg_ms, metrics.memory_stats(tr.device)["max_allocated_gb"]], dtype=torch.float64)
-    gpu = metrics.clean_gpu_name(torch.cuda.get_device_name(tr.device)) if cuda else "cpu"
-    if G.is_dist():
-        grp = tr.gloo_group if tr.gloo_group is not None else None
-        outs = [torch.zeros_like(t) for _ in range(tr.world)]
-        names = [None] * tr.world
-        if grp is not None or dist.get_backend() == "gloo":
-            dist.all_gather(outs, t, group=grp)
-            dist.all_gather_object(names, gpu, group=grp)
-        else:
-            outs, names = [t], [gpu]
-    else:
-        outs, names = [t], [gpu]
-    step_ms = max(float(o[0]) for o in outs)
-    spec = tr.spec
-    flops = metrics.compute_model_flops(registry.total_params(spec, cfg.sequence_length), spec.layers, spec.hidden,
-                                        cfg.sequence_length, cfg.global_batch_size, recompute=tr.schedule.recompute)
-    gl = tr.global_loss(loss)
-    predicted = cfg.latency
-    if predicted is None and cuda:
-        try:
-            from ..config.training_config import to_dict
-            from ..planner.predict import predict_step_ms
-
-            # a job on several GPU models: every rank of the plan is costed with its own model's profile
-            mixed = len(set(names)) > 1 and len(names) == tr.world and cfg.tensor_parallel_size == 1
-            predicted = predict_step_ms(to_dict(cfg), tr.schedule.name, recompute=tr.schedule.recompute,
-                                        gpu={i: n for i, n in enumerate(names)} if mixed else gpu,
-                                        defer_wgrad=opt.defer_wgrad, defer_tail_wgrad=opt.defer_tail_wgrad)["ms"]
-        except Exception:      # noqa: BLE001 - no profile table for this model / GPU: print no prediction
-            predicted = None
-    if tr.rank == 0:
-        print(metrics.format_summary(global_batch=cfg.global_batch_size, seq=cfg.sequence_length, step_ms=step_ms,
-                                     flops_per_step=flops, gpu_names=names, dtype=cfg.autocast_dtype,
-                                     max_alloc_gb=[float(o[1]) for o in outs], predicted_ms=predicted, loss=gl,
-                                     flashflex_ga=args.flashflex_ga))
+    report(avg_ms, loss)
     if args.trace_dir and not args.skip_profile and args.profiling_iterations > 0:
         # stream-classified trace figures of this rank's profiled iterations (reference utils/train_utils.py:104-221,
         # printed from print_metrics when analyze_trace is set)
