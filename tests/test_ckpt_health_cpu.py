@@ -65,9 +65,29 @@ def test_corrupt_checkpoint_is_detected(tmp_path):
         fh.truncate(os.path.getsize(f) // 2)
     with pytest.raises(RuntimeError, match="truncated"):
         run_workers(2, _load_and_step, tiny_cfg(PIPE_2x1), ck, 1, timeout=120)
+    import numpy as np
+
+    from zorse_b200.ckpt.reader import main as verify_main, verify_checkpoint
+
+    with pytest.raises(CheckpointError, match="truncated"):
+        verify_checkpoint(d)
+    assert verify_main([d]) == 2
     os.remove(os.path.join(d, "meta.json"))
     with pytest.raises(CheckpointError):
         read_meta(d)
+    # an intact checkpoint verifies; a NaN written into a shard file is found and located
+    ck2 = str(tmp_path / "ck2")
+    run_workers(2, _train_and_save, tiny_cfg(PIPE_2x1), ck2, 1)
+    d2 = os.path.join(ck2, "step_1")
+    ok = verify_checkpoint(d2)
+    assert ok["step"] == 1 and ok["files"] == 2 and not ok["bad_units"] and ok["model"] == "tiny_llama"
+    assert verify_main([d2]) == 0
+    with open(os.path.join(d2, "stage1_rank1.bin"), "r+b") as fh:
+        fh.seek(8)
+        fh.write(np.array([np.nan], dtype="<f4").tobytes())
+    bad = verify_checkpoint(d2)
+    assert len(bad["bad_units"]) == 1 and bad["bad_units"][0][0] == 1 and bad["bad_units"][0][3] == "master"
+    assert verify_main([d2]) == 1 and verify_main([d2, "--no-values"]) == 0
 
 
 def test_heartbeat_names_the_silent_rank():

@@ -128,3 +128,57 @@ def load_checkpoint(trainer, directory: str) -> int:
     trainer.step_idx = meta["step"]
     trainer.barrier()
     return meta["step"]
+
+
+def verify_checkpoint(directory: str, values: bool = True) -> dict:
+    """Checks a checkpoint directory without a trainer: meta.json readable, every shard file present and exactly as
+    long as the unit table says, and (with `values`) every master / moment value finite and every second moment
+    non-negative.  Returns a summary; raises CheckpointError at the first structural problem."""
+    meta = read_meta(directory)
+    offsets = _file_offsets(meta)
+    expect: dict = {}
+    for u in meta["units"]:
+        bd = _bounds(u)
+        for idx, r in enumerate(u["shard_ranks"]):
+            key = (u["stage"], r)
+            expect[key] = expect.get(key, 0) + 3 * (bd[idx + 1] - bd[idx]) * 4
+    for (stage, r), size in sorted(expect.items()):
+        path = os.path.join(directory, f"stage{stage}_rank{r}.bin")
+        if not os.path.exists(path):
+            raise CheckpointError(f"missing shard file {path}")
+        have = os.path.getsize(path)
+        if have != size:
+            raise CheckpointError(f"{path} holds {have} bytes, the unit table says {size}"
+                                  + (" (truncated)" if have < size else ""))
+    out = {"step": meta["step"], "units": len(meta["units"]), "files": len(expect),
+           "bytes": sum(expect.values()), "parameters": sum(u["numel"] for u in meta["units"] if u.get("tp_index", 0) == 0
+                                                            or meta.get("tensor_parallel_size", 1) > 1),
+           "model": meta["training_config"]["model_name"], "bad_units": []}
+    if values:
+        for u in meta["units"]:
+            for which, name in enumerate(("master", "m", "v")):
+                t = read_range(directory, meta, offsets, u, which, 0, u["numel"])
+                if not bool(torch.isfinite(t).all()) or (name == "v" and bool((t < 0).any())):
+                    out["bad_units"].append((u["stage"], u["gid"], u.get("tp_index", 0), name))
+    return out
+
+
+def main(argv=None) -> int:
+    """python -m zorse_b200.ckpt.reader <checkpoint directory> [--no-values]"""
+    import argparse
+
+    ap = argparse.ArgumentParser(description="verify a checkpoint directory (structure, sizes, finite values)")
+    ap.add_argument("directory")
+    ap.add_argument("--no-values", action="store_true", help="structure and sizes only")
+    a = ap.parse_args(argv)
+    try:
+        s = verify_checkpoint(a.directory, values=not a.no_values)
+    except CheckpointError as e:
+        print(f"BAD: {e}")
+        return 2
+    print(json.dumps(s))
+    return 1 if s["bad_units"] else 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
