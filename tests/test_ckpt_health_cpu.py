@@ -284,6 +284,15 @@ def test_recover_replans_for_the_gpus_that_are_left(tmp_path):
     os.makedirs(os.path.join(ck, "step_9"))                      # newer but incomplete: no meta.json
     assert recover.latest_checkpoint(ck) == os.path.join(ck, "step_2")
     assert recover.latest_checkpoint(str(tmp_path / "nothing")) is None
+    assert recover.latest_checkpoint(ck, verify=True) == os.path.join(ck, "step_2")
+    # a newer checkpoint with a cut-off shard file: named by the plain search, passed over by the verifying one
+    import shutil
+    shutil.copytree(os.path.join(ck, "step_2"), os.path.join(ck, "step_4"))
+    with open(os.path.join(ck, "step_4", "stage0_rank1.bin"), "r+b") as fh:
+        fh.truncate(100)
+    assert recover.latest_checkpoint(ck) == os.path.join(ck, "step_4")
+    assert recover.latest_checkpoint(ck, verify=True) == os.path.join(ck, "step_2")
+    shutil.rmtree(os.path.join(ck, "step_4"))
     gl = [{"index": i, "name": "NVIDIA B200", "memory_total_mib": 183359, "id": f"gpu_{i}", "machine": "m0",
            "global_rank": i} for i in range(2)]
     cluster = {"machines": [{"machine": "m0", "num_gpus": 2, "machine_index": 0, "gpus": gl}], "gpu_list": gl,

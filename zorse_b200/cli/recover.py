@@ -24,17 +24,28 @@ import sys
 from typing import Optional
 
 
-def latest_checkpoint(directory: str) -> Optional[str]:
-    """Path of the `step_<n>` sub-directory with the largest n that holds a meta.json."""
-    best, best_n = None, -1
+def latest_checkpoint(directory: str, verify: bool = False) -> Optional[str]:
+    """Path of the `step_<n>` sub-directory with the largest n that holds a meta.json; with `verify` also one whose
+    shard files are all there and as long as its unit table says (a newer but damaged checkpoint is passed over)."""
     if not os.path.isdir(directory):
         return None
+    found = []
     for name in os.listdir(directory):
         m = re.fullmatch(r"step_(\d+)", name)
         p = os.path.join(directory, name)
-        if m and os.path.exists(os.path.join(p, "meta.json")) and int(m.group(1)) > best_n:
-            best, best_n = p, int(m.group(1))
-    return best
+        if m and os.path.exists(os.path.join(p, "meta.json")):
+            found.append((int(m.group(1)), p))
+    for _, p in sorted(found, reverse=True):
+        if not verify:
+            return p
+        from ..ckpt.reader import CheckpointError, verify_checkpoint
+
+        try:
+            verify_checkpoint(p, values=False)
+            return p
+        except (CheckpointError, OSError, ValueError, KeyError):
+            continue
+    return None
 
 
 def shrink_cluster(data: dict, exclude_ranks) -> dict:

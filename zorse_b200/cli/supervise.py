@@ -165,7 +165,7 @@ def main(argv=None) -> int:
     for attempt in range(a.max_restarts + 1):
         cfg = parse_pipeline_config(config)
         world = cfg.world_size
-        ck = latest_checkpoint(a.checkpoint_dir)
+        ck = latest_checkpoint(a.checkpoint_dir, verify=True)
         args = ["--config_file", config, "--checkpoint_dir", a.checkpoint_dir, "--checkpoint_every", str(a.checkpoint_every),
                 "--train_steps", str(a.train_steps)] + (["--resume", ck] if ck else []) + extra
         if attempt > 0:
@@ -184,7 +184,7 @@ def main(argv=None) -> int:
             return 1
         if attempt == a.max_restarts:
             break
-        ck = latest_checkpoint(a.checkpoint_dir)
+        ck = latest_checkpoint(a.checkpoint_dir, verify=True)
         # ranks of the failed attempt number the GPUs of the CURRENT cluster description
         cluster = shrink_cluster(cluster, bad)
         alive = [g for r, g in enumerate(alive) if r not in set(bad)]
